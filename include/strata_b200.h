@@ -1,0 +1,185 @@
+/*
+ * strata_b200.h -- C ABI of the B200 (sm_100a) paged KV-cache / RoPE / grouped-query
+ * attention library (libstrata_b200.so).
+ *
+ * Every entry point returns an int32 status (SKV_OK == 0, negatives are errors),
+ * never throws and never aborts.  Host-side validation happens before any kernel
+ * launch; skv_last_error() gives the message of the last failing call on a pool.
+ * Device pointers are borrowed for the duration of the call on the given stream;
+ * the library never frees caller memory.  `stream` is a cudaStream_t passed as
+ * void* (NULL = the legacy default stream).
+ *
+ * Each declaration cites the interface of the reference project (Strata,
+ * Python package `ollm`) that it stands in for, as  path:line  inside that project.
+ */
+#ifndef STRATA_B200_H
+#define STRATA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SKV_API __attribute__((visibility("default")))
+#else
+#define SKV_API
+#endif
+
+#define SKV_ABI_VERSION 1
+
+/* status codes */
+enum {
+    SKV_OK = 0,
+    SKV_ERR_BAD_ARG = -1,       /* shape / index / pointer validation failed (ValueError in the reference) */
+    SKV_ERR_REPLAY = -2,        /* append does not start exactly after the cached sequence
+                                   (src/ollm/mlx_kvcache.py:143-158, "append exactly") */
+    SKV_ERR_OUT_OF_PAGES = -3,  /* page / sequence / host-slot allocator exhausted; nothing was changed */
+    SKV_ERR_NOT_RESIDENT = -4,  /* a page needed by the call is parked in host memory */
+    SKV_ERR_TIMEOUT = -5,       /* bounded wait ran out */
+    SKV_ERR_CUDA = -6,          /* a CUDA runtime call failed; message holds cudaGetErrorString */
+    SKV_ERR_UNSUPPORTED = -7,   /* shape or dtype outside what the kernels cover */
+    SKV_ERR_DEVICE_FLAG = -8    /* a kernel recorded an error in the pool's device status word */
+};
+
+/* element types of stored K/V, queries and outputs */
+enum { SKV_F32 = 0, SKV_BF16 = 1 };
+
+/* page-table entry encoding (int32): >= 0 device page, -1 unassigned, -2 - s = parked in host slot s */
+#define SKV_PAGE_UNASSIGNED (-1)
+
+typedef struct skv_pool skv_pool;
+
+typedef struct skv_config {
+    int32_t device;            /* CUDA device ordinal; -1 = bookkeeping only (no device memory, no launches) */
+    int32_t dtype;             /* SKV_F32 or SKV_BF16 */
+    int32_t num_layers;        /* config.num_hidden_layers of the reference cache ctor (mlx_kvcache.py:31-63) */
+    int32_t num_kv_heads;      /* KV heads held by THIS pool (the local heads under KV-head sharding) */
+    int32_t head_dim;
+    int32_t page_size;         /* tokens per page */
+    int32_t num_pages;         /* device pages; one page id covers all layers and local KV heads */
+    int32_t max_seqs;
+    int32_t max_pages_per_seq;
+    int32_t host_pages;        /* pinned host slots for parked pages (0 = no host tier) */
+} skv_config;
+
+/* Pool life cycle.  Stands in for MLXKVCache.__init__ / clear (mlx_kvcache.py:31-63, 271-284).
+ * Device layout per layer: K[page][kv_head][page_size][head_dim], V likewise. */
+SKV_API int32_t skv_abi_version(void);
+SKV_API int32_t skv_create(const skv_config* cfg, skv_pool** out);
+SKV_API int32_t skv_destroy(skv_pool* pool);
+SKV_API const char* skv_last_error(const skv_pool* pool);
+SKV_API const char* skv_status_string(int32_t status);
+
+/* Sequences.  The reference keeps one tensor per layer with a batch axis (mlx_kvcache.py:54);
+ * here each batch row is a sequence with its own page-table row and per-layer lengths. */
+SKV_API int32_t skv_alloc_sequence(skv_pool* pool, int32_t* seq_out);
+SKV_API int32_t skv_free_sequence(skv_pool* pool, int32_t seq);
+SKV_API int32_t skv_reserve(skv_pool* pool, int32_t seq, int32_t total_tokens);
+/* Adopt an externally chosen page-table row (validated: range, no page shared with a live sequence)
+ * and set every layer's length to `length`.  No reference counterpart. */
+SKV_API int32_t skv_set_page_table(skv_pool* pool, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t length);
+
+/* Shorten one layer's history of the listed sequences to `new_length` tokens; pages stay owned.
+ * Used when a layer is dropped to a file and later re-appended from position 0
+ * (the reference deletes the layer's tensors, mlx_kvcache.py:220-222). */
+SKV_API int32_t skv_truncate(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
+                             int32_t new_length, void* stream);
+
+/* Queries on host-side state: get_seq_length (mlx_kvcache.py:160-172). */
+SKV_API int32_t skv_length(const skv_pool* pool, int32_t layer, int32_t seq, int32_t* length_out);
+SKV_API int32_t skv_lengths(const skv_pool* pool, int32_t layer, int32_t* out, int32_t n);
+SKV_API int32_t skv_page_table(const skv_pool* pool, int32_t seq, int32_t* out, int32_t capacity, int32_t* n_pages_out);
+SKV_API int32_t skv_pool_counters(const skv_pool* pool, int64_t out[8]);
+/*   out[0] free device pages, [1] used device pages, [2] free host slots, [3] pages evicted (total),
+ *   [4] pages prefetched (total), [5] bytes device->host, [6] bytes host->device, [7] live sequences */
+
+/* Raw device views, for tests and for host code that fills a pool directly. */
+SKV_API int32_t skv_pool_pointers(const skv_pool* pool, int32_t layer, void** k_pool, void** v_pool);
+SKV_API int32_t skv_device_tables(const skv_pool* pool, int32_t** page_table, int32_t** lengths);
+
+/* RoPE table: inv_freq[head_dim/2] float32 exactly as MLXRotaryEmbedding builds it
+ * (src/ollm/llama_mlx.py:111-114); positions are divided by `scaling_factor` first
+ * (linear scaling; the reference has none, 1.0 reproduces it). */
+SKV_API int32_t skv_set_rope(skv_pool* pool, const float* inv_freq, int32_t n, float scaling_factor);
+
+/* K1: append `n_new` tokens per sequence to one layer (MLXKVCache.update, mlx_kvcache.py:65-125),
+ * optionally rotating K (and a query tensor) on the way in
+ * (apply_rotary_pos_emb_mlx, llama_mlx.py:149-182). */
+typedef struct skv_append_args {
+    int32_t layer;
+    int32_t n_seqs;
+    const int32_t* seq_ids;     /* host, n_seqs entries; NULL = sequences 0..n_seqs-1 */
+    const int32_t* start_pos;   /* host, n_seqs entries; must equal each sequence's length in this layer.
+                                   NULL = append at the current length (no replay check, as when the
+                                   reference is called without cache_position) */
+    int32_t n_new;              /* tokens appended per sequence */
+    const void* k;              /* device, element strides below, head_dim contiguous */
+    const void* v;
+    int64_t kv_stride_seq, kv_stride_head, kv_stride_tok;   /* in elements */
+    int32_t rope_k;             /* 1: rotate K with the pool's table at positions start..start+n_new */
+    /* optional query rotation in the same launch (q_out may alias q_in) */
+    const void* q_in;
+    void* q_out;
+    int32_t n_q_heads;
+    int64_t q_stride_seq, q_stride_head, q_stride_tok;
+} skv_append_args;
+SKV_API int32_t skv_append(skv_pool* pool, const skv_append_args* args, void* stream);
+
+/* K2: materialise the dense [n_seqs][kv_heads][max_len][head_dim] history of a layer
+ * (what update returns / __getitem__ holds, mlx_kvcache.py:125, 290-303).  Rows beyond a
+ * sequence's length are zero-filled. */
+SKV_API int32_t skv_gather(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
+                   void* out_k, void* out_v, int32_t max_len, void* stream);
+
+/* K3: one query token per sequence against its paged history
+ * (online_chunked_grouped_attention_mx with Lq == 1, src/ollm/backends/mlx_ops.py:32-152;
+ * call site llama_mlx.py:300-308).  q, out: [n_seqs][n_q_heads][head_dim], pool dtype.
+ * q_pos (host, may be NULL = length-1) are absolute query positions: keys 0..q_pos are attended.
+ * workspace holds the split-K partials; size from skv_decode_workspace_bytes. */
+SKV_API size_t skv_decode_workspace_bytes(const skv_pool* pool, int32_t n_seqs, int32_t n_q_heads);
+SKV_API int32_t skv_decode_attn(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
+                        const void* q, void* out, const int32_t* q_pos, int32_t n_q_heads,
+                        float eps, void* workspace, size_t workspace_bytes, void* stream);
+
+/* K4: chunked grouped-query attention on dense tensors
+ * (online_chunked_grouped_attention_mx, mlx_ops.py:32-152; unmasked twin :155-178).
+ * q,out [B][Hq][Lq][D], k,v [B][Hkv][Lk][D], contiguous.  positions: device int32 [B][Lq]
+ * absolute query positions, or NULL for bottom-right alignment arange(Lk-Lq, Lk) (:69-72).
+ * Rows with no allowed key produce 0 (:118, :146). */
+SKV_API int32_t skv_attn_dense(const void* q, const void* k, const void* v, void* out, const int32_t* positions,
+                       int32_t B, int32_t Hq, int32_t Hkv, int32_t Lq, int32_t Lk, int32_t D,
+                       int32_t dtype, int32_t causal, float eps, void* stream);
+
+/* K4 over pages: queries [n_seqs][Hq][Lq][D] against each sequence's first `lengths` tokens of a layer. */
+SKV_API int32_t skv_prefill_attn_paged(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
+                               const void* q, void* out, const int32_t* positions /* device [n_seqs][Lq] or NULL */,
+                               int32_t n_q_heads, int32_t Lq, int32_t causal, float eps, void* stream);
+
+/* K5: park pages in pinned host memory and bring them back
+ * (stands in for save_to_disk / _load_layer_from_disk, mlx_kvcache.py:183-255).
+ * Slots are page-table slots of one sequence; all layers of a page move together.  Copies run on the
+ * pool's own copy streams; skv_wait_resident bounds the wait and returns SKV_ERR_TIMEOUT instead of
+ * blocking forever.  Compute on `stream` issued after skv_sync_transfers(pool, stream) is ordered
+ * after the copies. */
+SKV_API int32_t skv_evict(skv_pool* pool, int32_t seq, int32_t first_slot, int32_t n_slots, void* stream);
+SKV_API int32_t skv_prefetch(skv_pool* pool, int32_t seq, int32_t first_slot, int32_t n_slots, void* stream);
+SKV_API int32_t skv_sync_transfers(skv_pool* pool, void* stream);
+SKV_API int32_t skv_wait_resident(skv_pool* pool, int32_t timeout_ms);
+
+/* Device status word: kernels record out-of-range page ids or lengths there and skip the access.
+ * Reads it back (synchronises `stream`), clears it, returns SKV_ERR_DEVICE_FLAG if it was set. */
+SKV_API int32_t skv_check_device_status(skv_pool* pool, void* stream, int32_t* flag_out);
+
+/* Stand-alone RoPE on a [n_rows][n_heads][head_dim] tensor with one position per row
+ * (apply_rotary_pos_emb_mlx, llama_mlx.py:149-182). positions: device int32 [n_rows]. */
+SKV_API int32_t skv_rope_rows(const void* x_in, void* x_out, const int32_t* positions, const float* inv_freq_dev,
+                      int32_t n_rows, int32_t n_heads, int32_t head_dim, int64_t stride_row, int64_t stride_head,
+                      float scaling_factor, int32_t dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STRATA_B200_H */

@@ -1,0 +1,18 @@
+"""B200-native (sm_100a) KV-cache, RoPE and chunked grouped-query attention behind the call
+surface of the Strata / ``ollm`` runtime.  Importing the package needs the built C-ABI library
+(``python -m lokahi_b200.build``); there is no CPU or PyTorch fallback for any compute call."""
+from ._lib import DeviceFlagError, NotResidentError, OutOfPagesError
+from .attention import PagedView, chunked_grouped_attention, chunked_grouped_attention_no_mask
+from .backend import B200Backend, BackendError, register
+from .generation import greedy_generate
+from .kvcache import PagedKVCache, PagedLlamaDiskCache, create_paged_kv_cache
+from .pool import PagedKVConfig, PagedPool, rope_inv_freq, rope_rows
+
+register()
+
+__all__ = [
+    "B200Backend", "BackendError", "DeviceFlagError", "NotResidentError", "OutOfPagesError", "PagedKVCache",
+    "PagedKVConfig", "PagedLlamaDiskCache", "PagedPool", "PagedView", "chunked_grouped_attention",
+    "chunked_grouped_attention_no_mask", "create_paged_kv_cache", "greedy_generate", "register",
+    "rope_inv_freq", "rope_rows",
+]

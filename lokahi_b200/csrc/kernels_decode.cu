@@ -1,0 +1,426 @@
+// K3: split-K flash-decoding grouped-query attention through the page table, and K3r, the
+// merge of the split partials.
+//
+// Mathematics: online_chunked_grouped_attention_mx with one query row
+// (src/ollm/backends/mlx_ops.py:81-152): scores = q.k * D^-0.5 in float32, keys 0..q_pos
+// allowed, running (max, sum, weighted V) merged across key chunks (:125-144), and
+// out = wv / max(s, eps) so that a row with no allowed key is exactly 0 (:118, :146).
+//
+// Two kernels produce the same partials (m, l, acc[D]) per (sequence, query head, split):
+//   * decode_generic_kernel: CUDA cores, float32 or bf16 storage, any head_dim <= 256, any group
+//     size; one CTA per query head, so K/V of a KV head are re-read by its G query heads (L2).
+//   * decode_mma_kernel: bf16, head_dim 128, group size <= 8.  One CTA serves all G query heads of
+//     a KV head, so every K/V byte is read from HBM once.  K and V go from global memory straight
+//     into mma.sync fragments with 16-byte loads that cover whole 32-byte sectors: the
+//     contraction index of Q.K^T and the column index of P.V are permuted so that each lane's
+//     fragment registers are the 16-byte units it loaded (no shared-memory staging, no
+//     transposes).  Row maxima and sums are reduced with warp shuffles inside the quad that
+//     shares a query row; the four warps of a CTA combine through shared memory.
+#include <cstdlib>
+
+#include "common.cuh"
+
+namespace skv {
+
+namespace {
+
+constexpr int kDecodeWarps = 4;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ int attend_count(const DecodeLaunch& d, int i, int seq) {
+    const PoolView& pv = d.pool;
+    int len = pv.lengths[(int64_t)d.layer * pv.max_seqs + seq];
+    const int cap = pv.max_pages_per_seq * pv.page_size;
+    if (len < 0 || len > cap) {
+        atomicOr(pv.status, FLAG_BAD_LENGTH);
+        len = len < 0 ? 0 : cap;
+    }
+    if (d.q_pos) {
+        const int qp = d.q_pos[i];
+        const int lim = qp < 0 ? 0 : qp + 1;
+        len = len < lim ? len : lim;
+    }
+    return len;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Generic CUDA-core kernel.  grid (max_splits, n_q_heads, n_seqs), 4 warps; warp w takes tokens
+// t0 + w, t0 + w + 4, ...; lane l holds elements l, l + 32, ... of the head dimension.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int DPL>
+__global__ void __launch_bounds__(kDecodeThreads) decode_generic_kernel(DecodeLaunch d) {
+    const PoolView& pv = d.pool;
+    const int split = blockIdx.x, hq = blockIdx.y, i = blockIdx.z;
+    const int seq = d.seq_ids ? d.seq_ids[i] : i;
+    if (!checked_seq(pv, seq)) return;
+    const int n_attend = attend_count(d, i, seq);
+    const int t0 = split * d.chunk_tokens;
+    if (t0 >= n_attend) return;
+    const int t1 = min(n_attend, t0 + d.chunk_tokens);
+    const int D = pv.head_dim;
+    const int G = d.n_q_heads / pv.num_kv_heads;
+    const int h = hq / G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float scale = rsqrtf((float)D);
+
+    float q[DPL], acc[DPL];
+    const T* qrow = reinterpret_cast<const T*>(d.q) + ((int64_t)i * d.n_q_heads + hq) * D;
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) {
+        const int dd = lane + 32 * e;
+        q[e] = dd < D ? to_f32(qrow[dd]) : 0.f;
+        acc[e] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    const T* kl = reinterpret_cast<const T*>(reinterpret_cast<const char*>(pv.k_base) + (int64_t)d.layer * pv.layer_stride_bytes);
+    const T* vl = reinterpret_cast<const T*>(reinterpret_cast<const char*>(pv.v_base) + (int64_t)d.layer * pv.layer_stride_bytes);
+    for (int t = t0 + warp; t < t1; t += kDecodeWarps) {
+        const int page = checked_page(pv, seq, t / pv.page_size);
+        if (page < 0) continue;
+        const int64_t off = row_offset(pv, page, h, t % pv.page_size);
+        float part = 0.f, v[DPL];
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            const int dd = lane + 32 * e;
+            const float kk = dd < D ? to_f32(kl[off + dd]) : 0.f;
+            v[e] = dd < D ? to_f32(vl[off + dd]) : 0.f;
+            part = fmaf(q[e], kk, part);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        const float s = part * scale;
+        const float m_new = fmaxf(m, s);
+        const float alpha = expf(m - m_new);   // m = -inf on the first token gives 0
+        const float p = expf(s - m_new);
+        l = l * alpha + p;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) acc[e] = acc[e] * alpha + p * v[e];
+        m = m_new;
+    }
+    // combine the four warps
+    __shared__ float sm_m[kDecodeWarps], sm_l[kDecodeWarps];
+    __shared__ float sm_acc[kDecodeWarps][DPL * 32];
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) sm_acc[warp][lane + 32 * e] = acc[e];
+    __syncthreads();
+    if (warp == 0) {
+        float M = -INFINITY;
+        for (int w = 0; w < kDecodeWarps; ++w)
+            if (sm_l[w] > 0.f) M = fmaxf(M, sm_m[w]);
+        float L = 0.f, wgt[kDecodeWarps];
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            wgt[w] = sm_l[w] > 0.f ? expf(sm_m[w] - M) : 0.f;
+            L += wgt[w] * sm_l[w];
+        }
+        const int64_t pidx = ((int64_t)i * d.n_q_heads + hq) * d.max_splits + split;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            const int dd = lane + 32 * e;
+            float a = 0.f;
+            for (int w = 0; w < kDecodeWarps; ++w) a += wgt[w] * sm_acc[w][dd];
+            if (dd < D) d.ws_acc[pidx * D + dd] = a;
+        }
+        if (lane == 0) {
+            d.ws_ml[pidx * 2 + 0] = M;
+            d.ws_ml[pidx * 2 + 1] = L;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-core kernel (mma.sync m16n8k16, bf16 in, f32 accumulate).  grid (max_splits, kv_heads,
+// n_seqs), 4 warps; warp w takes the 16-token tiles w, w + 4, ... of the CTA's chunk.
+// Only rows 0..7 of the 16-row A operand carry query heads (G <= 8); rows 8..15 are zero and
+// their accumulators are discarded, which halves the live accumulator registers.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_rows8(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float z0 = 0.f, z1 = 0.f;
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c0), "+f"(c1), "+f"(z0), "+f"(z1)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 r;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int kMmaD = 128;
+
+__global__ void __launch_bounds__(kDecodeThreads) decode_mma_kernel(DecodeLaunch d) {
+    const PoolView& pv = d.pool;
+    const int split = blockIdx.x, h = blockIdx.y, i = blockIdx.z;
+    const int seq = d.seq_ids ? d.seq_ids[i] : i;
+    if (!checked_seq(pv, seq)) return;
+    const int n_attend = attend_count(d, i, seq);
+    const int t0 = split * d.chunk_tokens;
+    if (t0 >= n_attend) return;
+    const int t1 = min(n_attend, t0 + d.chunk_tokens);
+    const int G = d.n_q_heads / pv.num_kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int P = pv.page_size;
+
+    // Q fragments: row g of the group, 16-byte units c, 4+c, 8+c, 12+c of the head dimension.
+    uint32_t qa[8][2];
+    {
+        const char* qrow = reinterpret_cast<const char*>(d.q) + (((int64_t)i * d.n_q_heads + h * G + g) * kMmaD) * 2;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            uint4 r = make_uint4(0, 0, 0, 0);
+            if (g < G) r = *reinterpret_cast<const uint4*>(qrow + (4 * u + c) * 16);
+            qa[2 * u][0] = r.x;
+            qa[2 * u][1] = r.y;
+            qa[2 * u + 1][0] = r.z;
+            qa[2 * u + 1][1] = r.w;
+        }
+    }
+    const char* kl = reinterpret_cast<const char*>(pv.k_base) + (int64_t)d.layer * pv.layer_stride_bytes;
+    const char* vl = reinterpret_cast<const char*>(pv.v_base) + (int64_t)d.layer * pv.layer_stride_bytes;
+    const int n_tiles = (t1 - t0 + 15) >> 4;
+
+    // page ids of this warp's tiles, one per lane, fetched up front (a warp owns at most 32 tiles)
+    int my_page = -1;
+    {
+        const int tile = warp + kDecodeWarps * lane;
+        if (tile < n_tiles) my_page = checked_page(pv, seq, (t0 + tile * 16) / P);
+    }
+
+    float o[2][8][2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[hh][e][0] = o[hh][e][1] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const float sc = rsqrtf((float)kMmaD) * kLog2e;
+
+    int it = 0;
+    for (int tile = warp; tile < n_tiles; tile += kDecodeWarps, ++it) {
+        const int page = __shfl_sync(0xffffffffu, my_page, it);
+        if (page < 0) continue;   // flagged in the status word
+        const int tb = t0 + tile * 16;
+        const int64_t tile_off = ((((int64_t)page * pv.num_kv_heads + h) * P) + (tb % P)) * (kMmaD * 2);
+        const char* kp = kl + tile_off;
+        const char* vp = vl + tile_off;
+        uint4 kr[2][4], vr[4][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) kr[j][u] = ld_stream(kp + (8 * j + g) * 256 + (4 * u + c) * 16);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int row = 2 * c + (r & 1) + 8 * (r >> 1);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) vr[r][hh] = ld_stream(vp + row * 256 + (g + 8 * hh) * 16);
+        }
+        // S = Q K^T for the two 8-token halves
+        float s[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            s[j][0] = s[j][1] = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                mma_bf16_rows8(s[j][0], s[j][1], qa[2 * u][0], qa[2 * u][1], kr[j][u].x, kr[j][u].y);
+                mma_bf16_rows8(s[j][0], s[j][1], qa[2 * u + 1][0], qa[2 * u + 1][1], kr[j][u].z, kr[j][u].w);
+            }
+        }
+        // mask the tail of the last tile; zero V rows there so that stale bytes cannot leak through 0 * x
+        const bool tail = tb + 16 > t1;
+        if (tail) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+                    if (tb + 8 * j + 2 * c + b >= t1) s[j][b] = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int row = 2 * c + (r & 1) + 8 * (r >> 1);
+                if (tb + row >= t1) vr[r][0] = vr[r][1] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx * sc);   // the tile holds at least one allowed key
+        const float alpha = exp2f(m_run - m_new);
+        float p[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int b = 0; b < 2; ++b) p[j][b] = exp2f(fmaf(s[j][b], sc, -m_new));
+        l_run = l_run * alpha + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
+        m_run = m_new;
+        const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]);
+        const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]);
+        // O = alpha * O + P V
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const uint32_t* ra = reinterpret_cast<const uint32_t*>(&vr[0][hh]);   // token 2c
+            const uint32_t* rb = reinterpret_cast<const uint32_t*>(&vr[1][hh]);   // token 2c+1
+            const uint32_t* rc = reinterpret_cast<const uint32_t*>(&vr[2][hh]);   // token 2c+8
+            const uint32_t* rd = reinterpret_cast<const uint32_t*>(&vr[3][hh]);   // token 2c+9
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(ra[e >> 1], rb[e >> 1], sel);
+                const uint32_t b1 = __byte_perm(rc[e >> 1], rd[e >> 1], sel);
+                o[hh][e][0] *= alpha;
+                o[hh][e][1] *= alpha;
+                mma_bf16_rows8(o[hh][e][0], o[hh][e][1], pa0, pa2, b0, b1);
+            }
+        }
+    }
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+    // combine the four warps: (m, l) per row and the 8 x 128 accumulator tile
+    __shared__ float sm_m[kDecodeWarps][8], sm_l[kDecodeWarps][8];
+    __shared__ __align__(16) float sm_o[kDecodeWarps][8][kMmaD];
+    if (c == 0) {
+        sm_m[warp][g] = m_run;
+        sm_l[warp][g] = l_run;
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            float* dst = &sm_o[warp][g][64 * hh + 16 * c + 8 * b];
+            *reinterpret_cast<float4*>(dst) = make_float4(o[hh][0][b], o[hh][1][b], o[hh][2][b], o[hh][3][b]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(o[hh][4][b], o[hh][5][b], o[hh][6][b], o[hh][7][b]);
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * kMmaD; idx += kDecodeThreads) {
+        const int r = idx >> 7, dd = idx & 127;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w)
+            if (sm_l[w][r] > 0.f) M = fmaxf(M, sm_m[w][r]);
+        float L = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            const float wgt = sm_l[w][r] > 0.f ? exp2f(sm_m[w][r] - M) : 0.f;
+            L += wgt * sm_l[w][r];
+            a += wgt * sm_o[w][r][dd];
+        }
+        const int64_t pidx = ((int64_t)i * d.n_q_heads + h * G + r) * d.max_splits + split;
+        d.ws_acc[pidx * kMmaD + dd] = a;
+        if (dd == 0) {
+            d.ws_ml[pidx * 2 + 0] = M * (1.0f / kLog2e);   // back to the natural-log domain
+            d.ws_ml[pidx * 2 + 1] = L;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// K3r: merge the partials of one (sequence, query head) with the reference's chunk-merge rule and
+// write out = wv / max(s, eps) in the storage dtype.  grid (n_q_heads, n_seqs).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void decode_reduce_kernel(DecodeLaunch d) {
+    const PoolView& pv = d.pool;
+    const int hq = blockIdx.x, i = blockIdx.y;
+    const int seq = d.seq_ids ? d.seq_ids[i] : i;
+    const int D = pv.head_dim;
+    T* out = reinterpret_cast<T*>(d.out) + ((int64_t)i * d.n_q_heads + hq) * D;
+    int n_attend = 0;
+    if (seq >= 0 && seq < pv.max_seqs) n_attend = attend_count(d, i, seq);
+    const int n_splits = (n_attend + d.chunk_tokens - 1) / d.chunk_tokens;
+    const int64_t base = ((int64_t)i * d.n_q_heads + hq) * d.max_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s)
+        if (d.ws_ml[(base + s) * 2 + 1] > 0.f) M = fmaxf(M, d.ws_ml[(base + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float l = d.ws_ml[(base + s) * 2 + 1];
+        if (l > 0.f) L += expf(d.ws_ml[(base + s) * 2] - M) * l;
+    }
+    const float inv = 1.0f / fmaxf(L, d.eps);
+    for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float l = d.ws_ml[(base + s) * 2 + 1];
+            if (l > 0.f) a += expf(d.ws_ml[(base + s) * 2] - M) * d.ws_acc[(base + s) * D + dd];
+        }
+        out[dd] = from_f32<T>(a * inv);
+    }
+}
+
+template <typename T>
+cudaError_t launch_generic(const DecodeLaunch& d, cudaStream_t stream) {
+    dim3 grid((unsigned)d.max_splits, (unsigned)d.n_q_heads, (unsigned)d.n_seqs);
+    const int dpl = (d.pool.head_dim + 31) / 32;
+    switch (dpl) {
+        case 1: decode_generic_kernel<T, 1><<<grid, kDecodeThreads, 0, stream>>>(d); break;
+        case 2: decode_generic_kernel<T, 2><<<grid, kDecodeThreads, 0, stream>>>(d); break;
+        case 3: decode_generic_kernel<T, 3><<<grid, kDecodeThreads, 0, stream>>>(d); break;
+        case 4: decode_generic_kernel<T, 4><<<grid, kDecodeThreads, 0, stream>>>(d); break;
+        case 5: case 6: decode_generic_kernel<T, 6><<<grid, kDecodeThreads, 0, stream>>>(d); break;
+        default: decode_generic_kernel<T, 8><<<grid, kDecodeThreads, 0, stream>>>(d); break;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, int32_t num_kv_heads,
+                 int64_t total_tokens_hint, int32_t* chunk_tokens, int32_t* max_splits) {
+    // Aim at about 8 waves of 3 CTAs per SM on 148 SMs so that ragged lengths even out, but never
+    // more than `splits` partials per sequence (bounds the workspace independently of the lengths).
+    const int64_t target = 148LL * 3 * 8;
+    const int64_t max_ctx = (int64_t)max_pages_per_seq * page_size;
+    int64_t splits = (2 * target + (int64_t)n_seqs * num_kv_heads - 1) / ((int64_t)n_seqs * num_kv_heads);
+    splits = splits < 1 ? 1 : (splits > 128 ? 128 : splits);
+    int64_t floor_chunk = (max_ctx + splits - 1) / splits;
+    int64_t chunk = total_tokens_hint > 0 ? (num_kv_heads * total_tokens_hint) / target : 0;
+    if (chunk < floor_chunk) chunk = floor_chunk;
+    const char* env = getenv("SKV_DECODE_CHUNK");
+    if (env && atoi(env) > 0 && atoi(env) >= floor_chunk) chunk = atoi(env);
+    chunk = ((chunk + 63) / 64) * 64;                 // 4 warps x 16-token tiles
+    if (chunk < 64) chunk = 64;
+    if (chunk > 2048) {                               // a warp holds at most 32 tile page ids
+        chunk = 2048;
+        splits = (max_ctx + chunk - 1) / chunk;
+    }
+    *chunk_tokens = (int32_t)chunk;
+    *max_splits = (int32_t)splits;
+}
+
+cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream) {
+    const int G = d.n_q_heads / d.pool.num_kv_heads;
+    const bool mma_ok = d.dtype == SKV_BF16 && d.pool.head_dim == kMmaD && d.pool.page_size % 16 == 0 && G <= 8 &&
+                        !d.force_generic && ((uintptr_t)d.q % 16 == 0);
+    cudaError_t e;
+    if (mma_ok) {
+        dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
+        decode_mma_kernel<<<grid, kDecodeThreads, 0, stream>>>(d);
+        e = cudaGetLastError();
+    } else if (d.dtype == SKV_BF16) {
+        e = launch_generic<__nv_bfloat16>(d, stream);
+    } else {
+        e = launch_generic<float>(d, stream);
+    }
+    if (e != cudaSuccess) return e;
+    dim3 rgrid((unsigned)d.n_q_heads, (unsigned)d.n_seqs);
+    const int threads = d.pool.head_dim >= 128 ? 128 : 64;
+    if (d.dtype == SKV_BF16)
+        decode_reduce_kernel<__nv_bfloat16><<<rgrid, threads, 0, stream>>>(d);
+    else
+        decode_reduce_kernel<float><<<rgrid, threads, 0, stream>>>(d);
+    return cudaGetLastError();
+}
+
+}  // namespace skv

@@ -1,0 +1,970 @@
+// Host side of the paged KV pool: allocator, page tables, lengths, replay rejection,
+// staging of per-call metadata, and the C ABI entry points that launch the kernels.
+//
+// The reference keeps one growing tensor per layer and re-copies it on every append
+// (src/ollm/mlx_kvcache.py:107-118).  Here a sequence owns a row of page ids; an append
+// writes only the new tokens.  All validation that the reference does in Python
+// (mlx_kvcache.py:127-158) happens here on the host before anything is launched.
+#include <algorithm>
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <thread>
+
+#include "skv_internal.h"
+
+using namespace skv;
+
+namespace {
+
+struct TableUpdate {
+    int32_t seq, slot, value;
+};
+
+// Pinned host slots with matching device slots.  A slot is reused only after the copy that
+// read it has finished (one event per slot), so per-call metadata can be uploaded without
+// blocking the host.
+struct StagingRing {
+    static constexpr int kSlots = 64;
+    static constexpr size_t kSlotBytes = 64 * 1024;
+    char* host = nullptr;
+    char* dev = nullptr;
+    cudaEvent_t ev[kSlots] = {};
+    bool pending[kSlots] = {};
+    int next = 0;
+
+    cudaError_t init() {
+        cudaError_t e = cudaHostAlloc((void**)&host, kSlots * kSlotBytes, cudaHostAllocDefault);
+        if (e != cudaSuccess) return e;
+        e = cudaMalloc((void**)&dev, kSlots * kSlotBytes);
+        if (e != cudaSuccess) return e;
+        for (int i = 0; i < kSlots; ++i) {
+            e = cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
+    void destroy() {
+        for (int i = 0; i < kSlots; ++i)
+            if (ev[i]) cudaEventDestroy(ev[i]);
+        if (dev) cudaFree(dev);
+        if (host) cudaFreeHost(host);
+    }
+    // Copies `bytes` of `src` to the device through the next slot; *dev_out is valid on `stream`.
+    cudaError_t upload(const void* src, size_t bytes, cudaStream_t stream, void** dev_out) {
+        if (bytes > kSlotBytes) return cudaErrorInvalidValue;
+        int s = next;
+        next = (next + 1) % kSlots;
+        if (pending[s]) {
+            cudaError_t e = cudaEventSynchronize(ev[s]);
+            if (e != cudaSuccess) return e;
+            pending[s] = false;
+        }
+        char* h = host + (size_t)s * kSlotBytes;
+        char* d = dev + (size_t)s * kSlotBytes;
+        std::memcpy(h, src, bytes);
+        cudaError_t e = cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return e;
+        e = cudaEventRecord(ev[s], stream);
+        if (e != cudaSuccess) return e;
+        pending[s] = true;
+        *dev_out = d;
+        return cudaSuccess;
+    }
+};
+
+}  // namespace
+
+struct skv_pool {
+    skv_config cfg{};
+    bool host_only = false;
+    size_t esize = 2;
+    size_t page_bytes = 0;          // one layer's K (or V) bytes of one page: heads * page_size * dim * esize
+    size_t layer_stride = 0;        // bytes between layers inside the K (or V) allocation
+
+    // host bookkeeping
+    std::vector<int32_t> page_table;     // [max_seqs][max_pages_per_seq]
+    std::vector<int32_t> n_seq_pages;    // [max_seqs]
+    std::vector<int32_t> lengths;        // [num_layers][max_seqs]
+    std::vector<uint8_t> live;           // [max_seqs]
+    std::vector<int32_t> page_owner;     // [num_pages] owning sequence or -1
+    std::vector<int32_t> free_pages, free_seqs, free_host;
+    int64_t n_evicted = 0, n_prefetched = 0, bytes_d2h = 0, bytes_h2d = 0;
+
+    // device state
+    char* d_k = nullptr;
+    char* d_v = nullptr;
+    int32_t* d_page_table = nullptr;
+    int32_t* d_lengths = nullptr;
+    int32_t* d_status = nullptr;
+    float* d_inv_freq = nullptr;
+    bool rope_set = false;
+    float rope_scaling = 1.0f;
+    StagingRing ring;
+
+    // host tier
+    char* h_tier = nullptr;              // pinned + mapped: [host_pages][num_layers][2][page_bytes]
+    char* h_tier_dev = nullptr;          // device alias of h_tier
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_compute = nullptr, ev_copy = nullptr;
+    bool copy_pending = false;           // copies enqueued on copy_stream not yet ordered before compute
+    std::vector<TableUpdate> deferred_updates;   // page-table entries to publish once prefetch copies are ordered
+
+    std::string err;
+
+    int32_t fail(int32_t code, const char* fmt, ...) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        err = buf;
+        return code;
+    }
+    int32_t cuda_fail(cudaError_t e, const char* what) {
+        return fail(SKV_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    }
+    PoolView view() const {
+        PoolView v;
+        v.k_base = d_k;
+        v.v_base = d_v;
+        v.layer_stride_bytes = (int64_t)layer_stride;
+        v.page_table = d_page_table;
+        v.lengths = d_lengths;
+        v.status = d_status;
+        v.num_kv_heads = cfg.num_kv_heads;
+        v.head_dim = cfg.head_dim;
+        v.page_size = cfg.page_size;
+        v.num_pages = cfg.num_pages;
+        v.max_seqs = cfg.max_seqs;
+        v.max_pages_per_seq = cfg.max_pages_per_seq;
+        return v;
+    }
+    int32_t& pt(int32_t seq, int32_t slot) { return page_table[(size_t)seq * cfg.max_pages_per_seq + slot]; }
+    int32_t& len(int32_t layer, int32_t seq) { return lengths[(size_t)layer * cfg.max_seqs + seq]; }
+};
+
+namespace {
+
+#define CUDA_TRY(pool, call)                                   \
+    do {                                                       \
+        cudaError_t _e = (call);                               \
+        if (_e != cudaSuccess) return (pool)->cuda_fail(_e, #call); \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool active = false;
+    explicit DeviceGuard(const skv_pool* p) {
+        if (!p->host_only && cudaGetDevice(&prev) == cudaSuccess && prev != p->cfg.device) {
+            cudaSetDevice(p->cfg.device);
+            active = true;
+        }
+    }
+    ~DeviceGuard() {
+        if (active) cudaSetDevice(prev);
+    }
+};
+
+__global__ void apply_table_updates_kernel(int32_t* __restrict__ table, const TableUpdate* __restrict__ ups, int n,
+                                           int max_seqs, int max_pages) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    TableUpdate u = ups[i];
+    if (u.seq < 0 || u.seq >= max_seqs || u.slot < 0 || u.slot >= max_pages) return;
+    table[(size_t)u.seq * max_pages + u.slot] = u.value;
+}
+
+struct LengthUpdate {
+    int32_t index, value;
+};
+__global__ void apply_length_updates_kernel(int32_t* __restrict__ lengths, const LengthUpdate* __restrict__ ups, int n,
+                                            int total) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    LengthUpdate u = ups[i];
+    if (u.index >= 0 && u.index < total) lengths[u.index] = u.value;
+}
+
+// 16-byte vector copy of whole pages between the device pools and the mapped host tier.
+struct CopyItem {
+    int32_t page, slot;
+};
+__global__ void page_copy_kernel(char* __restrict__ k_base, char* __restrict__ v_base, char* __restrict__ tier,
+                                 const CopyItem* __restrict__ items, int64_t layer_stride, int64_t page_bytes,
+                                 int num_layers, int to_host) {
+    CopyItem it = items[blockIdx.x];
+    int layer = blockIdx.y >> 1;
+    int is_v = blockIdx.y & 1;
+    char* dev = (is_v ? v_base : k_base) + (int64_t)layer * layer_stride + (int64_t)it.page * page_bytes;
+    char* hst = tier + (((int64_t)it.slot * num_layers + layer) * 2 + is_v) * page_bytes;
+    const int4* src = reinterpret_cast<const int4*>(to_host ? dev : hst);
+    int4* dst = reinterpret_cast<int4*>(to_host ? hst : dev);
+    int n = (int)(page_bytes / 16);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+}
+
+int32_t publish_table_updates(skv_pool* p, const std::vector<TableUpdate>& ups, cudaStream_t stream) {
+    if (p->host_only || ups.empty()) return SKV_OK;
+    const size_t per = StagingRing::kSlotBytes / sizeof(TableUpdate);
+    for (size_t off = 0; off < ups.size(); off += per) {
+        size_t n = std::min(per, ups.size() - off);
+        void* dev = nullptr;
+        CUDA_TRY(p, p->ring.upload(ups.data() + off, n * sizeof(TableUpdate), stream, &dev));
+        apply_table_updates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+            p->d_page_table, (const TableUpdate*)dev, (int)n, p->cfg.max_seqs, p->cfg.max_pages_per_seq);
+        CUDA_TRY(p, cudaGetLastError());
+    }
+    return SKV_OK;
+}
+
+int32_t publish_length_updates(skv_pool* p, const std::vector<LengthUpdate>& ups, cudaStream_t stream) {
+    if (p->host_only || ups.empty()) return SKV_OK;
+    const size_t per = StagingRing::kSlotBytes / sizeof(LengthUpdate);
+    for (size_t off = 0; off < ups.size(); off += per) {
+        size_t n = std::min(per, ups.size() - off);
+        void* dev = nullptr;
+        CUDA_TRY(p, p->ring.upload(ups.data() + off, n * sizeof(LengthUpdate), stream, &dev));
+        apply_length_updates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+            p->d_lengths, (const LengthUpdate*)dev, (int)n, p->cfg.num_layers * p->cfg.max_seqs);
+        CUDA_TRY(p, cudaGetLastError());
+    }
+    return SKV_OK;
+}
+
+bool valid_seq(const skv_pool* p, int32_t seq) { return seq >= 0 && seq < p->cfg.max_seqs && p->live[seq]; }
+
+// Orders everything enqueued on the copy stream before later work on `stream` and publishes
+// page-table entries that were waiting for those copies.
+int32_t order_transfers(skv_pool* p, cudaStream_t stream) {
+    if (p->host_only) return SKV_OK;
+    if (p->copy_pending) {
+        CUDA_TRY(p, cudaEventRecord(p->ev_copy, p->copy_stream));
+        CUDA_TRY(p, cudaStreamWaitEvent(stream, p->ev_copy, 0));
+        p->copy_pending = false;
+    }
+    if (!p->deferred_updates.empty()) {
+        int32_t st = publish_table_updates(p, p->deferred_updates, stream);
+        if (st != SKV_OK) return st;
+        p->deferred_updates.clear();
+    }
+    return SKV_OK;
+}
+
+// Grows a sequence's page-table row to cover `total_tokens`; all-or-nothing.
+int32_t grow(skv_pool* p, int32_t seq, int32_t total_tokens, std::vector<TableUpdate>* ups) {
+    const int32_t P = p->cfg.page_size;
+    int32_t need = (total_tokens + P - 1) / P;
+    int32_t have = p->n_seq_pages[seq];
+    if (need <= have) return SKV_OK;
+    if (need > p->cfg.max_pages_per_seq)
+        return p->fail(SKV_ERR_OUT_OF_PAGES, "sequence %d needs %d pages, row holds %d", seq, need,
+                       p->cfg.max_pages_per_seq);
+    if ((size_t)(need - have) > p->free_pages.size())
+        return p->fail(SKV_ERR_OUT_OF_PAGES, "need %d pages, %zu free", need - have, p->free_pages.size());
+    for (int32_t slot = have; slot < need; ++slot) {
+        int32_t page = p->free_pages.back();
+        p->free_pages.pop_back();
+        p->pt(seq, slot) = page;
+        p->page_owner[page] = seq;
+        ups->push_back({seq, slot, page});
+    }
+    p->n_seq_pages[seq] = need;
+    return SKV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t skv_abi_version(void) { return SKV_ABI_VERSION; }
+
+const char* skv_status_string(int32_t s) {
+    switch (s) {
+        case SKV_OK: return "ok";
+        case SKV_ERR_BAD_ARG: return "bad argument";
+        case SKV_ERR_REPLAY: return "append does not start exactly after the cached sequence";
+        case SKV_ERR_OUT_OF_PAGES: return "out of pages";
+        case SKV_ERR_NOT_RESIDENT: return "page not resident";
+        case SKV_ERR_TIMEOUT: return "timeout";
+        case SKV_ERR_CUDA: return "CUDA error";
+        case SKV_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+        case SKV_ERR_DEVICE_FLAG: return "device status flag set";
+        default: return "unknown status";
+    }
+}
+
+const char* skv_last_error(const skv_pool* pool) { return pool ? pool->err.c_str() : "null pool"; }
+
+int32_t skv_create(const skv_config* cfg, skv_pool** out) {
+    if (!cfg || !out) return SKV_ERR_BAD_ARG;
+    *out = nullptr;
+    if (cfg->num_layers <= 0 || cfg->num_kv_heads <= 0 || cfg->head_dim <= 0 || cfg->page_size <= 0 ||
+        cfg->num_pages <= 0 || cfg->max_seqs <= 0 || cfg->max_pages_per_seq <= 0 || cfg->host_pages < 0)
+        return SKV_ERR_BAD_ARG;
+    if (cfg->dtype != SKV_F32 && cfg->dtype != SKV_BF16) return SKV_ERR_BAD_ARG;
+    if (cfg->head_dim % 2 != 0 || cfg->head_dim > 256) return SKV_ERR_UNSUPPORTED;
+    skv_pool* p = new (std::nothrow) skv_pool();
+    if (!p) return SKV_ERR_BAD_ARG;
+    p->cfg = *cfg;
+    p->host_only = cfg->device < 0;
+    p->esize = dtype_size(cfg->dtype);
+    p->page_bytes = (size_t)cfg->num_kv_heads * cfg->page_size * cfg->head_dim * p->esize;
+    p->layer_stride = p->page_bytes * (size_t)cfg->num_pages;
+    p->page_table.assign((size_t)cfg->max_seqs * cfg->max_pages_per_seq, SKV_PAGE_UNASSIGNED);
+    p->n_seq_pages.assign(cfg->max_seqs, 0);
+    p->lengths.assign((size_t)cfg->num_layers * cfg->max_seqs, 0);
+    p->live.assign(cfg->max_seqs, 0);
+    p->page_owner.assign(cfg->num_pages, -1);
+    for (int32_t i = cfg->num_pages - 1; i >= 0; --i) p->free_pages.push_back(i);
+    for (int32_t i = cfg->max_seqs - 1; i >= 0; --i) p->free_seqs.push_back(i);
+    for (int32_t i = cfg->host_pages - 1; i >= 0; --i) p->free_host.push_back(i);
+    *out = p;
+    if (p->host_only) return SKV_OK;
+
+    int32_t st = [&]() -> int32_t {
+        DeviceGuard g(p);
+        CUDA_TRY(p, cudaSetDevice(cfg->device));
+        size_t total = p->layer_stride * (size_t)cfg->num_layers;
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_k, total));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_v, total));
+        CUDA_TRY(p, cudaMemset(p->d_k, 0, total));
+        CUDA_TRY(p, cudaMemset(p->d_v, 0, total));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_page_table, p->page_table.size() * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMemset(p->d_page_table, 0xFF, p->page_table.size() * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_lengths, p->lengths.size() * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMemset(p->d_lengths, 0, p->lengths.size() * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_status, sizeof(int32_t)));
+        CUDA_TRY(p, cudaMemset(p->d_status, 0, sizeof(int32_t)));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_inv_freq, (size_t)cfg->head_dim / 2 * sizeof(float)));
+        CUDA_TRY(p, p->ring.init());
+        CUDA_TRY(p, cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
+        CUDA_TRY(p, cudaEventCreateWithFlags(&p->ev_compute, cudaEventDisableTiming));
+        CUDA_TRY(p, cudaEventCreateWithFlags(&p->ev_copy, cudaEventDisableTiming));
+        if (cfg->host_pages > 0) {
+            if (p->page_bytes % 16 != 0)
+                return p->fail(SKV_ERR_UNSUPPORTED, "host tier needs page bytes to be a multiple of 16");
+            size_t bytes = (size_t)cfg->host_pages * cfg->num_layers * 2 * p->page_bytes;
+            CUDA_TRY(p, cudaHostAlloc((void**)&p->h_tier, bytes, cudaHostAllocMapped | cudaHostAllocPortable));
+            CUDA_TRY(p, cudaHostGetDevicePointer((void**)&p->h_tier_dev, p->h_tier, 0));
+        }
+        CUDA_TRY(p, cudaDeviceSynchronize());
+        return SKV_OK;
+    }();
+    return st;   // on failure the caller still owns *out and may read skv_last_error before skv_destroy
+}
+
+int32_t skv_destroy(skv_pool* p) {
+    if (!p) return SKV_OK;
+    if (!p->host_only) {
+        DeviceGuard g(p);
+        cudaDeviceSynchronize();
+        p->ring.destroy();
+        if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
+        if (p->ev_compute) cudaEventDestroy(p->ev_compute);
+        if (p->ev_copy) cudaEventDestroy(p->ev_copy);
+        if (p->h_tier) cudaFreeHost(p->h_tier);
+        cudaFree(p->d_k);
+        cudaFree(p->d_v);
+        cudaFree(p->d_page_table);
+        cudaFree(p->d_lengths);
+        cudaFree(p->d_status);
+        cudaFree(p->d_inv_freq);
+    }
+    delete p;
+    return SKV_OK;
+}
+
+int32_t skv_alloc_sequence(skv_pool* p, int32_t* seq_out) {
+    if (!p || !seq_out) return SKV_ERR_BAD_ARG;
+    if (p->free_seqs.empty()) return p->fail(SKV_ERR_OUT_OF_PAGES, "no free sequence id (max_seqs %d)", p->cfg.max_seqs);
+    int32_t s = p->free_seqs.back();
+    p->free_seqs.pop_back();
+    p->live[s] = 1;
+    *seq_out = s;
+    return SKV_OK;
+}
+
+int32_t skv_free_sequence(skv_pool* p, int32_t seq) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (!valid_seq(p, seq)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", seq);
+    std::vector<TableUpdate> ups;
+    std::vector<LengthUpdate> lups;
+    for (int32_t slot = p->n_seq_pages[seq] - 1; slot >= 0; --slot) {
+        int32_t e = p->pt(seq, slot);
+        if (e >= 0) {
+            p->free_pages.push_back(e);
+            p->page_owner[e] = -1;
+        } else if (e <= -2) {
+            p->free_host.push_back(-2 - e);
+        }
+        p->pt(seq, slot) = SKV_PAGE_UNASSIGNED;
+        ups.push_back({seq, slot, SKV_PAGE_UNASSIGNED});
+    }
+    p->n_seq_pages[seq] = 0;
+    for (int32_t l = 0; l < p->cfg.num_layers; ++l) {
+        p->len(l, seq) = 0;
+        lups.push_back({l * p->cfg.max_seqs + seq, 0});
+    }
+    p->live[seq] = 0;
+    p->free_seqs.push_back(seq);
+    // drop deferred entries of this sequence
+    p->deferred_updates.erase(std::remove_if(p->deferred_updates.begin(), p->deferred_updates.end(),
+                                             [&](const TableUpdate& u) { return u.seq == seq; }),
+                              p->deferred_updates.end());
+    DeviceGuard g(p);
+    int32_t st = publish_table_updates(p, ups, nullptr);
+    if (st != SKV_OK) return st;
+    return publish_length_updates(p, lups, nullptr);
+}
+
+int32_t skv_reserve(skv_pool* p, int32_t seq, int32_t total_tokens) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (!valid_seq(p, seq)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", seq);
+    if (total_tokens < 0) return p->fail(SKV_ERR_BAD_ARG, "total_tokens must be non-negative");
+    std::vector<TableUpdate> ups;
+    int32_t st = grow(p, seq, total_tokens, &ups);
+    if (st != SKV_OK) return st;
+    DeviceGuard g(p);
+    return publish_table_updates(p, ups, nullptr);
+}
+
+int32_t skv_set_page_table(skv_pool* p, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t length) {
+    if (!p || (!pages && n_pages > 0)) return SKV_ERR_BAD_ARG;
+    if (!valid_seq(p, seq)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", seq);
+    if (n_pages < 0 || n_pages > p->cfg.max_pages_per_seq)
+        return p->fail(SKV_ERR_BAD_ARG, "n_pages %d outside [0, %d]", n_pages, p->cfg.max_pages_per_seq);
+    if (length < 0 || (int64_t)length > (int64_t)n_pages * p->cfg.page_size)
+        return p->fail(SKV_ERR_BAD_ARG, "length %d does not fit %d pages", length, n_pages);
+    if (p->n_seq_pages[seq] != 0) return p->fail(SKV_ERR_BAD_ARG, "sequence %d already owns pages", seq);
+    // validate: in range, owned by nobody, no duplicates
+    std::vector<int32_t> sorted(pages, pages + n_pages);
+    std::sort(sorted.begin(), sorted.end());
+    for (int32_t i = 0; i < n_pages; ++i) {
+        int32_t pg = sorted[i];
+        if (pg < 0 || pg >= p->cfg.num_pages) return p->fail(SKV_ERR_BAD_ARG, "page id %d outside the pool", pg);
+        if (i > 0 && sorted[i - 1] == pg) return p->fail(SKV_ERR_BAD_ARG, "page id %d listed twice", pg);
+        if (p->page_owner[pg] != -1) return p->fail(SKV_ERR_BAD_ARG, "page id %d belongs to sequence %d", pg, p->page_owner[pg]);
+    }
+    // take the pages out of the free stack, keeping the order of the rest
+    std::vector<uint8_t> taken(p->cfg.num_pages, 0);
+    for (int32_t i = 0; i < n_pages; ++i) taken[pages[i]] = 1;
+    p->free_pages.erase(std::remove_if(p->free_pages.begin(), p->free_pages.end(), [&](int32_t pg) { return taken[pg] != 0; }),
+                        p->free_pages.end());
+    std::vector<TableUpdate> ups;
+    std::vector<LengthUpdate> lups;
+    for (int32_t i = 0; i < n_pages; ++i) {
+        p->pt(seq, i) = pages[i];
+        p->page_owner[pages[i]] = seq;
+        ups.push_back({seq, i, pages[i]});
+    }
+    p->n_seq_pages[seq] = n_pages;
+    for (int32_t l = 0; l < p->cfg.num_layers; ++l) {
+        p->len(l, seq) = length;
+        lups.push_back({l * p->cfg.max_seqs + seq, length});
+    }
+    DeviceGuard g(p);
+    int32_t st = publish_table_updates(p, ups, nullptr);
+    if (st != SKV_OK) return st;
+    return publish_length_updates(p, lups, nullptr);
+}
+
+int32_t skv_truncate(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, int32_t new_length, void* stream_) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (layer < 0) return p->fail(SKV_ERR_BAD_ARG, "layer_idx must be a non-negative integer");
+    if (layer >= p->cfg.num_layers)
+        return p->fail(SKV_ERR_BAD_ARG, "layer_idx %d is outside configured layer count %d", layer, p->cfg.num_layers);
+    if (n_seqs <= 0 || n_seqs > p->cfg.max_seqs || new_length < 0) return p->fail(SKV_ERR_BAD_ARG, "n_seqs %d / new_length %d out of range", n_seqs, new_length);
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        int32_t s = seq_ids ? seq_ids[i] : i;
+        if (!valid_seq(p, s)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", s);
+        if (new_length > p->len(layer, s)) return p->fail(SKV_ERR_BAD_ARG, "new_length %d exceeds sequence %d's length %d", new_length, s, p->len(layer, s));
+    }
+    std::vector<LengthUpdate> lups;
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        int32_t s = seq_ids ? seq_ids[i] : i;
+        p->len(layer, s) = new_length;
+        lups.push_back({layer * p->cfg.max_seqs + s, new_length});
+    }
+    DeviceGuard g(p);
+    return publish_length_updates(p, lups, (cudaStream_t)stream_);
+}
+
+int32_t skv_length(const skv_pool* p, int32_t layer, int32_t seq, int32_t* out) {
+    if (!p || !out) return SKV_ERR_BAD_ARG;
+    if (layer < 0 || layer >= p->cfg.num_layers || seq < 0 || seq >= p->cfg.max_seqs) return SKV_ERR_BAD_ARG;
+    *out = p->lengths[(size_t)layer * p->cfg.max_seqs + seq];
+    return SKV_OK;
+}
+
+int32_t skv_lengths(const skv_pool* p, int32_t layer, int32_t* out, int32_t n) {
+    if (!p || !out || layer < 0 || layer >= p->cfg.num_layers || n < 0 || n > p->cfg.max_seqs) return SKV_ERR_BAD_ARG;
+    std::memcpy(out, p->lengths.data() + (size_t)layer * p->cfg.max_seqs, (size_t)n * sizeof(int32_t));
+    return SKV_OK;
+}
+
+int32_t skv_page_table(const skv_pool* p, int32_t seq, int32_t* out, int32_t capacity, int32_t* n_out) {
+    if (!p || seq < 0 || seq >= p->cfg.max_seqs) return SKV_ERR_BAD_ARG;
+    int32_t n = p->n_seq_pages[seq];
+    if (n_out) *n_out = n;
+    if (out) {
+        if (capacity < n) return SKV_ERR_BAD_ARG;
+        std::memcpy(out, p->page_table.data() + (size_t)seq * p->cfg.max_pages_per_seq, (size_t)n * sizeof(int32_t));
+    }
+    return SKV_OK;
+}
+
+int32_t skv_pool_counters(const skv_pool* p, int64_t out[8]) {
+    if (!p || !out) return SKV_ERR_BAD_ARG;
+    out[0] = (int64_t)p->free_pages.size();
+    out[1] = (int64_t)p->cfg.num_pages - out[0];
+    out[2] = (int64_t)p->free_host.size();
+    out[3] = p->n_evicted;
+    out[4] = p->n_prefetched;
+    out[5] = p->bytes_d2h;
+    out[6] = p->bytes_h2d;
+    int64_t n = 0;
+    for (uint8_t l : p->live) n += l;
+    out[7] = n;
+    return SKV_OK;
+}
+
+int32_t skv_pool_pointers(const skv_pool* p, int32_t layer, void** k, void** v) {
+    if (!p || layer < 0 || layer >= p->cfg.num_layers) return SKV_ERR_BAD_ARG;
+    if (k) *k = p->d_k ? p->d_k + (size_t)layer * p->layer_stride : nullptr;
+    if (v) *v = p->d_v ? p->d_v + (size_t)layer * p->layer_stride : nullptr;
+    return SKV_OK;
+}
+
+int32_t skv_device_tables(const skv_pool* p, int32_t** page_table, int32_t** lengths) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (page_table) *page_table = p->d_page_table;
+    if (lengths) *lengths = p->d_lengths;
+    return SKV_OK;
+}
+
+int32_t skv_set_rope(skv_pool* p, const float* inv_freq, int32_t n, float scaling) {
+    if (!p || !inv_freq) return SKV_ERR_BAD_ARG;
+    if (n != p->cfg.head_dim / 2) return p->fail(SKV_ERR_BAD_ARG, "inv_freq has %d entries, head_dim/2 is %d", n, p->cfg.head_dim / 2);
+    if (!(scaling > 0.0f)) return p->fail(SKV_ERR_BAD_ARG, "scaling_factor must be positive");
+    p->rope_scaling = scaling;
+    p->rope_set = true;
+    if (p->host_only) return SKV_OK;
+    DeviceGuard g(p);
+    CUDA_TRY(p, cudaMemcpy(p->d_inv_freq, inv_freq, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+    return SKV_OK;
+}
+
+int32_t skv_append(skv_pool* p, const skv_append_args* a, void* stream_) {
+    if (!p || !a) return SKV_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    // -- validation, in the reference's order (mlx_kvcache.py:85-104) --
+    if (a->layer < 0) return p->fail(SKV_ERR_BAD_ARG, "layer_idx must be a non-negative integer");
+    if (a->layer >= p->cfg.num_layers)
+        return p->fail(SKV_ERR_BAD_ARG, "layer_idx %d is outside configured layer count %d", a->layer, p->cfg.num_layers);
+    if (a->n_seqs <= 0 || a->n_seqs > p->cfg.max_seqs || a->n_new < 0)
+        return p->fail(SKV_ERR_BAD_ARG, "n_seqs %d / n_new %d out of range", a->n_seqs, a->n_new);
+    if (!p->host_only && a->n_new > 0 && (!a->k || !a->v)) return p->fail(SKV_ERR_BAD_ARG, "k and v must be given");
+    if ((a->rope_k || a->q_in) && !p->rope_set) return p->fail(SKV_ERR_BAD_ARG, "RoPE requested but skv_set_rope was not called");
+    if (a->q_in && (!a->q_out || a->n_q_heads <= 0)) return p->fail(SKV_ERR_BAD_ARG, "q_out and n_q_heads must accompany q_in");
+    std::vector<AppendMeta> meta(a->n_seqs);
+    std::vector<uint8_t> seen(p->cfg.max_seqs, 0);
+    for (int32_t i = 0; i < a->n_seqs; ++i) {
+        int32_t s = a->seq_ids ? a->seq_ids[i] : i;
+        if (!valid_seq(p, s)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", s);
+        if (seen[s]) return p->fail(SKV_ERR_BAD_ARG, "sequence %d listed twice", s);
+        seen[s] = 1;
+        int32_t cur = p->len(a->layer, s);
+        int32_t start = a->start_pos ? a->start_pos[i] : cur;
+        if (start != cur)
+            return p->fail(SKV_ERR_REPLAY,
+                           "cache_position must append exactly after the cached sequence; sequence %d layer %d expected start %d, got %d",
+                           s, a->layer, cur, start);
+        meta[i] = {s, start};
+    }
+    if (a->n_new == 0) return SKV_OK;
+    // -- page allocation: all-or-nothing across the batch --
+    {
+        int64_t need_total = 0;
+        const int32_t P = p->cfg.page_size;
+        for (int32_t i = 0; i < a->n_seqs; ++i) {
+            int32_t need = (meta[i].start + a->n_new + P - 1) / P;
+            if (need > p->cfg.max_pages_per_seq)
+                return p->fail(SKV_ERR_OUT_OF_PAGES, "sequence %d needs %d pages, row holds %d", meta[i].seq, need, p->cfg.max_pages_per_seq);
+            need_total += std::max(0, need - p->n_seq_pages[meta[i].seq]);
+        }
+        if (need_total > (int64_t)p->free_pages.size())
+            return p->fail(SKV_ERR_OUT_OF_PAGES, "need %lld pages, %zu free", (long long)need_total, p->free_pages.size());
+    }
+    // target pages must be resident
+    for (int32_t i = 0; i < a->n_seqs; ++i) {
+        int32_t first = meta[i].start / p->cfg.page_size;
+        for (int32_t slot = first; slot < p->n_seq_pages[meta[i].seq]; ++slot)
+            if (p->pt(meta[i].seq, slot) < 0)
+                return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", meta[i].seq, slot);
+    }
+    std::vector<TableUpdate> ups;
+    for (int32_t i = 0; i < a->n_seqs; ++i) {
+        int32_t st = grow(p, meta[i].seq, meta[i].start + a->n_new, &ups);
+        if (st != SKV_OK) return st;   // cannot happen after the check above
+    }
+    for (int32_t i = 0; i < a->n_seqs; ++i) p->len(a->layer, meta[i].seq) = meta[i].start + a->n_new;
+    if (p->host_only) return SKV_OK;
+
+    DeviceGuard g(p);
+    int32_t st = order_transfers(p, stream);
+    if (st != SKV_OK) return st;
+    st = publish_table_updates(p, ups, stream);
+    if (st != SKV_OK) return st;
+    AppendLaunch L{};
+    L.pool = p->view();
+    L.layer = a->layer;
+    L.n_seqs = a->n_seqs;
+    L.n_new = a->n_new;
+    L.dtype = p->cfg.dtype;
+    L.k = a->k;
+    L.v = a->v;
+    L.kv_stride_seq = a->kv_stride_seq;
+    L.kv_stride_head = a->kv_stride_head;
+    L.kv_stride_tok = a->kv_stride_tok;
+    L.rope_k = a->rope_k;
+    L.q_in = a->q_in;
+    L.q_out = a->q_out;
+    L.n_q_heads = a->q_in ? a->n_q_heads : 0;
+    L.q_stride_seq = a->q_stride_seq;
+    L.q_stride_head = a->q_stride_head;
+    L.q_stride_tok = a->q_stride_tok;
+    L.inv_freq = p->d_inv_freq;
+    L.scaling = p->rope_scaling;
+    const size_t per = StagingRing::kSlotBytes / sizeof(AppendMeta);
+    for (size_t off = 0; off < meta.size(); off += per) {
+        size_t n = std::min(per, meta.size() - off);
+        void* dev = nullptr;
+        CUDA_TRY(p, p->ring.upload(meta.data() + off, n * sizeof(AppendMeta), stream, &dev));
+        L.meta = (const AppendMeta*)dev;
+        L.n_seqs = (int32_t)n;
+        // advance the tensor pointers to the first sequence of this slice
+        L.k = (const char*)a->k + (int64_t)off * a->kv_stride_seq * (int64_t)p->esize;
+        L.v = (const char*)a->v + (int64_t)off * a->kv_stride_seq * (int64_t)p->esize;
+        if (a->q_in) {
+            L.q_in = (const char*)a->q_in + (int64_t)off * a->q_stride_seq * (int64_t)p->esize;
+            L.q_out = (char*)a->q_out + (int64_t)off * a->q_stride_seq * (int64_t)p->esize;
+        }
+        CUDA_TRY(p, launch_append(L, stream));
+    }
+    return SKV_OK;
+}
+
+static int32_t upload_ids(skv_pool* p, const int32_t* ids, int32_t n, cudaStream_t stream, const int32_t** dev_out) {
+    *dev_out = nullptr;
+    if (!ids) return SKV_OK;
+    if ((size_t)n * sizeof(int32_t) > StagingRing::kSlotBytes) return p->fail(SKV_ERR_BAD_ARG, "too many entries (%d) for one call", n);
+    void* dev = nullptr;
+    CUDA_TRY(p, p->ring.upload(ids, (size_t)n * sizeof(int32_t), stream, &dev));
+    *dev_out = (const int32_t*)dev;
+    return SKV_OK;
+}
+
+// Validates a list of sequences for a read over the first `upto[i]` tokens (or the whole length).
+static int32_t check_readable(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const int32_t* upto) {
+    if (layer < 0) return p->fail(SKV_ERR_BAD_ARG, "layer_idx must be a non-negative integer");
+    if (layer >= p->cfg.num_layers)
+        return p->fail(SKV_ERR_BAD_ARG, "layer_idx %d is outside configured layer count %d", layer, p->cfg.num_layers);
+    if (n_seqs <= 0 || n_seqs > p->cfg.max_seqs) return p->fail(SKV_ERR_BAD_ARG, "n_seqs %d out of range", n_seqs);
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        int32_t s = seq_ids ? seq_ids[i] : i;
+        if (!valid_seq(p, s)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", s);
+        int32_t T = p->len(layer, s);
+        if (upto) T = std::min(T, upto[i]);
+        int32_t pages = (T + p->cfg.page_size - 1) / p->cfg.page_size;
+        for (int32_t slot = 0; slot < pages; ++slot)
+            if (p->pt(s, slot) < 0) return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", s, slot);
+    }
+    return SKV_OK;
+}
+
+int32_t skv_gather(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* out_k, void* out_v,
+                   int32_t max_len, void* stream_) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int32_t st = check_readable(p, layer, seq_ids, n_seqs, nullptr);
+    if (st != SKV_OK) return st;
+    if (max_len < 0) return p->fail(SKV_ERR_BAD_ARG, "max_len must be non-negative");
+    for (int32_t i = 0; i < n_seqs; ++i)
+        if (p->len(layer, seq_ids ? seq_ids[i] : i) > max_len)
+            return p->fail(SKV_ERR_BAD_ARG, "max_len %d is shorter than a sequence", max_len);
+    if (p->host_only || max_len == 0) return SKV_OK;
+    if (!out_k || !out_v) return p->fail(SKV_ERR_BAD_ARG, "output pointers must be given");
+    DeviceGuard g(p);
+    st = order_transfers(p, stream);
+    if (st != SKV_OK) return st;
+    GatherLaunch G{};
+    G.pool = p->view();
+    G.layer = layer;
+    G.n_seqs = n_seqs;
+    G.max_len = max_len;
+    G.dtype = p->cfg.dtype;
+    st = upload_ids(p, seq_ids, n_seqs, stream, &G.seq_ids);
+    if (st != SKV_OK) return st;
+    G.out_k = out_k;
+    G.out_v = out_v;
+    CUDA_TRY(p, launch_gather(G, stream));
+    return SKV_OK;
+}
+
+size_t skv_decode_workspace_bytes(const skv_pool* p, int32_t n_seqs, int32_t n_q_heads) {
+    if (!p || n_seqs <= 0 || n_q_heads <= 0) return 0;
+    int32_t chunk = 0, splits = 0;
+    // the largest split count any plan can produce: the smallest chunk
+    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, 0, &chunk, &splits);
+    return (size_t)n_seqs * n_q_heads * splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
+}
+
+int32_t skv_decode_attn(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q, void* out,
+                        const int32_t* q_pos, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                        void* stream_) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (n_q_heads <= 0 || n_q_heads % p->cfg.num_kv_heads != 0)
+        return p->fail(SKV_ERR_BAD_ARG, "query heads must be divisible by key/value heads");
+    std::vector<int32_t> upto;
+    if (q_pos) {
+        upto.resize(n_seqs > 0 ? n_seqs : 0);
+        for (int32_t i = 0; i < n_seqs; ++i) upto[i] = std::max(0, q_pos[i] + 1);
+    }
+    int32_t st = check_readable(p, layer, seq_ids, n_seqs, q_pos ? upto.data() : nullptr);
+    if (st != SKV_OK) return st;
+    if (p->host_only) return SKV_OK;
+    if (!q || !out) return p->fail(SKV_ERR_BAD_ARG, "q and out must be given");
+    int64_t total = 0;
+    for (int32_t i = 0; i < n_seqs; ++i) total += p->len(layer, seq_ids ? seq_ids[i] : i);
+    DecodeLaunch D{};
+    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
+    size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
+    if (!workspace || workspace_bytes < need)
+        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need);
+    DeviceGuard g(p);
+    st = order_transfers(p, stream);
+    if (st != SKV_OK) return st;
+    D.pool = p->view();
+    D.layer = layer;
+    D.n_seqs = n_seqs;
+    D.n_q_heads = n_q_heads;
+    D.dtype = p->cfg.dtype;
+    st = upload_ids(p, seq_ids, n_seqs, stream, &D.seq_ids);
+    if (st != SKV_OK) return st;
+    st = upload_ids(p, q_pos, n_seqs, stream, &D.q_pos);
+    if (st != SKV_OK) return st;
+    D.q = q;
+    D.out = out;
+    D.eps = eps;
+    D.ws_acc = (float*)workspace;
+    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
+    const char* force = getenv("SKV_DECODE_GENERIC");
+    D.force_generic = (force && force[0] == '1') ? 1 : 0;
+    CUDA_TRY(p, launch_decode(D, stream));
+    return SKV_OK;
+}
+
+int32_t skv_attn_dense(const void* q, const void* k, const void* v, void* out, const int32_t* positions, int32_t B,
+                       int32_t Hq, int32_t Hkv, int32_t Lq, int32_t Lk, int32_t D, int32_t dtype, int32_t causal,
+                       float eps, void* stream_) {
+    // shape rules of mlx_ops.py:51-67
+    if (!q || !k || !v || !out) return SKV_ERR_BAD_ARG;
+    if (B <= 0 || Hq <= 0 || Lq < 0 || Lk < 0 || D <= 0) return SKV_ERR_BAD_ARG;
+    if (Hkv <= 0 || Hq % Hkv != 0) return SKV_ERR_BAD_ARG;
+    if (causal && Lk < Lq) return SKV_ERR_BAD_ARG;
+    if (dtype != SKV_F32 && dtype != SKV_BF16) return SKV_ERR_BAD_ARG;
+    if (D > 256) return SKV_ERR_UNSUPPORTED;
+    if (Lq == 0) return SKV_OK;
+    DenseAttnLaunch A{};
+    A.q = q; A.k = k; A.v = v; A.out = out; A.positions = positions;
+    A.B = B; A.Hq = Hq; A.Hkv = Hkv; A.Lq = Lq; A.Lk = Lk; A.D = D; A.dtype = dtype; A.causal = causal;
+    A.eps = eps;
+    A.pool.k_base = nullptr;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const char* force = getenv("SKV_PREFILL_GENERIC");
+    cudaError_t e = cudaErrorNotSupported;
+    if (!(force && force[0] == '1')) e = launch_attn_tc(A, stream);
+    if (e == cudaErrorNotSupported) e = launch_attn_generic(A, stream);
+    return e == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+
+int32_t skv_prefill_attn_paged(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q, void* out,
+                               const int32_t* positions, int32_t n_q_heads, int32_t Lq, int32_t causal, float eps, void* stream_) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (n_q_heads <= 0 || n_q_heads % p->cfg.num_kv_heads != 0)
+        return p->fail(SKV_ERR_BAD_ARG, "query heads must be divisible by key/value heads");
+    int32_t st = check_readable(p, layer, seq_ids, n_seqs, nullptr);
+    if (st != SKV_OK) return st;
+    if (Lq < 0) return p->fail(SKV_ERR_BAD_ARG, "Lq must be non-negative");
+    if (causal && !positions)
+        for (int32_t i = 0; i < n_seqs; ++i)
+            if (p->len(layer, seq_ids ? seq_ids[i] : i) < Lq)
+                return p->fail(SKV_ERR_BAD_ARG, "causal attention requires key length >= query length");
+    if (p->host_only || Lq == 0) return SKV_OK;
+    if (!q || !out) return p->fail(SKV_ERR_BAD_ARG, "q and out must be given");
+    DeviceGuard g(p);
+    st = order_transfers(p, stream);
+    if (st != SKV_OK) return st;
+    DenseAttnLaunch A{};
+    A.q = q; A.out = out; A.positions = positions;
+    A.B = n_seqs; A.Hq = n_q_heads; A.Hkv = p->cfg.num_kv_heads; A.Lq = Lq; A.Lk = 0; A.D = p->cfg.head_dim;
+    A.dtype = p->cfg.dtype; A.causal = causal ? 1 : 0; A.eps = eps;
+    A.pool = p->view();
+    A.layer = layer;
+    st = upload_ids(p, seq_ids, n_seqs, stream, &A.seq_ids);
+    if (st != SKV_OK) return st;
+    CUDA_TRY(p, launch_attn_generic(A, stream));
+    return SKV_OK;
+}
+
+int32_t skv_evict(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slots, void* stream_) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!valid_seq(p, seq)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", seq);
+    if (first_slot < 0 || n_slots < 0 || first_slot + n_slots > p->n_seq_pages[seq])
+        return p->fail(SKV_ERR_BAD_ARG, "slots [%d, %d) outside the sequence's %d pages", first_slot, first_slot + n_slots, p->n_seq_pages[seq]);
+    if (p->cfg.host_pages == 0) return p->fail(SKV_ERR_BAD_ARG, "pool was created without a host tier");
+    int32_t movable = 0;
+    for (int32_t s = first_slot; s < first_slot + n_slots; ++s) movable += p->pt(seq, s) >= 0;
+    if ((size_t)movable > p->free_host.size())
+        return p->fail(SKV_ERR_OUT_OF_PAGES, "need %d host slots, %zu free", movable, p->free_host.size());
+    std::vector<CopyItem> items;
+    std::vector<TableUpdate> ups;
+    for (int32_t s = first_slot; s < first_slot + n_slots; ++s) {
+        int32_t e = p->pt(seq, s);
+        if (e < 0) continue;
+        int32_t h = p->free_host.back();
+        p->free_host.pop_back();
+        p->pt(seq, s) = -2 - h;
+        p->page_owner[e] = -1;
+        items.push_back({e, h});
+        ups.push_back({seq, s, -2 - h});
+    }
+    for (auto it = items.rbegin(); it != items.rend(); ++it) p->free_pages.push_back(it->page);
+    p->n_evicted += (int64_t)items.size();
+    p->bytes_d2h += (int64_t)items.size() * p->cfg.num_layers * 2 * (int64_t)p->page_bytes;
+    if (p->host_only || items.empty()) return SKV_OK;
+    DeviceGuard g(p);
+    // the copy must see everything already enqueued on the compute stream
+    CUDA_TRY(p, cudaEventRecord(p->ev_compute, stream));
+    CUDA_TRY(p, cudaStreamWaitEvent(p->copy_stream, p->ev_compute, 0));
+    const size_t per = StagingRing::kSlotBytes / sizeof(CopyItem);
+    for (size_t off = 0; off < items.size(); off += per) {
+        size_t n = std::min(per, items.size() - off);
+        void* dev = nullptr;
+        CUDA_TRY(p, p->ring.upload(items.data() + off, n * sizeof(CopyItem), p->copy_stream, &dev));
+        dim3 grid((unsigned)n, (unsigned)p->cfg.num_layers * 2);
+        page_copy_kernel<<<grid, 256, 0, p->copy_stream>>>(p->d_k, p->d_v, p->h_tier_dev, (const CopyItem*)dev,
+                                                           (int64_t)p->layer_stride, (int64_t)p->page_bytes,
+                                                           p->cfg.num_layers, 1);
+        CUDA_TRY(p, cudaGetLastError());
+    }
+    p->copy_pending = true;   // freed pages may be rewritten only after the copy: order_transfers enforces it
+    return publish_table_updates(p, ups, stream);
+}
+
+int32_t skv_prefetch(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slots, void* stream_) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!valid_seq(p, seq)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", seq);
+    if (first_slot < 0 || n_slots < 0 || first_slot + n_slots > p->n_seq_pages[seq])
+        return p->fail(SKV_ERR_BAD_ARG, "slots [%d, %d) outside the sequence's %d pages", first_slot, first_slot + n_slots, p->n_seq_pages[seq]);
+    int32_t parked = 0;
+    for (int32_t s = first_slot; s < first_slot + n_slots; ++s) parked += p->pt(seq, s) <= -2;
+    if ((size_t)parked > p->free_pages.size())
+        return p->fail(SKV_ERR_OUT_OF_PAGES, "need %d device pages, %zu free", parked, p->free_pages.size());
+    std::vector<CopyItem> items;
+    for (int32_t s = first_slot; s < first_slot + n_slots; ++s) {
+        int32_t e = p->pt(seq, s);
+        if (e > -2) continue;
+        int32_t h = -2 - e;
+        int32_t page = p->free_pages.back();
+        p->free_pages.pop_back();
+        p->pt(seq, s) = page;
+        p->page_owner[page] = seq;
+        items.push_back({page, h});
+        p->deferred_updates.push_back({seq, s, page});
+    }
+    for (auto it = items.rbegin(); it != items.rend(); ++it) p->free_host.push_back(it->slot);
+    p->n_prefetched += (int64_t)items.size();
+    p->bytes_h2d += (int64_t)items.size() * p->cfg.num_layers * 2 * (int64_t)p->page_bytes;
+    if (p->host_only) {
+        p->deferred_updates.clear();
+        return SKV_OK;
+    }
+    if (items.empty()) return SKV_OK;
+    DeviceGuard g(p);
+    // target pages may still be read by kernels already enqueued on the compute stream
+    CUDA_TRY(p, cudaEventRecord(p->ev_compute, stream));
+    CUDA_TRY(p, cudaStreamWaitEvent(p->copy_stream, p->ev_compute, 0));
+    const size_t per = StagingRing::kSlotBytes / sizeof(CopyItem);
+    for (size_t off = 0; off < items.size(); off += per) {
+        size_t n = std::min(per, items.size() - off);
+        void* dev = nullptr;
+        CUDA_TRY(p, p->ring.upload(items.data() + off, n * sizeof(CopyItem), p->copy_stream, &dev));
+        dim3 grid((unsigned)n, (unsigned)p->cfg.num_layers * 2);
+        page_copy_kernel<<<grid, 256, 0, p->copy_stream>>>(p->d_k, p->d_v, p->h_tier_dev, (const CopyItem*)dev,
+                                                           (int64_t)p->layer_stride, (int64_t)p->page_bytes,
+                                                           p->cfg.num_layers, 0);
+        CUDA_TRY(p, cudaGetLastError());
+    }
+    p->copy_pending = true;
+    return SKV_OK;
+}
+
+int32_t skv_sync_transfers(skv_pool* p, void* stream_) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    DeviceGuard g(p);
+    return order_transfers(p, (cudaStream_t)stream_);
+}
+
+int32_t skv_wait_resident(skv_pool* p, int32_t timeout_ms) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (p->host_only) return SKV_OK;
+    DeviceGuard g(p);
+    auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        cudaError_t e = cudaStreamQuery(p->copy_stream);
+        if (e == cudaSuccess) return SKV_OK;
+        if (e != cudaErrorNotReady) return p->cuda_fail(e, "cudaStreamQuery(copy_stream)");
+        auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms >= timeout_ms) return p->fail(SKV_ERR_TIMEOUT, "transfers still running after %d ms", timeout_ms);
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+int32_t skv_check_device_status(skv_pool* p, void* stream_, int32_t* flag_out) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (flag_out) *flag_out = 0;
+    if (p->host_only) return SKV_OK;
+    DeviceGuard g(p);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int32_t flag = 0;
+    CUDA_TRY(p, cudaMemcpyAsync(&flag, p->d_status, sizeof flag, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(p, cudaStreamSynchronize(stream));
+    if (flag_out) *flag_out = flag;
+    if (flag != 0) {
+        CUDA_TRY(p, cudaMemsetAsync(p->d_status, 0, sizeof flag, stream));
+        return p->fail(SKV_ERR_DEVICE_FLAG, "device status word 0x%x (1 bad page id, 2 bad length, 4 bad sequence id)", flag);
+    }
+    return SKV_OK;
+}
+
+int32_t skv_rope_rows(const void* x_in, void* x_out, const int32_t* positions, const float* inv_freq_dev, int32_t n_rows,
+                      int32_t n_heads, int32_t head_dim, int64_t stride_row, int64_t stride_head, float scaling,
+                      int32_t dtype, void* stream_) {
+    if (!x_in || !x_out || !positions || !inv_freq_dev) return SKV_ERR_BAD_ARG;
+    if (n_rows < 0 || n_heads <= 0 || head_dim <= 0 || head_dim % 2 != 0 || !(scaling > 0.0f)) return SKV_ERR_BAD_ARG;
+    if (dtype != SKV_F32 && dtype != SKV_BF16) return SKV_ERR_BAD_ARG;
+    if (n_rows == 0) return SKV_OK;
+    RopeRowsLaunch R{x_in, x_out, positions, inv_freq_dev, n_rows, n_heads, head_dim, dtype, stride_row, stride_head, scaling};
+    return launch_rope_rows(R, (cudaStream_t)stream_) == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,111 @@
+// Internal declarations shared by the host pool and the kernel translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "strata_b200.h"
+
+namespace skv {
+
+// Device-visible description of one pool, passed to kernels by value.
+struct PoolView {
+    void* k_base;                 // layer 0 K pool; layers are layer_stride bytes apart
+    void* v_base;
+    int64_t layer_stride_bytes;
+    const int32_t* page_table;    // [max_seqs][max_pages_per_seq]
+    int32_t* lengths;             // [num_layers][max_seqs]
+    int32_t* status;              // device status word (0 = fine)
+    int32_t num_kv_heads, head_dim, page_size, num_pages, max_seqs, max_pages_per_seq;
+};
+
+// Bits recorded in the device status word.
+enum : int32_t {
+    FLAG_BAD_PAGE = 1,       // page-table entry outside [0, num_pages)
+    FLAG_BAD_LENGTH = 2,     // length beyond the page-table row
+    FLAG_BAD_SEQ = 4,        // sequence id outside [0, max_seqs)
+};
+
+// Per-call metadata uploaded through the staging ring.
+struct AppendMeta {            // followed in memory by n_seqs x {seq, start}
+    int32_t seq;
+    int32_t start;
+};
+
+struct AppendLaunch {
+    PoolView pool;
+    int32_t layer, n_seqs, n_new, dtype;
+    const AppendMeta* meta;      // device, n_seqs entries
+    const void* k;
+    const void* v;
+    int64_t kv_stride_seq, kv_stride_head, kv_stride_tok;
+    int32_t rope_k;
+    const void* q_in;
+    void* q_out;
+    int32_t n_q_heads;
+    int64_t q_stride_seq, q_stride_head, q_stride_tok;
+    const float* inv_freq;       // device, head_dim/2
+    float inv_scaling;           // 1 / scaling_factor applied as a division of the position
+    float scaling;
+};
+cudaError_t launch_append(const AppendLaunch& a, cudaStream_t stream);
+
+struct GatherLaunch {
+    PoolView pool;
+    int32_t layer, n_seqs, max_len, dtype;
+    const int32_t* seq_ids;      // device or nullptr (identity)
+    void* out_k;
+    void* out_v;
+};
+cudaError_t launch_gather(const GatherLaunch& g, cudaStream_t stream);
+
+struct DecodeLaunch {
+    PoolView pool;
+    int32_t layer, n_seqs, n_q_heads, dtype;
+    const int32_t* seq_ids;      // device or nullptr (identity)
+    const int32_t* q_pos;        // device or nullptr (length - 1)
+    const void* q;
+    void* out;
+    float eps;
+    float* ws_acc;               // [n_seqs][n_q_heads][max_splits][head_dim]
+    float* ws_ml;                // [n_seqs][n_q_heads][max_splits][2]
+    int32_t max_splits, chunk_tokens;
+    int32_t force_generic;       // 1: take the CUDA-core kernel even where the tensor-core one applies
+};
+cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
+// chunk length (tokens handled by one CTA) and the number of splits that follow from it
+void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, int32_t num_kv_heads,
+                 int64_t total_tokens_hint, int32_t* chunk_tokens, int32_t* max_splits);
+
+struct DenseAttnLaunch {
+    const void *q, *k, *v;
+    void* out;
+    const int32_t* positions;    // device [B][Lq] or nullptr
+    int32_t B, Hq, Hkv, Lq, Lk, D, dtype, causal;
+    float eps;
+    // paged K/V instead of dense (k, v ignored) when pool.k_base != nullptr
+    PoolView pool;
+    int32_t layer;
+    const int32_t* seq_ids;      // device or nullptr
+};
+cudaError_t launch_attn_generic(const DenseAttnLaunch& a, cudaStream_t stream);
+// Tensor-core (tcgen05) causal prefill; returns cudaErrorNotSupported when the shape is outside its cover.
+cudaError_t launch_attn_tc(const DenseAttnLaunch& a, cudaStream_t stream);
+
+struct RopeRowsLaunch {
+    const void* x_in;
+    void* x_out;
+    const int32_t* positions;
+    const float* inv_freq;
+    int32_t n_rows, n_heads, head_dim, dtype;
+    int64_t stride_row, stride_head;
+    float scaling;
+};
+cudaError_t launch_rope_rows(const RopeRowsLaunch& r, cudaStream_t stream);
+
+inline size_t dtype_size(int32_t dtype) { return dtype == SKV_BF16 ? 2 : 4; }
+
+}  // namespace skv
