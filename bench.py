@@ -1,0 +1,407 @@
+#!/usr/bin/env python
+"""Paged grouped-query decode benchmark (the Llama-3-8B attention-layer workload).
+
+Workload "paged_decode_llama3_8b_layer": 32 query heads, 8 KV heads, head_dim 128, bf16, page size 16,
+64 sequences with context lengths uniform in [512, 8192], the page table a random permutation of a
+shared pool, K/V ~ N(0,1).  One step = append one token per sequence with RoPE (theta 500000) on write
+(K and Q rotated in the same launch), then attend over the whole paged history.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints one JSON line.  `value` is decode tokens/s with inputs resident in HBM; `e2e` is the same step
+driven from pinned host buffers through the public API with the output read back every step;
+`roofline` relates the attention call's algorithmic HBM bytes to the measured copy bandwidth;
+`cpu_baseline` times the NumPy restatement of the reference path on the host.  With N > 1 the KV heads
+(and their query heads) are sharded over the ranks and the outputs are all-gathered with NCCL.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HQ, HKV, D, P, THETA = 32, 8, 128, 16, 500000.0
+N_SEQS, CTX_LO, CTX_HI = 64, 512, 8192
+SEED = 1234
+WORKLOAD = "paged_decode_llama3_8b_layer"
+
+
+def workload_lengths():
+    return np.random.default_rng(SEED).integers(CTX_LO, CTX_HI + 1, size=N_SEQS).astype(np.int64)
+
+
+def algorithmic_bytes(lens_after_append, hq, hkv):
+    """HBM bytes one attention call must move: K and V of every attended token once, q in, out out,
+    and one page-table entry per page touched."""
+    kv = int(np.sum(lens_after_append)) * hkv * D * 2 * 2
+    qo = 2 * len(lens_after_append) * hq * D * 2
+    pt = int(np.sum(-(-lens_after_append // P))) * 4
+    return kv + qo + pt
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import lokahi_b200 as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if HKV % world:
+        raise SystemExit(f"KV-head sharding needs {HKV} % n_gpus == 0")
+    hkv, hq = HKV // world, HQ // world
+
+    K, W = args.steps, args.warmup
+    total_steps = W + K
+    lens0 = workload_lengths()
+    rng = np.random.default_rng(SEED + 1)
+    cap = lens0 + 2 * total_steps + 1                      # room for both legs
+    pages_per_seq = int(-(-cap.max() // P))
+    pages_each = (-(-cap // P)).astype(np.int64)
+    n_pages = int(pages_each.sum()) + 16
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=hkv, head_dim=D, num_pages=n_pages, max_seqs=N_SEQS,
+                                       max_pages_per_seq=pages_per_seq, page_size=P, dtype=torch.bfloat16,
+                                       device=local_rank, rope_theta=THETA))
+    perm = rng.permutation(n_pages)                        # page table = random permutation of the shared pool
+    at = 0
+    for s in range(N_SEQS):
+        assert pool.alloc_sequence() == s
+        pool.set_page_table(s, perm[at:at + pages_each[s]].tolist(), int(lens0[s]))
+        at += int(pages_each[s])
+    kp, vp = pool.layer_views(0)
+    gen = torch.Generator(device=dev).manual_seed(SEED + 17 * rank)
+    kp.normal_(generator=gen)
+    vp.normal_(generator=gen)
+
+    # per-step inputs, resident in HBM (device leg) and in pinned host memory (e2e leg)
+    q_all = torch.randn((total_steps, N_SEQS, hq, D), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    k_all = torch.randn((total_steps, N_SEQS, hkv, D), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    v_all = torch.randn((total_steps, N_SEQS, hkv, D), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    out_buf = torch.empty((N_SEQS, hq, D), device=dev, dtype=torch.bfloat16)
+    gathered = torch.empty((world, N_SEQS, hq, D), device=dev, dtype=torch.bfloat16) if world > 1 else None
+
+    def step(q, k, v):
+        pool.append(0, k, v, rope_k=True, q=q, layout="bhd")
+        pool.decode_attention(0, q, out=out_buf)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out_buf)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident leg ---------------------------------------------------------------------------
+    for i in range(W):
+        step(q_all[i], k_all[i], v_all[i])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = L._lib.lib.skv_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    barrier()
+    ev0.record()
+    for i in range(K):
+        j = W + i
+        pool.append(0, k_all[j], v_all[j], rope_k=True, q=q_all[j], layout="bhd")
+        attn_ev[i][0].record()
+        pool.decode_attention(0, q_all[j], out=out_buf)
+        attn_ev[i][1].record()
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out_buf)
+    ev1.record()
+    barrier()
+    launches = L._lib.lib.skv_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = ev0.elapsed_time(ev1)
+    attn_ms = np.array([a.elapsed_time(b) for a, b in attn_ev])
+    if pool.check_device_status() != 0:
+        raise SystemExit("device status flag set during the timed region")
+    lens_timed = lens0[None, :] + W + 1 + np.arange(K)[:, None]      # attended tokens per step
+    algo_bytes = float(np.mean([algorithmic_bytes(lens_timed[i], hq, hkv) for i in range(K)]))
+
+    # ---- end-to-end leg: pinned host inputs, output read back every step ----------------------------------
+    Ke = K
+    q_h = q_all[:Ke].cpu().pin_memory(); k_h = k_all[:Ke].cpu().pin_memory(); v_h = v_all[:Ke].cpu().pin_memory()
+    q_d = torch.empty_like(q_all[0]); k_d = torch.empty_like(k_all[0]); v_d = torch.empty_like(v_all[0])
+    out_h = torch.empty((world if world > 1 else 1, N_SEQS, hq, D), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):
+        q_d.copy_(q_h[i], non_blocking=True)
+        k_d.copy_(k_h[i], non_blocking=True)
+        v_d.copy_(v_h[i], non_blocking=True)
+        step(q_d, k_d, v_d)
+        out_h.copy_((gathered if world > 1 else out_buf).view(out_h.shape), non_blocking=True)
+        torch.cuda.current_stream().synchronize()          # a decode loop consumes the result before the next step
+
+    for i in range(min(W, Ke)):
+        e2e_step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(Ke):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if pool.check_device_status() != 0:
+        raise SystemExit("device status flag set during the end-to-end leg")
+
+    # ---- max over ranks --------------------------------------------------------------------------------------
+    stats = torch.tensor([ms_total, ms_e2e, float(attn_ms.mean())], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e, attn_mean_ms = [float(x) for x in stats.tolist()]
+
+    result = None
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        achieved = algo_bytes / (attn_mean_ms * 1e-3) / 1e9
+        tokens = N_SEQS * K
+        result = {
+            "metric": "paged GQA decode tokens/s", "value": tokens / (ms_total * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "n_seqs": N_SEQS, "context": [CTX_LO, CTX_HI], "q_heads": HQ, "kv_heads": HKV,
+                       "head_dim": D, "page_size": P, "rope_theta": THETA, "layers": 1,
+                       "parallelism": f"kv_head_shard{world}" if world > 1 else "single",
+                       "l2": "inputs larger than L2 (KV working set per step >= 1 GB / n_gpus)"},
+            "e2e": {"value": N_SEQS * Ke / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / Ke,
+                    "h2d_bytes_per_step": int(q_d.numel() + k_d.numel() + v_d.numel()) * 2,
+                    "d2h_bytes_per_step": int(out_h.numel()) * 2},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "kernel": "decode attention call (split-K kernel + merge kernel)",
+                         "algorithmic_bytes_per_launch": algo_bytes, "launch_ms": attn_mean_ms,
+                         "launch_ms_min": float(attn_ms.min()), "traffic": TRAFFIC_BYTES_PER_LAUNCH},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            result["cpu_baseline"] = cpu_baseline_sample(pool, kp, vp, lens0 + W + K + min(W, Ke) + Ke, hq, hkv)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result
+
+
+# ncu dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at this workload, from the capture
+# summarised under profiles/ (None until a capture exists)
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+# ------------------------------------------------------------------------------------------------------
+# CPU legs (the only code here that runs the oracle)
+# ------------------------------------------------------------------------------------------------------
+def _oracle_step(q, k_new, v_new, k_hist, v_hist, length):
+    """One sequence, one step of the reference path on the CPU: RoPE on the new q/k, append, attend."""
+    from oracle import attention as oattn
+    from oracle import paged as opaged
+    pos = np.array([length])
+    qr = opaged.rope_rows(q[None], pos, THETA)[0]
+    kr = opaged.rope_rows(k_new[None], pos, THETA)[0]
+    k_hist[:, length] = kr
+    v_hist[:, length] = v_new
+    T = length + 1
+    return oattn.chunked_grouped_attention(qr[None, :, None, :], k_hist[None, :, :T], v_hist[None, :, :T],
+                                           query_positions=np.array([[length]], dtype=np.int32), causal=True,
+                                           q_block_size=32768, k_block_size=1000000)
+
+
+def cpu_baseline_sample(pool, kp, vp, lens_now, hq, hkv, budget_s=12.0):
+    """Scalar (one core) timing of the oracle on a bounded sample of the same workload."""
+    import torch
+    rng = np.random.default_rng(SEED + 5)
+    order = rng.permutation(N_SEQS)
+    done, t_used, steps_per_seq = 0, 0.0, 2
+    for s in order:
+        T = int(lens_now[s])
+        n = -(-(T + steps_per_seq) // P)
+        pages = torch.from_numpy(pool.page_table(int(s))[:n].astype(np.int64)).to(kp.device)
+        kh = kp[pages].float().permute(1, 0, 2, 3).reshape(hkv, n * P, D).cpu().numpy().copy()
+        vh = vp[pages].float().permute(1, 0, 2, 3).reshape(hkv, n * P, D).cpu().numpy().copy()
+        for j in range(steps_per_seq):
+            q = rng.standard_normal((hq, D), dtype=np.float32)
+            k = rng.standard_normal((hkv, D), dtype=np.float32)
+            v = rng.standard_normal((hkv, D), dtype=np.float32)
+            t0 = time.perf_counter()
+            _oracle_step(q, k, v, kh, vh, T + j)
+            t_used += time.perf_counter() - t0
+            done += 1
+        if t_used > budget_s:
+            break
+    return {"value": done / t_used, "unit": "tokens/s", "cores": 1, "kind": "port",
+            "sample": f"{done} (sequence, step) pairs of the same workload ({done // steps_per_seq} sequences x "
+                      f"{steps_per_seq} steps), NumPy restatement of the reference path, one thread"}
+
+
+def _ref_worker(conn, seq_ids, lens, seed):
+    rng = np.random.default_rng(seed)
+    hist = {}
+    for s in seq_ids:
+        cap = int(lens[s]) + 4096
+        hist[s] = [rng.standard_normal((HKV, cap, D), dtype=np.float32), rng.standard_normal((HKV, cap, D), dtype=np.float32),
+                   int(lens[s])]
+    conn.send("ready")
+    while True:
+        msg = conn.recv()
+        if msg is None:
+            break
+        step_seed = msg
+        r = np.random.default_rng(step_seed)
+        for s in seq_ids:
+            kh, vh, T = hist[s]
+            q = r.standard_normal((HQ, D), dtype=np.float32)
+            k = r.standard_normal((HKV, D), dtype=np.float32)
+            v = r.standard_normal((HKV, D), dtype=np.float32)
+            _oracle_step(q, k, v, kh, vh, T)
+            hist[s][2] = T + 1
+        conn.send(len(seq_ids))
+
+
+def run_reference(args):
+    """The reference's CPU path (NumPy restatement) on all host cores: one process per core, each owning a
+    fixed share of the sequences.  A step is the full workload step (64 sequences, one token each)."""
+    import multiprocessing as mp
+    if int(os.environ.get("RANK", "0")) != 0:
+        return None
+    cores = max(1, min(os.cpu_count() or 1, N_SEQS))
+    lens0 = workload_lengths()
+    ctx = mp.get_context("fork")
+    workers = []
+    for w in range(cores):
+        parent, child = ctx.Pipe()
+        p = ctx.Process(target=_ref_worker, args=(child, list(range(w, N_SEQS, cores)), lens0, SEED + 100 + w), daemon=True)
+        p.start()
+        workers.append((p, parent))
+    for _, c in workers:
+        assert c.recv() == "ready"
+
+    def one_step(i):
+        for _, c in workers:
+            c.send(SEED + 1000 + i)
+        return sum(c.recv() for _, c in workers)
+
+    # bounded: at most ~3 minutes in total whatever K and W are
+    t_probe = time.perf_counter()
+    one_step(-1)
+    per_step = time.perf_counter() - t_probe
+    K = max(1, min(args.steps, int(150.0 / max(per_step, 1e-3))))
+    W = max(0, min(args.warmup, int(20.0 / max(per_step, 1e-3))))
+    for i in range(W):
+        one_step(i)
+    t0 = time.perf_counter()
+    tokens = 0
+    for i in range(K):
+        tokens += one_step(W + i)
+    dt = time.perf_counter() - t0
+    for p, c in workers:
+        c.send(None)
+        p.join(timeout=5)
+    value = tokens / dt
+    return {
+        "impl": "reference", "metric": "paged GQA decode tokens/s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": dt / K * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "n_seqs": N_SEQS, "context": [CTX_LO, CTX_HI], "q_heads": HQ, "kv_heads": HKV,
+                   "head_dim": D, "page_size": P, "rope_theta": THETA, "layers": 1},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"full workload step (64 sequences x 1 token) x {K} steps; NumPy restatement of the "
+                                   f"reference path, one process per core (requested steps {args.steps})"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if result is not None:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -72,6 +72,9 @@ SKV_API int32_t skv_create(const skv_config* cfg, skv_pool** out);
 SKV_API int32_t skv_destroy(skv_pool* pool);
 SKV_API const char* skv_last_error(const skv_pool* pool);
 SKV_API const char* skv_status_string(int32_t status);
+/* Number of kernels this library has launched in this process so far (all pools, all streams).
+ * No reference counterpart; lets a caller state how much work really ran on the GPU. */
+SKV_API int64_t skv_launch_count(void);
 
 /* Sequences.  The reference keeps one tensor per layer with a batch axis (mlx_kvcache.py:54);
  * here each batch row is a sequence with its own page-table row and per-layer lengths. */

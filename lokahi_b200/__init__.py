@@ -1,6 +1,6 @@
 """B200-native (sm_100a) KV-cache, RoPE and chunked grouped-query attention behind the call
 surface of the Strata / ``ollm`` runtime.  Importing the package needs the built C-ABI library
-(``python -m lokahi_b200.build``); there is no CPU or PyTorch fallback for any compute call."""
+(``python lokahi_b200/build.py``); there is no CPU or PyTorch fallback for any compute call."""
 from ._lib import DeviceFlagError, NotResidentError, OutOfPagesError
 from .attention import PagedView, chunked_grouped_attention, chunked_grouped_attention_no_mask
 from .backend import B200Backend, BackendError, register

@@ -60,6 +60,7 @@ SIGNATURES = {
     "skv_destroy": (_i32, [_vp]),
     "skv_last_error": (C.c_char_p, [_vp]),
     "skv_status_string": (C.c_char_p, [_i32]),
+    "skv_launch_count": (_i64, []),
     "skv_alloc_sequence": (_i32, [_vp, _pi32]),
     "skv_free_sequence": (_i32, [_vp, _i32]),
     "skv_reserve": (_i32, [_vp, _i32, _i32]),
@@ -90,7 +91,7 @@ SIGNATURES = {
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m lokahi_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python lokahi_b200/build.py` "
             "(nvcc, sm_100a). There is no fallback path."
         )
     lib = C.CDLL(LIB_PATH)

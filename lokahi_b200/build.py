@@ -1,6 +1,6 @@
 """Build libstrata_b200.so (sm_100a only) in-tree with nvcc.
 
-    python -m lokahi_b200.build [--force] [--verbose]
+    python lokahi_b200/build.py [--force] [--verbose]
 
 The library is the product's only compute path; there is no fallback when it is missing.
 """

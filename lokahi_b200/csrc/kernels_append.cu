@@ -86,6 +86,7 @@ cudaError_t launch_append(const AppendLaunch& a, cudaStream_t stream) {
         append_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(a);
     else
         append_kernel<float><<<grid, block, 0, stream>>>(a);
+    count_launches(1);
     return cudaGetLastError();
 }
 
@@ -114,6 +115,7 @@ cudaError_t launch_rope_rows(const RopeRowsLaunch& r, cudaStream_t stream) {
         rope_rows_kernel<__nv_bfloat16><<<r.n_rows, threads, 0, stream>>>(r);
     else
         rope_rows_kernel<float><<<r.n_rows, threads, 0, stream>>>(r);
+    count_launches(1);
     return cudaGetLastError();
 }
 
@@ -178,6 +180,7 @@ cudaError_t launch_gather(const GatherLaunch& g, cudaStream_t stream) {
         gather_kernel<4><<<grid, 256, 0, stream>>>(g, esize);
     else
         gather_kernel<2><<<grid, 256, 0, stream>>>(g, esize);
+    count_launches(1);
     return cudaGetLastError();
 }
 

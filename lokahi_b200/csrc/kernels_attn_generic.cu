@@ -120,6 +120,7 @@ cudaError_t launch_t(const DenseAttnLaunch& a, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_attn_generic(const DenseAttnLaunch& a, cudaStream_t stream) {
+    count_launches(1);
     return a.dtype == SKV_BF16 ? launch_t<__nv_bfloat16>(a, stream) : launch_t<float>(a, stream);
 }
 

@@ -414,6 +414,7 @@ cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream) {
         e = launch_generic<float>(d, stream);
     }
     if (e != cudaSuccess) return e;
+    count_launches(2);
     dim3 rgrid((unsigned)d.n_q_heads, (unsigned)d.n_seqs);
     const int threads = d.pool.head_dim >= 128 ? 128 : 64;
     if (d.dtype == SKV_BF16)

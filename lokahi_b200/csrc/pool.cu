@@ -16,7 +16,12 @@
 
 #include "skv_internal.h"
 
+#include <atomic>
+
 using namespace skv;
+
+static std::atomic<long long> g_launches{0};
+void skv::count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 namespace {
 
@@ -217,6 +222,7 @@ int32_t publish_table_updates(skv_pool* p, const std::vector<TableUpdate>& ups, 
         apply_table_updates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
             p->d_page_table, (const TableUpdate*)dev, (int)n, p->cfg.max_seqs, p->cfg.max_pages_per_seq);
         CUDA_TRY(p, cudaGetLastError());
+        count_launches(1);
     }
     return SKV_OK;
 }
@@ -231,6 +237,7 @@ int32_t publish_length_updates(skv_pool* p, const std::vector<LengthUpdate>& ups
         apply_length_updates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
             p->d_lengths, (const LengthUpdate*)dev, (int)n, p->cfg.num_layers * p->cfg.max_seqs);
         CUDA_TRY(p, cudaGetLastError());
+        count_launches(1);
     }
     return SKV_OK;
 }
@@ -281,6 +288,8 @@ int32_t grow(skv_pool* p, int32_t seq, int32_t total_tokens, std::vector<TableUp
 extern "C" {
 
 int32_t skv_abi_version(void) { return SKV_ABI_VERSION; }
+
+int64_t skv_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 
 const char* skv_status_string(int32_t s) {
     switch (s) {
@@ -864,6 +873,7 @@ int32_t skv_evict(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slots,
                                                            (int64_t)p->layer_stride, (int64_t)p->page_bytes,
                                                            p->cfg.num_layers, 1);
         CUDA_TRY(p, cudaGetLastError());
+        count_launches(1);
     }
     p->copy_pending = true;   // freed pages may be rewritten only after the copy: order_transfers enforces it
     return publish_table_updates(p, ups, stream);
@@ -913,6 +923,7 @@ int32_t skv_prefetch(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slo
                                                            (int64_t)p->layer_stride, (int64_t)p->page_bytes,
                                                            p->cfg.num_layers, 0);
         CUDA_TRY(p, cudaGetLastError());
+        count_launches(1);
     }
     p->copy_pending = true;
     return SKV_OK;

@@ -106,6 +106,9 @@ struct RopeRowsLaunch {
 };
 cudaError_t launch_rope_rows(const RopeRowsLaunch& r, cudaStream_t stream);
 
+// process-wide count of kernel launches issued by this library
+void count_launches(int n);
+
 inline size_t dtype_size(int32_t dtype) { return dtype == SKV_BF16 ? 2 : 4; }
 
 }  // namespace skv

@@ -1,0 +1,221 @@
+"""Attention kernels on the GPU, through the C ABI, against the oracle, the reference's own oracle
+outputs (golden fixtures) and the reference's attention tests (tests/test_mlx_attention.py:53-137)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import lokahi_b200 as L
+from oracle import attention as oattn
+from oracle import paged as opaged
+from parity import TOL_BF16, TOL_F32, assert_parity, bf16_round, to_np
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _t(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV).to(dtype)
+
+
+def _load(golden_dir, name):
+    with np.load(os.path.join(golden_dir, f"attention_{name}.npz")) as d:
+        return {k: d[k] for k in d.files}
+
+
+# ---- dense attention: reference fixtures (tolerance of the reference's tests: 1e-5) ----------------
+@pytest.mark.parametrize("name", ["unmasked", "causal_prefill", "decode_abs_position", "gqa_d128_offsets"])
+def test_dense_attention_matches_reference_fixtures(golden_dir, name):
+    c = _load(golden_dir, name)
+    q, k, v = _t(c["q"]), _t(c["k"]), _t(c["v"])
+    if int(c["causal"]):
+        out = L.chunked_grouped_attention(q, k, v, query_positions=c["positions"], causal=True,
+                                          q_block_size=int(c["q_block"]), k_block_size=int(c["k_block"]))
+    else:
+        out = L.chunked_grouped_attention_no_mask(q, k, v, position_ids=[0], q_block_size=int(c["q_block"]),
+                                                  k_block_size=int(c["k_block"]))
+    assert out.dtype == q.dtype and out.shape == q.shape
+    assert np.allclose(c["out"], to_np(out), atol=1e-5, rtol=1e-5)
+
+
+def test_future_values_do_not_change_earlier_outputs(golden_dir):
+    c = _load(golden_dir, "future_values")
+    q, k = _t(c["q"]), _t(c["k"])
+    a = to_np(L.chunked_grouped_attention(q, k, _t(c["v"]), k_block_size=2))
+    b = to_np(L.chunked_grouped_attention(q, k, _t(c["v_changed"]), k_block_size=2))
+    assert np.allclose(a, c["out"], atol=1e-5, rtol=1e-5)
+    assert np.allclose(a[:, :, :3], b[:, :, :3]) and not np.allclose(a[:, :, 3:], b[:, :, 3:])
+
+
+def test_rejections_carry_reference_messages():
+    ones = lambda *s: torch.ones(*s, device=DEV)
+    with pytest.raises(ValueError, match="divisible"):
+        L.chunked_grouped_attention(ones(1, 3, 2, 4), ones(1, 2, 2, 4), ones(1, 2, 2, 4))
+    with pytest.raises(ValueError, match="key length >= query length"):
+        L.chunked_grouped_attention(ones(1, 2, 3, 4), ones(1, 2, 2, 4), ones(1, 2, 2, 4))
+    with pytest.raises(ValueError, match="block sizes must be positive"):
+        L.chunked_grouped_attention(ones(1, 2, 2, 4), ones(1, 2, 2, 4), ones(1, 2, 2, 4), k_block_size=0)
+    with pytest.raises(ValueError, match="query_positions must have shape"):
+        L.chunked_grouped_attention(ones(1, 2, 2, 4), ones(1, 2, 2, 4), ones(1, 2, 2, 4), query_positions=np.zeros((3, 2)))
+    with pytest.raises(ValueError, match="share last-dim"):
+        L.chunked_grouped_attention(ones(1, 2, 2, 8), ones(1, 2, 2, 4), ones(1, 2, 2, 4))
+
+
+def test_fully_masked_rows_are_zero():
+    rng = np.random.default_rng(4)
+    q = rng.standard_normal((1, 2, 2, 4), dtype=np.float32)
+    k = rng.standard_normal((1, 2, 5, 4), dtype=np.float32)
+    out = to_np(L.chunked_grouped_attention(_t(q), _t(k), _t(k), query_positions=[[-1, 2]]))
+    ref = oattn.chunked_grouped_attention(q, k, k, query_positions=[[-1, 2]])
+    assert np.array_equal(out[:, :, 0], np.zeros_like(out[:, :, 0])) and np.allclose(out, ref, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 33, 70, 64), (1, 8, 2, 130, 130, 128), (1, 2, 2, 1, 257, 96)])
+def test_dense_attention_matches_oracle(dtype, tol, shape):
+    B, Hq, Hkv, Lq, Lk, D = shape
+    rng = np.random.default_rng(Lq * 7 + D)
+    rnd = (lambda a: a) if dtype == torch.float32 else bf16_round
+    q = rnd(rng.standard_normal((B, Hq, Lq, D), dtype=np.float32))
+    k = rnd(rng.standard_normal((B, Hkv, Lk, D), dtype=np.float32))
+    v = rnd(rng.standard_normal((B, Hkv, Lk, D), dtype=np.float32))
+    for causal in (True, False):
+        out = L.chunked_grouped_attention(_t(q, dtype), _t(k, dtype), _t(v, dtype), causal=causal)
+        ref = oattn.chunked_grouped_attention(q, k, v, causal=causal, k_block_size=64)
+        assert_parity(out, ref, tol, f"dense causal={causal}")
+
+
+# ---- paged decode ----------------------------------------------------------------------------------------
+def _paged_setup(rng, dtype, n_seqs, Hkv, D, P, lens, n_pages=None, layers=1):
+    pages_per_seq = max(1, max(-(-(t + 1) // P) for t in lens))
+    n_pages = n_pages or n_seqs * pages_per_seq + 3
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=layers, num_kv_heads=Hkv, head_dim=D, num_pages=n_pages, max_seqs=n_seqs,
+                                       max_pages_per_seq=pages_per_seq, page_size=P, dtype=dtype))
+    perm = rng.permutation(n_pages)
+    rnd = (lambda a: a) if dtype == torch.float32 else bf16_round
+    k_ref = rnd(rng.standard_normal((n_pages, Hkv, P, D), dtype=np.float32))
+    v_ref = rnd(rng.standard_normal((n_pages, Hkv, P, D), dtype=np.float32))
+    table = np.full((n_seqs, pages_per_seq), -1, np.int32)
+    for s in range(n_seqs):
+        assert pool.alloc_sequence() == s
+        pages = perm[s * pages_per_seq:(s + 1) * pages_per_seq]
+        table[s] = pages
+        pool.set_page_table(s, pages.tolist(), lens[s])
+    kp, vp = pool.layer_views(layers - 1)
+    kp.copy_(_t(k_ref, dtype)); vp.copy_(_t(v_ref, dtype))
+    return pool, k_ref, v_ref, table, rnd
+
+
+@pytest.mark.parametrize("dtype,tol,D,Hq,Hkv", [
+    (torch.bfloat16, TOL_BF16, 128, 32, 8),     # tensor-core kernel, the benchmark's head geometry
+    (torch.bfloat16, TOL_BF16, 128, 16, 16),    # MHA through the tensor-core kernel
+    (torch.bfloat16, TOL_BF16, 64, 8, 2),       # CUDA-core kernel, bf16
+    (torch.float32, TOL_F32, 64, 4, 2),         # two-layer fixture geometry, float32
+    (torch.float32, TOL_F32, 6, 4, 2),          # the reference tests' head_dim
+])
+def test_paged_decode_matches_oracle_on_ragged_lengths(dtype, tol, D, Hq, Hkv):
+    rng = np.random.default_rng(D + Hq)
+    P = 16
+    lens = [1, 2, 15, 16, 17, 31, 32, 33, 64, 100, 257, 700, 1024, 1500]
+    pool, k_ref, v_ref, table, rnd = _paged_setup(rng, dtype, len(lens), Hkv, D, P, lens, layers=2)
+    q = rnd(rng.standard_normal((len(lens), Hq, D), dtype=np.float32))
+    out = pool.decode_attention(1, _t(q, dtype))
+    ref = opaged.paged_decode_attention(q, k_ref, v_ref, table, np.array(lens), out_dtype=np.float32)
+    assert pool.check_device_status() == 0
+    assert_parity(out, ref, tol, "paged decode")
+    # absolute query positions below the newest token restrict the keys (mlx_ops.py:107-112)
+    qpos = [max(0, t - 1 - (i % 5) * 3) for i, t in enumerate(lens)]
+    out2 = pool.decode_attention(1, _t(q, dtype), q_pos=qpos)
+    ref2 = opaged.paged_decode_attention(q, k_ref, v_ref, table, np.array(lens), q_positions=qpos, out_dtype=np.float32)
+    assert_parity(out2, ref2, tol, "paged decode with absolute positions")
+    # a subset of sequences in another order
+    ids = [13, 0, 7]
+    out3 = pool.decode_attention(1, _t(q[:3], dtype), seq_ids=ids)
+    ref3 = opaged.paged_decode_attention(q[:3], k_ref, v_ref, table, np.array(lens), seq_ids=ids, out_dtype=np.float32)
+    assert_parity(out3, ref3, tol, "paged decode with sequence ids")
+
+
+def test_paged_decode_kernels_agree_and_empty_sequences_give_zero(monkeypatch):
+    rng = np.random.default_rng(3)
+    lens = [0, 5, 48, 333]
+    pool, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, len(lens), 8, 128, 16, lens)
+    q = _t(rnd(rng.standard_normal((len(lens), 32, 128), dtype=np.float32)), torch.bfloat16)
+    a = pool.decode_attention(0, q)
+    assert not to_np(a[0]).any()
+    monkeypatch.setenv("SKV_DECODE_GENERIC", "1")
+    b = pool.decode_attention(0, q)
+    monkeypatch.delenv("SKV_DECODE_GENERIC")
+    assert_parity(a, to_np(b), TOL_BF16, "tensor-core vs CUDA-core decode")
+    ref = opaged.paged_decode_attention(to_np(q), k_ref, v_ref, table, np.array(lens), out_dtype=np.float32)
+    assert_parity(b, ref, TOL_BF16, "CUDA-core decode")
+    q_neg = pool.decode_attention(0, q, q_pos=[-1, -1, -1, -1])
+    assert not to_np(q_neg).any()
+
+
+def test_cache_update_then_attention_like_the_reference_call_site():
+    """QKV -> RoPE -> cache.update -> attention with position_ids, as llama_mlx.py:284-308, prefill then decode."""
+    from types import SimpleNamespace
+    rng = np.random.default_rng(12)
+    B, Hq, Hkv, D, Lp = 2, 4, 2, 64, 37
+    cfg = SimpleNamespace(num_hidden_layers=1, max_position_embeddings=128)
+    cache = L.PagedKVCache(cfg, cache_dir=None)
+    from oracle.kvcache import ConcatKVCache
+    ref_cache = ConcatKVCache(cfg, cache_dir=None)
+    attn = L.B200Backend().attention_kernel()
+    for step, Lnew in enumerate([Lp, 1, 1, 1]):
+        past = cache.get_seq_length(0)
+        q = rng.standard_normal((B, Hq, Lnew, D), dtype=np.float32)
+        k = rng.standard_normal((B, Hkv, Lnew, D), dtype=np.float32)
+        v = rng.standard_normal((B, Hkv, Lnew, D), dtype=np.float32)
+        pos = np.arange(past, past + Lnew, dtype=np.int32)
+        kk, vv = cache.update(_t(k), _t(v), 0, {"cache_position": torch.from_numpy(pos)})
+        rk, rv = ref_cache.update(k, v, 0, {"cache_position": pos})
+        out = attn(_t(q), kk, vv, query_positions=pos[None], causal=True, q_block_size=32768,
+                   k_block_size=(1024 if Lnew > 128 else 1000000))
+        ref = oattn.chunked_grouped_attention(q, rk, rv, query_positions=pos[None], causal=True,
+                                              k_block_size=(1024 if Lnew > 128 else 1000000))
+        assert_parity(out, ref, TOL_F32, f"step {step}")
+        assert np.array_equal(to_np(kk.materialize()), rk)
+    assert cache.get_seq_length() == Lp + 3
+
+
+def test_full_size_paged_decode_properties():
+    """At the benchmark's full size (64 sequences, contexts 512..8192, 32/8 heads, D 128, bf16):
+    oracle parity on a sample of sequences and the sum-to-one property of the softmax weights."""
+    rng = np.random.default_rng(2024)
+    n_seqs, Hq, Hkv, D, P = 64, 32, 8, 128, 16
+    lens = rng.integers(512, 8193, size=n_seqs)
+    pages_per_seq = int(-(-(lens.max() + 1) // P))
+    n_pages = int(sum(-(-(int(t) + 1) // P) for t in lens)) + 8
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=n_pages, max_seqs=n_seqs,
+                                       max_pages_per_seq=pages_per_seq, page_size=P, dtype=torch.bfloat16))
+    perm = rng.permutation(n_pages)
+    table = np.full((n_seqs, pages_per_seq), -1, np.int32)
+    at = 0
+    for s in range(n_seqs):
+        n = -(-(int(lens[s]) + 1) // P)
+        table[s, :n] = perm[at:at + n]
+        at += n
+        assert pool.alloc_sequence() == s
+        pool.set_page_table(s, table[s, :n].tolist(), int(lens[s]))
+    kp, vp = pool.layer_views(0)
+    gen = torch.Generator(device=DEV).manual_seed(7)
+    kp.copy_(torch.randn(kp.shape, generator=gen, device=DEV, dtype=torch.float32))
+    vp.copy_(torch.randn(vp.shape, generator=gen, device=DEV, dtype=torch.float32))
+    q = bf16_round(rng.standard_normal((n_seqs, Hq, D), dtype=np.float32))
+    out = pool.decode_attention(0, _t(q, torch.bfloat16))
+    assert pool.check_device_status() == 0
+    sample = [0, 17, int(np.argmax(lens)), int(np.argmin(lens))]
+    for s in sample:   # the oracle reads only this sequence's pages
+        n = -(-int(lens[s]) // P)
+        pages = torch.from_numpy(table[s, :n].astype(np.int64)).to(DEV)
+        k_s, v_s = to_np(kp[pages]), to_np(vp[pages])
+        local = np.arange(n, dtype=np.int32)[None]
+        ref = opaged.paged_decode_attention(q[s:s + 1], k_s, v_s, local, np.array([lens[s]]), out_dtype=np.float32)
+        assert_parity(out[s:s + 1], ref, TOL_BF16, f"full-size sequence {s}")
+    # softmax weights sum to one: with V == 1 everywhere every output element is 1 (up to bf16 rounding of P)
+    vp.fill_(1.0)
+    ones = to_np(pool.decode_attention(0, _t(q, torch.bfloat16)))
+    assert np.abs(ones - 1.0).max() <= 2e-2
+    assert pool.check_device_status() == 0

@@ -1,0 +1,213 @@
+"""Paged KV cache on the GPU, through the C ABI: the reference's cache tests
+(tests/test_mlx_kvcache.py:28-93) and bit-exact comparison of copied KV bytes, page tables and
+lengths with the oracle."""
+import os
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import lokahi_b200 as L
+from oracle import paged as opaged
+from oracle import rope as orope
+from oracle.kvcache import ConcatKVCache
+from parity import TOL_BF16, TOL_F32, assert_parity, bf16_round, to_np
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+CONFIG = SimpleNamespace(num_hidden_layers=2, max_position_embeddings=64)
+
+
+def _states(start, length):
+    values = np.arange(start, start + length * 8, dtype=np.float32).reshape(1, 2, length, 4)
+    return values, values + 100
+
+
+def _t(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV).to(dtype)
+
+
+def test_update_appends_values_and_tracks_each_layer_length():
+    cache = L.PagedKVCache(CONFIG, cache_dir=None, page_size=2)
+    ref = ConcatKVCache(CONFIG, cache_dir=None)
+    k0, v0 = _states(0, 3)
+    k1, v1 = _states(24, 1)
+    cache.update(_t(k0), _t(v0), 0, {"cache_position": torch.arange(0, 3)})
+    ref.update(k0, v0, 0, {"cache_position": np.arange(0, 3)})
+    keys, values = cache.update(_t(k1), _t(v1), 0, {"cache_position": torch.tensor([3])})
+    rk, rv = ref.update(k1, v1, 0, {"cache_position": np.array([3])})
+    assert cache.get_seq_length(0) == 4 and cache.get_seq_length(1) == 0 and cache.get_seq_length(None) == 4
+    assert keys.shape == (1, 2, 4, 4)
+    assert np.array_equal(to_np(keys.materialize()), rk) and np.array_equal(to_np(values.materialize()), rv)
+    assert np.array_equal(to_np(keys[:, :, :3]), k0) and np.array_equal(to_np(values[:, :, 3:]), v1)
+    assert len(cache) == 1 and 0 in cache and 1 not in cache and cache[1] == {"key": None, "value": None}
+    assert cache.pool.page_table(cache.seq_ids[0]).tolist() == [0, 1]
+    assert cache.pool.check_device_status() == 0
+
+
+def test_update_rejects_replay_and_bad_shapes():
+    cache = L.PagedKVCache(CONFIG, cache_dir=None)
+    k, v = (_t(x) for x in _states(0, 2))
+    cache.update(k, v, 0, {"cache_position": torch.tensor([0, 1])})
+    with pytest.raises(ValueError, match="append exactly"):
+        cache.update(k, v, 0, {"cache_position": torch.tensor([0, 1])})
+    with pytest.raises(ValueError, match="non-negative integer"):
+        cache.update(k, v, -1)
+    with pytest.raises(ValueError, match="outside configured layer count"):
+        cache.update(k, v, 2)
+    with pytest.raises(ValueError, match="rank 4"):
+        cache.update(k[0], v[0], 0)
+    with pytest.raises(ValueError, match="identical shapes"):
+        cache.update(k, v[:, :, :1], 0)
+    with pytest.raises(ValueError, match="must match cached batch, head, and feature"):
+        cache.update(k[:, :1], v[:, :1], 0)
+    assert cache.get_seq_length(0) == 2
+
+
+def test_disk_round_trip_preserves_values_and_length(tmp_path):
+    for dtype in (torch.float32, torch.bfloat16):
+        cache = L.PagedKVCache(CONFIG, cache_dir=str(tmp_path))
+        k, v = _states(0, 2)
+        cache.update(_t(k, dtype), _t(v, dtype), 1, {"cache_position": torch.tensor([0, 1])})
+        cache.save_to_disk(1)
+        path = tmp_path / "kvcache_layer_1.npz"
+        assert cache.get_seq_length(1) == 2 and 1 not in cache._resident and path.exists() and 1 in cache
+        restored = cache[1]
+        assert np.array_equal(to_np(restored["key"]), k) and np.array_equal(to_np(restored["value"]), v)
+        assert cache.get_seq_length(1) == 2
+        # appending after a reload continues the same history
+        k2, v2 = _states(16, 1)
+        keys, _ = cache.update(_t(k2, dtype), _t(v2, dtype), 1, {"cache_position": torch.tensor([2])})
+        assert np.array_equal(to_np(keys.materialize()), np.concatenate([k, k2], axis=2))
+        cache.clear()
+        assert not path.exists() and cache.get_seq_length(None) == 0
+
+
+def test_memory_only_cache_requires_explicit_destination():
+    cache = L.PagedKVCache(CONFIG, cache_dir=None)
+    k, v = (_t(x) for x in _states(0, 1))
+    cache.update(k, v, 0)
+    with pytest.raises(ValueError, match="filename is required"):
+        cache.save_to_disk(0)
+
+
+def test_layer_window_cache_spills_lowest_layers(tmp_path):
+    cfg = SimpleNamespace(num_hidden_layers=6, max_position_embeddings=32)
+    cache = L.PagedLlamaDiskCache(cfg, cache_dir=str(tmp_path), max_layers_in_memory=2)
+    k, v = (_t(x) for x in _states(0, 1))
+    for layer in range(4):
+        cache.update(k, v, layer)
+    assert sorted(cache._resident) == [2, 3] and sorted(cache._disk_offloaded) == [0, 1] and len(cache) == 4
+    assert np.array_equal(to_np(cache[0]["key"]), to_np(k))
+    with pytest.raises(ValueError, match="must be positive"):
+        L.PagedLlamaDiskCache(cfg, cache_dir=str(tmp_path), max_layers_in_memory=0)
+    assert isinstance(L.create_paged_kv_cache("llama3-1B", cfg, str(tmp_path)), L.PagedLlamaDiskCache)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+def test_ragged_append_with_rope_matches_oracle(dtype, tol):
+    """Ragged sequences, external random page table, RoPE-on-write for K and Q in one launch."""
+    rng = np.random.default_rng(21)
+    n_seqs, Hkv, Hq, D, P = 5, 2, 4, 64, 16
+    theta = 500000.0
+    lens = [0, 1, 15, 16, 37]
+    n_pages = 32
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=n_pages, max_seqs=n_seqs,
+                                       max_pages_per_seq=6, page_size=P, dtype=dtype, rope_theta=theta))
+    perm = rng.permutation(n_pages)
+    tables = []
+    for s in range(n_seqs):
+        assert pool.alloc_sequence() == s
+        pages = perm[s * 6:(s + 1) * 6].tolist()
+        pool.set_page_table(s, pages, 0)
+        tables.append(pages)
+    k_ref = np.zeros((n_pages, Hkv, P, D), np.float32)
+    v_ref = np.zeros_like(k_ref)
+    rnd = (lambda a: a) if dtype == torch.float32 else bf16_round
+    # first a prefill of different lengths per sequence (one call per sequence), then a joint decode append
+    for s, n in enumerate(lens):
+        if n == 0:
+            continue
+        k = rnd(rng.standard_normal((1, Hkv, n, D), dtype=np.float32))
+        v = rnd(rng.standard_normal((1, Hkv, n, D), dtype=np.float32))
+        pool.append(0, _t(k, dtype), _t(v, dtype), seq_ids=[s], start_pos=[0], rope_k=True)
+        kr = rnd(orope.apply(k, *orope.cos_sin(np.arange(n)[None], D, theta)))
+        opaged.write_tokens(k_ref, np.array(tables[s]), 0, kr[0])
+        opaged.write_tokens(v_ref, np.array(tables[s]), 0, v[0])
+    k = rnd(rng.standard_normal((n_seqs, Hkv, D), dtype=np.float32))
+    v = rnd(rng.standard_normal((n_seqs, Hkv, D), dtype=np.float32))
+    q = rnd(rng.standard_normal((n_seqs, Hq, D), dtype=np.float32))
+    qt = _t(q, dtype)
+    pool.append(0, _t(k, dtype), _t(v, dtype), start_pos=lens, rope_k=True, q=qt, layout="bhd")
+    kr = rnd(opaged.rope_rows(k, np.array(lens), theta))
+    qr = rnd(opaged.rope_rows(q, np.array(lens), theta))
+    for s in range(n_seqs):
+        opaged.write_tokens(k_ref, np.array(tables[s]), lens[s], kr[s][:, None, :])
+        opaged.write_tokens(v_ref, np.array(tables[s]), lens[s], v[s][:, None, :])
+    kp, vp = pool.layer_views(0)
+    assert pool.check_device_status() == 0
+    assert np.array_equal(pool.lengths(0), np.array(lens) + 1)
+    assert np.array_equal(to_np(vp), v_ref), "copied V bytes must be bit-exact"
+    assert_parity(kp, k_ref, tol, "rotated K in pages")
+    assert_parity(qt, qr, tol, "rotated Q")
+    # device copy of the lengths matches the host's
+    gk, gv = pool.gather(0, n_seqs=n_seqs)
+    for s in range(n_seqs):
+        T = lens[s] + 1
+        assert np.array_equal(to_np(gv[s, :, :T]), opaged.logical_kv(v_ref, np.array(tables[s]), T))
+        assert not to_np(gv[s, :, T:]).any()
+
+
+def test_rope_rows_matches_reference_fixture(golden_dir):
+    with np.load(os.path.join(golden_dir, "rope_half_rotation.npz")) as d:
+        q = _t(d["q"][0].transpose(1, 0, 2))            # [rows=3, heads=2, dim=4]
+        inv = torch.from_numpy(L.rope_inv_freq(int(d["dim"]), float(d["base"])))
+        out = L.rope_rows(q, torch.from_numpy(d["positions"][0]), inv)
+        assert np.allclose(to_np(out).transpose(1, 0, 2)[None], d["q_out"], atol=1e-6)
+
+
+def test_rope_linear_scaling_and_large_positions():
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((7, 3, 128), dtype=np.float32)
+    pos = np.array([0, 1, 4095, 8192, 65537, 98303, 131071])
+    inv = L.rope_inv_freq(128, 100000.0)
+    out = L.rope_rows(_t(x), torch.from_numpy(pos), torch.from_numpy(inv), scaling_factor=4.0)
+    ref = opaged.rope_rows(x, pos, 100000.0, 4.0)
+    assert_parity(out, ref, TOL_F32, "scaled RoPE")
+
+
+def test_evict_prefetch_round_trip_is_bit_exact_and_moves_pages():
+    rng = np.random.default_rng(8)
+    Hkv, D, P, T = 2, 32, 4, 26
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=3, num_kv_heads=Hkv, head_dim=D, num_pages=12, max_seqs=2,
+                                       max_pages_per_seq=8, page_size=P, dtype=torch.bfloat16, host_pages=8))
+    model = opaged.PagePoolModel(3, 12, P, 2, 8, 8)
+    s = pool.alloc_sequence(); model.alloc_sequence()
+    ks, vs = [], []
+    for layer in range(3):
+        k = bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32))
+        v = bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32))
+        pool.append(layer, _t(k, torch.bfloat16), _t(v, torch.bfloat16), seq_ids=[s], start_pos=[0])
+        model.append(layer, s, 0, T)
+        ks.append(k); vs.append(v)
+    pool.evict(s, 0, 4); model.evict(s, 0, 4)
+    assert np.array_equal(pool.page_table(s), model.page_table[s, :7]) and (pool.page_table(s)[:4] <= -2).all()
+    with pytest.raises(L.NotResidentError):
+        pool.gather(0, seq_ids=[s])
+    q = _t(bf16_round(rng.standard_normal((1, 4, D), dtype=np.float32)), torch.bfloat16)
+    with pytest.raises(L.NotResidentError):
+        pool.decode_attention(0, q, seq_ids=[s])
+    # another sequence takes the freed device pages, so the prefetch must land elsewhere
+    s2 = pool.alloc_sequence(); model.alloc_sequence()
+    filler = _t(np.ones((1, Hkv, 3 * P, D), np.float32), torch.bfloat16)
+    pool.append(0, filler, filler, seq_ids=[s2], start_pos=[0]); model.append(0, s2, 0, 3 * P)
+    pool.prefetch(s, 0, 7); model.prefetch(s, 0, 7)
+    pool.wait_resident(5000)
+    assert np.array_equal(pool.page_table(s), model.page_table[s, :7])
+    for layer in range(3):
+        gk, gv = pool.gather(layer, seq_ids=[s])
+        assert np.array_equal(to_np(gk), ks[layer]) and np.array_equal(to_np(gv), vs[layer])
+    c = pool.counters()
+    assert c["pages_evicted"] == 4 and c["pages_prefetched"] == 4 and c["bytes_d2h"] == c["bytes_h2d"] == 4 * 3 * 2 * Hkv * P * D * 2
+    assert pool.check_device_status() == 0
