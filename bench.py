@@ -127,7 +127,7 @@ def run_ours(args):
     total_steps = W + K
     lens0 = workload_lengths()
     rng = np.random.default_rng(SEED + 1)
-    cap = lens0 + 2 * total_steps + 1                      # room for both legs
+    cap = lens0 + 2 * total_steps + 2 * P                   # room for both legs
     pages_per_seq = int(-(-cap.max() // P))
     pages_each = (-(-cap // P)).astype(np.int64)
     n_pages = int(pages_each.sum()) + 16
