@@ -147,6 +147,20 @@ SKV_API int32_t skv_decode_attn(skv_pool* pool, int32_t layer, const int32_t* se
                         const void* q, void* out, const int32_t* q_pos, int32_t n_q_heads,
                         float eps, void* workspace, size_t workspace_bytes, void* stream);
 
+/* K3 without a caller workspace.  This entry point has no counterpart in the reference; it exists for
+ * hosts that cannot allocate device memory (a process whose memory is handed out once at start-up,
+ * a plugin inside a foreign arena, code that must not trigger a device-synchronising allocation).
+ * Same arguments and result as skv_decode_attn, but the split-K partials live in an array of
+ * SKV_STATIC_SCRATCH_BYTES that is part of the library image on every GPU that loads it.
+ *   - a call whose partials need more than that returns SKV_ERR_UNSUPPORTED (message names both sizes);
+ *   - no cudaMalloc / cudaFree / allocating library call is made;
+ *   - the first call on a device resolves the array's address: make it outside stream capture;
+ *   - all calls on a device share the array; calls that overlap on the GPU race, so order them. */
+#define SKV_STATIC_SCRATCH_BYTES (16u << 20)
+SKV_API int32_t skv_decode_attn_static(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
+                                       const void* q, void* out, const int32_t* q_pos, int32_t n_q_heads,
+                                       float eps, void* stream);
+
 /* K4: chunked grouped-query attention on dense tensors
  * (online_chunked_grouped_attention_mx, mlx_ops.py:32-152; unmasked twin :155-178).
  * q,out [B][Hq][Lq][D], k,v [B][Hkv][Lk][D], contiguous.  positions: device int32 [B][Lq]

@@ -18,6 +18,7 @@ SOURCES = [
     "pool.cu",
     "kernels_append.cu",
     "kernels_decode.cu",
+    "decode_static.cu",
     "kernels_attn_generic.cu",
     "kernels_prefill_tc.cu",
 ]

@@ -724,6 +724,61 @@ int32_t skv_gather(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n
     return SKV_OK;
 }
 
+}  // extern "C"
+
+namespace skv {
+
+int32_t pool_fail(skv_pool* p, int32_t code, const char* message) { return p->fail(code, "%s", message); }
+int32_t pool_device(const skv_pool* p) { return p->cfg.device; }
+
+int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const int32_t* q_pos,
+                       int32_t n_q_heads, const void* q, void* out, float eps, cudaStream_t stream, DecodeLaunch* d,
+                       int64_t* total_tokens, int32_t* launchable) {
+    *launchable = 0;
+    *total_tokens = 0;
+    if (n_q_heads <= 0 || n_q_heads % p->cfg.num_kv_heads != 0)
+        return p->fail(SKV_ERR_BAD_ARG, "query heads must be divisible by key/value heads");
+    if (layer < 0) return p->fail(SKV_ERR_BAD_ARG, "layer_idx must be a non-negative integer");
+    if (layer >= p->cfg.num_layers)
+        return p->fail(SKV_ERR_BAD_ARG, "layer_idx %d is outside configured layer count %d", layer, p->cfg.num_layers);
+    if (n_seqs <= 0 || n_seqs > p->cfg.max_seqs) return p->fail(SKV_ERR_BAD_ARG, "n_seqs %d out of range", n_seqs);
+    if ((size_t)n_seqs * sizeof(int32_t) > StagingRing::kSlotBytes)
+        return p->fail(SKV_ERR_BAD_ARG, "too many sequences (%d) for one call", n_seqs);
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        const int32_t s = seq_ids ? seq_ids[i] : i;
+        if (!valid_seq(p, s)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", s);
+        int32_t T = p->len(layer, s);
+        *total_tokens += T;
+        if (q_pos) T = std::min(T, std::max(0, q_pos[i] + 1));
+        const int32_t pages = (T + p->cfg.page_size - 1) / p->cfg.page_size;
+        for (int32_t slot = 0; slot < pages; ++slot)
+            if (p->pt(s, slot) < 0) return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", s, slot);
+    }
+    if (p->host_only) return SKV_OK;
+    if (!q || !out) return p->fail(SKV_ERR_BAD_ARG, "q and out must be given");
+    int32_t st = order_transfers(p, stream);
+    if (st != SKV_OK) return st;
+    d->pool = p->view();
+    d->layer = layer;
+    d->n_seqs = n_seqs;
+    d->n_q_heads = n_q_heads;
+    d->dtype = p->cfg.dtype;
+    st = upload_ids(p, seq_ids, n_seqs, stream, &d->seq_ids);
+    if (st != SKV_OK) return st;
+    st = upload_ids(p, q_pos, n_seqs, stream, &d->q_pos);
+    if (st != SKV_OK) return st;
+    d->q = q;
+    d->out = out;
+    d->eps = eps;
+    d->force_generic = 0;
+    *launchable = 1;
+    return SKV_OK;
+}
+
+}  // namespace skv
+
+extern "C" {
+
 size_t skv_decode_workspace_bytes(const skv_pool* p, int32_t n_seqs, int32_t n_q_heads) {
     if (!p || n_seqs <= 0 || n_q_heads <= 0) return 0;
     int32_t chunk = 0, splits = 0;

@@ -106,6 +106,16 @@ struct RopeRowsLaunch {
 };
 cudaError_t launch_rope_rows(const RopeRowsLaunch& r, cudaStream_t stream);
 
+// Front half of a decode call without any allocation: validates the arguments against the pool's host
+// state, orders the call after pending page transfers, uploads seq_ids / q_pos through the pool's
+// staging ring and fills every field of *d except the split plan and the workspace pointers.
+// *launchable is 0 for bookkeeping-only pools.
+int32_t prepare_decode(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const int32_t* q_pos,
+                       int32_t n_q_heads, const void* q, void* out, float eps, cudaStream_t stream, DecodeLaunch* d,
+                       int64_t* total_tokens, int32_t* launchable);
+int32_t pool_fail(skv_pool* pool, int32_t code, const char* message);
+int32_t pool_device(const skv_pool* pool);
+
 // process-wide count of kernel launches issued by this library
 void count_launches(int n);
 

@@ -280,6 +280,23 @@ class PagedPool:
                                         i32_array(q_pos), hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
         return out
 
+    def decode_attention_static(self, layer: int, q: torch.Tensor, *, seq_ids=None, q_pos=None, eps: float = 1e-12,
+                                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``decode_attention`` for callers that may not allocate device memory: the split-K partials
+        go to a 16 MiB array built into the library instead of a workspace tensor, so this wrapper
+        creates nothing but (optionally) the output.  Pass ``out`` to allocate nothing at all.
+        Raises NotImplementedError when the partials would not fit; calls on one device share the
+        array and must not overlap on the GPU."""
+        self._check_tensor(q, "q")
+        if q.dim() != 3 or not q.is_contiguous():
+            raise ValueError("q must be a contiguous [n_seqs, q_heads, head_dim] tensor")
+        n_seqs, hq, _ = q.shape
+        if out is None:
+            out = torch.empty_like(q)
+        self._check(lib.skv_decode_attn_static(self._h, layer, i32_array(seq_ids), n_seqs, q.data_ptr(), out.data_ptr(),
+                                               i32_array(q_pos), hq, float(eps), self.stream))
+        return out
+
     # -- K4 over pages ------------------------------------------------------------------------------------
     def prefill_attention(self, layer: int, q: torch.Tensor, *, seq_ids=None, positions: Optional[torch.Tensor] = None,
                           causal: bool = True, eps: float = 1e-12) -> torch.Tensor:
