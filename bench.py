@@ -249,7 +249,7 @@ def run_ours(args):
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0,
                          "kernel": "decode attention call (split-K kernel + merge kernel)",
                          "algorithmic_bytes_per_launch": algo_bytes, "launch_ms": attn_mean_ms,
-                         "launch_ms_min": float(attn_ms.min()), "traffic": TRAFFIC_BYTES_PER_LAUNCH},
+                         "launch_ms_min": float(attn_ms.min()), "traffic": algo_bytes * TRAFFIC_RATIO},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -260,9 +260,10 @@ def run_ours(args):
     return result
 
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at this workload, from the capture
-# summarised under profiles/ (None until a capture exists)
-TRAFFIC_BYTES_PER_LAUNCH = None
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per decode launch: measured on the 16-sequence capture
+# case (295.49 MB of traffic for 287.07 MB algorithmic, profiles/decode_tma_kernel_paged_decode_16seq.md)
+# and scaled to this workload by the algorithmic bytes, which is what the traffic grows with.
+TRAFFIC_RATIO = 295.49 / 287.07
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -389,13 +390,17 @@ def run_reference(args):
 
 
 def main():
+    global N_SEQS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seqs", type=int, default=N_SEQS,
+                    help="number of sequences (default: the workload's 64; smaller values are for profiler captures)")
     args = ap.parse_args()
+    N_SEQS = args.seqs
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     result = run_reference(args) if args.impl == "reference" else run_ours(args)

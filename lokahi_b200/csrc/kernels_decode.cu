@@ -19,6 +19,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace skv {
 
@@ -326,6 +327,257 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_mma_kernel(DecodeLaunch
 }
 
 // ---------------------------------------------------------------------------------------------
+// TMA-staged variant of the tensor-core kernel.  Same work split, same fragments, same partials;
+// the difference is how K/V reach the fragments.  Every warp owns a private ring of NS stages in
+// shared memory; lane 0 fills a stage with four cp.async.bulk.tensor 2-D boxes ([16 tokens][64 dims]
+// of K and of V, 128-byte swizzle) that complete on the stage's mbarrier, so the bytes in flight per
+// SM are set by the ring depth (NS x 8 KB per warp) instead of by the register file.  Fragments are
+// read back with 16-byte shared loads whose lane-to-unit mapping is conflict-free under the
+// hardware swizzle: for K a lane takes units 2c and 2c+1 of each 128-byte half-row (rows g and g+1
+// of a quarter-warp then fall into opposite bank parities), for V a lane takes unit g of rows
+// 2c, 2c+1, 2c+8, 2c+9.  No cluster, no multicast; every mbarrier wait is bounded and a timeout sets
+// FLAG_WAIT_TIMEOUT, drains the copies still in flight and writes an empty partial.
+// ---------------------------------------------------------------------------------------------
+constexpr int kStageBytes = 8192;   // one 16-token tile: K (2 boxes x 2 KB) + V (2 boxes x 2 KB)
+
+template <int NS>
+__global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch d, const __grid_constant__ CUtensorMap kmap,
+                                                                    const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ uint8_t smem_raw[];
+    const PoolView& pv = d.pool;
+    const int split = blockIdx.x, h = blockIdx.y, i = blockIdx.z;
+    const int seq = d.seq_ids ? d.seq_ids[i] : i;
+    if (!checked_seq(pv, seq)) return;
+    const int n_attend = attend_count(d, i, seq);
+    const int t0 = split * d.chunk_tokens;
+    if (t0 >= n_attend) return;
+    const int t1 = min(n_attend, t0 + d.chunk_tokens);
+    const int G = d.n_q_heads / pv.num_kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int P = pv.page_size;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* ring = smem + warp * NS * kStageBytes;
+    uint64_t* wbar = reinterpret_cast<uint64_t*>(smem + kDecodeWarps * NS * kStageBytes) + warp * NS;
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) mbar_init(&wbar[s], 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+
+    // Q fragments: row g, 16-byte units 2c and 2c+1 of each 128-byte half (the K lane mapping)
+    uint32_t qa[8][2];
+    {
+        const char* qrow = reinterpret_cast<const char*>(d.q) + (((int64_t)i * d.n_q_heads + h * G + g) * kMmaD) * 2;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            uint4 r = make_uint4(0, 0, 0, 0);
+            if (g < G) r = *reinterpret_cast<const uint4*>(qrow + (8 * (u >> 1) + 2 * c + (u & 1)) * 16);
+            qa[2 * u][0] = r.x;
+            qa[2 * u][1] = r.y;
+            qa[2 * u + 1][0] = r.z;
+            qa[2 * u + 1][1] = r.w;
+        }
+    }
+    const int n_tiles = (t1 - t0 + 15) >> 4;
+    const int n_my = n_tiles > warp ? (n_tiles - warp + kDecodeWarps - 1) / kDecodeWarps : 0;
+    int my_page = -1;
+    {
+        const int tile = warp + kDecodeWarps * lane;
+        if (tile < n_tiles) my_page = checked_page(pv, seq, (t0 + tile * 16) / P);
+    }
+    const int layer_rows = (int)((int64_t)d.layer * (pv.layer_stride_bytes / (kMmaD * 2)));
+
+    auto issue = [&](int k) {   // called by the whole warp
+        const int page = __shfl_sync(0xffffffffu, my_page, k);
+        if (lane == 0) {
+            uint64_t* bar = &wbar[k % NS];
+            if (page >= 0) {
+                const int tb = t0 + (warp + kDecodeWarps * k) * 16;
+                const int y = layer_rows + (page * pv.num_kv_heads + h) * P + (tb % P);
+                uint8_t* st = ring + (k % NS) * kStageBytes;
+                mbar_expect_tx(bar, kStageBytes);
+                tma_load_2d(st, &kmap, 0, y, bar);
+                tma_load_2d(st + 2048, &kmap, 64, y, bar);
+                tma_load_2d(st + 4096, &vmap, 0, y, bar);
+                tma_load_2d(st + 6144, &vmap, 64, y, bar);
+            } else {
+                mbar_arrive(bar);   // keep the stage's phase in step for a skipped tile
+            }
+        }
+    };
+
+    float o[2][8][2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[hh][e][0] = o[hh][e][1] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const float sc = rsqrtf((float)kMmaD) * kLog2e;
+
+    for (int k = 0; k < NS && k < n_my; ++k) issue(k);
+    bool dead = false;
+    int k = 0;
+    for (; k < n_my; ++k) {
+        const int page = __shfl_sync(0xffffffffu, my_page, k);
+        const int stage = k % NS;
+        if (!mbar_wait(&wbar[stage], (k / NS) & 1)) {
+            dead = true;
+            break;
+        }
+        if (page >= 0) {
+            const int tb = t0 + (warp + kDecodeWarps * k) * 16;
+            const uint8_t* st = ring + stage * kStageBytes;
+            uint4 kr[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    kr[j][u] = *reinterpret_cast<const uint4*>(st + (u >> 1) * 2048 + (8 * j + g) * 128 +
+                                                               (((2 * c + (u & 1)) ^ g) << 4));
+            float s[2][2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][0] = s[j][1] = 0.f;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    mma_bf16_rows8(s[j][0], s[j][1], qa[2 * u][0], qa[2 * u][1], kr[j][u].x, kr[j][u].y);
+                    mma_bf16_rows8(s[j][0], s[j][1], qa[2 * u + 1][0], qa[2 * u + 1][1], kr[j][u].z, kr[j][u].w);
+                }
+            }
+            uint4 vr[4][2];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int row = 2 * c + (r & 1) + 8 * (r >> 1);
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                    vr[r][hh] = *reinterpret_cast<const uint4*>(st + 4096 + hh * 2048 + row * 128 + ((g ^ (row & 7)) << 4));
+            }
+            const bool tail = tb + 16 > t1;
+            if (tail) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
+                        if (tb + 8 * j + 2 * c + b >= t1) s[j][b] = -INFINITY;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int row = 2 * c + (r & 1) + 8 * (r >> 1);
+                    if (tb + row >= t1) vr[r][0] = vr[r][1] = make_uint4(0, 0, 0, 0);
+                }
+            }
+            float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run, mx * sc);
+            const float alpha = exp2f(m_run - m_new);
+            float p[2][2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int b = 0; b < 2; ++b) p[j][b] = exp2f(fmaf(s[j][b], sc, -m_new));
+            l_run = l_run * alpha + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
+            m_run = m_new;
+            const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]);
+            const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const uint32_t* ra = reinterpret_cast<const uint32_t*>(&vr[0][hh]);
+                const uint32_t* rb = reinterpret_cast<const uint32_t*>(&vr[1][hh]);
+                const uint32_t* rc = reinterpret_cast<const uint32_t*>(&vr[2][hh]);
+                const uint32_t* rd = reinterpret_cast<const uint32_t*>(&vr[3][hh]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t b0 = __byte_perm(ra[e >> 1], rb[e >> 1], sel);
+                    const uint32_t b1 = __byte_perm(rc[e >> 1], rd[e >> 1], sel);
+                    o[hh][e][0] *= alpha;
+                    o[hh][e][1] *= alpha;
+                    mma_bf16_rows8(o[hh][e][0], o[hh][e][1], pa0, pa2, b0, b1);
+                }
+            }
+        }
+        // the stage has been read into registers and consumed: hand it back to the copy engine
+        if (k + NS < n_my) {
+            __syncwarp();
+            fence_proxy_async();
+            issue(k + NS);
+        }
+    }
+    if (dead) {
+        if (lane == 0) atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
+        // copies already issued for later tiles still target this CTA's shared memory: wait for them (bounded)
+        for (int kk = k + 1; kk < n_my && kk < k + NS; ++kk) mbar_wait(&wbar[kk % NS], (kk / NS) & 1);
+        l_run = 0.f;
+        m_run = -INFINITY;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[hh][e][0] = o[hh][e][1] = 0.f;
+    }
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+    // all rings are idle now: reuse the start of shared memory for the cross-warp combine
+    __syncthreads();
+    float* sm_m = reinterpret_cast<float*>(smem);                  // [warps][8]
+    float* sm_l = sm_m + kDecodeWarps * 8;                          // [warps][8]
+    float* sm_o = sm_l + kDecodeWarps * 8;                          // [warps][8][128]
+    if (c == 0) {
+        sm_m[warp * 8 + g] = m_run;
+        sm_l[warp * 8 + g] = l_run;
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            float* dst = sm_o + (warp * 8 + g) * kMmaD + 64 * hh + 16 * c + 8 * b;
+            *reinterpret_cast<float4*>(dst) = make_float4(o[hh][0][b], o[hh][1][b], o[hh][2][b], o[hh][3][b]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(o[hh][4][b], o[hh][5][b], o[hh][6][b], o[hh][7][b]);
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * kMmaD; idx += kDecodeThreads) {
+        const int r = idx >> 7, dd = idx & 127;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w)
+            if (sm_l[w * 8 + r] > 0.f) M = fmaxf(M, sm_m[w * 8 + r]);
+        float L = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            const float wgt = sm_l[w * 8 + r] > 0.f ? exp2f(sm_m[w * 8 + r] - M) : 0.f;
+            L += wgt * sm_l[w * 8 + r];
+            a += wgt * sm_o[(w * 8 + r) * kMmaD + dd];
+        }
+        const int64_t pidx = ((int64_t)i * d.n_q_heads + h * G + r) * d.max_splits + split;
+        d.ws_acc[pidx * kMmaD + dd] = a;
+        if (dd == 0) {
+            d.ws_ml[pidx * 2 + 0] = M * (1.0f / kLog2e);
+            d.ws_ml[pidx * 2 + 1] = L;
+        }
+    }
+}
+
+template <int NS>
+cudaError_t launch_tma(const DecodeLaunch& d, cudaStream_t stream) {
+    static bool configured[64] = {};
+    const int smem = kDecodeWarps * NS * kStageBytes + kDecodeWarps * NS * 8 + 1024;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
+    decode_tma_kernel<NS><<<grid, kDecodeThreads, smem, stream>>>(d, *reinterpret_cast<const CUtensorMap*>(d.k_map),
+                                                                  *reinterpret_cast<const CUtensorMap*>(d.v_map));
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
 // K3r: merge the partials of one (sequence, query head) with the reference's chunk-merge rule and
 // write out = wv / max(s, eps) in the storage dtype.  grid (n_q_heads, n_seqs).
 // ---------------------------------------------------------------------------------------------
@@ -404,7 +656,13 @@ cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream) {
     const bool mma_ok = d.dtype == SKV_BF16 && d.pool.head_dim == kMmaD && d.pool.page_size % 16 == 0 && G <= 8 &&
                         !d.force_generic && ((uintptr_t)d.q % 16 == 0);
     cudaError_t e;
-    if (mma_ok) {
+    const char* impl = getenv("SKV_DECODE_IMPL");   // "reg": direct-to-register loads; default: TMA ring when maps exist
+    const bool tma_ok = mma_ok && d.k_map && d.v_map && !(impl && impl[0] == 'r');
+    if (tma_ok) {
+        const char* st = getenv("SKV_DECODE_STAGES");
+        const int ns = st ? atoi(st) : 2;   // 2 stages -> 3 CTAs per SM (24 stages of 8 KB in flight), the measured best
+        e = ns == 3 ? launch_tma<3>(d, stream) : ns == 4 ? launch_tma<4>(d, stream) : launch_tma<2>(d, stream);
+    } else if (mma_ok) {
         dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
         decode_mma_kernel<<<grid, kDecodeThreads, 0, stream>>>(d);
         e = cudaGetLastError();

@@ -15,6 +15,7 @@
 #include <thread>
 
 #include "skv_internal.h"
+#include "tma.cuh"
 
 #include <atomic>
 
@@ -106,6 +107,10 @@ struct skv_pool {
     int32_t* d_lengths = nullptr;
     int32_t* d_status = nullptr;
     float* d_inv_freq = nullptr;
+    // K and V pools as 2-D bf16 tensors [layers*pages*heads*page_size][head_dim] with [16][64] boxes
+    alignas(64) CUtensorMap k_map;
+    alignas(64) CUtensorMap v_map;
+    bool has_maps = false;
     bool rope_set = false;
     float rope_scaling = 1.0f;
     StagingRing ring;
@@ -359,6 +364,12 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
             size_t bytes = (size_t)cfg->host_pages * cfg->num_layers * 2 * p->page_bytes;
             CUDA_TRY(p, cudaHostAlloc((void**)&p->h_tier, bytes, cudaHostAllocMapped | cudaHostAllocPortable));
             CUDA_TRY(p, cudaHostGetDevicePointer((void**)&p->h_tier_dev, p->h_tier, 0));
+        }
+        if (cfg->dtype == SKV_BF16 && cfg->head_dim == 128 && cfg->page_size % 16 == 0) {
+            const uint64_t rows = (uint64_t)cfg->num_layers * cfg->num_pages * cfg->num_kv_heads * cfg->page_size;
+            if (rows < (1ull << 31))
+                p->has_maps = encode_bf16_2d(&p->k_map, p->d_k, rows, 128, 256, 16, 64) &&
+                              encode_bf16_2d(&p->v_map, p->d_v, rows, 128, 256, 16, 64);
         }
         CUDA_TRY(p, cudaDeviceSynchronize());
         return SKV_OK;
@@ -771,6 +782,8 @@ int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32
     d->out = out;
     d->eps = eps;
     d->force_generic = 0;
+    d->k_map = p->has_maps ? &p->k_map : nullptr;
+    d->v_map = p->has_maps ? &p->v_map : nullptr;
     *launchable = 1;
     return SKV_OK;
 }
@@ -829,6 +842,8 @@ int32_t skv_decode_attn(skv_pool* p, int32_t layer, const int32_t* seq_ids, int3
     D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
     const char* force = getenv("SKV_DECODE_GENERIC");
     D.force_generic = (force && force[0] == '1') ? 1 : 0;
+    D.k_map = p->has_maps ? &p->k_map : nullptr;
+    D.v_map = p->has_maps ? &p->v_map : nullptr;
     CUDA_TRY(p, launch_decode(D, stream));
     return SKV_OK;
 }

@@ -27,6 +27,7 @@ enum : int32_t {
     FLAG_BAD_PAGE = 1,       // page-table entry outside [0, num_pages)
     FLAG_BAD_LENGTH = 2,     // length beyond the page-table row
     FLAG_BAD_SEQ = 4,        // sequence id outside [0, max_seqs)
+    FLAG_WAIT_TIMEOUT = 8,   // a bounded wait on an mbarrier ran out
 };
 
 // Per-call metadata uploaded through the staging ring.
@@ -74,6 +75,10 @@ struct DecodeLaunch {
     float* ws_ml;                // [n_seqs][n_q_heads][max_splits][2]
     int32_t max_splits, chunk_tokens;
     int32_t force_generic;       // 1: take the CUDA-core kernel even where the tensor-core one applies
+    // tensor maps (host pointers to CUtensorMap) of the K and V pools viewed as [rows][head_dim] bf16 with
+    // [16][64] boxes; nullptr when the pool has none, and then the direct-load kernel runs
+    const void* k_map;
+    const void* v_map;
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
 // chunk length (tokens handled by one CTA) and the number of splits that follow from it
