@@ -350,9 +350,16 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     if (!checked_seq(pv, seq)) return;
     const int n_attend = attend_count(d, i, seq);
     const int t0 = split * d.chunk_tokens;
-    if (t0 >= n_attend) return;
-    const int t1 = min(n_attend, t0 + d.chunk_tokens);
     const int G = d.n_q_heads / pv.num_kv_heads;
+    if (t0 >= n_attend) {
+        if (split == 0) {   // nothing to attend: the output row is exactly 0 (mlx_ops.py:118, :146)
+            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(d.out) + ((int64_t)i * d.n_q_heads + h * G) * kMmaD;
+            for (int idx = threadIdx.x; idx < G * kMmaD; idx += kDecodeThreads) orow[idx] = __float2bfloat16_rn(0.f);
+        }
+        return;
+    }
+    const int t1 = min(n_attend, t0 + d.chunk_tokens);
+    const int n_splits = (n_attend + d.chunk_tokens - 1) / d.chunk_tokens;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int P = pv.page_size;
@@ -538,6 +545,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
             *reinterpret_cast<float4*>(dst + 4) = make_float4(o[hh][4][b], o[hh][5][b], o[hh][6][b], o[hh][7][b]);
         }
     __syncthreads();
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(d.out) + ((int64_t)i * d.n_q_heads + h * G) * kMmaD;
     for (int idx = threadIdx.x; idx < G * kMmaD; idx += kDecodeThreads) {
         const int r = idx >> 7, dd = idx & 127;
         float M = -INFINITY;
@@ -551,12 +559,64 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
             L += wgt * sm_l[w * 8 + r];
             a += wgt * sm_o[(w * 8 + r) * kMmaD + dd];
         }
-        const int64_t pidx = ((int64_t)i * d.n_q_heads + h * G + r) * d.max_splits + split;
-        d.ws_acc[pidx * kMmaD + dd] = a;
-        if (dd == 0) {
-            d.ws_ml[pidx * 2 + 0] = M * (1.0f / kLog2e);
-            d.ws_ml[pidx * 2 + 1] = L;
+        if (n_splits == 1 && d.fuse_merge) {   // the only chunk of this sequence: finish here, no partial is written
+            orow[idx] = __float2bfloat16_rn(a / fmaxf(L, d.eps));
+        } else {
+            const int64_t pidx = ((int64_t)i * d.n_q_heads + h * G + r) * d.max_splits + split;
+            d.ws_acc[pidx * kMmaD + dd] = a;
+            if (dd == 0) {
+                d.ws_ml[pidx * 2 + 0] = M * (1.0f / kLog2e);
+                d.ws_ml[pidx * 2 + 1] = L;
+            }
         }
+    }
+    if (n_splits == 1 || !d.fuse_merge) return;
+    // The CTA that arrives last for this (sequence, KV head) merges all partials (K3r fused in).
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t* ticket = d.tickets + (int64_t)i * pv.num_kv_heads + h;
+        const int t = atomicAdd(ticket, 1);
+        s_last = (t == n_splits - 1);
+        if (s_last) *ticket = 0;   // ready for the next call
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float* w_s = reinterpret_cast<float*>(smem);   // [G][n_splits] merge weights, then 1 / max(s, eps) per row
+    float* inv_s = w_s + 8 * 128;
+    for (int r = warp; r < G; r += kDecodeWarps) {
+        const int64_t base = ((int64_t)i * d.n_q_heads + h * G + r) * d.max_splits;
+        float M = -INFINITY;
+        for (int sp = lane; sp < n_splits; sp += 32)
+            if (__ldcg(&d.ws_ml[(base + sp) * 2 + 1]) > 0.f) M = fmaxf(M, __ldcg(&d.ws_ml[(base + sp) * 2]));
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
+        float L = 0.f;
+        for (int sp = lane; sp < n_splits; sp += 32) {
+            const float l = __ldcg(&d.ws_ml[(base + sp) * 2 + 1]);
+            const float wgt = l > 0.f ? expf(__ldcg(&d.ws_ml[(base + sp) * 2]) - M) : 0.f;
+            w_s[r * 128 + sp] = wgt;
+            L += wgt * l;
+        }
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o2);
+        if (lane == 0) inv_s[r] = 1.0f / fmaxf(L, d.eps);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * kMmaD; idx += kDecodeThreads) {
+        const int r = idx >> 7, dd = idx & 127;
+        const int64_t base = ((int64_t)i * d.n_q_heads + h * G + r) * d.max_splits;
+        float a = 0.f;
+        for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {   // eight independent loads in flight per thread
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = sp0 + j < n_splits ? __ldcg(&d.ws_acc[(base + sp0 + j) * kMmaD + dd]) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a += (sp0 + j < n_splits ? w_s[r * 128 + sp0 + j] : 0.f) * v[j];
+        }
+        orow[idx] = __float2bfloat16_rn(a * inv_s[r]);
     }
 }
 
@@ -651,7 +711,13 @@ void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, i
     *max_splits = (int32_t)splits;
 }
 
-cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream) {
+cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
+    DecodeLaunch d = d_in;
+    const char* fuse = getenv("SKV_DECODE_FUSE");
+    // Measured on B200 at the 64-sequence workload: the in-kernel merge (last-arriving CTA) costs about
+    // 2 us more per call than the separate merge launch (device-wide fences in every CTA plus a serial
+    // tail), so the separate launch is the default; SKV_DECODE_FUSE=1 selects the in-kernel merge.
+    d.fuse_merge = (fuse && fuse[0] == '1') ? 1 : 0;
     const int G = d.n_q_heads / d.pool.num_kv_heads;
     const bool mma_ok = d.dtype == SKV_BF16 && d.pool.head_dim == kMmaD && d.pool.page_size % 16 == 0 && G <= 8 &&
                         !d.force_generic && ((uintptr_t)d.q % 16 == 0);
@@ -672,6 +738,10 @@ cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream) {
         e = launch_generic<float>(d, stream);
     }
     if (e != cudaSuccess) return e;
+    if (tma_ok && d.fuse_merge) {   // merge is fused into the kernel
+        count_launches(1);
+        return cudaSuccess;
+    }
     count_launches(2);
     dim3 rgrid((unsigned)d.n_q_heads, (unsigned)d.n_seqs);
     const int threads = d.pool.head_dim >= 128 ? 128 : 64;

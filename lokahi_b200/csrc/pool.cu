@@ -106,6 +106,7 @@ struct skv_pool {
     int32_t* d_page_table = nullptr;
     int32_t* d_lengths = nullptr;
     int32_t* d_status = nullptr;
+    int32_t* d_tickets = nullptr;        // [max_seqs][num_kv_heads], zero between decode calls
     float* d_inv_freq = nullptr;
     // K and V pools as 2-D bf16 tensors [layers*pages*heads*page_size][head_dim] with [16][64] boxes
     alignas(64) CUtensorMap k_map;
@@ -353,6 +354,8 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
         CUDA_TRY(p, cudaMemset(p->d_lengths, 0, p->lengths.size() * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_status, sizeof(int32_t)));
         CUDA_TRY(p, cudaMemset(p->d_status, 0, sizeof(int32_t)));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_tickets, (size_t)cfg->max_seqs * cfg->num_kv_heads * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMemset(p->d_tickets, 0, (size_t)cfg->max_seqs * cfg->num_kv_heads * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_inv_freq, (size_t)cfg->head_dim / 2 * sizeof(float)));
         CUDA_TRY(p, p->ring.init());
         CUDA_TRY(p, cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
@@ -392,6 +395,7 @@ int32_t skv_destroy(skv_pool* p) {
         cudaFree(p->d_page_table);
         cudaFree(p->d_lengths);
         cudaFree(p->d_status);
+        cudaFree(p->d_tickets);
         cudaFree(p->d_inv_freq);
     }
     delete p;
@@ -784,6 +788,7 @@ int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32
     d->force_generic = 0;
     d->k_map = p->has_maps ? &p->k_map : nullptr;
     d->v_map = p->has_maps ? &p->v_map : nullptr;
+    d->tickets = p->d_tickets;
     *launchable = 1;
     return SKV_OK;
 }
@@ -844,6 +849,7 @@ int32_t skv_decode_attn(skv_pool* p, int32_t layer, const int32_t* seq_ids, int3
     D.force_generic = (force && force[0] == '1') ? 1 : 0;
     D.k_map = p->has_maps ? &p->k_map : nullptr;
     D.v_map = p->has_maps ? &p->v_map : nullptr;
+    D.tickets = p->d_tickets;
     CUDA_TRY(p, launch_decode(D, stream));
     return SKV_OK;
 }
@@ -1032,6 +1038,8 @@ int32_t skv_check_device_status(skv_pool* p, void* stream_, int32_t* flag_out) {
     if (flag_out) *flag_out = flag;
     if (flag != 0) {
         CUDA_TRY(p, cudaMemsetAsync(p->d_status, 0, sizeof flag, stream));
+        // a kernel that gave up may have left arrival counters behind
+        CUDA_TRY(p, cudaMemsetAsync(p->d_tickets, 0, (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads * sizeof(int32_t), stream));
         return p->fail(SKV_ERR_DEVICE_FLAG, "device status word 0x%x (1 bad page id, 2 bad length, 4 bad sequence id)", flag);
     }
     return SKV_OK;

@@ -79,6 +79,10 @@ struct DecodeLaunch {
     // [16][64] boxes; nullptr when the pool has none, and then the direct-load kernel runs
     const void* k_map;
     const void* v_map;
+    // [n_seqs][kv_heads] arrival counters, zero between calls: the CTA that finishes last for a
+    // (sequence, KV head) merges the partials itself, so no separate merge launch is needed
+    int32_t* tickets;
+    int32_t fuse_merge;          // 0: leave the merge to decode_reduce_kernel (kept for A/B measurements)
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
 // chunk length (tokens handled by one CTA) and the number of splits that follow from it
