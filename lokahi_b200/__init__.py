@@ -4,6 +4,7 @@ surface of the Strata / ``ollm`` runtime.  Importing the package needs the built
 from ._lib import DeviceFlagError, NotResidentError, OutOfPagesError
 from .attention import PagedView, chunked_grouped_attention, chunked_grouped_attention_no_mask
 from .backend import B200Backend, BackendError, register
+from .decoder import PagedDecoder
 from .generation import greedy_generate
 from .kvcache import PagedKVCache, PagedLlamaDiskCache, create_paged_kv_cache
 from .pool import PagedKVConfig, PagedPool, rope_inv_freq, rope_rows
@@ -12,7 +13,7 @@ register()
 
 __all__ = [
     "B200Backend", "BackendError", "DeviceFlagError", "NotResidentError", "OutOfPagesError", "PagedKVCache",
-    "PagedKVConfig", "PagedLlamaDiskCache", "PagedPool", "PagedView", "chunked_grouped_attention",
+    "PagedDecoder", "PagedKVConfig", "PagedLlamaDiskCache", "PagedPool", "PagedView", "chunked_grouped_attention",
     "chunked_grouped_attention_no_mask", "create_paged_kv_cache", "greedy_generate", "register",
     "rope_inv_freq", "rope_rows",
 ]

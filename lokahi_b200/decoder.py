@@ -1,0 +1,141 @@
+"""Llama / DeepSeek-style decoder around the B200 hot path.
+
+The linear layers, RMSNorm and the SiLU-gate MLP are plain torch ops (cuBLAS): they are the callers
+of the hot path, not part of it.  What matters here is the call sequence around the cache, which
+follows the reference exactly (MLXLlamaAttention.__call__, src/ollm/llama_mlx.py:220-342;
+MLXLlamaModel.__call__, :740-833; MLXLlamaForCausalLM.__call__, :863-912; DeepSeek twin
+src/ollm/deepseek_mlx.py:72-169, 426-549):
+
+    past = cache.get_seq_length(); cache_position = arange(past, past + L); position_ids = [1, L]
+    q, k, v = projections -> [B, H, L, D]
+    RoPE(q, k) -> cache.update(k, v, layer, {"cache_position"}) -> attention(q, K, V,
+        query_positions=position_ids, causal=True, q_block_size=32768,
+        k_block_size=1024 if L > 128 else 1000000) -> o_proj
+
+With ``fused_rope=True`` (default) RoPE and the append are one launch (``update_with_rope``); with
+``False`` RoPE runs first and ``cache.update`` receives rotated K, as in the reference.
+``use_cache=False`` never touches the cache (llama_mlx.py:762).
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+from .attention import chunked_grouped_attention
+from .generation import greedy_generate
+from .pool import rope_inv_freq, rope_rows
+
+
+def rope_scaling_factor(config: Any) -> float:
+    """Linear position scaling factor of a config (1.0 when absent).  The reference reads only
+    ``rope_theta`` (llama_mlx.py:698-702); the factor follows the Hugging Face "linear" convention."""
+    f = getattr(config, "rope_scaling_factor", None)
+    if f:
+        return float(f)
+    rs = getattr(config, "rope_scaling", None)
+    if isinstance(rs, dict) and rs.get("type", rs.get("rope_type")) == "linear":
+        return float(rs.get("factor", 1.0))
+    return 1.0
+
+
+class PagedDecoder:
+    def __init__(self, config: Any, weights: Dict[str, torch.Tensor], *, tracer: Optional[Any] = None,
+                 fused_rope: bool = True):
+        self.config = config
+        self.w = weights
+        self.tracer = tracer
+        self.fused_rope = fused_rope
+        self.H = config.hidden_size
+        self.Hq = config.num_attention_heads
+        # deepseek_mlx.py:235: KV heads default to the attention-head count (MHA)
+        self.Hkv = getattr(config, "num_key_value_heads", None) or self.Hq
+        self.D = self.H // self.Hq
+        self.eps = getattr(config, "rms_norm_eps", 1e-6)
+        self.theta = float(getattr(config, "rope_theta", 10000.0))
+        self.rope_scale = rope_scaling_factor(config)
+        any_w = next(iter(weights.values()))
+        self.device, self.dtype = any_w.device, any_w.dtype
+        if not any_w.is_cuda:
+            raise RuntimeError("PagedDecoder needs CUDA weights; there is no CPU path")
+        self.inv_freq_np = rope_inv_freq(self.D, self.theta)
+        self.inv_freq = torch.from_numpy(self.inv_freq_np).to(self.device)
+
+    # -- glue (llama_mlx.py:53-92, 345-408) ------------------------------------------------------------
+    def _rms_norm(self, x, weight):
+        x32 = x.float()
+        var = x32.pow(2).mean(-1, keepdim=True)
+        return (weight.float() * (x32 * torch.rsqrt(var + self.eps))).to(x.dtype)
+
+    def _mlp(self, x, b):
+        gate = F.linear(x, self.w[f"{b}.mlp.gate_proj.weight"])
+        up = F.linear(x, self.w[f"{b}.mlp.up_proj.weight"])
+        return F.linear(F.silu(gate) * up, self.w[f"{b}.mlp.down_proj.weight"])
+
+    def _rope_inplace(self, x: torch.Tensor, positions: torch.Tensor):
+        """x [B, H, L, D] contiguous, one position per token shared by the batch (llama_mlx.py:777)."""
+        B, H, L, D = x.shape
+        view = x.view(B * H, L, D).transpose(0, 1)          # [L, B*H, D] with strides (D, L*D, 1)
+        rope_rows(view, positions, self.inv_freq, self.rope_scale, out=view)
+        return x
+
+    # -- attention layer (llama_mlx.py:220-342) -----------------------------------------------------------
+    def _attention(self, layer, hidden, position_ids, cache, cache_position):
+        B, L, _ = hidden.shape
+        b = f"model.layers.{layer}.self_attn"
+        past_length = cache.get_seq_length(layer) if cache is not None else 0
+        phase = "decode" if past_length > 0 else ("prefill" if cache is not None else "forward")
+        started = time.perf_counter()
+        q = F.linear(hidden, self.w[f"{b}.q_proj.weight"]).view(B, L, self.Hq, self.D).transpose(1, 2).contiguous()
+        k = F.linear(hidden, self.w[f"{b}.k_proj.weight"]).view(B, L, self.Hkv, self.D).transpose(1, 2).contiguous()
+        v = F.linear(hidden, self.w[f"{b}.v_proj.weight"]).view(B, L, self.Hkv, self.D).transpose(1, 2).contiguous()
+        kwargs = {"cache_position": cache_position}
+        if cache is not None and self.fused_rope and hasattr(cache, "update_with_rope"):
+            k_hist, v_hist = cache.update_with_rope(q, k, v, layer, kwargs, inv_freq=self.inv_freq_np,
+                                                    scaling_factor=self.rope_scale)
+        else:
+            pos_dev = torch.as_tensor(cache_position, dtype=torch.int32, device=self.device)
+            self._rope_inplace(q, pos_dev)
+            self._rope_inplace(k, pos_dev)
+            k_hist, v_hist = (k, v) if cache is None else cache.update(k, v, layer, kwargs)
+        out = chunked_grouped_attention(q, k_hist, v_hist, query_positions=position_ids, causal=True,
+                                        q_block_size=32768, k_block_size=(1024 if L > 128 else 1000000))
+        out = out.transpose(1, 2).reshape(B, L, -1)
+        out = F.linear(out, self.w[f"{b}.o_proj.weight"])
+        if self.tracer is not None:
+            torch.cuda.synchronize(self.device)
+            self.tracer.record_tensor("query", q, phase=phase, layer=layer)
+            self.tracer.record_tensor("attention_output", out, phase=phase, layer=layer)
+            self.tracer.record_operation("attention", (time.perf_counter() - started) * 1000.0, phase=phase, layer=layer,
+                                         active_memory_bytes=torch.cuda.memory_allocated(self.device),
+                                         peak_memory_bytes=torch.cuda.max_memory_allocated(self.device))
+        return out
+
+    # -- model (llama_mlx.py:740-833, 863-912) ---------------------------------------------------------------
+    def __call__(self, input_ids: torch.Tensor, past_key_values: Optional[Any] = None, use_cache: bool = False) -> torch.Tensor:
+        input_ids = input_ids.to(self.device)
+        B, L = input_ids.shape
+        hidden = self.w["model.embed_tokens.weight"][input_ids]
+        cache = past_key_values if use_cache else None
+        past = cache.get_seq_length() if cache is not None else 0
+        cache_position = list(range(past, past + L))            # host values: no device sync to validate them
+        position_ids = torch.tensor([cache_position], dtype=torch.int32)
+        for i in range(self.config.num_hidden_layers):
+            b = f"model.layers.{i}"
+            x = self._rms_norm(hidden, self.w[f"{b}.input_layernorm.weight"])
+            hidden = hidden + self._attention(i, x, position_ids, cache, cache_position)
+            x = self._rms_norm(hidden, self.w[f"{b}.post_attention_layernorm.weight"])
+            hidden = hidden + self._mlp(x, b)
+        hidden = self._rms_norm(hidden, self.w["model.norm.weight"])
+        head = self.w.get("lm_head.weight")
+        if head is None:                                          # tied-embedding fallback (llama_mlx.py:886-890)
+            head = self.w["model.embed_tokens.weight"]
+        return F.linear(hidden, head)
+
+    def generate(self, input_ids, max_new_tokens: int = 100, temperature: float = 1.0, top_p: float = 1.0,
+                 past_key_values: Optional[Any] = None):
+        del top_p   # greedy, as in the reference (llama_mlx.py:934)
+        return greedy_generate(self, input_ids, max_new_tokens=max_new_tokens, temperature=temperature,
+                               past_key_values=past_key_values)

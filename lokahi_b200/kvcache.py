@@ -100,8 +100,7 @@ class PagedKVCache:
             self.batch_size = B
 
     # -- update (mlx_kvcache.py:65-125) ----------------------------------------------------------------------
-    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
-               cache_kwargs: Optional[Dict[str, Any]] = None) -> Tuple[PagedView, PagedView]:
+    def _prepare_update(self, key_states, value_states, layer_idx, cache_kwargs) -> int:
         self._validate_layer_index(layer_idx)
         self._validate_state_shapes(key_states, value_states)
         if not isinstance(key_states, torch.Tensor) or not key_states.is_cuda:
@@ -114,13 +113,36 @@ class PagedKVCache:
         c = self.pool.cfg
         if (key_states.shape[0], key_states.shape[1], key_states.shape[3]) != (self.batch_size, c.num_kv_heads, c.head_dim):
             raise ValueError("new key states must match cached batch, head, and feature dimensions")
+        return previous
+
+    def _finish_update(self, layer_idx: int, previous: int, n_new: int):
+        self._resident.add(layer_idx)
+        self._layer_lengths[layer_idx] = previous + n_new
+        self._seen_tokens = max(self._layer_lengths.values(), default=0)
+        return PagedView(self, layer_idx, "key"), PagedView(self, layer_idx, "value")
+
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
+               cache_kwargs: Optional[Dict[str, Any]] = None) -> Tuple[PagedView, PagedView]:
+        previous = self._prepare_update(key_states, value_states, layer_idx, cache_kwargs)
         if key_states.shape[2] > 0:
             self.pool.append(layer_idx, key_states, value_states, seq_ids=self.seq_ids,
                              start_pos=[previous] * self.batch_size)
-        self._resident.add(layer_idx)
-        self._layer_lengths[layer_idx] = previous + key_states.shape[2]
-        self._seen_tokens = max(self._layer_lengths.values(), default=0)
-        return PagedView(self, layer_idx, "key"), PagedView(self, layer_idx, "value")
+        return self._finish_update(layer_idx, previous, key_states.shape[2])
+
+    def update_with_rope(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                         layer_idx: int, cache_kwargs: Optional[Dict[str, Any]] = None, *, inv_freq: np.ndarray,
+                         scaling_factor: float = 1.0) -> Tuple[PagedView, PagedView]:
+        """``update`` for un-rotated K: RoPE is applied on the way into the pages, and ``query_states``
+        is rotated in place by the same launch (apply_rotary_pos_emb_mlx + update, llama_mlx.py:284-297)."""
+        previous = self._prepare_update(key_states, value_states, layer_idx, cache_kwargs)
+        rope_key = (inv_freq.tobytes(), float(scaling_factor))
+        if getattr(self, "_rope_key", None) != rope_key:
+            self.pool.set_rope(inv_freq, scaling_factor)
+            self._rope_key = rope_key
+        if key_states.shape[2] > 0:
+            self.pool.append(layer_idx, key_states, value_states, seq_ids=self.seq_ids,
+                             start_pos=[previous] * self.batch_size, rope_k=True, q=query_states)
+        return self._finish_update(layer_idx, previous, key_states.shape[2])
 
     # -- lengths (mlx_kvcache.py:160-181) ----------------------------------------------------------------------
     def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:

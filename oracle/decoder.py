@@ -83,7 +83,7 @@ def random_weights(config, seed: int, std: float = 0.02) -> Dict[str, np.ndarray
 class DecoderOracle:
     """Float32 decoder forward with the reference's call sequence around the cache."""
 
-    def __init__(self, config, weights: Dict[str, np.ndarray], round_dtype=None):
+    def __init__(self, config, weights: Dict[str, np.ndarray], round_dtype=None, round_glue: bool = False):
         self.config = config
         self.w = weights
         self.H = config.hidden_size
@@ -98,6 +98,19 @@ class DecoderOracle:
         # storage dtype (e.g. ml_dtypes.bfloat16) at the points where the CUDA
         # path stores that dtype.
         self.round_dtype = round_dtype
+        # round_glue additionally rounds after every linear layer, norm, activation product and residual
+        # add, which is where a decoder whose glue runs in that storage dtype (cuBLAS, fp32 accumulate,
+        # one rounding per output) rounds.
+        self.round_glue = round_glue and round_dtype is not None
+
+    def _g(self, x):
+        return self._round(x) if self.round_glue else x
+
+    def _mlp(self, x, b):
+        gate = self._g(linear(x, self.w[f"{b}.mlp.gate_proj.weight"]))
+        up = self._g(linear(x, self.w[f"{b}.mlp.up_proj.weight"]))
+        act = self._g(self._g(silu(gate)) * up)
+        return self._g(linear(act, self.w[f"{b}.mlp.down_proj.weight"]))
 
     def _round(self, x):
         if self.round_dtype is None:
@@ -107,9 +120,9 @@ class DecoderOracle:
     def attention(self, layer, hidden, cos, sin, position_ids, cache, cache_position):
         B, L, _ = hidden.shape
         b = f"model.layers.{layer}.self_attn"
-        q = linear(hidden, self.w[f"{b}.q_proj.weight"]).reshape(B, L, self.Hq, self.D).transpose(0, 2, 1, 3)
-        k = linear(hidden, self.w[f"{b}.k_proj.weight"]).reshape(B, L, self.Hkv, self.D).transpose(0, 2, 1, 3)
-        v = linear(hidden, self.w[f"{b}.v_proj.weight"]).reshape(B, L, self.Hkv, self.D).transpose(0, 2, 1, 3)
+        q = self._g(linear(hidden, self.w[f"{b}.q_proj.weight"])).reshape(B, L, self.Hq, self.D).transpose(0, 2, 1, 3)
+        k = self._g(linear(hidden, self.w[f"{b}.k_proj.weight"])).reshape(B, L, self.Hkv, self.D).transpose(0, 2, 1, 3)
+        v = self._g(linear(hidden, self.w[f"{b}.v_proj.weight"])).reshape(B, L, self.Hkv, self.D).transpose(0, 2, 1, 3)
         q, k = _rope.apply_qk(self._round(q), self._round(k), cos, sin)
         q, k, v = self._round(q), self._round(k), self._round(v)
         if cache is not None:
@@ -119,7 +132,7 @@ class DecoderOracle:
             k_block_size=(1024 if L > 128 else 1000000),
         )
         o = self._round(o).transpose(0, 2, 1, 3).reshape(B, L, -1)
-        return linear(o, self.w[f"{b}.o_proj.weight"])
+        return self._g(linear(o, self.w[f"{b}.o_proj.weight"]))
 
     def forward(self, input_ids, past_key_values: Optional[ConcatKVCache] = None, use_cache: bool = False):
         input_ids = np.asarray(input_ids)
@@ -132,16 +145,15 @@ class DecoderOracle:
         cos, sin = _rope.cos_sin(position_ids, self.D, self.theta, self.rope_scale)
         for i in range(self.config.num_hidden_layers):
             b = f"model.layers.{i}"
-            x = rms_norm(hidden, self.w[f"{b}.input_layernorm.weight"], self.eps)
-            hidden = hidden + self.attention(i, x, cos, sin, position_ids, cache, cache_position)
-            x = rms_norm(hidden, self.w[f"{b}.post_attention_layernorm.weight"], self.eps)
-            hidden = hidden + mlp(x, self.w[f"{b}.mlp.gate_proj.weight"],
-                                  self.w[f"{b}.mlp.up_proj.weight"], self.w[f"{b}.mlp.down_proj.weight"])
-        hidden = rms_norm(hidden, self.w["model.norm.weight"], self.eps)
+            x = self._g(rms_norm(hidden, self.w[f"{b}.input_layernorm.weight"], self.eps))
+            hidden = self._g(hidden + self.attention(i, x, cos, sin, position_ids, cache, cache_position))
+            x = self._g(rms_norm(hidden, self.w[f"{b}.post_attention_layernorm.weight"], self.eps))
+            hidden = self._g(hidden + self._mlp(x, b))
+        hidden = self._g(rms_norm(hidden, self.w["model.norm.weight"], self.eps))
         head = self.w.get("lm_head.weight")
         if head is None:  # tied-embedding fallback, llama_mlx.py:886-890
             head = self.w["model.embed_tokens.weight"]
-        return linear(hidden, head)
+        return self._g(linear(hidden, head))
 
     __call__ = forward
 

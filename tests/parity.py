@@ -43,3 +43,17 @@ def bf16_round(a):
     """Round a float32 array to bfloat16 and back (ml_dtypes)."""
     import ml_dtypes
     return np.asarray(a, dtype=np.float32).astype(ml_dtypes.bfloat16).astype(np.float32)
+
+
+def assert_parity_logits(x, ref, tol, what="", max_outlier_fraction=0.01):
+    """Model-level variant for logits produced through bf16 GEMM glue (cuBLAS rounds every layer output
+    to bf16, so single elements move by one or two bf16 steps of an O(1) logit, i.e. up to a few per cent
+    of the rms): the normalised max error must hold, and all but `max_outlier_fraction` of the elements
+    must satisfy the allclose criterion."""
+    xn, rn = to_np(x).astype(np.float64), to_np(ref).astype(np.float64)
+    assert xn.shape == rn.shape and np.isfinite(xn).all(), what
+    err, rms = parity_errors(xn, rn)
+    assert err <= tol, f"{what}: normalised max error {err:.3e} > {tol}"
+    bad = np.abs(xn - rn) > tol * rms + tol * np.abs(rn)
+    assert bad.mean() <= max_outlier_fraction, f"{what}: {bad.mean():.4f} of the elements outside allclose"
+    return err
