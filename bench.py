@@ -260,6 +260,80 @@ def run_ours(args):
     return result
 
 
+def run_prefill(args):
+    """Secondary workload "chunked_gqa_prefill_4096": the stand-alone chunked causal GQA op, bf16, batch 1,
+    32 query heads, 8 KV heads, head_dim 128, sequence 4096, absolute positions 0..4095 (tensor-core bound).
+    One step = one attention call; L2 (126 MB) is flushed between timed calls because q, k, v and out
+    together are 84 MB."""
+    import torch
+
+    import lokahi_b200 as L
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, S = 1, 4096
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    q = torch.randn((B, HQ, S, D), generator=gen, device=dev).to(torch.bfloat16)
+    k = torch.randn((B, HKV, S, D), generator=gen, device=dev).to(torch.bfloat16)
+    v = torch.randn((B, HKV, S, D), generator=gen, device=dev).to(torch.bfloat16)
+    pos = np.arange(S, dtype=np.int32)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    K, W = args.steps, args.warmup
+    for _ in range(W):
+        L.chunked_grouped_attention(q, k, v, query_positions=pos, causal=True, q_block_size=512, k_block_size=512)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    l0 = L._lib.lib.skv_launch_count()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for a, b in evs:
+        flush.zero_()
+        a.record()
+        L.chunked_grouped_attention(q, k, v, query_positions=pos, causal=True, q_block_size=512, k_block_size=512)
+        b.record()
+    torch.cuda.synchronize()
+    launches = L._lib.lib.skv_launch_count() - l0
+    clocks = sampler.stop()
+    ms = np.array([a.elapsed_time(b) for a, b in evs])
+    # end to end: pinned host q, k, v in, out back, every step
+    qh, kh, vh = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
+    oh = torch.empty_like(qh).pin_memory()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    Ke = max(3, min(K, 20))
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(Ke):
+        q.copy_(qh, non_blocking=True); k.copy_(kh, non_blocking=True); v.copy_(vh, non_blocking=True)
+        o = L.chunked_grouped_attention(q, k, v, query_positions=pos, causal=True, q_block_size=512, k_block_size=512)
+        oh.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / Ke
+    flops = 4.0 * HQ * D * (S * (S + 1) / 2)            # causal-useful flops (dense-equivalent is 2x)
+    peak = 1590.0
+    kind = "fallback"
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak, kind = float(json.load(f)["bf16_tflops"]), "measured"
+    achieved = flops / (ms.mean() * 1e-3) / 1e12
+    return {
+        "metric": "chunked causal GQA prefill tokens/s", "value": B * S / (ms.mean() * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": K, "warmup": W, "ms_per_step": float(ms.mean()), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "chunked_gqa_prefill_4096", "batch": B, "q_heads": HQ, "kv_heads": HKV, "head_dim": D,
+                   "seq_len": S, "q_chunk": 512, "k_chunk": 512, "l2": "flushed between timed calls (256 MB write)"},
+        "e2e": {"value": B * S / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": int(q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": int(q.numel()) * 2},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "peak_kind": f"of {kind} (burst)", "flops_per_launch": flops, "flops_counted": "causal-useful 4*Hq*D*S(S+1)/2",
+                     "launch_ms": float(ms.mean()), "launch_ms_min": float(ms.min()), "traffic": None},
+        "clocks": clocks,
+    }
+
+
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per decode launch: measured on the 16-sequence capture
 # case (295.49 MB of traffic for 287.07 MB algorithmic, profiles/decode_tma_kernel_paged_decode_16seq.md)
 # and scaled to this workload by the algorithmic bytes, which is what the traffic grows with.
@@ -397,13 +471,20 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+                    help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")
     ap.add_argument("--seqs", type=int, default=N_SEQS,
                     help="number of sequences (default: the workload's 64; smaller values are for profiler captures)")
     args = ap.parse_args()
     N_SEQS = args.seqs
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        result = run_reference(args)
+    elif args.workload == "prefill":
+        result = run_prefill(args)
+    else:
+        result = run_ours(args)
     if result is not None:
         print(json.dumps(result), flush=True)
 

@@ -1,12 +1,374 @@
-// K4: causal chunked-prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM, TMA-fed).
+// K4: causal chunked-prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
+//
+// Mathematics: online_chunked_grouped_attention_mx (src/ollm/backends/mlx_ops.py:32-152) for bf16
+// tensors with head_dim 128: scores = q.k * D^-0.5, key t allowed for a query row iff t <= q_pos[row]
+// (:107-112), online softmax across key tiles with the (max, sum, weighted V) merge of :125-144, and
+// out = wv / max(s, eps) so that a row with no allowed key is exactly 0 (:118, :146).
+//
+// One CTA = 128 query rows of one query head (4 warps; thread r owns query row r, which is TMEM lane r).
+// Per 64-key tile:
+//   TMA   K tile and V tile -> shared memory (3-D tensor maps [batch*head][token][dim], 128-byte swizzle,
+//         rows past the end of a head are zero-filled by the copy engine);
+//   MMA 1 S[128x64]  = Q[128x128] . K^T        tcgen05.mma kind::f16, both operands K-major from smem,
+//                                              accumulator in TMEM columns [0, 64);
+//   soft  tcgen05.ld S -> registers, scale, mask by the row's absolute position, running max / sum,
+//         P = exp2(...) rounded to bf16 and written to shared memory in the swizzled K-major layout;
+//   MMA 2 O_tile[128x128] = P[128x64] . V[64x128]   V is the MN-major B operand straight from the TMA box,
+//                                              accumulator in TMEM columns [64, 192);
+//   acc   tcgen05.ld O_tile and o = o * alpha + O_tile in registers (no TMEM read-modify-write).
+// Two CTAs fit on an SM (80 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the
+// other's MMAs.  One elected thread issues TMA and MMA; completion travels through mbarriers
+// (tcgen05.commit), every wait is bounded, and on a timeout the CTA records FLAG_WAIT_TIMEOUT in the
+// caller's status word (when given), stops issuing work, frees its TMEM and returns.
+// No cluster launch and no multicast anywhere.
+#include <cstdlib>
+
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace skv {
 
+namespace {
+
+constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBN = 64;           // keys per tile
+constexpr int kD = 128;           // head_dim
+constexpr int kThreads = 128;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0;     // S accumulator: 64 fp32 columns
+constexpr uint32_t kColO = 64;    // O_tile accumulator: 128 fp32 columns
+constexpr float kLog2eF = 1.4426950408889634f;
+
+// shared memory map (offsets from a 1024-byte aligned base)
+constexpr int kOffQ = 0;                       // 2 boxes [128 rows][64 dims]   = 32 KB
+constexpr int kOffK = kOffQ + 2 * kBM * 128;   // 2 boxes [64 keys][64 dims]    = 16 KB
+constexpr int kOffV = kOffK + 2 * kBN * 128;   // 2 boxes [64 keys][64 dims]    = 16 KB
+constexpr int kOffP = kOffV + 2 * kBN * 128;   // [128 rows][64 keys] bf16      = 16 KB
+constexpr int kOffBar = kOffP + kBM * 128;     // mbarriers + TMEM base + flags
+constexpr int kSmemBytes = kOffBar + 128 + 1024;
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] . B[smem]; issued by one thread.
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (descriptor version 1).
+//   K-major operand  (rows of 128 bytes, 8-row groups 1024 bytes apart):  lbo = 16 (unused), sbo = 1024
+//   MN-major operand (64-element groups `lbo` bytes apart along MN, 8-row k-groups `sbo` bytes apart)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;   // version
+    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, M = 128, given N, A K-major, B K-major or MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
+struct TcParams {
+    const int32_t* positions;   // device [B][Lq] or nullptr
+    void* out;
+    int32_t* status;            // device status word or nullptr
+    int32_t B, Hq, Hkv, Lq, Lk, causal;
+    float eps;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                  const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + kOffBar);
+    uint64_t* bar_k = bar_q + 1;
+    uint64_t* bar_v = bar_q + 2;
+    uint64_t* bar_s = bar_q + 3;
+    uint64_t* bar_o = bar_q + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 5);
+    int32_t* sh_limit = reinterpret_cast<int32_t*>(bar_q + 6);   // max over the tile's rows of the allowed-key count
+    int32_t* sh_abort = sh_limit + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    // heavy (late) query tiles first so that the causal triangle balances across SMs
+    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int hq = blockIdx.y, b = blockIdx.z;
+    const int G = p.Hq / p.Hkv;
+    const int hkv = hq / G;
+    const int row = q_tile * kBM + tid;
+
+    // number of keys this row may attend: keys 0 .. min(Lk, q_pos + 1)
+    int limit = 0;
+    if (row < p.Lq) {
+        limit = p.Lk;
+        if (p.causal) {
+            const int qpos = p.positions ? p.positions[(int64_t)b * p.Lq + row] : (p.Lk - p.Lq + row);
+            const int lim = qpos < 0 ? 0 : qpos + 1;
+            limit = lim < p.Lk ? lim : p.Lk;
+        }
+    }
+    if (tid == 0) {
+        *sh_limit = 0;
+        *sh_abort = 0;
+        mbar_init(bar_q, 1);
+        mbar_init(bar_k, 1);
+        mbar_init(bar_v, 1);
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    atomicMax(sh_limit, limit);
+    __syncthreads();
+    const uint32_t tmem_base = *tmem_slot;
+    const int n_tiles = (*sh_limit + kBN - 1) / kBN;
+
+    if (tid == 0 && n_tiles > 0) {
+        mbar_expect_tx(bar_q, 2 * kBM * 128);
+        tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, b * p.Hq + hq, bar_q);
+        tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, b * p.Hq + hq, bar_q);
+        mbar_expect_tx(bar_k, 2 * kBN * 128);
+        tma_load_3d(smem + kOffK, &kmap, 0, 0, b * p.Hkv + hkv, bar_k);
+        tma_load_3d(smem + kOffK + kBN * 128, &kmap, 64, 0, b * p.Hkv + hkv, bar_k);
+        mbar_expect_tx(bar_v, 2 * kBN * 128);
+        tma_load_3d(smem + kOffV, &vmap, 0, 0, b * p.Hkv + hkv, bar_v);
+        tma_load_3d(smem + kOffV + kBN * 128, &vmap, 64, 0, b * p.Hkv + hkv, bar_v);
+    }
+
+    float o[kD];
+#pragma unroll
+    for (int i = 0; i < kD; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const float sc = rsqrtf((float)kD) * kLog2eF;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t q_addr = smem_u32(smem + kOffQ), k_addr = smem_u32(smem + kOffK);
+    const uint32_t v_addr = smem_u32(smem + kOffV), p_addr = smem_u32(smem + kOffP);
+    constexpr uint32_t kIdescS = instr_desc(kBN, 0);
+    constexpr uint32_t kIdescO = instr_desc(kD, 1);
+    bool ok = true;
+
+    for (int j = 0; j < n_tiles; ++j) {
+        const uint32_t ph = (uint32_t)(j & 1);
+        // ---- MMA 1: S = Q K^T ------------------------------------------------------------------
+        if (tid == 0) {
+            if (j == 0) ok = mbar_wait(bar_q, 0);
+            ok = ok && mbar_wait(bar_k, ph);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint32_t off = (uint32_t)(ks >> 2) , in = (uint32_t)(ks & 3) * 32;
+                    umma_ss(tmem_base + kColS, smem_desc(q_addr + off * (kBM * 128) + in, 16, 1024),
+                            smem_desc(k_addr + off * (kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(bar_s);
+            } else {
+                *sh_abort = 1;
+                mbar_arrive(bar_s);   // release the waiters; they see the abort flag after the next barrier
+            }
+        }
+        ok = mbar_wait(bar_s, ph) && ok;
+        tc_fence_after();
+        // K buffer is free again: fetch the next K tile while the softmax runs
+        if (tid == 0 && ok && j + 1 < n_tiles) {
+            mbar_expect_tx(bar_k, 2 * kBN * 128);
+            tma_load_3d(smem + kOffK, &kmap, 0, (j + 1) * kBN, b * p.Hkv + hkv, bar_k);
+            tma_load_3d(smem + kOffK + kBN * 128, &kmap, 64, (j + 1) * kBN, b * p.Hkv + hkv, bar_k);
+        }
+        // ---- softmax on this thread's row ---------------------------------------------------------
+        float s[kBN];
+        tmem_ld32(lane_addr + kColS, s);
+        tmem_ld32(lane_addr + kColS + 32, s + 32);
+        tc_wait_ld();
+        const int t0 = j * kBN;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < kBN; ++t) {
+            s[t] = (t0 + t < limit) ? s[t] * sc : -INFINITY;
+            mx = fmaxf(mx, s[t]);
+        }
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // row with no allowed key so far: everything stays 0
+        const float alpha = exp2f(m_run - m_use);
+        float rs = 0.f;
+        uint32_t pk[kBN / 2];
+#pragma unroll
+        for (int t = 0; t < kBN; t += 2) {
+            const float p0 = exp2f(s[t] - m_use), p1 = exp2f(s[t + 1] - m_use);
+            rs += p0 + p1;
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+            pk[t >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+        }
+        l_run = l_run * alpha + rs;
+        m_run = m_new;
+        // P row -> shared memory, K-major with the 128-byte swizzle the MMA descriptor expects
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t dst = p_addr + (uint32_t)tid * 128 + (((uint32_t)u ^ ((uint32_t)tid & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
+                         "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3])
+                         : "memory");
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        if (*sh_abort) {
+            ok = false;
+            break;
+        }
+        // ---- MMA 2: O_tile = P V ---------------------------------------------------------------------
+        if (tid == 0) {
+            ok = mbar_wait(bar_v, ph);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kBN / 16; ++ks)
+                    umma_ss(tmem_base + kColO, smem_desc(p_addr + (uint32_t)ks * 32, 16, 1024),
+                            smem_desc(v_addr + (uint32_t)ks * 2048, kBN * 128, 1024), kIdescO, ks > 0 ? 1u : 0u);
+                umma_commit(bar_o);
+            } else {
+                *sh_abort = 1;
+                mbar_arrive(bar_o);
+            }
+        }
+        ok = mbar_wait(bar_o, ph) && ok;
+        tc_fence_after();
+        if (tid == 0 && ok && j + 1 < n_tiles) {
+            mbar_expect_tx(bar_v, 2 * kBN * 128);
+            tma_load_3d(smem + kOffV, &vmap, 0, (j + 1) * kBN, b * p.Hkv + hkv, bar_v);
+            tma_load_3d(smem + kOffV + kBN * 128, &vmap, 64, (j + 1) * kBN, b * p.Hkv + hkv, bar_v);
+        }
+        // ---- o = o * alpha + O_tile --------------------------------------------------------------------
+#pragma unroll
+        for (int cc = 0; cc < kD / 32; ++cc) {
+            float t32[32];
+            tmem_ld32(lane_addr + kColO + cc * 32, t32);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[cc * 32 + i] = fmaf(o[cc * 32 + i], alpha, t32[i]);
+        }
+        tc_fence_before();
+        __syncthreads();
+        if (*sh_abort) {
+            ok = false;
+            break;
+        }
+    }
+    if (!ok && p.status && tid == 0) atomicOr(p.status, FLAG_WAIT_TIMEOUT);
+
+    // ---- epilogue ---------------------------------------------------------------------------------------
+    if (row < p.Lq && ok) {
+        const float inv = 1.0f / fmaxf(l_run, p.eps);
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (((int64_t)b * p.Hq + hq) * p.Lq + row) * kD;
+#pragma unroll
+        for (int u = 0; u < kD / 8; ++u) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * u + 2 * i] * inv, o[8 * u + 2 * i + 1] * inv);
+                w[i] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            *reinterpret_cast<uint4*>(orow + 8 * u) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// [batch*heads][tokens][128] bf16, contiguous; box = [1][box_rows][64], 128-byte swizzle.
+bool encode_heads_3d(CUtensorMap* map, const void* base, uint64_t n_heads, uint64_t tokens, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)kD, tokens, n_heads};
+    cuuint64_t strides[2] = {(cuuint64_t)kD * 2, tokens * (cuuint64_t)kD * 2};
+    cuuint32_t box[3] = {64, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
 cudaError_t launch_attn_tc(const DenseAttnLaunch& a, cudaStream_t stream) {
-    (void)a;
-    (void)stream;
-    return cudaErrorNotSupported;
+    const bool aligned = (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out) & 15) == 0;
+    if (a.pool.k_base != nullptr || a.dtype != SKV_BF16 || a.D != kD || !aligned || a.Lq < 32 || a.Lk < 1)
+        return cudaErrorNotSupported;
+    alignas(64) CUtensorMap qmap, kmap, vmap;
+    if (!encode_heads_3d(&qmap, a.q, (uint64_t)a.B * a.Hq, (uint64_t)a.Lq, kBM) ||
+        !encode_heads_3d(&kmap, a.k, (uint64_t)a.B * a.Hkv, (uint64_t)a.Lk, kBN) ||
+        !encode_heads_3d(&vmap, a.v, (uint64_t)a.B * a.Hkv, (uint64_t)a.Lk, kBN))
+        return cudaErrorNotSupported;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    TcParams p{};
+    p.positions = a.positions;
+    p.out = a.out;
+    p.status = nullptr;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk; p.causal = a.causal;
+    p.eps = a.eps;
+    dim3 grid((unsigned)((a.Lq + kBM - 1) / kBM), (unsigned)a.Hq, (unsigned)a.B);
+    prefill_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p, qmap, kmap, vmap);
+    count_launches(1);
+    return cudaGetLastError();
 }
 
 }  // namespace skv
