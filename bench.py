@@ -119,9 +119,9 @@ def run_ours(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    if HKV % world:
-        raise SystemExit(f"KV-head sharding needs {HKV} % n_gpus == 0")
-    hkv, hq = HKV // world, HQ // world
+    from lokahi_b200.sharding import HeadShard
+    shard = HeadShard(rank, world, HQ, HKV)          # raises when the KV heads do not divide over the ranks
+    hkv, hq = shard.local_kv_heads, shard.local_q_heads
 
     K, W = args.steps, args.warmup
     total_steps = W + K

@@ -1,0 +1,76 @@
+"""KV-head sharding across GPUs (one process per GPU).
+
+The reference is single-device; its attention is independent per KV head (it loops over them,
+src/ollm/backends/mlx_ops.py:81-87, and concatenates on the head axis, :152), so rank r keeps KV heads
+[r * Hkv / N, (r + 1) * Hkv / N) with their query heads and pages, and the only exchange is an all-gather
+of the attention outputs.  K/V never cross GPUs; page tables and lengths are identical on every rank
+because every rank issues the same cache calls.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class HeadShard:
+    rank: int
+    world: int
+    n_q_heads: int
+    n_kv_heads: int
+
+    def __post_init__(self):
+        if self.world <= 0 or not 0 <= self.rank < self.world:
+            raise ValueError("rank must lie in [0, world)")
+        if self.n_kv_heads <= 0 or self.n_q_heads % self.n_kv_heads:
+            raise ValueError("query heads must be divisible by key/value heads")
+        if self.n_kv_heads % self.world:
+            raise ValueError(f"KV-head sharding needs num_kv_heads ({self.n_kv_heads}) divisible by the world size ({self.world})")
+
+    @property
+    def local_kv_heads(self) -> int:
+        return self.n_kv_heads // self.world
+
+    @property
+    def local_q_heads(self) -> int:
+        return self.n_q_heads // self.world
+
+    @property
+    def kv_slice(self) -> slice:
+        return slice(self.rank * self.local_kv_heads, (self.rank + 1) * self.local_kv_heads)
+
+    @property
+    def q_slice(self) -> slice:
+        return slice(self.rank * self.local_q_heads, (self.rank + 1) * self.local_q_heads)
+
+    def take_q(self, x: torch.Tensor, head_dim: int = 1) -> torch.Tensor:
+        """This rank's query heads of a tensor whose `head_dim` axis holds all query heads."""
+        return x.narrow(head_dim, self.q_slice.start, self.local_q_heads)
+
+    def take_kv(self, x: torch.Tensor, head_dim: int = 1) -> torch.Tensor:
+        return x.narrow(head_dim, self.kv_slice.start, self.local_kv_heads)
+
+
+def gather_head_outputs(out_local: torch.Tensor, shard: HeadShard, group: Optional[dist.ProcessGroup] = None,
+                        buffer: Optional[torch.Tensor] = None, head_dim: int = 1) -> torch.Tensor:
+    """All-gather per-rank outputs (`head_dim` axis = local query heads) into the full head axis.
+
+    Query head h lives on rank h // local_q_heads, so concatenating the ranks' slices along the head axis in
+    rank order restores the reference's head order (mlx_ops.py:152).  `buffer` ([world, *out_local.shape])
+    avoids an allocation per step.
+    """
+    if shard.world == 1:
+        return out_local
+    out_local = out_local.contiguous()
+    if buffer is None:
+        buffer = torch.empty((shard.world,) + tuple(out_local.shape), dtype=out_local.dtype, device=out_local.device)
+    # dim-0 concatenation of the ranks' tensors: the one output form every backend (NCCL, gloo) accepts
+    dist.all_gather_into_tensor(buffer.view((-1,) + tuple(out_local.shape[1:])), out_local, group=group)
+    # [world, ..., local_heads, ...] -> [..., world * local_heads, ...]
+    moved = buffer.movedim(0, head_dim)                       # [..., world, local_heads, ...]
+    shape = list(out_local.shape)
+    shape[head_dim] = shard.world * shape[head_dim]
+    return moved.reshape(shape)
