@@ -13,10 +13,13 @@
 //                                              accumulator in TMEM columns [0, 64);
 //   soft  tcgen05.ld S -> registers, scale, mask by the row's absolute position, running max / sum,
 //         P = exp2(...) rounded to bf16 and written to shared memory in the swizzled K-major layout;
-//   MMA 2 O_tile[128x128] = P[128x64] . V[64x128]   V is the MN-major B operand straight from the TMA box,
-//                                              accumulator in TMEM columns [64, 192);
-//   acc   tcgen05.ld O_tile and o = o * alpha + O_tile in registers (no TMEM read-modify-write).
-// Two CTAs fit on an SM (80 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the
+//   MMA 2 O[128x128] += P[128x64] . V[64x128]  V is the MN-major B operand straight from the TMA box
+//                                              (two-stage ring); the accumulator stays in TMEM columns
+//                                              [64, 192) for the whole key loop.
+//   The running maximum that scales P and O is raised only when a tile's maximum exceeds it by more than
+//   8 in the log2 domain; only then is O read, scaled and written back (tcgen05.ld / tcgen05.st).  The
+//   final division by the row sum makes the stale maximum cancel exactly.
+// Two CTAs fit on an SM (96 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the
 // other's MMAs.  One elected thread issues TMA and MMA; completion travels through mbarriers
 // (tcgen05.commit), every wait is bounded, and on a timeout the CTA records FLAG_WAIT_TIMEOUT in the
 // caller's status word (when given), stops issuing work, frees its TMEM and returns.
@@ -42,8 +45,9 @@ constexpr float kLog2eF = 1.4426950408889634f;
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr int kOffQ = 0;                       // 2 boxes [128 rows][64 dims]   = 32 KB
 constexpr int kOffK = kOffQ + 2 * kBM * 128;   // 2 boxes [64 keys][64 dims]    = 16 KB
-constexpr int kOffV = kOffK + 2 * kBN * 128;   // 2 boxes [64 keys][64 dims]    = 16 KB
-constexpr int kOffP = kOffV + 2 * kBN * 128;   // [128 rows][64 keys] bf16      = 16 KB
+constexpr int kOffV = kOffK + 2 * kBN * 128;   // 2 stages x 2 boxes [64 keys][64 dims] = 32 KB
+constexpr int kVStage = 2 * kBN * 128;
+constexpr int kOffP = kOffV + 2 * kVStage;     // [128 rows][64 keys] bf16      = 16 KB
 constexpr int kOffBar = kOffP + kBM * 128;     // mbarriers + TMEM base + flags
 constexpr int kSmemBytes = kOffBar + 128 + 1024;
 
@@ -59,6 +63,12 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // D[tmem] (+)= A[smem] . B[smem]; issued by one thread.
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -86,6 +96,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
 
@@ -126,24 +149,26 @@ struct TcParams {
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                   const __grid_constant__ CUtensorMap vmap) {
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + kOffBar);
     uint64_t* bar_k = bar_q + 1;
-    uint64_t* bar_v = bar_q + 2;
-    uint64_t* bar_s = bar_q + 3;
-    uint64_t* bar_o = bar_q + 4;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 5);
-    int32_t* sh_limit = reinterpret_cast<int32_t*>(bar_q + 6);   // max over the tile's rows of the allowed-key count
+    uint64_t* bar_v = bar_q + 2;       // two stages: bar_v[0], bar_v[1]
+    uint64_t* bar_s = bar_q + 4;
+    uint64_t* bar_o = bar_q + 5;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 6);
+    int32_t* sh_limit = reinterpret_cast<int32_t*>(bar_q + 7);   // max over the tile's rows of the allowed-key count
     int32_t* sh_abort = sh_limit + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5;
     // heavy (late) query tiles first so that the causal triangle balances across SMs
-    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
-    const int hq = blockIdx.y, b = blockIdx.z;
+    // (blocks are dispatched x-fastest: all heads' heaviest tiles start first)
+    const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;
+    const int hq = blockIdx.x, b = blockIdx.z;
     const int G = p.Hq / p.Hkv;
     const int hkv = hq / G;
     const int row = q_tile * kBM + tid;
+    const int zq = b * p.Hq + hq, zkv = b * p.Hkv + hkv;
 
     // number of keys this row may attend: keys 0 .. min(Lk, q_pos + 1)
     int limit = 0;
@@ -160,7 +185,8 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         *sh_abort = 0;
         mbar_init(bar_q, 1);
         mbar_init(bar_k, 1);
-        mbar_init(bar_v, 1);
+        mbar_init(&bar_v[0], 1);
+        mbar_init(&bar_v[1], 1);
         mbar_init(bar_s, 1);
         mbar_init(bar_o, 1);
         fence_mbar_init();
@@ -174,21 +200,28 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     const uint32_t tmem_base = *tmem_slot;
     const int n_tiles = (*sh_limit + kBN - 1) / kBN;
 
+    auto load_k = [&](int j) {
+        mbar_expect_tx(bar_k, 2 * kBN * 128);
+        tma_load_3d(smem + kOffK, &kmap, 0, j * kBN, zkv, bar_k);
+        tma_load_3d(smem + kOffK + kBN * 128, &kmap, 64, j * kBN, zkv, bar_k);
+    };
+    auto load_v = [&](int j) {
+        uint8_t* dst = smem + kOffV + (j & 1) * kVStage;
+        mbar_expect_tx(&bar_v[j & 1], 2 * kBN * 128);
+        tma_load_3d(dst, &vmap, 0, j * kBN, zkv, &bar_v[j & 1]);
+        tma_load_3d(dst + kBN * 128, &vmap, 64, j * kBN, zkv, &bar_v[j & 1]);
+    };
     if (tid == 0 && n_tiles > 0) {
         mbar_expect_tx(bar_q, 2 * kBM * 128);
-        tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, b * p.Hq + hq, bar_q);
-        tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, b * p.Hq + hq, bar_q);
-        mbar_expect_tx(bar_k, 2 * kBN * 128);
-        tma_load_3d(smem + kOffK, &kmap, 0, 0, b * p.Hkv + hkv, bar_k);
-        tma_load_3d(smem + kOffK + kBN * 128, &kmap, 64, 0, b * p.Hkv + hkv, bar_k);
-        mbar_expect_tx(bar_v, 2 * kBN * 128);
-        tma_load_3d(smem + kOffV, &vmap, 0, 0, b * p.Hkv + hkv, bar_v);
-        tma_load_3d(smem + kOffV + kBN * 128, &vmap, 64, 0, b * p.Hkv + hkv, bar_v);
+        tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, zq, bar_q);
+        tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, zq, bar_q);
+        load_k(0);
+        load_v(0);
+        if (n_tiles > 1) load_v(1);
     }
 
-    float o[kD];
-#pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
+    // m_run is the maximum the stored numbers are scaled by.  It is only raised when a tile's maximum exceeds
+    // it by more than 8 (log2 domain), so P stays below 2^8 and the accumulator in TMEM is rescaled rarely.
     float m_run = -INFINITY, l_run = 0.f;
     const float sc = rsqrtf((float)kD) * kLog2eF;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
@@ -208,9 +241,9 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint32_t off = (uint32_t)(ks >> 2) , in = (uint32_t)(ks & 3) * 32;
-                    umma_ss(tmem_base + kColS, smem_desc(q_addr + off * (kBM * 128) + in, 16, 1024),
-                            smem_desc(k_addr + off * (kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u);
+                    const uint32_t blk = (uint32_t)(ks >> 2), in = (uint32_t)(ks & 3) * 32;
+                    umma_ss(tmem_base + kColS, smem_desc(q_addr + blk * (kBM * 128) + in, 16, 1024),
+                            smem_desc(k_addr + blk * (kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar_s);
             } else {
@@ -220,38 +253,62 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         }
         ok = mbar_wait(bar_s, ph) && ok;
         tc_fence_after();
-        // K buffer is free again: fetch the next K tile while the softmax runs
-        if (tid == 0 && ok && j + 1 < n_tiles) {
-            mbar_expect_tx(bar_k, 2 * kBN * 128);
-            tma_load_3d(smem + kOffK, &kmap, 0, (j + 1) * kBN, b * p.Hkv + hkv, bar_k);
-            tma_load_3d(smem + kOffK + kBN * 128, &kmap, 64, (j + 1) * kBN, b * p.Hkv + hkv, bar_k);
-        }
+        if (tid == 0 && ok && j + 1 < n_tiles) load_k(j + 1);   // the K buffer is free again
         // ---- softmax on this thread's row ---------------------------------------------------------
         float s[kBN];
         tmem_ld32(lane_addr + kColS, s);
         tmem_ld32(lane_addr + kColS + 32, s + 32);
         tc_wait_ld();
         const int t0 = j * kBN;
-        float mx = -INFINITY;
+        if (t0 + kBN > limit) {   // only tiles that cross the row's limit pay for the mask
 #pragma unroll
-        for (int t = 0; t < kBN; ++t) {
-            s[t] = (t0 + t < limit) ? s[t] * sc : -INFINITY;
-            mx = fmaxf(mx, s[t]);
+            for (int t = 0; t < kBN; ++t)
+                if (t0 + t >= limit) s[t] = -INFINITY;
         }
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // row with no allowed key so far: everything stays 0
-        const float alpha = exp2f(m_run - m_use);
-        float rs = 0.f;
+        float mx4[4] = {s[0], s[1], s[2], s[3]};   // four independent chains instead of one 64-long one
+#pragma unroll
+        for (int t = 4; t < kBN; t += 4) {
+            mx4[0] = fmaxf(mx4[0], s[t]);
+            mx4[1] = fmaxf(mx4[1], s[t + 1]);
+            mx4[2] = fmaxf(mx4[2], s[t + 2]);
+            mx4[3] = fmaxf(mx4[3], s[t + 3]);
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;   // sc > 0: the scaled maximum
+        const bool raise = mx > m_run + 8.0f;               // also true for the first allowed key (m_run = -inf)
+        const float m_new = raise ? mx : m_run;
+        const float alpha = raise ? ex2(m_run - m_new) : 1.0f;   // ex2(-inf) = 0 when nothing was accumulated yet
+        const bool rescale = raise && j > 0 && m_run != -INFINITY;
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;  // row with no allowed key so far: P = 0
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[kBN / 2];
 #pragma unroll
         for (int t = 0; t < kBN; t += 2) {
-            const float p0 = exp2f(s[t] - m_use), p1 = exp2f(s[t + 1] - m_use);
-            rs += p0 + p1;
+            const float p0 = ex2(fmaf(s[t], sc, -m_use)), p1 = ex2(fmaf(s[t + 1], sc, -m_use));
+            rs4[(t >> 1) & 3] += p0 + p1;
             __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
             pk[t >> 1] = *reinterpret_cast<uint32_t*>(&h2);
         }
-        l_run = l_run * alpha + rs;
+        l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
         m_run = m_new;
+        // P's buffer and the O accumulator are still in use by the previous tile's second MMA
+        if (j > 0) {
+            ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1)) && ok;
+            tc_fence_after();
+            if (tid == 0 && ok && j + 1 < n_tiles) load_v(j + 1);   // stage (j+1)&1 was read by tile j-1
+        }
+        if (__any_sync(0xffffffffu, rescale)) {   // warp-uniform: tcgen05.ld/st are warp-wide
+            const float f = rescale ? alpha : 1.0f;
+#pragma unroll
+            for (int cc = 0; cc < kD / 32; ++cc) {
+                float t32[32];
+                tmem_ld32(lane_addr + kColO + cc * 32, t32);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) t32[i] *= f;
+                tmem_st32(lane_addr + kColO + cc * 32, t32);
+            }
+            tc_wait_st();
+        }
         // P row -> shared memory, K-major with the 128-byte swizzle the MMA descriptor expects
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -267,59 +324,59 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
             ok = false;
             break;
         }
-        // ---- MMA 2: O_tile = P V ---------------------------------------------------------------------
+        // ---- MMA 2: O (+)= P V, accumulator stays in TMEM ---------------------------------------------
         if (tid == 0) {
-            ok = mbar_wait(bar_v, ph);
+            ok = ok && mbar_wait(&bar_v[j & 1], (uint32_t)((j >> 1) & 1));
             if (ok) {
                 tc_fence_after();
+                const uint32_t vs = v_addr + (uint32_t)(j & 1) * kVStage;
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ++ks)
                     umma_ss(tmem_base + kColO, smem_desc(p_addr + (uint32_t)ks * 32, 16, 1024),
-                            smem_desc(v_addr + (uint32_t)ks * 2048, kBN * 128, 1024), kIdescO, ks > 0 ? 1u : 0u);
+                            smem_desc(vs + (uint32_t)ks * 2048, kBN * 128, 1024), kIdescO, (j > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(bar_o);
             } else {
                 *sh_abort = 1;
                 mbar_arrive(bar_o);
             }
         }
-        ok = mbar_wait(bar_o, ph) && ok;
-        tc_fence_after();
-        if (tid == 0 && ok && j + 1 < n_tiles) {
-            mbar_expect_tx(bar_v, 2 * kBN * 128);
-            tma_load_3d(smem + kOffV, &vmap, 0, (j + 1) * kBN, b * p.Hkv + hkv, bar_v);
-            tma_load_3d(smem + kOffV + kBN * 128, &vmap, 64, (j + 1) * kBN, b * p.Hkv + hkv, bar_v);
-        }
-        // ---- o = o * alpha + O_tile --------------------------------------------------------------------
-#pragma unroll
-        for (int cc = 0; cc < kD / 32; ++cc) {
-            float t32[32];
-            tmem_ld32(lane_addr + kColO + cc * 32, t32);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[cc * 32 + i] = fmaf(o[cc * 32 + i], alpha, t32[i]);
-        }
-        tc_fence_before();
-        __syncthreads();
-        if (*sh_abort) {
-            ok = false;
-            break;
-        }
     }
+    // ---- epilogue: wait for the last accumulation, normalise, store -------------------------------------
+    if (n_tiles > 0 && ok) {
+        ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1)) && ok;
+        tc_fence_after();
+    }
+    __syncthreads();
+    if (*sh_abort) ok = false;
     if (!ok && p.status && tid == 0) atomicOr(p.status, FLAG_WAIT_TIMEOUT);
-
-    // ---- epilogue ---------------------------------------------------------------------------------------
-    if (row < p.Lq && ok) {
+    if (ok) {
         const float inv = 1.0f / fmaxf(l_run, p.eps);
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (((int64_t)b * p.Hq + hq) * p.Lq + row) * kD;
 #pragma unroll
-        for (int u = 0; u < kD / 8; ++u) {
-            uint32_t w[4];
+        for (int cc = 0; cc < kD / 32; ++cc) {
+            float t32[32];
+            if (n_tiles > 0) {   // uniform over the CTA
+                tmem_ld32(lane_addr + kColO + cc * 32, t32);
+                tc_wait_ld();
+            } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * u + 2 * i] * inv, o[8 * u + 2 * i + 1] * inv);
-                w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                for (int i = 0; i < 32; ++i) t32[i] = 0.f;
             }
-            *reinterpret_cast<uint4*>(orow + 8 * u) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (row < p.Lq) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        // a row with no allowed key has l = 0 and only zero-weight products: force an exact 0
+                        const float a0 = l_run > 0.f ? t32[8 * u + 2 * i] * inv : 0.f;
+                        const float a1 = l_run > 0.f ? t32[8 * u + 2 * i + 1] * inv : 0.f;
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(a0, a1);
+                        w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                    }
+                    *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * u) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
         }
     }
     tc_fence_before();
@@ -365,7 +422,7 @@ cudaError_t launch_attn_tc(const DenseAttnLaunch& a, cudaStream_t stream) {
     p.status = nullptr;
     p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk; p.causal = a.causal;
     p.eps = a.eps;
-    dim3 grid((unsigned)((a.Lq + kBM - 1) / kBM), (unsigned)a.Hq, (unsigned)a.B);
+    dim3 grid((unsigned)a.Hq, (unsigned)((a.Lq + kBM - 1) / kBM), (unsigned)a.B);
     prefill_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p, qmap, kmap, vmap);
     count_launches(1);
     return cudaGetLastError();
