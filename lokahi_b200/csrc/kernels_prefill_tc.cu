@@ -5,7 +5,9 @@
 // (:107-112), online softmax across key tiles with the (max, sum, weighted V) merge of :125-144, and
 // out = wv / max(s, eps) so that a row with no allowed key is exactly 0 (:118, :146).
 //
-// One CTA = 128 query rows of one query head (4 warps; thread r owns query row r, which is TMEM lane r).
+// One CTA = 128 query rows of one query head: four softmax warps (thread r owns query row r, which is TMEM
+// lane r) plus a fifth warp whose lane 0 issues every TMA copy and every MMA, so that instruction issue to
+// the tensor cores (about 64 clocks per M128 N64 K16 MMA, measured) never sits on a softmax warp's path.
 // Per 64-key tile:
 //   TMA   K tile and V tile -> shared memory (3-D tensor maps [batch*head][token][dim], 128-byte swizzle,
 //         rows past the end of a head are zero-filled by the copy engine);
@@ -36,20 +38,21 @@ namespace {
 constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 64;           // keys per tile
 constexpr int kD = 128;           // head_dim
-constexpr int kThreads = 128;
+constexpr int kSoftmaxWarps = 4;   // one query row per thread
+constexpr int kThreads = (kSoftmaxWarps + 1) * 32;   // plus one warp whose lane 0 issues TMA and MMA
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0;     // S accumulator: 64 fp32 columns
-constexpr uint32_t kColO = 64;    // O_tile accumulator: 128 fp32 columns
+constexpr uint32_t kColS = 0;     // S accumulators: two buffers of 64 fp32 columns, [0,64) and [64,128)
+constexpr uint32_t kColO = 128;   // O accumulator: 128 fp32 columns
 constexpr float kLog2eF = 1.4426950408889634f;
 
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr int kOffQ = 0;                       // 2 boxes [128 rows][64 dims]   = 32 KB
-constexpr int kOffK = kOffQ + 2 * kBM * 128;   // 2 boxes [64 keys][64 dims]    = 16 KB
-constexpr int kOffV = kOffK + 2 * kBN * 128;   // 2 stages x 2 boxes [64 keys][64 dims] = 32 KB
-constexpr int kVStage = 2 * kBN * 128;
+constexpr int kOffK = kOffQ + 2 * kBM * 128;   // 2 stages x 2 boxes [64 keys][64 dims] = 32 KB
+constexpr int kVStage = 2 * kBN * 128;         // bytes of one K or V stage
+constexpr int kOffV = kOffK + 2 * kVStage;     // 2 stages x 2 boxes [64 keys][64 dims] = 32 KB
 constexpr int kOffP = kOffV + 2 * kVStage;     // [128 rows][64 keys] bf16      = 16 KB
 constexpr int kOffBar = kOffP + kBM * 128;     // mbarriers + TMEM base + flags
-constexpr int kSmemBytes = kOffBar + 128 + 1024;
+constexpr int kSmemBytes = kOffBar + 128;       // the dynamic shared-memory base is 1024-byte aligned (checked in the kernel)
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
@@ -150,17 +153,22 @@ __global__ void __launch_bounds__(kThreads, 2)
 prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                   const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* smem = smem_raw;
     uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + kOffBar);
-    uint64_t* bar_k = bar_q + 1;
-    uint64_t* bar_v = bar_q + 2;       // two stages: bar_v[0], bar_v[1]
-    uint64_t* bar_s = bar_q + 4;
-    uint64_t* bar_o = bar_q + 5;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 6);
-    int32_t* sh_limit = reinterpret_cast<int32_t*>(bar_q + 7);   // max over the tile's rows of the allowed-key count
+    uint64_t* bar_k = bar_q + 1;       // two stages
+    uint64_t* bar_v = bar_q + 3;       // two stages
+    uint64_t* bar_s = bar_q + 5;       // two S buffers
+    uint64_t* bar_o = bar_q + 7;
+    uint64_t* bar_p = bar_q + 8;       // softmax threads -> issuer: P of this tile is in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 9);
+    int32_t* sh_limit = reinterpret_cast<int32_t*>(bar_q + 10);   // max over the tile's rows of the allowed-key count
     int32_t* sh_abort = sh_limit + 1;
+    if ((smem_u32(smem) & 1023u) != 0) {   // the swizzled layouts need a 1024-byte aligned base
+        if (p.status && threadIdx.x == 0) atomicOr(p.status, FLAG_WAIT_TIMEOUT);
+        return;
+    }
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // heavy (late) query tiles first so that the causal triangle balances across SMs
     // (blocks are dispatched x-fastest: all heads' heaviest tiles start first)
     const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;
@@ -172,7 +180,7 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
 
     // number of keys this row may attend: keys 0 .. min(Lk, q_pos + 1)
     int limit = 0;
-    if (row < p.Lq) {
+    if (row < p.Lq && warp < kSoftmaxWarps) {
         limit = p.Lk;
         if (p.causal) {
             const int qpos = p.positions ? p.positions[(int64_t)b * p.Lq + row] : (p.Lk - p.Lq + row);
@@ -184,11 +192,14 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         *sh_limit = 0;
         *sh_abort = 0;
         mbar_init(bar_q, 1);
-        mbar_init(bar_k, 1);
+        mbar_init(&bar_k[0], 1);
+        mbar_init(&bar_k[1], 1);
         mbar_init(&bar_v[0], 1);
         mbar_init(&bar_v[1], 1);
-        mbar_init(bar_s, 1);
+        mbar_init(&bar_s[0], 1);
+        mbar_init(&bar_s[1], 1);
         mbar_init(bar_o, 1);
+        mbar_init(bar_p, kSoftmaxWarps * 32);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, kTmemCols);
@@ -201,9 +212,10 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     const int n_tiles = (*sh_limit + kBN - 1) / kBN;
 
     auto load_k = [&](int j) {
-        mbar_expect_tx(bar_k, 2 * kBN * 128);
-        tma_load_3d(smem + kOffK, &kmap, 0, j * kBN, zkv, bar_k);
-        tma_load_3d(smem + kOffK + kBN * 128, &kmap, 64, j * kBN, zkv, bar_k);
+        uint8_t* dst = smem + kOffK + (j & 1) * kVStage;
+        mbar_expect_tx(&bar_k[j & 1], 2 * kBN * 128);
+        tma_load_3d(dst, &kmap, 0, j * kBN, zkv, &bar_k[j & 1]);
+        tma_load_3d(dst + kBN * 128, &kmap, 64, j * kBN, zkv, &bar_k[j & 1]);
     };
     auto load_v = [&](int j) {
         uint8_t* dst = smem + kOffV + (j & 1) * kVStage;
@@ -211,145 +223,154 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         tma_load_3d(dst, &vmap, 0, j * kBN, zkv, &bar_v[j & 1]);
         tma_load_3d(dst + kBN * 128, &vmap, 64, j * kBN, zkv, &bar_v[j & 1]);
     };
-    if (tid == 0 && n_tiles > 0) {
-        mbar_expect_tx(bar_q, 2 * kBM * 128);
-        tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, zq, bar_q);
-        tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, zq, bar_q);
-        load_k(0);
-        load_v(0);
-        if (n_tiles > 1) load_v(1);
-    }
-
     // m_run is the maximum the stored numbers are scaled by.  It is only raised when a tile's maximum exceeds
     // it by more than 8 (log2 domain), so P stays below 2^8 and the accumulator in TMEM is rescaled rarely.
     float m_run = -INFINITY, l_run = 0.f;
     const float sc = rsqrtf((float)kD) * kLog2eF;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t q_addr = smem_u32(smem + kOffQ), k_addr = smem_u32(smem + kOffK);
     const uint32_t v_addr = smem_u32(smem + kOffV), p_addr = smem_u32(smem + kOffP);
     constexpr uint32_t kIdescS = instr_desc(kBN, 0);
     constexpr uint32_t kIdescO = instr_desc(kD, 1);
     bool ok = true;
 
-    for (int j = 0; j < n_tiles; ++j) {
-        const uint32_t ph = (uint32_t)(j & 1);
-        // ---- MMA 1: S = Q K^T ------------------------------------------------------------------
-        if (tid == 0) {
-            if (j == 0) ok = mbar_wait(bar_q, 0);
-            ok = ok && mbar_wait(bar_k, ph);
-            if (ok) {
+    if (warp == kSoftmaxWarps) {
+        // =============================== issuer warp: TMA and MMA ===============================
+        if (lane == 0 && n_tiles > 0) {
+            mbar_expect_tx(bar_q, 2 * kBM * 128);
+            tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, zq, bar_q);
+            tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, zq, bar_q);
+            load_k(0);
+            load_v(0);
+            if (n_tiles > 1) {
+                load_k(1);
+                load_v(1);
+            }
+            auto issue_qk = [&](int jj) {
+                ok = ok && mbar_wait(&bar_k[jj & 1], (uint32_t)((jj >> 1) & 1));
+                if (!ok) return;
                 tc_fence_after();
+                const uint32_t ks_addr = k_addr + (uint32_t)(jj & 1) * kVStage;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint32_t blk = (uint32_t)(ks >> 2), in = (uint32_t)(ks & 3) * 32;
-                    umma_ss(tmem_base + kColS, smem_desc(q_addr + blk * (kBM * 128) + in, 16, 1024),
-                            smem_desc(k_addr + blk * (kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u);
+                    umma_ss(tmem_base + kColS + (uint32_t)(jj & 1) * kBN, smem_desc(q_addr + blk * (kBM * 128) + in, 16, 1024),
+                            smem_desc(ks_addr + blk * (kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(bar_s);
-            } else {
-                *sh_abort = 1;
-                mbar_arrive(bar_s);   // release the waiters; they see the abort flag after the next barrier
-            }
-        }
-        ok = mbar_wait(bar_s, ph) && ok;
-        tc_fence_after();
-        if (tid == 0 && ok && j + 1 < n_tiles) load_k(j + 1);   // the K buffer is free again
-        // ---- softmax on this thread's row ---------------------------------------------------------
-        float s[kBN];
-        tmem_ld32(lane_addr + kColS, s);
-        tmem_ld32(lane_addr + kColS + 32, s + 32);
-        tc_wait_ld();
-        const int t0 = j * kBN;
-        if (t0 + kBN > limit) {   // only tiles that cross the row's limit pay for the mask
-#pragma unroll
-            for (int t = 0; t < kBN; ++t)
-                if (t0 + t >= limit) s[t] = -INFINITY;
-        }
-        float mx4[4] = {s[0], s[1], s[2], s[3]};   // four independent chains instead of one 64-long one
-#pragma unroll
-        for (int t = 4; t < kBN; t += 4) {
-            mx4[0] = fmaxf(mx4[0], s[t]);
-            mx4[1] = fmaxf(mx4[1], s[t + 1]);
-            mx4[2] = fmaxf(mx4[2], s[t + 2]);
-            mx4[3] = fmaxf(mx4[3], s[t + 3]);
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;   // sc > 0: the scaled maximum
-        const bool raise = mx > m_run + 8.0f;               // also true for the first allowed key (m_run = -inf)
-        const float m_new = raise ? mx : m_run;
-        const float alpha = raise ? ex2(m_run - m_new) : 1.0f;   // ex2(-inf) = 0 when nothing was accumulated yet
-        const bool rescale = raise && j > 0 && m_run != -INFINITY;
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;  // row with no allowed key so far: P = 0
-        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[kBN / 2];
-#pragma unroll
-        for (int t = 0; t < kBN; t += 2) {
-            const float p0 = ex2(fmaf(s[t], sc, -m_use)), p1 = ex2(fmaf(s[t + 1], sc, -m_use));
-            rs4[(t >> 1) & 3] += p0 + p1;
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-            pk[t >> 1] = *reinterpret_cast<uint32_t*>(&h2);
-        }
-        l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
-        m_run = m_new;
-        // P's buffer and the O accumulator are still in use by the previous tile's second MMA
-        if (j > 0) {
-            ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1)) && ok;
-            tc_fence_after();
-            if (tid == 0 && ok && j + 1 < n_tiles) load_v(j + 1);   // stage (j+1)&1 was read by tile j-1
-        }
-        if (__any_sync(0xffffffffu, rescale)) {   // warp-uniform: tcgen05.ld/st are warp-wide
-            const float f = rescale ? alpha : 1.0f;
-#pragma unroll
-            for (int cc = 0; cc < kD / 32; ++cc) {
-                float t32[32];
-                tmem_ld32(lane_addr + kColO + cc * 32, t32);
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) t32[i] *= f;
-                tmem_st32(lane_addr + kColO + cc * 32, t32);
-            }
-            tc_wait_st();
-        }
-        // P row -> shared memory, K-major with the 128-byte swizzle the MMA descriptor expects
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const uint32_t dst = p_addr + (uint32_t)tid * 128 + (((uint32_t)u ^ ((uint32_t)tid & 7)) << 4);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
-                         "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3])
-                         : "memory");
-        }
-        fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();
-        if (*sh_abort) {
-            ok = false;
-            break;
-        }
-        // ---- MMA 2: O (+)= P V, accumulator stays in TMEM ---------------------------------------------
-        if (tid == 0) {
-            ok = ok && mbar_wait(&bar_v[j & 1], (uint32_t)((j >> 1) & 1));
-            if (ok) {
+                umma_commit(&bar_s[jj & 1]);
+            };
+            ok = mbar_wait(bar_q, 0);
+            if (ok) issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                // S[(j+1)&1] was last read by the softmax of tile j-1, whose arrival on bar_p has been seen
+                if (j + 1 < n_tiles) issue_qk(j + 1);
+                // K stage j&1 is free as soon as S_j has been computed: refill it a whole tile ahead of its use
+                if (j + 2 < n_tiles) {
+                    ok = ok && mbar_wait(&bar_s[j & 1], (uint32_t)((j >> 1) & 1));
+                    if (!ok) break;
+                    load_k(j + 2);
+                }
+                // softmax of tile j done: P_j is in shared memory, S_j has been read, PV_{j-1} has completed
+                ok = ok && mbar_wait(bar_p, (uint32_t)(j & 1));
+                if (!ok) break;
                 tc_fence_after();
+                if (j >= 1 && j + 1 < n_tiles) load_v(j + 1);     // V stage (j+1)&1 was consumed by PV_{j-1}
+                ok = mbar_wait(&bar_v[j & 1], (uint32_t)((j >> 1) & 1));
+                if (!ok) break;
                 const uint32_t vs = v_addr + (uint32_t)(j & 1) * kVStage;
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ++ks)
                     umma_ss(tmem_base + kColO, smem_desc(p_addr + (uint32_t)ks * 32, 16, 1024),
                             smem_desc(vs + (uint32_t)ks * 2048, kBN * 128, 1024), kIdescO, (j > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(bar_o);
-            } else {
-                *sh_abort = 1;
-                mbar_arrive(bar_o);
             }
+            if (!ok) *sh_abort = 1;
         }
+    } else {
+        // =============================== softmax warps: one query row per thread ===============================
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = mbar_wait(&bar_s[j & 1], (uint32_t)((j >> 1) & 1));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t s_col = kColS + (uint32_t)(j & 1) * kBN;
+            float s[kBN];
+            tmem_ld32(lane_addr + s_col, s);
+            tmem_ld32(lane_addr + s_col + 32, s + 32);
+            tc_wait_ld();
+            const int t0 = j * kBN;
+            if (t0 + kBN > limit) {   // only tiles that cross the row's limit pay for the mask
+#pragma unroll
+                for (int t = 0; t < kBN; ++t)
+                    if (t0 + t >= limit) s[t] = -INFINITY;
+            }
+            float mx4[4] = {s[0], s[1], s[2], s[3]};   // four independent chains instead of one 64-long one
+#pragma unroll
+            for (int t = 4; t < kBN; t += 4) {
+                mx4[0] = fmaxf(mx4[0], s[t]);
+                mx4[1] = fmaxf(mx4[1], s[t + 1]);
+                mx4[2] = fmaxf(mx4[2], s[t + 2]);
+                mx4[3] = fmaxf(mx4[3], s[t + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;   // sc > 0: the scaled maximum
+            const bool raise = mx > m_run + 8.0f;               // also true for the first allowed key (m_run = -inf)
+            const float m_new = raise ? mx : m_run;
+            const float alpha = raise ? ex2(m_run - m_new) : 1.0f;   // ex2(-inf) = 0 when nothing was accumulated yet
+            const bool rescale = raise && j > 0 && m_run != -INFINITY;
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;  // row with no allowed key so far: P = 0
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[kBN / 2];
+#pragma unroll
+            for (int t = 0; t < kBN; t += 2) {
+                const float p0 = ex2(fmaf(s[t], sc, -m_use)), p1 = ex2(fmaf(s[t + 1], sc, -m_use));
+                rs4[(t >> 1) & 3] += p0 + p1;
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                pk[t >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
+            m_run = m_new;
+            // P's buffer and the O accumulator are still in use by the previous tile's second MMA
+            if (j > 0) {
+                ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1));
+                if (!ok) break;
+                tc_fence_after();
+            }
+            if (__any_sync(0xffffffffu, rescale)) {   // warp-uniform: tcgen05.ld/st are warp-wide
+                const float f = rescale ? alpha : 1.0f;
+#pragma unroll
+                for (int cc = 0; cc < kD / 32; ++cc) {
+                    float t32[32];
+                    tmem_ld32(lane_addr + kColO + cc * 32, t32);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) t32[i] *= f;
+                    tmem_st32(lane_addr + kColO + cc * 32, t32);
+                }
+                tc_wait_st();
+            }
+            // P row -> shared memory, K-major with the 128-byte swizzle the MMA descriptor expects
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t dst = p_addr + (uint32_t)tid * 128 + (((uint32_t)u ^ ((uint32_t)tid & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
+                             "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3])
+                             : "memory");
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(bar_p);
+        }
+        // wait for the last accumulation
+        if (n_tiles > 0 && ok) {
+            ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1));
+            tc_fence_after();
+        }
+        if (!ok) *sh_abort = 1;
     }
-    // ---- epilogue: wait for the last accumulation, normalise, store -------------------------------------
-    if (n_tiles > 0 && ok) {
-        ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1)) && ok;
-        tc_fence_after();
-    }
+    // ---- epilogue: normalise and store ------------------------------------------------------------------
     __syncthreads();
     if (*sh_abort) ok = false;
     if (!ok && p.status && tid == 0) atomicOr(p.status, FLAG_WAIT_TIMEOUT);
-    if (ok) {
+    if (ok && warp < kSoftmaxWarps) {
         const float inv = 1.0f / fmaxf(l_run, p.eps);
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (((int64_t)b * p.Hq + hq) * p.Lq + row) * kD;
 #pragma unroll

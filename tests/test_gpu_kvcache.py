@@ -211,3 +211,69 @@ def test_evict_prefetch_round_trip_is_bit_exact_and_moves_pages():
     c = pool.counters()
     assert c["pages_evicted"] == 4 and c["pages_prefetched"] == 4 and c["bytes_d2h"] == c["bytes_h2d"] == 4 * 3 * 2 * Hkv * P * D * 2
     assert pool.check_device_status() == 0
+
+
+def test_long_context_decode_with_eviction_every_step():
+    """The long-context configuration at reduced scale: 4 sequences, one KV head with its 4 query heads per
+    GPU, several layers, bf16; every step appends one token with RoPE, parks the oldest quarter of each
+    sequence's pages in pinned host memory, brings them back (they land in other device pages), and attends.
+    Outputs must match the oracle every step and the page tables must match the allocator model."""
+    rng = np.random.default_rng(96)
+    n_seqs, Hq, Hkv, D, P, layers, T0, steps = 4, 4, 1, 128, 16, 3, 1500, 6
+    theta = 500000.0
+    pages_per_seq = -(-(T0 + steps) // P)
+    n_pages = n_seqs * pages_per_seq + 8
+    host_pages = n_seqs * (pages_per_seq // 4 + 1)
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=layers, num_kv_heads=Hkv, head_dim=D, num_pages=n_pages, max_seqs=n_seqs,
+                                       max_pages_per_seq=pages_per_seq, page_size=P, dtype=torch.bfloat16,
+                                       host_pages=host_pages, rope_theta=theta))
+    model = opaged.PagePoolModel(layers, n_pages, P, n_seqs, pages_per_seq, host_pages)
+    for s in range(n_seqs):
+        assert pool.alloc_sequence() == model.alloc_sequence() == s
+    # logical history per (layer, sequence) kept on the host for the oracle
+    hist_k = np.zeros((layers, n_seqs, Hkv, T0 + steps, D), np.float32)
+    hist_v = np.zeros_like(hist_k)
+    for layer in range(layers):
+        k = bf16_round(rng.standard_normal((n_seqs, Hkv, T0, D), dtype=np.float32))
+        v = bf16_round(rng.standard_normal((n_seqs, Hkv, T0, D), dtype=np.float32))
+        pool.append(layer, _t(k, torch.bfloat16), _t(v, torch.bfloat16), start_pos=[0] * n_seqs)   # history stored as given
+        for s in range(n_seqs):
+            model.append(layer, s, 0, T0)
+        hist_k[layer, :, :, :T0] = k
+        hist_v[layer, :, :, :T0] = v
+    for step in range(steps):
+        T = T0 + step
+        n_old = (T // P) // 4
+        for s in range(n_seqs):
+            pool.evict(s, 0, n_old); model.evict(s, 0, n_old)
+        for s in range(n_seqs):
+            pool.prefetch(s, 0, n_old); model.prefetch(s, 0, n_old)
+        for s in range(n_seqs):
+            assert np.array_equal(pool.page_table(s), model.page_table[s, :model.num_seq_pages[s]])
+        for layer in range(layers):
+            q = bf16_round(rng.standard_normal((n_seqs, Hq, D), dtype=np.float32))
+            k = bf16_round(rng.standard_normal((n_seqs, Hkv, D), dtype=np.float32))
+            v = bf16_round(rng.standard_normal((n_seqs, Hkv, D), dtype=np.float32))
+            qt = _t(q, torch.bfloat16)
+            pool.append(layer, _t(k, torch.bfloat16), _t(v, torch.bfloat16), start_pos=[T] * n_seqs, rope_k=True, q=qt,
+                        layout="bhd")
+            for s in range(n_seqs):
+                model.append(layer, s, T, 1)
+            out = pool.decode_attention(layer, qt)
+            kr = bf16_round(opaged.rope_rows(k, np.full(n_seqs, T), theta))
+            qr = bf16_round(opaged.rope_rows(q, np.full(n_seqs, T), theta))
+            hist_k[layer, :, :, T] = kr
+            hist_v[layer, :, :, T] = v
+            ref = np.stack([
+                oattn_decode(qr[s], hist_k[layer, s, :, :T + 1], hist_v[layer, s, :, :T + 1], T) for s in range(n_seqs)])
+            assert_parity(out, ref, TOL_BF16, f"step {step} layer {layer}")
+    c = pool.counters()
+    assert c["pages_evicted"] == c["pages_prefetched"] == sum(((T0 + st) // P) // 4 for st in range(steps)) * n_seqs
+    assert pool.check_device_status() == 0
+
+
+def oattn_decode(q, k_hist, v_hist, pos):
+    from oracle import attention as oattn
+    return oattn.chunked_grouped_attention(q[None, :, None, :], k_hist[None], v_hist[None],
+                                           query_positions=np.array([[pos]], dtype=np.int32), causal=True,
+                                           q_block_size=32768, k_block_size=1000000, out_dtype=np.float32)[0, :, 0, :]
