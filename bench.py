@@ -122,6 +122,8 @@ def run_ours(args):
     from lokahi_b200.sharding import HeadShard
     shard = HeadShard(rank, world, HQ, HKV)          # raises when the KV heads do not divide over the ranks
     hkv, hq = shard.local_kv_heads, shard.local_q_heads
+    if args.emulate_shard > 1 and world == 1:      # one GPU doing the per-GPU share of an N-way head sharding (tuning aid)
+        hkv, hq = HKV // args.emulate_shard, HQ // args.emulate_shard
 
     K, W = args.steps, args.warmup
     total_steps = W + K
@@ -197,14 +199,17 @@ def run_ours(args):
 
     # ---- end-to-end leg: pinned host inputs, output read back every step ----------------------------------
     Ke = K
-    q_h = q_all[:Ke].cpu().pin_memory(); k_h = k_all[:Ke].cpu().pin_memory(); v_h = v_all[:Ke].cpu().pin_memory()
-    q_d = torch.empty_like(q_all[0]); k_d = torch.empty_like(k_all[0]); v_d = torch.empty_like(v_all[0])
+    nq, nk = N_SEQS * hq * D, N_SEQS * hkv * D
+    # one pinned staging buffer per step, [q | k | v], so that a step costs one host->device copy
+    qkv_h = torch.cat([q_all[:Ke].reshape(Ke, nq), k_all[:Ke].reshape(Ke, nk), v_all[:Ke].reshape(Ke, nk)], dim=1).cpu().pin_memory()
+    qkv_d = torch.empty((nq + 2 * nk,), device=dev, dtype=torch.bfloat16)
+    q_d = qkv_d[:nq].view(N_SEQS, hq, D)
+    k_d = qkv_d[nq:nq + nk].view(N_SEQS, hkv, D)
+    v_d = qkv_d[nq + nk:].view(N_SEQS, hkv, D)
     out_h = torch.empty((world if world > 1 else 1, N_SEQS, hq, D), dtype=torch.bfloat16).pin_memory()
 
     def e2e_step(i):
-        q_d.copy_(q_h[i], non_blocking=True)
-        k_d.copy_(k_h[i], non_blocking=True)
-        v_d.copy_(v_h[i], non_blocking=True)
+        qkv_d.copy_(qkv_h[i], non_blocking=True)
         step(q_d, k_d, v_d)
         out_h.copy_((gathered if world > 1 else out_buf).view(out_h.shape), non_blocking=True)
         torch.cuda.current_stream().synchronize()          # a decode loop consumes the result before the next step
@@ -471,6 +476,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--emulate-shard", type=int, default=1, help=argparse.SUPPRESS)
     ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
                     help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")
     ap.add_argument("--seqs", type=int, default=N_SEQS,

@@ -642,7 +642,7 @@ cudaError_t launch_tma(const DecodeLaunch& d, cudaStream_t stream) {
 // write out = wv / max(s, eps) in the storage dtype.  grid (n_q_heads, n_seqs).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void decode_reduce_kernel(DecodeLaunch d) {
+__global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
     const PoolView& pv = d.pool;
     const int hq = blockIdx.x, i = blockIdx.y;
     const int seq = d.seq_ids ? d.seq_ids[i] : i;
@@ -650,22 +650,44 @@ __global__ void decode_reduce_kernel(DecodeLaunch d) {
     T* out = reinterpret_cast<T*>(d.out) + ((int64_t)i * d.n_q_heads + hq) * D;
     int n_attend = 0;
     if (seq >= 0 && seq < pv.max_seqs) n_attend = attend_count(d, i, seq);
-    const int n_splits = (n_attend + d.chunk_tokens - 1) / d.chunk_tokens;
+    const int n_splits = (n_attend + d.chunk_tokens - 1) / d.chunk_tokens;   // <= 128 by the plan
     const int64_t base = ((int64_t)i * d.n_q_heads + hq) * d.max_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s)
-        if (d.ws_ml[(base + s) * 2 + 1] > 0.f) M = fmaxf(M, d.ws_ml[(base + s) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float l = d.ws_ml[(base + s) * 2 + 1];
-        if (l > 0.f) L += expf(d.ws_ml[(base + s) * 2] - M) * l;
+    // one thread per split fetches (m, l): the loads of all splits are in flight together
+    __shared__ float sm_m[128], sm_w[128];
+    __shared__ float sm_red[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float m = -INFINITY, l = 0.f;
+    if (tid < n_splits) {
+        const float2 ml = *reinterpret_cast<const float2*>(&d.ws_ml[(base + tid) * 2]);
+        m = ml.y > 0.f ? ml.x : -INFINITY;
+        l = ml.y;
     }
+    float M = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) sm_red[warp] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3]));
+    const float w = l > 0.f ? expf(m - M) : 0.f;
+    if (tid < 128) {
+        sm_w[tid] = w;
+        sm_m[tid] = w * l;
+    }
+    float L = w * l;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (lane == 0) sm_red[4 + warp] = L;
+    __syncthreads();
+    L = (sm_red[4] + sm_red[5]) + (sm_red[6] + sm_red[7]);
     const float inv = 1.0f / fmaxf(L, d.eps);
-    for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+    for (int dd = tid; dd < D; dd += blockDim.x) {
         float a = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float l = d.ws_ml[(base + s) * 2 + 1];
-            if (l > 0.f) a += expf(d.ws_ml[(base + s) * 2] - M) * d.ws_acc[(base + s) * D + dd];
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {   // eight independent loads per thread in flight
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = s0 + j < n_splits ? d.ws_acc[(base + s0 + j) * D + dd] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a += (s0 + j < n_splits ? sm_w[s0 + j] : 0.f) * v[j];
         }
         out[dd] = from_f32<T>(a * inv);
     }
@@ -690,9 +712,12 @@ cudaError_t launch_generic(const DecodeLaunch& d, cudaStream_t stream) {
 
 void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, int32_t num_kv_heads,
                  int64_t total_tokens_hint, int32_t* chunk_tokens, int32_t* max_splits) {
-    // Aim at about 8 waves of 3 CTAs per SM on 148 SMs so that ragged lengths even out, but never
-    // more than `splits` partials per sequence (bounds the workspace independently of the lengths).
-    const int64_t target = 148LL * 3 * 8;
+    // Aim at a little over two waves of 3 CTAs per SM on 148 SMs (about 1000 CTAs): measured on B200 with the
+    // work of 1, 1/2, 1/4 and 1/8 of the 64-sequence workload, the best chunk was the one that gives each
+    // CTA total_tokens * kv_heads / ~1000 tokens (2048, ~1000, ~512, ~256); smaller chunks pay the per-CTA
+    // start-up (lengths -> page ids -> first copy) too often, larger ones leave SMs idle in the last wave.
+    // `splits` bounds the partials per sequence, and with them the workspace, independently of the lengths.
+    const int64_t target = 1000;
     const int64_t max_ctx = (int64_t)max_pages_per_seq * page_size;
     int64_t splits = (2 * target + (int64_t)n_seqs * num_kv_heads - 1) / ((int64_t)n_seqs * num_kv_heads);
     splits = splits < 1 ? 1 : (splits > 128 ? 128 : splits);
@@ -702,7 +727,7 @@ void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, i
     const char* env = getenv("SKV_DECODE_CHUNK");
     if (env && atoi(env) > 0 && atoi(env) >= floor_chunk) chunk = atoi(env);
     chunk = ((chunk + 63) / 64) * 64;                 // 4 warps x 16-token tiles
-    if (chunk < 64) chunk = 64;
+    if (chunk < 256) chunk = 256;
     if (chunk > 2048) {                               // a warp holds at most 32 tile page ids
         chunk = 2048;
         splits = (max_ctx + chunk - 1) / chunk;
@@ -721,6 +746,7 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     const int G = d.n_q_heads / d.pool.num_kv_heads;
     const bool mma_ok = d.dtype == SKV_BF16 && d.pool.head_dim == kMmaD && d.pool.page_size % 16 == 0 && G <= 8 &&
                         !d.force_generic && ((uintptr_t)d.q % 16 == 0);
+    if (d.max_splits > 128) return cudaErrorInvalidValue;   // the merge kernel handles one split per thread
     cudaError_t e;
     const char* impl = getenv("SKV_DECODE_IMPL");   // "reg": direct-to-register loads; default: TMA ring when maps exist
     const bool tma_ok = mma_ok && d.k_map && d.v_map && !(impl && impl[0] == 'r');
@@ -744,7 +770,7 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     }
     count_launches(2);
     dim3 rgrid((unsigned)d.n_q_heads, (unsigned)d.n_seqs);
-    const int threads = d.pool.head_dim >= 128 ? 128 : 64;
+    const int threads = 128;
     if (d.dtype == SKV_BF16)
         decode_reduce_kernel<__nv_bfloat16><<<rgrid, threads, 0, stream>>>(d);
     else

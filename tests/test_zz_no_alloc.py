@@ -85,7 +85,7 @@ def test_static_scratch_decode_matches_workspace_decode_on_consecutive_calls():
 
 
 def test_static_scratch_rejects_requests_beyond_its_size():
-    # 256 sequences x 32 query heads with a row capacity that forces 14 splits needs > 16 MiB of partials
+    # 256 sequences x 32 query heads whose page-table rows hold 9600 tokens need 5 partials each: > 16 MiB
     lens = [8] * 256
     pool, gen = _pool(lens, max_pages_per_seq=600)
     q = torch.randn((256, 32, 128), generator=gen, device=DEV).to(torch.bfloat16)
