@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cstdlib>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -22,6 +23,12 @@ template <>
 __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// Programmatic dependent launch: a kernel launched with launch_pdl may start while the previous kernel in
+// the stream is still draining; it must execute pdl_wait() before it reads anything that kernel wrote
+// (the wait returns once the previous grid has completed and its writes are visible).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Page id of (sequence, slot) with range checks: a bad id sets a bit in the status word and the
 // caller skips the access instead of faulting.
@@ -50,5 +57,23 @@ __device__ __forceinline__ bool checked_seq(const PoolView& pv, int32_t seq) {
 __device__ __forceinline__ int64_t row_offset(const PoolView& pv, int32_t page, int32_t head, int32_t row) {
     return (((int64_t)page * pv.num_kv_heads + head) * pv.page_size + row) * pv.head_dim;
 }
+
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    static const bool enabled = [] { const char* e = getenv("SKV_PDL"); return !(e && e[0] == '0'); }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = enabled ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
 
 }  // namespace skv

@@ -21,6 +21,7 @@ __device__ __forceinline__ void rope_pair(float x1, float x2, float pos, float i
 template <typename T>
 __global__ void append_kernel(AppendLaunch a) {
     const PoolView& pv = a.pool;
+    pdl_wait();
     const int half = pv.head_dim >> 1;
     const int tok = blockIdx.x;                 // i * n_new + j
     const int i = tok / a.n_new;
@@ -82,12 +83,10 @@ cudaError_t launch_append(const AppendLaunch& a, cudaStream_t stream) {
     if (heads_per_block > n_slots) heads_per_block = n_slots;
     dim3 grid((unsigned)(a.n_seqs * a.n_new), (unsigned)((n_slots + heads_per_block - 1) / heads_per_block));
     dim3 block((unsigned)(heads_per_block * half));
-    if (a.dtype == SKV_BF16)
-        append_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(a);
-    else
-        append_kernel<float><<<grid, block, 0, stream>>>(a);
+    cudaError_t e = a.dtype == SKV_BF16 ? launch_pdl(append_kernel<__nv_bfloat16>, grid, block, 0, stream, a)
+                                        : launch_pdl(append_kernel<float>, grid, block, 0, stream, a);
     count_launches(1);
-    return cudaGetLastError();
+    return e;
 }
 
 template <typename T>

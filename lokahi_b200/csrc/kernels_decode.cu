@@ -346,6 +346,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     extern __shared__ uint8_t smem_raw[];
     const PoolView& pv = d.pool;
     const int split = blockIdx.x, h = blockIdx.y, i = blockIdx.z;
+    pdl_wait();
     const int seq = d.seq_ids ? d.seq_ids[i] : i;
     if (!checked_seq(pv, seq)) return;
     const int n_attend = attend_count(d, i, seq);
@@ -513,6 +514,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
             issue(k + NS);
         }
     }
+    pdl_launch_dependents();   // the merge kernel may begin launching while this CTA combines and stores
     if (dead) {
         if (lane == 0) atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
         // copies already issued for later tiles still target this CTA's shared memory: wait for them (bounded)
@@ -632,9 +634,8 @@ cudaError_t launch_tma(const DecodeLaunch& d, cudaStream_t stream) {
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
-    decode_tma_kernel<NS><<<grid, kDecodeThreads, smem, stream>>>(d, *reinterpret_cast<const CUtensorMap*>(d.k_map),
-                                                                  *reinterpret_cast<const CUtensorMap*>(d.v_map));
-    return cudaGetLastError();
+    return launch_pdl(decode_tma_kernel<NS>, grid, dim3(kDecodeThreads), (size_t)smem, stream, d,
+                      *reinterpret_cast<const CUtensorMap*>(d.k_map), *reinterpret_cast<const CUtensorMap*>(d.v_map));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -645,6 +646,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
     const PoolView& pv = d.pool;
     const int hq = blockIdx.x, i = blockIdx.y;
+    pdl_wait();
     const int seq = d.seq_ids ? d.seq_ids[i] : i;
     const int D = pv.head_dim;
     T* out = reinterpret_cast<T*>(d.out) + ((int64_t)i * d.n_q_heads + hq) * D;
@@ -771,11 +773,8 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     count_launches(2);
     dim3 rgrid((unsigned)d.n_q_heads, (unsigned)d.n_seqs);
     const int threads = 128;
-    if (d.dtype == SKV_BF16)
-        decode_reduce_kernel<__nv_bfloat16><<<rgrid, threads, 0, stream>>>(d);
-    else
-        decode_reduce_kernel<float><<<rgrid, threads, 0, stream>>>(d);
-    return cudaGetLastError();
+    return d.dtype == SKV_BF16 ? launch_pdl(decode_reduce_kernel<__nv_bfloat16>, rgrid, dim3(threads), 0, stream, d)
+                               : launch_pdl(decode_reduce_kernel<float>, rgrid, dim3(threads), 0, stream, d);
 }
 
 }  // namespace skv
