@@ -339,6 +339,87 @@ def run_prefill(args):
     }
 
 
+def run_decoder(args):
+    """Secondary workload "deepseek_1p3b_shaped_decoder": random-init decoder, 24 layers, hidden 2048, 16 MHA heads
+    of 128, SiLU MLP 5504, vocab 32256, RoPE theta 100000 with linear scaling 4, bf16; batch 8, 2048-token prompt
+    prefill then 256 greedy decode tokens with the KV cache held in pages.  The linear layers are torch/cuBLAS
+    and are reported separately from the hot path (RoPE + cache update + attention)."""
+    import torch
+    from types import SimpleNamespace
+
+    import lokahi_b200 as L
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Bt, Lp, Ld = 8, 2048, max(1, min(args.steps, 256))
+    cfg = SimpleNamespace(vocab_size=32256, hidden_size=2048, intermediate_size=5504, num_hidden_layers=24,
+                          num_attention_heads=16, num_key_value_heads=16, rms_norm_eps=1e-6, max_position_embeddings=4096,
+                          rope_theta=100000.0, rope_scaling_factor=4.0)
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    H, I, Dh = cfg.hidden_size, cfg.intermediate_size, 128
+
+    def mat(*shape):
+        return (torch.randn(shape, generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+
+    w = {}
+    for i in range(cfg.num_hidden_layers):
+        b = f"model.layers.{i}"
+        for n, shp in (("self_attn.q_proj", (H, H)), ("self_attn.k_proj", (H, H)), ("self_attn.v_proj", (H, H)),
+                       ("self_attn.o_proj", (H, H)), ("mlp.gate_proj", (I, H)), ("mlp.up_proj", (I, H)), ("mlp.down_proj", (H, I))):
+            w[f"{b}.{n}.weight"] = mat(*shp)
+        w[f"{b}.input_layernorm.weight"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        w[f"{b}.post_attention_layernorm.weight"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    w["model.embed_tokens.weight"] = mat(cfg.vocab_size, H)
+    w["lm_head.weight"] = mat(cfg.vocab_size, H)
+    w["model.norm.weight"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    model = L.PagedDecoder(cfg, w)
+    prompt = torch.randint(0, cfg.vocab_size, (Bt, Lp), generator=gen, device=dev)
+
+    def one_run(timed):
+        cache = L.PagedKVCache(cfg, cache_dir=None, max_tokens=Lp + Ld + 16)
+        model.hot_path_events = [] if timed else None
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        logits = model(prompt, past_key_values=cache, use_cache=True)
+        nxt = logits[:, -1, :].argmax(-1, keepdim=True)
+        e[1].record()
+        n_pre = len(model.hot_path_events) if timed else 0
+        for _ in range(Ld):
+            logits = model(nxt, past_key_values=cache, use_cache=True)
+            nxt = logits[:, -1, :].argmax(-1, keepdim=True)
+        e[2].record()
+        torch.cuda.synchronize()
+        hot = model.hot_path_events or []
+        pre_hot = sum(a.elapsed_time(b) for a, b in hot[:n_pre])
+        dec_hot = sum(a.elapsed_time(b) for a, b in hot[n_pre:])
+        flag = cache.pool.check_device_status()
+        cache.clear()
+        return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), pre_hot, dec_hot, flag
+
+    one_run(False)                                   # warm-up (cuBLAS handles, page pool, autotuning)
+    l0 = L._lib.lib.skv_launch_count()
+    pre_ms, dec_ms, pre_hot, dec_hot, flag = one_run(True)
+    launches = L._lib.lib.skv_launch_count() - l0
+    if flag:
+        raise SystemExit("device status flag set")
+    peak_t = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"] if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 1590.0
+    peak_b, _ = measured_peak_gbs()
+    layers = cfg.num_hidden_layers
+    pre_flops = layers * Bt * 4.0 * 16 * Dh * (Lp * (Lp + 1) / 2)
+    dec_bytes = sum(layers * Bt * (Lp + s + 1) * 16 * Dh * 2 * 2 for s in range(Ld))
+    return {
+        "metric": "decoder decode tokens/s", "value": Bt * Ld / (dec_ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": Ld,
+        "warmup": 1, "ms_per_step": dec_ms / Ld, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "deepseek_1p3b_shaped_decoder", "batch": Bt, "prompt": Lp, "decode_tokens": Ld, "layers": layers,
+                   "hidden": H, "heads": 16, "head_dim": Dh, "mlp": I, "vocab": cfg.vocab_size, "rope": "theta 1e5, linear x4"},
+        "prefill": {"tokens_per_s": Bt * Lp / (pre_ms * 1e-3), "ms": pre_ms, "hot_path_ms": pre_hot,
+                    "hot_path_tflops": pre_flops / (pre_hot * 1e-3) / 1e12, "hot_path_frac_of_bf16_peak": pre_flops / (pre_hot * 1e-3) / 1e12 / peak_t},
+        "decode": {"tokens_per_s": Bt * Ld / (dec_ms * 1e-3), "ms": dec_ms, "hot_path_ms": dec_hot,
+                   "hot_path_gbs": dec_bytes / (dec_hot * 1e-3) / 1e9, "hot_path_frac_of_hbm_peak": dec_bytes / (dec_hot * 1e-3) / 1e9 / peak_b},
+        "gpu_launches": int(launches),
+    }
+
+
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per decode launch: measured on the 16-sequence capture
 # case (295.49 MB of traffic for 287.07 MB algorithmic, profiles/decode_tma_kernel_paged_decode_16seq.md)
 # and scaled to this workload by the algorithmic bytes, which is what the traffic grows with.
@@ -477,7 +558,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--emulate-shard", type=int, default=1, help=argparse.SUPPRESS)
-    ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "decoder"], default="decode",
                     help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")
     ap.add_argument("--seqs", type=int, default=N_SEQS,
                     help="number of sequences (default: the workload's 64; smaller values are for profiler captures)")
@@ -489,6 +570,8 @@ def main():
         result = run_reference(args)
     elif args.workload == "prefill":
         result = run_prefill(args)
+    elif args.workload == "decoder":
+        result = run_decoder(args)
     else:
         result = run_ours(args)
     if result is not None:

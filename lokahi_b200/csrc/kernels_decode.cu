@@ -349,8 +349,15 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     pdl_wait();
     const int seq = d.seq_ids ? d.seq_ids[i] : i;
     if (!checked_seq(pv, seq)) return;
-    const int n_attend = attend_count(d, i, seq);
     const int t0 = split * d.chunk_tokens;
+    // The page id of this lane's tile does not depend on the sequence length: fetch it now, next to the
+    // length, instead of after it (one dependent memory round trip less in every CTA's start-up).
+    int raw_page = -1;
+    {
+        const int slot = (t0 + ((int)(threadIdx.x >> 5) + kDecodeWarps * (int)(threadIdx.x & 31)) * 16) / pv.page_size;
+        if (slot < pv.max_pages_per_seq) raw_page = pv.page_table[(int64_t)seq * pv.max_pages_per_seq + slot];
+    }
+    const int n_attend = attend_count(d, i, seq);
     const int G = d.n_q_heads / pv.num_kv_heads;
     if (t0 >= n_attend) {
         if (split == 0) {   // nothing to attend: the output row is exactly 0 (mlx_ops.py:118, :146)
@@ -394,7 +401,12 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     int my_page = -1;
     {
         const int tile = warp + kDecodeWarps * lane;
-        if (tile < n_tiles) my_page = checked_page(pv, seq, (t0 + tile * 16) / P);
+        if (tile < n_tiles) {
+            if (raw_page >= 0 && raw_page < pv.num_pages)
+                my_page = raw_page;
+            else
+                atomicOr(pv.status, FLAG_BAD_PAGE);   // skipped, not dereferenced
+        }
     }
     const int layer_rows = (int)((int64_t)d.layer * (pv.layer_stride_bytes / (kMmaD * 2)));
 

@@ -62,6 +62,9 @@ class PagedDecoder:
             raise RuntimeError("PagedDecoder needs CUDA weights; there is no CPU path")
         self.inv_freq_np = rope_inv_freq(self.D, self.theta)
         self.inv_freq = torch.from_numpy(self.inv_freq_np).to(self.device)
+        # when set to a list, (start, end) CUDA events around the hot path (RoPE + cache update + attention)
+        # of every layer call are appended to it
+        self.hot_path_events = None
 
     # -- glue (llama_mlx.py:53-92, 345-408) ------------------------------------------------------------
     def _rms_norm(self, x, weight):
@@ -92,6 +95,9 @@ class PagedDecoder:
         k = F.linear(hidden, self.w[f"{b}.k_proj.weight"]).view(B, L, self.Hkv, self.D).transpose(1, 2).contiguous()
         v = F.linear(hidden, self.w[f"{b}.v_proj.weight"]).view(B, L, self.Hkv, self.D).transpose(1, 2).contiguous()
         kwargs = {"cache_position": cache_position}
+        if self.hot_path_events is not None:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         if cache is not None and self.fused_rope and hasattr(cache, "update_with_rope"):
             k_hist, v_hist = cache.update_with_rope(q, k, v, layer, kwargs, inv_freq=self.inv_freq_np,
                                                     scaling_factor=self.rope_scale)
@@ -102,6 +108,9 @@ class PagedDecoder:
             k_hist, v_hist = (k, v) if cache is None else cache.update(k, v, layer, kwargs)
         out = chunked_grouped_attention(q, k_hist, v_hist, query_positions=position_ids, causal=True,
                                         q_block_size=32768, k_block_size=(1024 if L > 128 else 1000000))
+        if self.hot_path_events is not None:
+            ev[1].record()
+            self.hot_path_events.append(ev)
         out = out.transpose(1, 2).reshape(B, L, -1)
         out = F.linear(out, self.w[f"{b}.o_proj.weight"])
         if self.tracer is not None:
