@@ -420,6 +420,104 @@ def run_decoder(args):
     }
 
 
+def run_longctx(args):
+    """Secondary workload "long_context_llama3_8b_kv": one GPU's share of the 8-way KV-head sharding of a
+    Llama-3-8B KV path: 32 layers, 1 KV head with its 4 query heads, head_dim 128, bf16, 4 sequences at 96k
+    (98304) tokens of N(0,1) K/V.  Every step parks the oldest 25 % of each sequence's pages in pinned host
+    memory, brings them back, then appends one token and attends in all 32 layers.  Two rooflines: HBM for the
+    attention bytes, the host link for the parked bytes."""
+    import torch
+
+    import lokahi_b200 as L
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    layers, n_seq, hkv, hq, T0 = 32, 4, 1, 4, 98304
+    K, W = max(1, min(args.steps, 64)), max(1, min(args.warmup, 3))
+    pages_per_seq = -(-(T0 + K + W + 16) // P)
+    park = (T0 // P) // 4
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=layers, num_kv_heads=hkv, head_dim=D, num_pages=n_seq * pages_per_seq + 8,
+                                       max_seqs=n_seq, max_pages_per_seq=pages_per_seq, page_size=P, dtype=torch.bfloat16,
+                                       device=0, host_pages=n_seq * park + 8, rope_theta=THETA))
+    for s_ in range(n_seq):
+        assert pool.alloc_sequence() == s_
+        pool.reserve(s_, T0 + K + W + 16)
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    pool_set_lengths(pool, layers, n_seq, T0)        # declares the history (writes zeros) ...
+    for layer in range(layers):                      # ... which is then filled with N(0,1) K/V in place
+        kp, vp = pool.layer_views(layer)
+        kp.normal_(generator=gen)
+        vp.normal_(generator=gen)
+    q = torch.randn((n_seq, hq, D), generator=gen, device=dev).to(torch.bfloat16)
+    kn = torch.randn((n_seq, hkv, D), generator=gen, device=dev).to(torch.bfloat16)
+    vn = torch.randn((n_seq, hkv, D), generator=gen, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+
+    def step(timers=None):
+        if timers:
+            timers[0].record()
+        for s_ in range(n_seq):
+            pool.evict(s_, 0, park)
+        for s_ in range(n_seq):
+            pool.prefetch(s_, 0, park)
+        pool.sync_transfers()
+        if timers:
+            timers[1].record()
+        for layer in range(layers):
+            pool.append(layer, kn, vn, rope_k=True, q=q.clone(), layout="bhd")
+            pool.decode_attention(layer, q, out=out)
+        if timers:
+            timers[2].record()
+
+    for _ in range(W):
+        step()
+    torch.cuda.synchronize()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    l0 = L._lib.lib.skv_launch_count()
+    c0 = pool.counters()
+    for i in range(K):
+        step(evs[i])
+    torch.cuda.synchronize()
+    launches = L._lib.lib.skv_launch_count() - l0
+    c1 = pool.counters()
+    if pool.check_device_status() != 0:
+        raise SystemExit("device status flag set")
+    xfer_ms = np.array([e[0].elapsed_time(e[1]) for e in evs])
+    attn_ms = np.array([e[1].elapsed_time(e[2]) for e in evs])
+    d2h = (c1["bytes_d2h"] - c0["bytes_d2h"]) / K
+    h2d = (c1["bytes_h2d"] - c0["bytes_h2d"]) / K
+    attn_bytes = float(np.mean([layers * n_seq * (T0 + W + i + 1) * hkv * D * 2 * 2 for i in range(K)]))
+    peak, kind = measured_peak_gbs()
+    step_ms = float((xfer_ms + attn_ms).mean())
+    return {
+        "metric": "long-context decode tokens/s per GPU (1 of 8 KV heads)", "value": n_seq / (step_ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "long_context_llama3_8b_kv", "layers": layers, "sequences": n_seq, "context": T0, "kv_heads_local": hkv,
+                   "q_heads_local": hq, "head_dim": D, "page_size": P, "parked_fraction": 0.25},
+        "attention": {"ms_per_step": float(attn_ms.mean()), "algorithmic_bytes": attn_bytes,
+                      "achieved_gbs": attn_bytes / (attn_ms.mean() * 1e-3) / 1e9,
+                      "frac_of_hbm_peak": attn_bytes / (attn_ms.mean() * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}"},
+        "transfers": {"ms_per_step": float(xfer_ms.mean()), "d2h_bytes_per_step": d2h, "h2d_bytes_per_step": h2d,
+                      "achieved_gbs_each_way": (d2h + h2d) / 2 / (xfer_ms.mean() * 1e-3 / 2) / 1e9,
+                      "note": "evict then prefetch of the same pages, serial on one copy stream; host-link bound"},
+        "gpu_launches": int(launches),
+    }
+
+
+def pool_set_lengths(pool, layers, n_seq, length):
+    """Give every layer a history of `length` tokens by appending zero rows in blocks (bench set-up only;
+    the caller overwrites the pages afterwards)."""
+    import torch
+    zero = torch.zeros((n_seq, pool.cfg.num_kv_heads, 1, pool.cfg.head_dim), device=pool.torch_device, dtype=pool.cfg.dtype)
+    for layer in range(layers):
+        done = 0
+        while done < length:
+            n = min(8192, length - done)
+            kv = zero.expand(n_seq, pool.cfg.num_kv_heads, n, pool.cfg.head_dim)   # stride 0 along tokens
+            pool.append(layer, kv, kv, start_pos=[done] * n_seq)
+            done += n
+
+
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per decode launch: measured on the 16-sequence capture
 # case (295.49 MB of traffic for 287.07 MB algorithmic, profiles/decode_tma_kernel_paged_decode_16seq.md)
 # and scaled to this workload by the algorithmic bytes, which is what the traffic grows with.
@@ -558,7 +656,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--emulate-shard", type=int, default=1, help=argparse.SUPPRESS)
-    ap.add_argument("--workload", choices=["decode", "prefill", "decoder"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "decoder", "longctx"], default="decode",
                     help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")
     ap.add_argument("--seqs", type=int, default=N_SEQS,
                     help="number of sequences (default: the workload's 64; smaller values are for profiler captures)")
@@ -572,6 +670,8 @@ def main():
         result = run_prefill(args)
     elif args.workload == "decoder":
         result = run_decoder(args)
+    elif args.workload == "longctx":
+        result = run_longctx(args)
     else:
         result = run_ours(args)
     if result is not None:

@@ -204,18 +204,36 @@ __global__ void apply_length_updates_kernel(int32_t* __restrict__ lengths, const
 struct CopyItem {
     int32_t page, slot;
 };
-__global__ void page_copy_kernel(char* __restrict__ k_base, char* __restrict__ v_base, char* __restrict__ tier,
-                                 const CopyItem* __restrict__ items, int64_t layer_stride, int64_t page_bytes,
-                                 int num_layers, int to_host) {
-    CopyItem it = items[blockIdx.x];
-    int layer = blockIdx.y >> 1;
-    int is_v = blockIdx.y & 1;
-    char* dev = (is_v ? v_base : k_base) + (int64_t)layer * layer_stride + (int64_t)it.page * page_bytes;
-    char* hst = tier + (((int64_t)it.slot * num_layers + layer) * 2 + is_v) * page_bytes;
-    const int4* src = reinterpret_cast<const int4*>(to_host ? dev : hst);
-    int4* dst = reinterpret_cast<int4*>(to_host ? hst : dev);
-    int n = (int)(page_bytes / 16);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+__global__ void __launch_bounds__(256) page_copy_kernel(char* __restrict__ k_base, char* __restrict__ v_base, char* __restrict__ tier,
+                                                         const CopyItem* __restrict__ items, int64_t layer_stride, int64_t page_bytes,
+                                                         int num_layers, int to_host) {
+    // One block moves several (layer, K|V) chunks of one page; every thread keeps four 16-byte loads in
+    // flight, which is what the host link needs (loads from mapped host memory are latency-bound otherwise).
+    const CopyItem it = items[blockIdx.x];
+    const int n = (int)(page_bytes / 16);
+    const int n_chunks = num_layers * 2;
+    for (int c0 = blockIdx.y; c0 < n_chunks; c0 += 4 * gridDim.y) {
+        const int4* src[4];
+        int4* dst[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int chunk = c0 + u * gridDim.y;
+            const int cc = chunk < n_chunks ? chunk : c0;
+            const int layer = cc >> 1, is_v = cc & 1;
+            char* dev = (is_v ? v_base : k_base) + (int64_t)layer * layer_stride + (int64_t)it.page * page_bytes;
+            char* hst = tier + (((int64_t)it.slot * num_layers + layer) * 2 + is_v) * page_bytes;
+            src[u] = reinterpret_cast<const int4*>(to_host ? dev : hst);
+            dst[u] = reinterpret_cast<int4*>(to_host ? hst : dev);
+        }
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            int4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = src[u][i];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (c0 + u * (int)gridDim.y < n_chunks) dst[u][i] = v[u];
+        }
+    }
 }
 
 int32_t publish_table_updates(skv_pool* p, const std::vector<TableUpdate>& ups, cudaStream_t stream) {
@@ -944,7 +962,7 @@ int32_t skv_evict(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slots,
         size_t n = std::min(per, items.size() - off);
         void* dev = nullptr;
         CUDA_TRY(p, p->ring.upload(items.data() + off, n * sizeof(CopyItem), p->copy_stream, &dev));
-        dim3 grid((unsigned)n, (unsigned)p->cfg.num_layers * 2);
+        dim3 grid((unsigned)n, (unsigned)std::min(p->cfg.num_layers * 2, 8));
         page_copy_kernel<<<grid, 256, 0, p->copy_stream>>>(p->d_k, p->d_v, p->h_tier_dev, (const CopyItem*)dev,
                                                            (int64_t)p->layer_stride, (int64_t)p->page_bytes,
                                                            p->cfg.num_layers, 1);
@@ -994,7 +1012,7 @@ int32_t skv_prefetch(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slo
         size_t n = std::min(per, items.size() - off);
         void* dev = nullptr;
         CUDA_TRY(p, p->ring.upload(items.data() + off, n * sizeof(CopyItem), p->copy_stream, &dev));
-        dim3 grid((unsigned)n, (unsigned)p->cfg.num_layers * 2);
+        dim3 grid((unsigned)n, (unsigned)std::min(p->cfg.num_layers * 2, 8));
         page_copy_kernel<<<grid, 256, 0, p->copy_stream>>>(p->d_k, p->d_v, p->h_tier_dev, (const CopyItem*)dev,
                                                            (int64_t)p->layer_stride, (int64_t)p->page_bytes,
                                                            p->cfg.num_layers, 0);
