@@ -155,8 +155,7 @@ def run_ours(args):
     gathered = torch.empty((world, N_SEQS, hq, D), device=dev, dtype=torch.bfloat16) if world > 1 else None
 
     def step(q, k, v):
-        pool.append(0, k, v, rope_k=True, q=q, layout="bhd")
-        pool.decode_attention(0, q, out=out_buf)
+        pool.decode_step(0, q, k, v, out=out_buf)         # RoPE-on-write append + attention, one library call
         if world > 1:
             dist.all_gather_into_tensor(gathered, out_buf)
 

@@ -147,6 +147,15 @@ SKV_API int32_t skv_decode_attn(skv_pool* pool, int32_t layer, const int32_t* se
                         const void* q, void* out, const int32_t* q_pos, int32_t n_q_heads,
                         float eps, void* workspace, size_t workspace_bytes, void* stream);
 
+/* K1 + K3 in one call for the cached decode step of a layer: rotate q (in place) and the new k with the pool's
+ * RoPE table, append k, v at each sequence's current length, then attend
+ * (the sequence apply_rotary_pos_emb_mlx -> cache.update -> attention of src/ollm/llama_mlx.py:284-308 for L == 1).
+ * Sequences are 0..n_seqs-1; q, out: [n_seqs][n_q_heads][head_dim]; k, v: [n_seqs][kv_heads][head_dim], contiguous.
+ * Same workspace as skv_decode_attn.  One host call instead of two halves the per-step host overhead. */
+SKV_API int32_t skv_decode_step(skv_pool* pool, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
+                                void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
 /* K3 without a caller workspace.  This entry point has no counterpart in the reference; it exists for
  * hosts that cannot allocate device memory (a process whose memory is handed out once at start-up,
  * a plugin inside a foreign arena, code that must not trigger a device-synchronising allocation).

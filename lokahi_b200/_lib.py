@@ -78,6 +78,7 @@ SIGNATURES = {
     "skv_gather": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _i32, _vp]),
     "skv_decode_workspace_bytes": (C.c_size_t, [_vp, _i32, _i32]),
     "skv_decode_attn": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp, C.c_size_t, _vp]),
+    "skv_decode_step": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp]),
     "skv_decode_attn_static": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp]),
     "skv_attn_dense": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f, _vp]),
     "skv_prefill_attn_paged": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _f, _vp]),

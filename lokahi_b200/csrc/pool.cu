@@ -872,6 +872,30 @@ int32_t skv_decode_attn(skv_pool* p, int32_t layer, const int32_t* seq_ids, int3
     return SKV_OK;
 }
 
+int32_t skv_decode_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v, void* out,
+                        int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    skv_append_args a{};
+    a.layer = layer;
+    a.n_seqs = n_seqs;
+    a.n_new = 1;
+    a.k = k;
+    a.v = v;
+    a.kv_stride_seq = (int64_t)p->cfg.num_kv_heads * p->cfg.head_dim;
+    a.kv_stride_head = p->cfg.head_dim;
+    a.kv_stride_tok = 0;
+    a.rope_k = 1;
+    a.q_in = q;
+    a.q_out = q;
+    a.n_q_heads = n_q_heads;
+    a.q_stride_seq = (int64_t)n_q_heads * p->cfg.head_dim;
+    a.q_stride_head = p->cfg.head_dim;
+    a.q_stride_tok = 0;
+    int32_t st = skv_append(p, &a, stream);
+    if (st != SKV_OK) return st;
+    return skv_decode_attn(p, layer, nullptr, n_seqs, q, out, nullptr, n_q_heads, eps, workspace, workspace_bytes, stream);
+}
+
 int32_t skv_attn_dense(const void* q, const void* k, const void* v, void* out, const int32_t* positions, int32_t B,
                        int32_t Hq, int32_t Hkv, int32_t Lq, int32_t Lk, int32_t D, int32_t dtype, int32_t causal,
                        float eps, void* stream_) {

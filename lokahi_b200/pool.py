@@ -280,6 +280,25 @@ class PagedPool:
                                         i32_array(q_pos), hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
         return out
 
+    def decode_step(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: float = 1e-12,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """RoPE-on-write append of one token per sequence plus decode attention in one library call.
+        ``q`` ``[n_seqs, q_heads, head_dim]`` is rotated in place; ``k``, ``v`` ``[n_seqs, kv_heads, head_dim]``;
+        sequences are 0..n_seqs-1 and the token goes to each sequence's current length."""
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            self._check_tensor(t, name)
+            if t.dim() != 3 or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous rank-3 tensor")
+        n_seqs, hq, _ = q.shape
+        if k.shape != (n_seqs, self.cfg.num_kv_heads, self.cfg.head_dim) or v.shape != k.shape:
+            raise ValueError("new key states must match cached batch, head, and feature dimensions")
+        if out is None:
+            out = torch.empty_like(q)
+        ws = self.workspace(n_seqs, hq)
+        self._check(lib.skv_decode_step(self._h, layer, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                        hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
+        return out
+
     def decode_attention_static(self, layer: int, q: torch.Tensor, *, seq_ids=None, q_pos=None, eps: float = 1e-12,
                                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``decode_attention`` for callers that may not allocate device memory: the split-K partials

@@ -281,3 +281,22 @@ def test_tensor_core_prefill_at_full_sequence_4096(monkeypatch):
     # both sides are bf16-rounded, so element-wise they may sit two roundings apart: normalised error only
     from parity import parity_errors
     assert parity_errors(out[:, ::8], to_np(ref_all))[0] <= TOL_BF16, "tcgen05 vs CUDA-core at S=4096"
+
+
+def test_decode_step_equals_append_then_attention():
+    rng = np.random.default_rng(55)
+    lens = [5, 16, 300, 1025]
+    pool_a, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, len(lens), 8, 128, 16, lens)
+    rng = np.random.default_rng(55)
+    pool_b, _, _, _, _ = _paged_setup(rng, torch.bfloat16, len(lens), 8, 128, 16, lens)
+    for p in (pool_a, pool_b):
+        p.set_rope(L.rope_inv_freq(128, 500000.0))
+    q = _t(rnd(rng.standard_normal((len(lens), 32, 128), dtype=np.float32)), torch.bfloat16)
+    k = _t(rnd(rng.standard_normal((len(lens), 8, 128), dtype=np.float32)), torch.bfloat16)
+    v = _t(rnd(rng.standard_normal((len(lens), 8, 128), dtype=np.float32)), torch.bfloat16)
+    qa, qb = q.clone(), q.clone()
+    pool_a.append(0, k, v, start_pos=lens, rope_k=True, q=qa, layout="bhd")
+    out_a = pool_a.decode_attention(0, qa)
+    out_b = pool_b.decode_step(0, qb, k, v)
+    assert torch.equal(qa, qb) and torch.equal(out_a, out_b)
+    assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
