@@ -156,6 +156,25 @@ SKV_API int32_t skv_decode_step(skv_pool* pool, int32_t layer, int32_t n_seqs, v
                                 void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
                                 void* stream);
 
+/* K3 with the output all-gather of KV-head sharding fused into the merge kernel (no reference counterpart: the
+ * reference is single-device and concatenates its per-KV-head results in place, mlx_ops.py:152).
+ * Rank `rank` of `world` (<= 8) stores its [n_seqs][n_q_heads][head_dim] output rows with plain peer stores into
+ * slot `rank` of every rank's gathered buffer [world][n_seqs][n_q_heads][head_dim] (out_ptrs[r], peer-mapped device
+ * pointers, e.g. from CUDA IPC or symmetric memory) and then writes `epoch` to flag_ptrs[r][rank].  Epochs must
+ * grow by one per call and callers alternate between two gathered buffers.  skv_gather_wait enqueues a kernel
+ * that waits (bounded, about a second; a timeout sets bit 8 of the pool's status word) until all `world` local
+ * flags reached `epoch`; work enqueued after it on the stream sees every rank's rows. */
+typedef struct skv_peer_gather {
+    int32_t rank, world, epoch;
+    void* const* out_ptrs;        /* host array, world entries */
+    int32_t* const* flag_ptrs;    /* host array, world entries; each points to int32 flags[world] on that rank */
+} skv_peer_gather;
+SKV_API int32_t skv_decode_attn_gather(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
+                                       const void* q, const int32_t* q_pos, int32_t n_q_heads, float eps,
+                                       void* workspace, size_t workspace_bytes, const skv_peer_gather* gather,
+                                       void* stream);
+SKV_API int32_t skv_gather_wait(skv_pool* pool, const int32_t* local_flags, int32_t world, int32_t epoch, void* stream);
+
 /* K3 without a caller workspace.  This entry point has no counterpart in the reference; it exists for
  * hosts that cannot allocate device memory (a process whose memory is handed out once at start-up,
  * a plugin inside a foreign arena, code that must not trigger a device-synchronising allocation).

@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     const int n_attend = attend_count(d, i, seq);
     const int G = d.n_q_heads / pv.num_kv_heads;
     if (t0 >= n_attend) {
-        if (split == 0) {   // nothing to attend: the output row is exactly 0 (mlx_ops.py:118, :146)
+        if (split == 0 && d.fuse_merge) {   // nothing to attend: the output row is exactly 0 (mlx_ops.py:118, :146)
             __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(d.out) + ((int64_t)i * d.n_q_heads + h * G) * kMmaD;
             for (int idx = threadIdx.x; idx < G * kMmaD; idx += kDecodeThreads) orow[idx] = __float2bfloat16_rn(0.f);
         }
@@ -703,8 +703,46 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) a += (s0 + j < n_splits ? sm_w[s0 + j] : 0.f) * v[j];
         }
-        out[dd] = from_f32<T>(a * inv);
+        const T val = from_f32<T>(a * inv);
+        if (d.gather.world == 0) {
+            out[dd] = val;
+        } else {   // the same row into every rank's gathered buffer, slot [rank][i][hq]
+            const int64_t off = (((int64_t)d.gather.rank * d.n_seqs + i) * d.n_q_heads + hq) * D + dd;
+#pragma unroll 1
+            for (int r = 0; r < d.gather.world; ++r) reinterpret_cast<T*>(d.gather.out[r])[off] = val;
+        }
     }
+    if (d.gather.world > 0) {
+        // When the last merge block has stored its rows, tell every rank (itself included) that this rank's
+        // slice of epoch `epoch` has landed.  fence -> ticket -> fence -> flag keeps the rows ahead of the flag.
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            const int n_blocks = (int)(gridDim.x * gridDim.y);
+            if (atomicAdd(d.gather.ticket, 1) == n_blocks - 1) {
+                *d.gather.ticket = 0;
+                __threadfence_system();
+                for (int r = 0; r < d.gather.world; ++r)
+                    *reinterpret_cast<volatile int32_t*>(d.gather.flags[r] + d.gather.rank) = d.gather.epoch;
+            }
+        }
+    }
+}
+
+// Waits (bounded, about a second) until every rank's flag has reached `epoch`; lane r watches rank r.
+__global__ void gather_wait_kernel(const int32_t* flags, int world, int epoch, int32_t* status) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        const volatile int32_t* f = flags + r;
+        const long long start = clock64();
+        while (*f < epoch) {
+            if (clock64() - start > 2000000000LL) {
+                if (status) atomicOr(status, FLAG_WAIT_TIMEOUT);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
 }
 
 template <typename T>
@@ -753,10 +791,13 @@ void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, i
 cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     DecodeLaunch d = d_in;
     const char* fuse = getenv("SKV_DECODE_FUSE");
-    // Measured on B200 at the 64-sequence workload: the in-kernel merge (last-arriving CTA) costs about
-    // 2 us more per call than the separate merge launch (device-wide fences in every CTA plus a serial
-    // tail), so the separate launch is the default; SKV_DECODE_FUSE=1 selects the in-kernel merge.
-    d.fuse_merge = (fuse && fuse[0] == '1') ? 1 : 0;
+    // Measured on B200: the in-kernel merge (last-arriving CTA) costs about 2 us more per call than the
+    // separate merge launch at the full 64-sequence workload and at a quarter of it (device-wide fences in
+    // every CTA plus a serial tail), but saves about 5 us at an eighth of it, where the call is latency-bound.
+    // So it is chosen only for small calls; SKV_DECODE_FUSE=0/1 overrides.
+    d.fuse_merge = d.total_tokens * d.pool.num_kv_heads < 400000 ? 1 : 0;
+    if (d.gather.world > 0) d.fuse_merge = 0;   // the gather lives in the merge kernel
+    if (fuse && (fuse[0] == '0' || fuse[0] == '1') && d.gather.world == 0) d.fuse_merge = fuse[0] == '1';
     const int G = d.n_q_heads / d.pool.num_kv_heads;
     const bool mma_ok = d.dtype == SKV_BF16 && d.pool.head_dim == kMmaD && d.pool.page_size % 16 == 0 && G <= 8 &&
                         !d.force_generic && ((uintptr_t)d.q % 16 == 0);
@@ -787,6 +828,12 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     const int threads = 128;
     return d.dtype == SKV_BF16 ? launch_pdl(decode_reduce_kernel<__nv_bfloat16>, rgrid, dim3(threads), 0, stream, d)
                                : launch_pdl(decode_reduce_kernel<float>, rgrid, dim3(threads), 0, stream, d);
+}
+
+cudaError_t launch_gather_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, cudaStream_t stream) {
+    gather_wait_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, status);
+    count_launches(1);
+    return cudaGetLastError();
 }
 
 }  // namespace skv

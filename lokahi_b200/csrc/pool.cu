@@ -106,7 +106,7 @@ struct skv_pool {
     int32_t* d_page_table = nullptr;
     int32_t* d_lengths = nullptr;
     int32_t* d_status = nullptr;
-    int32_t* d_tickets = nullptr;        // [max_seqs][num_kv_heads], zero between decode calls
+    int32_t* d_tickets = nullptr;        // [max_seqs][num_kv_heads] + 1 (gather), zero between decode calls
     float* d_inv_freq = nullptr;
     // K and V pools as 2-D bf16 tensors [layers*pages*heads*page_size][head_dim] with [16][64] boxes
     alignas(64) CUtensorMap k_map;
@@ -372,8 +372,8 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
         CUDA_TRY(p, cudaMemset(p->d_lengths, 0, p->lengths.size() * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_status, sizeof(int32_t)));
         CUDA_TRY(p, cudaMemset(p->d_status, 0, sizeof(int32_t)));
-        CUDA_TRY(p, cudaMalloc((void**)&p->d_tickets, (size_t)cfg->max_seqs * cfg->num_kv_heads * sizeof(int32_t)));
-        CUDA_TRY(p, cudaMemset(p->d_tickets, 0, (size_t)cfg->max_seqs * cfg->num_kv_heads * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_tickets, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 1) * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMemset(p->d_tickets, 0, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 1) * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_inv_freq, (size_t)cfg->head_dim / 2 * sizeof(float)));
         CUDA_TRY(p, p->ring.init());
         CUDA_TRY(p, cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
@@ -868,7 +868,52 @@ int32_t skv_decode_attn(skv_pool* p, int32_t layer, const int32_t* seq_ids, int3
     D.k_map = p->has_maps ? &p->k_map : nullptr;
     D.v_map = p->has_maps ? &p->v_map : nullptr;
     D.tickets = p->d_tickets;
+    D.total_tokens = total;
     CUDA_TRY(p, launch_decode(D, stream));
+    return SKV_OK;
+}
+
+int32_t skv_decode_attn_gather(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q,
+                               const int32_t* q_pos, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                               const skv_peer_gather* g, void* stream_) {
+    if (!p || !g) return SKV_ERR_BAD_ARG;
+    if (g->world < 1 || g->world > 8 || g->rank < 0 || g->rank >= g->world || !g->out_ptrs || !g->flag_ptrs)
+        return p->fail(SKV_ERR_BAD_ARG, "peer gather needs 1 <= world <= 8, a rank inside it and both pointer arrays");
+    for (int32_t r = 0; r < g->world; ++r)
+        if (!g->out_ptrs[r] || !g->flag_ptrs[r]) return p->fail(SKV_ERR_BAD_ARG, "peer pointer %d is null", r);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    DeviceGuard guard(p);
+    DecodeLaunch D{};
+    int64_t total = 0;
+    int32_t launchable = 0;
+    // q doubles as the non-null `out` argument of the shared front half; the merge kernel never writes it here
+    int32_t st = prepare_decode(p, layer, seq_ids, n_seqs, q_pos, n_q_heads, q, const_cast<void*>(q), eps, stream, &D, &total, &launchable);
+    if (st != SKV_OK || !launchable) return st;
+    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
+    size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
+    if (!workspace || workspace_bytes < need)
+        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need);
+    D.ws_acc = (float*)workspace;
+    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
+    D.total_tokens = total;
+    D.out = nullptr;
+    D.gather.world = g->world;
+    D.gather.rank = g->rank;
+    D.gather.epoch = g->epoch;
+    D.gather.ticket = p->d_tickets + (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads;
+    for (int32_t r = 0; r < g->world; ++r) {
+        D.gather.out[r] = g->out_ptrs[r];
+        D.gather.flags[r] = g->flag_ptrs[r];
+    }
+    CUDA_TRY(p, launch_decode(D, stream));
+    return SKV_OK;
+}
+
+int32_t skv_gather_wait(skv_pool* p, const int32_t* local_flags, int32_t world, int32_t epoch, void* stream_) {
+    if (!p || !local_flags || world < 1 || world > 8) return SKV_ERR_BAD_ARG;
+    if (p->host_only) return SKV_OK;
+    DeviceGuard guard(p);
+    CUDA_TRY(p, launch_gather_wait(local_flags, world, epoch, p->d_status, (cudaStream_t)stream_));
     return SKV_OK;
 }
 
@@ -1081,7 +1126,7 @@ int32_t skv_check_device_status(skv_pool* p, void* stream_, int32_t* flag_out) {
     if (flag != 0) {
         CUDA_TRY(p, cudaMemsetAsync(p->d_status, 0, sizeof flag, stream));
         // a kernel that gave up may have left arrival counters behind
-        CUDA_TRY(p, cudaMemsetAsync(p->d_tickets, 0, (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads * sizeof(int32_t), stream));
+        CUDA_TRY(p, cudaMemsetAsync(p->d_tickets, 0, ((size_t)p->cfg.max_seqs * p->cfg.num_kv_heads + 1) * sizeof(int32_t), stream));
         return p->fail(SKV_ERR_DEVICE_FLAG, "device status word 0x%x (1 bad page id, 2 bad length, 4 bad sequence id)", flag);
     }
     return SKV_OK;

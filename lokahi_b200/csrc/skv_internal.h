@@ -27,7 +27,7 @@ enum : int32_t {
     FLAG_BAD_PAGE = 1,       // page-table entry outside [0, num_pages)
     FLAG_BAD_LENGTH = 2,     // length beyond the page-table row
     FLAG_BAD_SEQ = 4,        // sequence id outside [0, max_seqs)
-    FLAG_WAIT_TIMEOUT = 8,   // a bounded wait on an mbarrier ran out
+    FLAG_WAIT_TIMEOUT = 8,   // a bounded wait (mbarrier, peer flag) ran out
 };
 
 // Per-call metadata uploaded through the staging ring.
@@ -63,6 +63,17 @@ struct GatherLaunch {
 };
 cudaError_t launch_gather(const GatherLaunch& g, cudaStream_t stream);
 
+// Output gather fused into the merge kernel: every rank stores its output rows straight into all ranks'
+// gathered buffers over NVLink (plain peer stores) and then raises its flag on each peer.
+struct PeerGatherView {
+    int32_t world;               // 0: no gather, the merge kernel writes `out`
+    int32_t rank;
+    int32_t epoch;               // value written to the flags when this call's rows have landed
+    int32_t* ticket;             // device counter of finished merge blocks (zero between calls)
+    void* out[8];                // per rank: base of its gathered buffer [world][n_seqs][q_heads][head_dim]
+    int32_t* flags[8];           // per rank: its flag array [world]
+};
+
 struct DecodeLaunch {
     PoolView pool;
     int32_t layer, n_seqs, n_q_heads, dtype;
@@ -82,7 +93,9 @@ struct DecodeLaunch {
     // [n_seqs][kv_heads] arrival counters, zero between calls: the CTA that finishes last for a
     // (sequence, KV head) merges the partials itself, so no separate merge launch is needed
     int32_t* tickets;
-    int32_t fuse_merge;          // 0: leave the merge to decode_reduce_kernel (kept for A/B measurements)
+    int32_t fuse_merge;          // 0: leave the merge to decode_reduce_kernel
+    int64_t total_tokens;        // host's sum of the attended lengths (drives the plan and the merge choice)
+    PeerGatherView gather;
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
 // chunk length (tokens handled by one CTA) and the number of splits that follow from it
@@ -124,6 +137,8 @@ int32_t prepare_decode(skv_pool* pool, int32_t layer, const int32_t* seq_ids, in
                        int64_t* total_tokens, int32_t* launchable);
 int32_t pool_fail(skv_pool* pool, int32_t code, const char* message);
 int32_t pool_device(const skv_pool* pool);
+
+cudaError_t launch_gather_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, cudaStream_t stream);
 
 // process-wide count of kernel launches issued by this library
 void count_launches(int n);

@@ -280,6 +280,31 @@ class PagedPool:
                                         i32_array(q_pos), hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
         return out
 
+    def decode_attention_gather(self, layer: int, q: torch.Tensor, gather, *, seq_ids=None, q_pos=None,
+                                eps: float = 1e-12, wait: bool = True) -> torch.Tensor:
+        """``decode_attention`` under KV-head sharding with the all-gather fused into the merge kernel:
+        this rank's rows go by peer stores into every rank's gathered buffer (``gather`` is a
+        ``sharding.PeerGather``).  Returns this rank's gathered view ``[world, n_seqs, local_q_heads, head_dim]``;
+        with ``wait`` a kernel that waits for all ranks' rows is enqueued first."""
+        self._check_tensor(q, "q")
+        if q.dim() != 3 or not q.is_contiguous():
+            raise ValueError("q must be a contiguous [n_seqs, q_heads, head_dim] tensor")
+        n_seqs, hq, _ = q.shape
+        if tuple(gather.shape) != (gather.shard.world, n_seqs, hq, self.cfg.head_dim):
+            raise ValueError("gather buffers do not match q")
+        epoch, ptrs, view = gather.begin()
+        world = gather.shard.world
+        out_arr = (C.c_void_p * world)(*ptrs)
+        flag_arr = (C.c_void_p * world)(*gather.flag_ptrs)
+        g = _lib.SkvPeerGather(rank=gather.shard.rank, world=world, epoch=epoch,
+                               out_ptrs=C.cast(out_arr, C.POINTER(C.c_void_p)), flag_ptrs=C.cast(flag_arr, C.POINTER(C.c_void_p)))
+        ws = self.workspace(n_seqs, hq)
+        self._check(lib.skv_decode_attn_gather(self._h, layer, i32_array(seq_ids), n_seqs, q.data_ptr(), i32_array(q_pos), hq,
+                                               float(eps), ws.data_ptr(), ws.numel(), C.byref(g), self.stream))
+        if wait:
+            self._check(lib.skv_gather_wait(self._h, gather.flags.data_ptr(), world, epoch, self.stream))
+        return view
+
     def decode_step(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: float = 1e-12,
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """RoPE-on-write append of one token per sequence plus decode attention in one library call.

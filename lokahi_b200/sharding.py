@@ -74,3 +74,48 @@ def gather_head_outputs(out_local: torch.Tensor, shard: HeadShard, group: Option
     shape = list(out_local.shape)
     shape[head_dim] = shard.world * shape[head_dim]
     return moved.reshape(shape)
+
+
+class PeerGather:
+    """Buffers for the output gather that is fused into the decode merge kernel.
+
+    Every rank holds two gathered buffers ``[world, n_seqs, local_q_heads, head_dim]`` (used alternately) and
+    a flag array ``[world]``; all of them are peer-mapped (torch symmetric memory over NVLink), so a rank's
+    merge kernel can store its rows straight into every rank's buffer and raise its flag there.  With
+    ``world == 1`` plain device tensors are used, which exercises the same kernel path on one GPU.
+    K/V never cross GPUs; only the outputs do.
+    """
+
+    def __init__(self, shard: HeadShard, n_seqs: int, head_dim: int, dtype: torch.dtype, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None):
+        self.shard = shard
+        self.shape = (shard.world, n_seqs, shard.local_q_heads, head_dim)
+        self.epoch = 0
+        esize = torch.empty((), dtype=dtype).element_size()
+        self.slab_bytes = int(torch.Size(self.shape).numel()) * esize
+        if shard.world == 1:
+            self.buf = torch.zeros((2,) + self.shape, dtype=dtype, device=device)
+            self.flags = torch.zeros((1,), dtype=torch.int32, device=device)
+            self.buf_ptrs = [self.buf.data_ptr()]
+            self.flag_ptrs = [self.flags.data_ptr()]
+        else:
+            import torch.distributed._symmetric_memory as symm
+            group = group or dist.group.WORLD
+            self.buf = symm.empty((2,) + self.shape, dtype=dtype, device=device)
+            self.flags = symm.empty((shard.world,), dtype=torch.int32, device=device)
+            self.buf.zero_()
+            self.flags.zero_()
+            hb = symm.rendezvous(self.buf, group.group_name)
+            hf = symm.rendezvous(self.flags, group.group_name)
+            self.buf_ptrs = [int(p) for p in hb.buffer_ptrs]
+            self.flag_ptrs = [int(p) for p in hf.buffer_ptrs]
+            self._handles = (hb, hf)
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)
+
+    def begin(self):
+        """Advance to the next epoch; returns (epoch, per-rank output base pointers, local gathered view)."""
+        self.epoch += 1
+        parity = self.epoch & 1
+        ptrs = [p + parity * self.slab_bytes for p in self.buf_ptrs]
+        return self.epoch, ptrs, self.buf[parity]

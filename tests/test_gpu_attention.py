@@ -300,3 +300,18 @@ def test_decode_step_equals_append_then_attention():
     out_b = pool_b.decode_step(0, qb, k, v)
     assert torch.equal(qa, qb) and torch.equal(out_a, out_b)
     assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
+
+
+def test_fused_gather_path_on_one_gpu_matches_plain_decode():
+    """world == 1 runs the same merge-kernel code (peer stores, ticket, flag, wait kernel) against local buffers."""
+    rng = np.random.default_rng(71)
+    lens = [1, 40, 777, 2050, 0]
+    pool, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, len(lens), 8, 128, 16, lens)
+    q = _t(rnd(rng.standard_normal((len(lens), 32, 128), dtype=np.float32)), torch.bfloat16)
+    expect = pool.decode_attention(0, q)
+    gather = L.PeerGather(L.HeadShard(0, 1, 32, 8), len(lens), 128, torch.bfloat16, torch.device(DEV))
+    for _ in range(3):     # epochs 1..3 alternate between the two gathered buffers
+        view = pool.decode_attention_gather(0, q, gather)
+        torch.cuda.synchronize()
+        assert torch.equal(view[0], expect)
+    assert int(gather.flags[0]) == 3 and pool.check_device_status() == 0
