@@ -129,7 +129,7 @@ def run_ours(args):
     total_steps = W + K
     lens0 = workload_lengths()
     rng = np.random.default_rng(SEED + 1)
-    cap = lens0 + 2 * total_steps + 2 * P                   # room for both legs
+    cap = lens0 + 3 * total_steps + 2 * P                   # room for the timed leg, the instrumented pass and the e2e leg
     pages_per_seq = int(-(-cap.max() // P))
     pages_each = (-(-cap // P)).astype(np.int64)
     n_pages = int(pages_each.sum()) + 16
@@ -153,11 +153,27 @@ def run_ours(args):
     v_all = torch.randn((total_steps, N_SEQS, hkv, D), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
     out_buf = torch.empty((N_SEQS, hq, D), device=dev, dtype=torch.bfloat16)
     gathered = torch.empty((world, N_SEQS, hq, D), device=dev, dtype=torch.bfloat16) if world > 1 else None
+    fused_gather = world > 1 and args.gather == "fused"
+    peer = L.PeerGather(shard, N_SEQS, D, torch.bfloat16, dev) if fused_gather else None
+    state = {"view": gathered}
+
+    def attend(q):
+        """Decode attention (+ output gather under sharding); returns the tensor a consumer would read."""
+        if fused_gather:      # merge kernel stores into every rank's buffer, then a bounded wait kernel
+            state["view"] = pool.decode_attention_gather(0, q, peer)
+        else:
+            pool.decode_attention(0, q, out=out_buf)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, out_buf)
 
     def step(q, k, v):
-        pool.decode_step(0, q, k, v, out=out_buf)         # RoPE-on-write append + attention, one library call
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, out_buf)
+        if world == 1:
+            pool.decode_step(0, q, k, v, out=out_buf)     # RoPE-on-write append + attention, one library call
+        elif fused_gather:                                # ... plus the output gather by peer stores and the wait
+            state["view"] = pool.decode_step_gather(0, q, k, v, peer)
+        else:
+            pool.append(0, k, v, rope_k=True, q=q, layout="bhd")
+            attend(q)
 
     def barrier():
         if world > 1:
@@ -174,27 +190,40 @@ def run_ours(args):
         time.sleep(0.3)
     launches0 = L._lib.lib.skv_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     barrier()
     ev0.record()
     for i in range(K):
         j = W + i
-        pool.append(0, k_all[j], v_all[j], rope_k=True, q=q_all[j], layout="bhd")
-        attn_ev[i][0].record()
-        pool.decode_attention(0, q_all[j], out=out_buf)
-        attn_ev[i][1].record()
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, out_buf)
+        step(q_all[j], k_all[j], v_all[j])
     ev1.record()
     barrier()
     launches = L._lib.lib.skv_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     ms_total = ev0.elapsed_time(ev1)
+    # instrumented pass (not part of `value`): the same steps with CUDA events around the attention call only
+    # (split-K kernel + merge kernel, under sharding with the fused gather and its wait), for the roofline
+    K2 = min(K, 32)
+    attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K2)]
+    barrier()                                             # rank 0 spent time stopping the clock sampler
+    for i in range(K2):
+        j = W + i
+        pool.append(0, k_all[j], v_all[j], rope_k=True, q=q_all[j], layout="bhd")
+        attn_ev[i][0].record()
+        if fused_gather:
+            attend(q_all[j])
+        else:
+            pool.decode_attention(0, q_all[j], out=out_buf)
+        attn_ev[i][1].record()
+        if world > 1 and not fused_gather:
+            dist.all_gather_into_tensor(gathered, out_buf)
+    barrier()
     attn_ms = np.array([a.elapsed_time(b) for a, b in attn_ev])
+    if K2 > 4:
+        attn_ms = attn_ms[2:]                             # the first launches after a barrier absorb rank skew
     if pool.check_device_status() != 0:
         raise SystemExit("device status flag set during the timed region")
-    lens_timed = lens0[None, :] + W + 1 + np.arange(K)[:, None]      # attended tokens per step
-    algo_bytes = float(np.mean([algorithmic_bytes(lens_timed[i], hq, hkv) for i in range(K)]))
+    lens_timed = lens0[None, :] + W + K + 1 + np.arange(K2)[:, None]      # attended tokens per instrumented step
+    algo_bytes = float(np.mean([algorithmic_bytes(lens_timed[i], hq, hkv) for i in range(K2 - len(attn_ms), K2)]))
 
     # ---- end-to-end leg: pinned host inputs, output read back every step ----------------------------------
     Ke = K
@@ -210,7 +239,7 @@ def run_ours(args):
     def e2e_step(i):
         qkv_d.copy_(qkv_h[i], non_blocking=True)
         step(q_d, k_d, v_d)
-        out_h.copy_((gathered if world > 1 else out_buf).view(out_h.shape), non_blocking=True)
+        out_h.copy_((state["view"] if world > 1 else out_buf).view(out_h.shape), non_blocking=True)
         torch.cuda.current_stream().synchronize()          # a decode loop consumes the result before the next step
 
     for i in range(min(W, Ke)):
@@ -243,7 +272,7 @@ def run_ours(args):
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "n_seqs": N_SEQS, "context": [CTX_LO, CTX_HI], "q_heads": HQ, "kv_heads": HKV,
                        "head_dim": D, "page_size": P, "rope_theta": THETA, "layers": 1,
-                       "parallelism": f"kv_head_shard{world}" if world > 1 else "single",
+                       "parallelism": (f"kv_head_shard{world}, output gather " + ("fused into the merge kernel (peer stores)" if fused_gather else "NCCL all-gather")) if world > 1 else "single",
                        "l2": "inputs larger than L2 (KV working set per step >= 1 GB / n_gpus)"},
             "e2e": {"value": N_SEQS * Ke / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / Ke,
                     "h2d_bytes_per_step": int(q_d.numel() + k_d.numel() + v_d.numel()) * 2,
@@ -257,7 +286,7 @@ def run_ours(args):
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
-            result["cpu_baseline"] = cpu_baseline_sample(pool, kp, vp, lens0 + W + K + min(W, Ke) + Ke, hq, hkv)
+            result["cpu_baseline"] = cpu_baseline_sample(pool, kp, vp, lens0 + W + K + K2 + min(W, Ke) + Ke, hq, hkv)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -654,6 +683,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: how the per-rank attention outputs are gathered")
     ap.add_argument("--emulate-shard", type=int, default=1, help=argparse.SUPPRESS)
     ap.add_argument("--workload", choices=["decode", "prefill", "decoder", "longctx"], default="decode",
                     help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")

@@ -168,11 +168,16 @@ typedef struct skv_peer_gather {
     int32_t rank, world, epoch;
     void* const* out_ptrs;        /* host array, world entries */
     int32_t* const* flag_ptrs;    /* host array, world entries; each points to int32 flags[world] on that rank */
+    const int32_t* wait_flags;    /* this rank's own flag array: when not NULL the call also enqueues skv_gather_wait */
 } skv_peer_gather;
 SKV_API int32_t skv_decode_attn_gather(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
                                        const void* q, const int32_t* q_pos, int32_t n_q_heads, float eps,
                                        void* workspace, size_t workspace_bytes, const skv_peer_gather* gather,
                                        void* stream);
+/* skv_decode_step with the fused gather: append (RoPE on write, q rotated in place), attend, gather, wait. */
+SKV_API int32_t skv_decode_step_gather(skv_pool* pool, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
+                                       int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                                       const skv_peer_gather* gather, void* stream);
 SKV_API int32_t skv_gather_wait(skv_pool* pool, const int32_t* local_flags, int32_t world, int32_t epoch, void* stream);
 
 /* K3 without a caller workspace.  This entry point has no counterpart in the reference; it exists for

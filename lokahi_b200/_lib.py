@@ -53,7 +53,7 @@ class SkvAppendArgs(C.Structure):
 
 class SkvPeerGather(C.Structure):
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("epoch", C.c_int32),
-                ("out_ptrs", C.POINTER(C.c_void_p)), ("flag_ptrs", C.POINTER(C.c_void_p))]
+                ("out_ptrs", C.POINTER(C.c_void_p)), ("flag_ptrs", C.POINTER(C.c_void_p)), ("wait_flags", C.c_void_p)]
 
 
 _i32, _i64, _vp, _f = C.c_int32, C.c_int64, C.c_void_p, C.c_float
@@ -84,6 +84,7 @@ SIGNATURES = {
     "skv_decode_workspace_bytes": (C.c_size_t, [_vp, _i32, _i32]),
     "skv_decode_attn": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp, C.c_size_t, _vp]),
     "skv_decode_attn_gather": (_i32, [_vp, _i32, _pi32, _i32, _vp, _pi32, _i32, _f, _vp, C.c_size_t, _vp, _vp]),
+    "skv_decode_step_gather": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp, _vp]),
     "skv_gather_wait": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "skv_decode_step": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp]),
     "skv_decode_attn_static": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp]),

@@ -906,6 +906,7 @@ int32_t skv_decode_attn_gather(skv_pool* p, int32_t layer, const int32_t* seq_id
         D.gather.flags[r] = g->flag_ptrs[r];
     }
     CUDA_TRY(p, launch_decode(D, stream));
+    if (g->wait_flags) CUDA_TRY(p, launch_gather_wait(g->wait_flags, g->world, g->epoch, p->d_status, stream));
     return SKV_OK;
 }
 
@@ -939,6 +940,29 @@ int32_t skv_decode_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, con
     int32_t st = skv_append(p, &a, stream);
     if (st != SKV_OK) return st;
     return skv_decode_attn(p, layer, nullptr, n_seqs, q, out, nullptr, n_q_heads, eps, workspace, workspace_bytes, stream);
+}
+
+int32_t skv_decode_step_gather(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
+                               int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                               const skv_peer_gather* gather, void* stream) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    skv_append_args a{};
+    a.layer = layer;
+    a.n_seqs = n_seqs;
+    a.n_new = 1;
+    a.k = k;
+    a.v = v;
+    a.kv_stride_seq = (int64_t)p->cfg.num_kv_heads * p->cfg.head_dim;
+    a.kv_stride_head = p->cfg.head_dim;
+    a.rope_k = 1;
+    a.q_in = q;
+    a.q_out = q;
+    a.n_q_heads = n_q_heads;
+    a.q_stride_seq = (int64_t)n_q_heads * p->cfg.head_dim;
+    a.q_stride_head = p->cfg.head_dim;
+    int32_t st = skv_append(p, &a, stream);
+    if (st != SKV_OK) return st;
+    return skv_decode_attn_gather(p, layer, nullptr, n_seqs, q, nullptr, n_q_heads, eps, workspace, workspace_bytes, gather, stream);
 }
 
 int32_t skv_attn_dense(const void* q, const void* k, const void* v, void* out, const int32_t* positions, int32_t B,

@@ -292,17 +292,10 @@ class PagedPool:
         n_seqs, hq, _ = q.shape
         if tuple(gather.shape) != (gather.shard.world, n_seqs, hq, self.cfg.head_dim):
             raise ValueError("gather buffers do not match q")
-        epoch, ptrs, view = gather.begin()
-        world = gather.shard.world
-        out_arr = (C.c_void_p * world)(*ptrs)
-        flag_arr = (C.c_void_p * world)(*gather.flag_ptrs)
-        g = _lib.SkvPeerGather(rank=gather.shard.rank, world=world, epoch=epoch,
-                               out_ptrs=C.cast(out_arr, C.POINTER(C.c_void_p)), flag_ptrs=C.cast(flag_arr, C.POINTER(C.c_void_p)))
+        desc, view = gather.begin(wait)
         ws = self.workspace(n_seqs, hq)
         self._check(lib.skv_decode_attn_gather(self._h, layer, i32_array(seq_ids), n_seqs, q.data_ptr(), i32_array(q_pos), hq,
-                                               float(eps), ws.data_ptr(), ws.numel(), C.byref(g), self.stream))
-        if wait:
-            self._check(lib.skv_gather_wait(self._h, gather.flags.data_ptr(), world, epoch, self.stream))
+                                               float(eps), ws.data_ptr(), ws.numel(), C.byref(desc), self.stream))
         return view
 
     def decode_step(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: float = 1e-12,
@@ -323,6 +316,17 @@ class PagedPool:
         self._check(lib.skv_decode_step(self._h, layer, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                         hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
         return out
+
+    def decode_step_gather(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gather, *,
+                           eps: float = 1e-12) -> torch.Tensor:
+        """``decode_step`` under KV-head sharding: append, attend, fused output gather and wait in one library call.
+        Returns this rank's gathered view ``[world, n_seqs, local_q_heads, head_dim]``."""
+        n_seqs, hq, _ = q.shape
+        desc, view = gather.begin(True)
+        ws = self.workspace(n_seqs, hq)
+        self._check(lib.skv_decode_step_gather(self._h, layer, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(), hq, float(eps),
+                                               ws.data_ptr(), ws.numel(), C.byref(desc), self.stream))
+        return view
 
     def decode_attention_static(self, layer: int, q: torch.Tensor, *, seq_ids=None, q_pos=None, eps: float = 1e-12,
                                 out: Optional[torch.Tensor] = None) -> torch.Tensor:

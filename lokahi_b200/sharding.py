@@ -113,9 +113,31 @@ class PeerGather:
             torch.cuda.synchronize(device)
             dist.barrier(group=group)
 
-    def begin(self):
-        """Advance to the next epoch; returns (epoch, per-rank output base pointers, local gathered view)."""
+    def _descriptors(self):
+        # the two argument blocks (one per buffer parity) are built once: a decode step must not pay for
+        # marshalling 2 x world pointers every time
+        import ctypes as C
+        from . import _lib
+        if not hasattr(self, "_desc"):
+            world = self.shard.world
+            self._keep, self._desc = [], []
+            flag_arr = (C.c_void_p * world)(*self.flag_ptrs)
+            for parity in (0, 1):
+                out_arr = (C.c_void_p * world)(*[p + parity * self.slab_bytes for p in self.buf_ptrs])
+                d = _lib.SkvPeerGather(rank=self.shard.rank, world=world, epoch=0,
+                                       out_ptrs=C.cast(out_arr, C.POINTER(C.c_void_p)),
+                                       flag_ptrs=C.cast(flag_arr, C.POINTER(C.c_void_p)), wait_flags=self.flags.data_ptr())
+                self._keep.append((out_arr, flag_arr))
+                self._desc.append(d)
+            self._views = [self.buf[0], self.buf[1]]
+        return self._desc
+
+    def begin(self, wait: bool = True):
+        """Advance to the next epoch; returns (argument block for the library call, local gathered view)."""
+        desc = self._descriptors()
         self.epoch += 1
         parity = self.epoch & 1
-        ptrs = [p + parity * self.slab_bytes for p in self.buf_ptrs]
-        return self.epoch, ptrs, self.buf[parity]
+        d = desc[parity]
+        d.epoch = self.epoch
+        d.wait_flags = self.flags.data_ptr() if wait else None
+        return d, self._views[parity]
