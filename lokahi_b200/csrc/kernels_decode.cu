@@ -6,7 +6,9 @@
 // allowed, running (max, sum, weighted V) merged across key chunks (:125-144), and
 // out = wv / max(s, eps) so that a row with no allowed key is exactly 0 (:118, :146).
 //
-// Two kernels produce the same partials (m, l, acc[D]) per (sequence, query head, split):
+// Three kernels produce the same partials (m, l, acc[D]) per (sequence, query head, split); the third,
+// decode_tma_kernel (described at its definition), is decode_mma_kernel with K/V staged through shared memory
+// by TMA and is the default where it applies:
 //   * decode_generic_kernel: CUDA cores, float32 or bf16 storage, any head_dim <= 256, any group
 //     size; one CTA per query head, so K/V of a KV head are re-read by its G query heads (L2).
 //   * decode_mma_kernel: bf16, head_dim 128, group size <= 8.  One CTA serves all G query heads of
