@@ -180,6 +180,19 @@ SKV_API int32_t skv_decode_step_gather(skv_pool* pool, int32_t layer, int32_t n_
                                        const skv_peer_gather* gather, void* stream);
 SKV_API int32_t skv_gather_wait(skv_pool* pool, const int32_t* local_flags, int32_t world, int32_t epoch, void* stream);
 
+/* Sequence sharding (no reference counterpart; the merge is the reference's own chunk-merge rule,
+ * src/ollm/backends/mlx_ops.py:125-144, applied across ranks instead of across key blocks).
+ * skv_decode_partial: K3 over the keys THIS pool holds, writing un-normalised float32 rows
+ *   partial_out[n_seqs][n_q_heads][head_dim + 2] = (weighted V sum relative to m, m, l); q_pos are positions in this
+ *   pool's own token numbering (a negative position means "none of my keys": l = 0).
+ * skv_merge_partials: merges n_parts (<= 128) such buffers (part p at parts + p * part_stride floats) of n_rows =
+ *   n_seqs * n_q_heads rows and writes out[n_rows][head_dim] = wv / max(s, eps) in `dtype`. */
+SKV_API int32_t skv_decode_partial(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q,
+                                   const int32_t* q_pos, int32_t n_q_heads, void* workspace, size_t workspace_bytes,
+                                   float* partial_out, void* stream);
+SKV_API int32_t skv_merge_partials(const float* parts, int32_t n_parts, int64_t part_stride, int32_t n_rows,
+                                   int32_t head_dim, float eps, void* out, int32_t dtype, void* stream);
+
 /* K3 without a caller workspace.  This entry point has no counterpart in the reference; it exists for
  * hosts that cannot allocate device memory (a process whose memory is handed out once at start-up,
  * a plugin inside a foreign arena, code that must not trigger a device-synchronising allocation).

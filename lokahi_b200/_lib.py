@@ -85,6 +85,8 @@ SIGNATURES = {
     "skv_decode_attn": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp, C.c_size_t, _vp]),
     "skv_decode_attn_gather": (_i32, [_vp, _i32, _pi32, _i32, _vp, _pi32, _i32, _f, _vp, C.c_size_t, _vp, _vp]),
     "skv_decode_step_gather": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp, _vp]),
+    "skv_decode_partial": (_i32, [_vp, _i32, _pi32, _i32, _vp, _pi32, _i32, _vp, C.c_size_t, _vp, _vp]),
+    "skv_merge_partials": (_i32, [_vp, _i32, _i64, _i32, _i32, _f, _vp, _i32, _vp]),
     "skv_gather_wait": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "skv_decode_step": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp]),
     "skv_decode_attn_static": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp]),

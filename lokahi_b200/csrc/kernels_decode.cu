@@ -705,6 +705,15 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) a += (s0 + j < n_splits ? sm_w[s0 + j] : 0.f) * v[j];
         }
+        if (d.partial_out) {   // un-normalised partial for a cross-rank merge: (acc, m, l) relative to M
+            float* prow = d.partial_out + ((int64_t)i * d.n_q_heads + hq) * (D + 2);
+            prow[dd] = a;
+            if (dd == 0) {
+                prow[D] = M;
+                prow[D + 1] = L;
+            }
+            continue;
+        }
         const T val = from_f32<T>(a * inv);
         if (d.gather.world == 0) {
             out[dd] = val;
@@ -728,6 +737,43 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
                     *reinterpret_cast<volatile int32_t*>(d.gather.flags[r] + d.gather.rank) = d.gather.epoch;
             }
         }
+    }
+}
+
+// Merge of partial rows (acc[D], m, l) from several key ranges of the same query rows (sequence sharding, or any
+// split of the keys): the reference's chunk-merge rule (mlx_ops.py:125-144) and out = wv / max(s, eps).
+// parts[p] starts at parts + p * part_stride; each holds [n_rows][D + 2] floats.  grid n_rows, 128 threads.
+template <typename T>
+__global__ void __launch_bounds__(128) merge_partials_kernel(const float* __restrict__ parts, int n_parts, int64_t part_stride,
+                                                             int D, float eps, T* __restrict__ out) {
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float sm_w[128];
+    __shared__ float sm_red[8];
+    float m = -INFINITY, l = 0.f;
+    if (tid < n_parts) {
+        const float* prow = parts + tid * part_stride + (int64_t)row * (D + 2);
+        l = prow[D + 1];
+        m = l > 0.f ? prow[D] : -INFINITY;
+    }
+    float M = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) sm_red[warp] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3]));
+    const float w = l > 0.f ? expf(m - M) : 0.f;
+    sm_w[tid] = w;
+    float L = w * l;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (lane == 0) sm_red[4 + warp] = L;
+    __syncthreads();
+    L = (sm_red[4] + sm_red[5]) + (sm_red[6] + sm_red[7]);
+    const float inv = 1.0f / fmaxf(L, eps);
+    for (int dd = tid; dd < D; dd += 128) {
+        float a = 0.f;
+        for (int p = 0; p < n_parts; ++p) a += sm_w[p] * parts[p * part_stride + (int64_t)row * (D + 2) + dd];
+        out[(int64_t)row * D + dd] = from_f32<T>(a * inv);
     }
 }
 
@@ -798,8 +844,8 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     // every CTA plus a serial tail), but saves about 5 us at an eighth of it, where the call is latency-bound.
     // So it is chosen only for small calls; SKV_DECODE_FUSE=0/1 overrides.
     d.fuse_merge = d.total_tokens * d.pool.num_kv_heads < 400000 ? 1 : 0;
-    if (d.gather.world > 0) d.fuse_merge = 0;   // the gather lives in the merge kernel
-    if (fuse && (fuse[0] == '0' || fuse[0] == '1') && d.gather.world == 0) d.fuse_merge = fuse[0] == '1';
+    if (d.gather.world > 0 || d.partial_out) d.fuse_merge = 0;   // the gather / the partial output live in the merge kernel
+    if (fuse && (fuse[0] == '0' || fuse[0] == '1') && d.gather.world == 0 && !d.partial_out) d.fuse_merge = fuse[0] == '1';
     const int G = d.n_q_heads / d.pool.num_kv_heads;
     const bool mma_ok = d.dtype == SKV_BF16 && d.pool.head_dim == kMmaD && d.pool.page_size % 16 == 0 && G <= 8 &&
                         !d.force_generic && ((uintptr_t)d.q % 16 == 0);
@@ -830,6 +876,18 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     const int threads = 128;
     return d.dtype == SKV_BF16 ? launch_pdl(decode_reduce_kernel<__nv_bfloat16>, rgrid, dim3(threads), 0, stream, d)
                                : launch_pdl(decode_reduce_kernel<float>, rgrid, dim3(threads), 0, stream, d);
+}
+
+cudaError_t launch_merge_partials(const float* parts, int32_t n_parts, int64_t part_stride, int32_t n_rows, int32_t head_dim,
+                                  float eps, void* out, int32_t dtype, cudaStream_t stream) {
+    if (dtype == SKV_BF16)
+        merge_partials_kernel<__nv_bfloat16><<<n_rows, 128, 0, stream>>>(parts, n_parts, part_stride, head_dim, eps,
+                                                                       reinterpret_cast<__nv_bfloat16*>(out));
+    else
+        merge_partials_kernel<float><<<n_rows, 128, 0, stream>>>(parts, n_parts, part_stride, head_dim, eps,
+                                                               reinterpret_cast<float*>(out));
+    count_launches(1);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_gather_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, cudaStream_t stream) {

@@ -910,6 +910,39 @@ int32_t skv_decode_attn_gather(skv_pool* p, int32_t layer, const int32_t* seq_id
     return SKV_OK;
 }
 
+int32_t skv_decode_partial(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q, const int32_t* q_pos,
+                           int32_t n_q_heads, void* workspace, size_t workspace_bytes, float* partial_out, void* stream_) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (!partial_out && !p->host_only) return p->fail(SKV_ERR_BAD_ARG, "partial_out must be given");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    DeviceGuard guard(p);
+    DecodeLaunch D{};
+    int64_t total = 0;
+    int32_t launchable = 0;
+    int32_t st = prepare_decode(p, layer, seq_ids, n_seqs, q_pos, n_q_heads, q, partial_out, 0.f, stream, &D, &total, &launchable);
+    if (st != SKV_OK || !launchable) return st;
+    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
+    size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
+    if (!workspace || workspace_bytes < need)
+        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need);
+    D.ws_acc = (float*)workspace;
+    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
+    D.total_tokens = total;
+    D.out = nullptr;
+    D.partial_out = partial_out;
+    CUDA_TRY(p, launch_decode(D, stream));
+    return SKV_OK;
+}
+
+int32_t skv_merge_partials(const float* parts, int32_t n_parts, int64_t part_stride, int32_t n_rows, int32_t head_dim, float eps,
+                           void* out, int32_t dtype, void* stream) {
+    if (!parts || !out || n_parts < 1 || n_parts > 128 || n_rows < 0 || head_dim <= 0) return SKV_ERR_BAD_ARG;
+    if (dtype != SKV_F32 && dtype != SKV_BF16) return SKV_ERR_BAD_ARG;
+    if (n_rows == 0) return SKV_OK;
+    return launch_merge_partials(parts, n_parts, part_stride, n_rows, head_dim, eps, out, dtype, (cudaStream_t)stream) == cudaSuccess
+               ? SKV_OK : SKV_ERR_CUDA;
+}
+
 int32_t skv_gather_wait(skv_pool* p, const int32_t* local_flags, int32_t world, int32_t epoch, void* stream_) {
     if (!p || !local_flags || world < 1 || world > 8) return SKV_ERR_BAD_ARG;
     if (p->host_only) return SKV_OK;

@@ -96,6 +96,8 @@ struct DecodeLaunch {
     int32_t fuse_merge;          // 0: leave the merge to decode_reduce_kernel
     int64_t total_tokens;        // host's sum of the attended lengths (drives the plan and the merge choice)
     PeerGatherView gather;
+    float* partial_out;          // when set, the merge kernel writes un-normalised [n_seqs][q_heads][head_dim + 2]
+                                 // rows (acc..., m, l) instead of the output: the unit of sequence sharding
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
 // chunk length (tokens handled by one CTA) and the number of splits that follow from it
@@ -138,6 +140,8 @@ int32_t prepare_decode(skv_pool* pool, int32_t layer, const int32_t* seq_ids, in
 int32_t pool_fail(skv_pool* pool, int32_t code, const char* message);
 int32_t pool_device(const skv_pool* pool);
 
+cudaError_t launch_merge_partials(const float* parts, int32_t n_parts, int64_t part_stride, int32_t n_rows, int32_t head_dim,
+                                  float eps, void* out, int32_t dtype, cudaStream_t stream);
 cudaError_t launch_gather_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, cudaStream_t stream);
 
 // process-wide count of kernel launches issued by this library

@@ -298,6 +298,22 @@ class PagedPool:
                                                float(eps), ws.data_ptr(), ws.numel(), C.byref(desc), self.stream))
         return view
 
+    def decode_partial(self, layer: int, q: torch.Tensor, *, seq_ids=None, q_pos=None,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Attention of ``q`` ``[n_seqs, q_heads, head_dim]`` over the keys this pool holds, as un-normalised
+        float32 rows ``[n_seqs, q_heads, head_dim + 2]`` = (weighted V sum, max, sum): the unit that
+        ``merge_partials`` combines across key ranges (sequence sharding)."""
+        self._check_tensor(q, "q")
+        if q.dim() != 3 or not q.is_contiguous():
+            raise ValueError("q must be a contiguous [n_seqs, q_heads, head_dim] tensor")
+        n_seqs, hq, d = q.shape
+        if out is None:
+            out = torch.empty((n_seqs, hq, d + 2), dtype=torch.float32, device=q.device)
+        ws = self.workspace(n_seqs, hq)
+        self._check(lib.skv_decode_partial(self._h, layer, i32_array(seq_ids), n_seqs, q.data_ptr(), i32_array(q_pos), hq,
+                                           ws.data_ptr(), ws.numel(), out.data_ptr(), self.stream))
+        return out
+
     def decode_step(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: float = 1e-12,
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """RoPE-on-write append of one token per sequence plus decode attention in one library call.
@@ -392,6 +408,23 @@ def _alias(ptr: int, shape, dtype: torch.dtype, device: int) -> torch.Tensor:
 
     raw = torch.as_tensor(_Mem(), device=torch.device("cuda", device))
     return raw.view(dtype).view(*shape)
+
+
+def merge_partials(parts: torch.Tensor, *, eps: float = 1e-12, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Merge ``parts`` ``[n_parts, n_seqs, q_heads, head_dim + 2]`` (float32 rows from ``decode_partial``, one per key
+    range) into the attention output ``[n_seqs, q_heads, head_dim]`` with the reference's chunk-merge rule
+    (src/ollm/backends/mlx_ops.py:125-146)."""
+    if not parts.is_cuda:
+        raise RuntimeError("merge_partials needs a CUDA tensor; there is no CPU path")
+    if parts.dim() != 4 or parts.dtype != torch.float32 or not parts.is_contiguous():
+        raise ValueError("parts must be a contiguous float32 [n_parts, n_seqs, q_heads, head_dim + 2] tensor")
+    n_parts, n_seqs, hq, d2 = parts.shape
+    out = torch.empty((n_seqs, hq, d2 - 2), dtype=dtype, device=parts.device)
+    st = lib.skv_merge_partials(parts.data_ptr(), n_parts, n_seqs * hq * d2, n_seqs * hq, d2 - 2, float(eps), out.data_ptr(),
+                                _lib.BF16 if dtype == torch.bfloat16 else _lib.F32,
+                                torch.cuda.current_stream(parts.device).cuda_stream)
+    raise_for_status(st)
+    return out
 
 
 def rope_rows(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, scaling_factor: float = 1.0,

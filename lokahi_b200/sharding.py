@@ -141,3 +141,51 @@ class PeerGather:
         d.epoch = self.epoch
         d.wait_flags = self.flags.data_ptr() if wait else None
         return d, self._views[parity]
+
+
+@dataclass(frozen=True)
+class SequenceShard:
+    """Contiguous, page-aligned split of every sequence's tokens over the ranks: rank r holds tokens
+    ``[r * span, (r + 1) * span)`` of each sequence, ``span`` a multiple of the page size.  Attention is
+    associative along the key axis through the reference's (max, sum, weighted-V) merge
+    (src/ollm/backends/mlx_ops.py:125-144), so every rank attends its own keys and the un-normalised partials
+    are merged after one all-gather."""
+
+    rank: int
+    world: int
+    span: int            # tokens per rank per sequence
+    page_size: int = 16
+
+    def __post_init__(self):
+        if self.world <= 0 or not 0 <= self.rank < self.world:
+            raise ValueError("rank must lie in [0, world)")
+        if self.span <= 0 or self.span % self.page_size:
+            raise ValueError("span must be a positive multiple of the page size")
+
+    def owner(self, position: int) -> int:
+        """Rank that stores the token at a global position (the last rank also takes everything beyond)."""
+        return min(position // self.span, self.world - 1)
+
+    def local_range(self, length: int):
+        """(first global position, number of tokens) this rank holds of a sequence of ``length`` tokens."""
+        start = self.rank * self.span
+        end = length if self.rank == self.world - 1 else min(length, start + self.span)
+        return start, max(0, end - start)
+
+    def local_position(self, position: int) -> int:
+        """A global query position in this rank's own token numbering (negative: none of its keys are allowed)."""
+        return position - self.rank * self.span
+
+
+def sequence_sharded_decode(pool, layer: int, q: torch.Tensor, q_pos_global, seq_shard: SequenceShard, *,
+                            group: Optional[dist.ProcessGroup] = None, eps: float = 1e-12) -> torch.Tensor:
+    """Decode attention when each rank's pool holds a token range of every sequence: local partial, all-gather
+    of the float32 partials (``[n_seqs, q_heads, head_dim + 2]`` per rank), merge on every rank."""
+    from .pool import merge_partials
+    local = pool.decode_partial(layer, q, q_pos=[seq_shard.local_position(int(p)) for p in q_pos_global])
+    if seq_shard.world == 1:
+        parts = local.unsqueeze(0)
+    else:
+        parts = torch.empty((seq_shard.world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(parts.view((-1,) + tuple(local.shape[1:])), local, group=group)
+    return merge_partials(parts, eps=eps, dtype=q.dtype)

@@ -161,3 +161,44 @@ def full_softmax_attention(q, k, v, query_positions=None) -> np.ndarray:
         w = np.divide(w, den, out=np.zeros_like(w), where=den > 0)
         out[:, hq] = w @ v[:, hq // G]
     return out
+
+
+def attention_partial(q, k, v, query_positions):
+    """Un-normalised state (m, s, wv) of the reference's online softmax over ONE key block, i.e. what
+    mlx_ops.py:106-123 computes for a block before the merge of :125-144; rows with no allowed key have s = 0.
+    q [B, Hq, Lq, D]; k, v [B, Hkv, Lk, D]; query_positions [B, Lq] in this block's own key numbering."""
+    q = np.asarray(q, dtype=np.float32)
+    B, Hq, Lq, D = q.shape
+    Hkv, Lk = k.shape[1], k.shape[2]
+    G = Hq // Hkv
+    scale = np.float32(1.0 / (D ** 0.5))
+    pos = normalize_query_positions(query_positions, B, Lq)
+    kk = np.repeat(np.asarray(k, dtype=np.float32), G, axis=1)
+    vv = np.repeat(np.asarray(v, dtype=np.float32), G, axis=1)
+    scores = np.einsum("bhqd,bhkd->bhqk", q, kk).astype(np.float32) * scale
+    allowed = np.arange(Lk, dtype=np.int32)[None, None, None, :] <= pos[:, None, :, None]
+    scores = np.where(allowed, scores, _NEG_INF)
+    valid = allowed.any(axis=-1)
+    valid = np.broadcast_to(valid, scores.shape[:3])
+    m = np.where(valid, scores.max(axis=-1) if Lk else _NEG_INF, np.float32(0.0)).astype(np.float32)
+    with np.errstate(invalid="ignore"):
+        p = np.where(allowed, np.exp(scores - m[..., None]), np.float32(0.0)).astype(np.float32)
+    s = p.sum(axis=-1, dtype=np.float32)
+    wv = np.einsum("bhqk,bhkd->bhqd", p, vv).astype(np.float32)
+    return m, s, wv
+
+
+def merge_partials(states, eps: float = 1e-12):
+    """Merge (m, s, wv) states of disjoint key blocks with the rule of mlx_ops.py:125-146 and normalise."""
+    m, s, wv = states[0]
+    for lm, ls, lwv in states[1:]:
+        prev_valid, local_valid = s > 0, ls > 0
+        both = prev_valid & local_valid
+        new_m = np.where(both, np.maximum(m, lm), np.where(prev_valid, m, lm))
+        with np.errstate(invalid="ignore", over="ignore"):
+            alpha = np.where(prev_valid, np.exp(m - new_m), np.float32(0.0)).astype(np.float32)
+            beta = np.where(local_valid, np.exp(lm - new_m), np.float32(0.0)).astype(np.float32)
+        s = (alpha * s + beta * ls).astype(np.float32)
+        wv = (alpha[..., None] * wv + beta[..., None] * lwv).astype(np.float32)
+        m = new_m.astype(np.float32)
+    return (wv / np.maximum(s[..., None], np.float32(eps))).astype(np.float32)

@@ -315,3 +315,50 @@ def test_fused_gather_path_on_one_gpu_matches_plain_decode():
         torch.cuda.synchronize()
         assert torch.equal(view[0], expect)
     assert int(gather.flags[0]) == 3 and pool.check_device_status() == 0
+
+
+def test_sequence_sharding_partials_merge_to_the_unsharded_result():
+    """Three pools on one GPU stand in for three ranks that each hold a contiguous, page-aligned token range of
+    every sequence: local partials + merge must equal decode attention over the whole history, and each local
+    partial must equal the oracle's block state."""
+    rng = np.random.default_rng(123)
+    R, n, Hq, Hkv, D, P, span = 3, 4, 32, 8, 128, 16, 512
+    lens = [5, 512, 700, 1400]
+    qpos = [4, 511, 650, 1399]
+    rnd = bf16_round
+    k_hist = [rnd(rng.standard_normal((Hkv, t, D), dtype=np.float32)) for t in lens]
+    v_hist = [rnd(rng.standard_normal((Hkv, t, D), dtype=np.float32)) for t in lens]
+    q = rnd(rng.standard_normal((n, Hq, D), dtype=np.float32))
+    qt = _t(q, torch.bfloat16)
+
+    def pool_for(first, count_of):
+        pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=n * 100, max_seqs=n,
+                                           max_pages_per_seq=100, page_size=P, dtype=torch.bfloat16))
+        for s in range(n):
+            assert pool.alloc_sequence() == s
+            cnt = count_of(s)
+            if cnt > 0:
+                pool.append(0, _t(k_hist[s][None, :, first:first + cnt], torch.bfloat16),
+                            _t(v_hist[s][None, :, first:first + cnt], torch.bfloat16), seq_ids=[s], start_pos=[0])
+        return pool
+
+    whole = pool_for(0, lambda s: lens[s]).decode_attention(0, qt, q_pos=qpos)
+    parts, states = [], [[] for _ in range(n)]
+    for r in range(R):
+        sh = L.SequenceShard(r, R, span, P)
+        pool = pool_for(r * span, lambda s: sh.local_range(lens[s])[1])
+        parts.append(pool.decode_partial(0, qt, q_pos=[sh.local_position(p) for p in qpos]))
+        for s in range(n):
+            first, cnt = sh.local_range(lens[s])
+            states[s].append(oattn.attention_partial(q[s][None, :, None, :], k_hist[s][None, :, first:first + cnt],
+                                                     v_hist[s][None, :, first:first + cnt], [[sh.local_position(qpos[s])]]))
+        assert pool.check_device_status() == 0
+    merged = L.merge_partials(torch.stack(parts).contiguous())
+    assert_parity(merged, to_np(whole), TOL_BF16, "merged partials vs unsharded decode")
+    ref = np.stack([oattn.merge_partials(states[s])[0, :, 0, :] for s in range(n)])
+    assert_parity(merged, ref, TOL_BF16, "merged partials vs oracle merge")
+    # the l of a rank that holds none of the allowed keys is exactly 0
+    assert float(parts[2][0, :, D + 1].abs().max()) == 0.0 and float(parts[1][0, :, D + 1].abs().max()) == 0.0
+    # world == 1 path of the helper
+    one = L.sequence_sharded_decode(pool_for(0, lambda s: lens[s]), 0, qt, qpos, L.SequenceShard(0, 1, 2048, P))
+    assert_parity(one, to_np(whole), TOL_BF16, "single-rank sequence sharding")

@@ -87,3 +87,50 @@ def test_shard_validation():
         sh.HeadShard(2, 2, 32, 8)
     x = torch.arange(6.0).reshape(1, 6, 1)
     assert sh.gather_head_outputs(x, sh.HeadShard(0, 1, 6, 6)) is x
+
+
+def _seq_worker(rank, world, port, q, k, v, qpos, full, queue):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import importlib.util, sys
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        spec = importlib.util.spec_from_file_location("_sharding3", os.path.join(root, "lokahi_b200", "sharding.py"))
+        sh = importlib.util.module_from_spec(spec)
+        sys.modules["_sharding3"] = sh
+        spec.loader.exec_module(sh)
+        shard = sh.SequenceShard(rank, world, 16, 16)
+        first, cnt = shard.local_range(k.shape[2])
+        m, s, wv = oattn.attention_partial(q.numpy(), k.numpy()[:, :, first:first + cnt], v.numpy()[:, :, first:first + cnt],
+                                           qpos - first)
+        local = torch.from_numpy(np.concatenate([wv, m[..., None], s[..., None]], axis=-1))   # rows (acc, m, l)
+        parts = torch.empty((world,) + tuple(local.shape))
+        dist.all_gather_into_tensor(parts.view((-1,) + tuple(local.shape[1:])), local.contiguous())
+        p = parts.numpy()
+        merged = oattn.merge_partials([(p[r][..., -2], p[r][..., -1], p[r][..., :-2]) for r in range(world)])
+        queue.put((rank, bool(np.allclose(merged, full, atol=1e-6, rtol=1e-6)), shard.owner(40), shard.local_position(20)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_two_rank_sequence_sharding_merges_to_the_unsharded_result():
+    rng = np.random.default_rng(32)
+    q = rng.standard_normal((2, 4, 1, 16), dtype=np.float32)
+    k = rng.standard_normal((2, 2, 27, 16), dtype=np.float32)
+    v = rng.standard_normal((2, 2, 27, 16), dtype=np.float32)
+    qpos = np.array([[26], [9]], dtype=np.int32)
+    full = oattn.chunked_grouped_attention(q, k, v, query_positions=qpos, k_block_size=1000000)
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_seq_worker, args=(r, 2, port, torch.from_numpy(q), torch.from_numpy(k), torch.from_numpy(v), qpos, full, queue))
+             for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(queue.get(timeout=100) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    assert results == [(0, True, 1, 20), (1, True, 1, 4)]
