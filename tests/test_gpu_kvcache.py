@@ -277,3 +277,35 @@ def oattn_decode(q, k_hist, v_hist, pos):
     return oattn.chunked_grouped_attention(q[None, :, None, :], k_hist[None], v_hist[None],
                                            query_positions=np.array([[pos]], dtype=np.int32), causal=True,
                                            q_block_size=32768, k_block_size=1000000, out_dtype=np.float32)[0, :, 0, :]
+
+
+def test_residency_manager_keeps_results_exact_under_lru_churn():
+    """Three sequences, device budget for two: attending them round-robin forces a park/fetch on every turn;
+    every output must still equal the all-resident result bit for bit."""
+    rng = np.random.default_rng(17)
+    n, Hq, Hkv, D, P, T = 3, 8, 2, 128, 16, 320
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=2, num_kv_heads=Hkv, head_dim=D, num_pages=64, max_seqs=n,
+                                       max_pages_per_seq=24, page_size=P, dtype=torch.bfloat16, host_pages=64))
+    qs = []
+    for s in range(n):
+        assert pool.alloc_sequence() == s
+        for layer in range(2):
+            k = _t(bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32)), torch.bfloat16)
+            v = _t(bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32)), torch.bfloat16)
+            pool.append(layer, k, v, seq_ids=[s], start_pos=[0])
+        qs.append(_t(bf16_round(rng.standard_normal((1, Hq, D), dtype=np.float32)), torch.bfloat16))
+    expect = [[pool.decode_attention(layer, qs[s], seq_ids=[s]).clone() for layer in range(2)] for s in range(n)]
+    res = L.KVPageResidency(pool, budget_pages=2 * (T // P), group_pages=8)
+    for s in range(n):
+        res.track(s)
+    assert res.snapshot().parked_pages == T // P
+    for turn in range(7):
+        s = turn % n
+        res.ensure_resident(s, 0, T // P)
+        res.pin(s, 0, T // P)
+        for layer in range(2):
+            assert torch.equal(pool.decode_attention(layer, qs[s], seq_ids=[s]), expect[s][layer])
+        res.release(s, 0, T // P)
+    snap = res.snapshot()
+    assert snap.resident_pages <= snap.budget_pages and snap.stalls >= 6 and snap.pinned_pages == 0
+    assert pool.check_device_status() == 0
