@@ -154,7 +154,20 @@ def run_ours(args):
     out_buf = torch.empty((N_SEQS, hq, D), device=dev, dtype=torch.bfloat16)
     gathered = torch.empty((world, N_SEQS, hq, D), device=dev, dtype=torch.bfloat16) if world > 1 else None
     fused_gather = world > 1 and args.gather == "fused"
-    peer = L.PeerGather(shard, N_SEQS, D, torch.bfloat16, dev) if fused_gather else None
+    peer = None
+    if fused_gather:
+        # peer-mapped buffers need torch symmetric memory on every rank; if any rank cannot set them up,
+        # all ranks fall back to the NCCL all-gather together
+        try:
+            peer = L.PeerGather(shard, N_SEQS, D, torch.bfloat16, dev)
+            ok_local = 1
+        except Exception as exc:   # noqa: BLE001 - any failure means "no peer mapping here"
+            sys.stderr.write(f"[bench] rank {rank}: fused gather unavailable ({exc}); using NCCL all-gather\n")
+            ok_local = 0
+        flag = torch.tensor([ok_local], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            fused_gather, peer = False, None
     state = {"view": gathered}
 
     def attend(q):
