@@ -151,7 +151,13 @@ SKV_API int32_t skv_decode_attn(skv_pool* pool, int32_t layer, const int32_t* se
  * RoPE table, append k, v at each sequence's current length, then attend
  * (the sequence apply_rotary_pos_emb_mlx -> cache.update -> attention of src/ollm/llama_mlx.py:284-308 for L == 1).
  * Sequences are 0..n_seqs-1; q, out: [n_seqs][n_q_heads][head_dim]; k, v: [n_seqs][kv_heads][head_dim], contiguous.
- * Same workspace as skv_decode_attn.  One host call instead of two halves the per-step host overhead. */
+ * Same workspace as skv_decode_attn.  One host call instead of two halves the per-step host overhead.
+ * For bf16, head_dim 128, page_size a multiple of 16 and at most 8 query heads per KV head the whole step is two
+ * launches: the split-K kernel rotates q and the new k itself, stores the new rows into their page and attends
+ * them from shared memory; the merge kernel writes the rotated q back and counts the token into the device
+ * lengths.  The stored pages and the rotated q are bit-identical to the append + attention pair; the output
+ * differs from it by rounding only (the new token's weight stays in float32).  SKV_STEP_FUSED=0 in the
+ * environment selects the pair. */
 SKV_API int32_t skv_decode_step(skv_pool* pool, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
                                 void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
                                 void* stream);

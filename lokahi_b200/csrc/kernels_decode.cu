@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_mma_kernel(DecodeLaunch
 // ---------------------------------------------------------------------------------------------
 constexpr int kStageBytes = 8192;   // one 16-token tile: K (2 boxes x 2 KB) + V (2 boxes x 2 KB)
 
-template <int NS>
+template <int NS, bool FA>
 __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch d, const __grid_constant__ CUtensorMap kmap,
                                                                     const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ uint8_t smem_raw[];
@@ -359,7 +359,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
         const int slot = (t0 + ((int)(threadIdx.x >> 5) + kDecodeWarps * (int)(threadIdx.x & 31)) * 16) / pv.page_size;
         if (slot < pv.max_pages_per_seq) raw_page = pv.page_table[(int64_t)seq * pv.max_pages_per_seq + slot];
     }
-    const int n_attend = attend_count(d, i, seq);
+    // With the fused append the device length does not count this step's token yet: it sits at position
+    // len_old, is attended from registers by the CTA whose chunk contains it, and t1 bounds the tokens that
+    // are read from the pages.
+    const int len_old = attend_count(d, i, seq);
+    const int n_attend = FA ? len_old + 1 : len_old;
     const int G = d.n_q_heads / pv.num_kv_heads;
     if (t0 >= n_attend) {
         if (split == 0 && d.fuse_merge) {   // nothing to attend: the output row is exactly 0 (mlx_ops.py:118, :146)
@@ -368,7 +372,8 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
         }
         return;
     }
-    const int t1 = min(n_attend, t0 + d.chunk_tokens);
+    const int t1 = min(len_old, t0 + d.chunk_tokens);
+    const bool owner = FA && len_old >= t0 && len_old < t0 + d.chunk_tokens;
     const int n_splits = (n_attend + d.chunk_tokens - 1) / d.chunk_tokens;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
@@ -386,18 +391,48 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
 
     // Q fragments: row g, 16-byte units 2c and 2c+1 of each 128-byte half (the K lane mapping)
     uint32_t qa[8][2];
-    {
+    float* fa_cos = reinterpret_cast<float*>(smem + kDecodeWarps * NS * kStageBytes + 128);   // [64]
+    float* fa_sin = fa_cos + 64;                                                             // [64]
+    float* fa_k = fa_sin + 64;                                                               // [128] rotated new K row
+    float* fa_v = fa_k + kMmaD;                                                              // [128] new V row
+    auto load_q = [&]() {
         const char* qrow = reinterpret_cast<const char*>(d.q) + (((int64_t)i * d.n_q_heads + h * G + g) * kMmaD) * 2;
+        uint4 r[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            uint4 r = make_uint4(0, 0, 0, 0);
-            if (g < G) r = *reinterpret_cast<const uint4*>(qrow + (8 * (u >> 1) + 2 * c + (u & 1)) * 16);
-            qa[2 * u][0] = r.x;
-            qa[2 * u][1] = r.y;
-            qa[2 * u + 1][0] = r.z;
-            qa[2 * u + 1][1] = r.w;
+            r[u] = make_uint4(0, 0, 0, 0);
+            if (g < G) r[u] = *reinterpret_cast<const uint4*>(qrow + (8 * (u >> 1) + 2 * c + (u & 1)) * 16);
         }
-    }
+        if constexpr (FA) {
+            // unit u (first half) pairs with unit u + 2 (second half): dims 8 * (2c + u) + e and 64 more
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                uint32_t* lo = reinterpret_cast<uint32_t*>(&r[u]);
+                uint32_t* hi = reinterpret_cast<uint32_t*>(&r[u + 2]);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo[w]));
+                    const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi[w]));
+                    const int dd = 8 * (2 * c + u) + 2 * w;
+                    const float c0 = fa_cos[dd], s0 = fa_sin[dd], c1 = fa_cos[dd + 1], s1 = fa_sin[dd + 1];
+                    const float y1a = __fadd_rn(__fmul_rn(x1.x, c0), __fmul_rn(-x2.x, s0));
+                    const float y2a = __fadd_rn(__fmul_rn(x2.x, c0), __fmul_rn(x1.x, s0));
+                    const float y1b = __fadd_rn(__fmul_rn(x1.y, c1), __fmul_rn(-x2.y, s1));
+                    const float y2b = __fadd_rn(__fmul_rn(x2.y, c1), __fmul_rn(x1.y, s1));
+                    lo[w] = pack_bf16(y1a, y1b);
+                    hi[w] = pack_bf16(y2a, y2b);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            qa[2 * u][0] = r[u].x;
+            qa[2 * u][1] = r[u].y;
+            qa[2 * u + 1][0] = r[u].z;
+            qa[2 * u + 1][1] = r[u].w;
+        }
+    };
+    if constexpr (!FA) load_q();
     const int n_tiles = (t1 - t0 + 15) >> 4;
     const int n_my = n_tiles > warp ? (n_tiles - warp + kDecodeWarps - 1) / kDecodeWarps : 0;
     int my_page = -1;
@@ -440,6 +475,44 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     const float sc = rsqrtf((float)kMmaD) * kLog2e;
 
     for (int k = 0; k < NS && k < n_my; ++k) issue(k);
+    if constexpr (FA) {
+        // While the first tiles are in flight: cos/sin of this step's position (the append kernel's arithmetic,
+        // llama_mlx.py:132-136, :172-182), and in the owning CTA the new token's rows.
+        const int tid = threadIdx.x;
+        if (tid < kMmaD / 2) {
+            float fpos = (float)len_old;
+            if (d.rope_scaling != 1.0f) fpos = __fdiv_rn(fpos, d.rope_scaling);
+            float sn, cs;
+            sincosf(__fmul_rn(fpos, d.inv_freq[tid]), &sn, &cs);
+            fa_cos[tid] = cs;
+            fa_sin[tid] = sn;
+            if (owner) {
+                const int64_t src = ((int64_t)i * pv.num_kv_heads + h) * kMmaD;
+                const __nv_bfloat16* ks = reinterpret_cast<const __nv_bfloat16*>(d.new_k) + src;
+                const __nv_bfloat16* vs = reinterpret_cast<const __nv_bfloat16*>(d.new_v) + src;
+                const float x1 = __bfloat162float(ks[tid]), x2 = __bfloat162float(ks[tid + 64]);
+                const __nv_bfloat16 k1 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn)));
+                const __nv_bfloat16 k2 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn)));
+                const __nv_bfloat16 v1 = vs[tid], v2 = vs[tid + 64];
+                fa_k[tid] = __bfloat162float(k1);
+                fa_k[tid + 64] = __bfloat162float(k2);
+                fa_v[tid] = __bfloat162float(v1);
+                fa_v[tid + 64] = __bfloat162float(v2);
+                const int page = checked_page(pv, seq, len_old / P);
+                if (page >= 0) {
+                    const int64_t off = (int64_t)d.layer * (pv.layer_stride_bytes / 2) + row_offset(pv, page, h, len_old % P);
+                    __nv_bfloat16* kdst = reinterpret_cast<__nv_bfloat16*>(pv.k_base) + off;
+                    __nv_bfloat16* vdst = reinterpret_cast<__nv_bfloat16*>(pv.v_base) + off;
+                    kdst[tid] = k1;
+                    kdst[tid + 64] = k2;
+                    vdst[tid] = v1;
+                    vdst[tid + 64] = v2;
+                }
+            }
+        }
+        __syncthreads();
+        load_q();
+    }
     bool dead = false;
     int k = 0;
     for (; k < n_my; ++k) {
@@ -540,6 +613,38 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
 #pragma unroll
             for (int e = 0; e < 8; ++e) o[hh][e][0] = o[hh][e][1] = 0.f;
     }
+    if constexpr (FA) {
+        if (owner && warp == 0 && !dead) {   // this step's token: one more key, taken from shared memory
+            float part = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float* kk = fa_k + 64 * (u >> 1) + 8 * (2 * c + (u & 1));
+                const uint32_t regs[4] = {qa[2 * u][0], qa[2 * u][1], qa[2 * u + 1][0], qa[2 * u + 1][1]};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float2 qf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&regs[w]));
+                    part = fmaf(qf.x, kk[2 * w], part);
+                    part = fmaf(qf.y, kk[2 * w + 1], part);
+                }
+            }
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            const float sl = part * sc;
+            const float m_new = fmaxf(m_run, sl);
+            const float alpha = exp2f(m_run - m_new);
+            const float pn = exp2f(sl - m_new);
+            l_run = l_run * alpha + (c == 0 ? pn : 0.f);   // l_run is a per-lane share of the row sum
+            m_run = m_new;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const float* vv = fa_v + 64 * hh + 16 * c + 8 * b;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[hh][e][b] = fmaf(pn, vv[e], o[hh][e][b] * alpha);
+                }
+        }
+    }
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
 
@@ -636,19 +741,20 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     }
 }
 
-template <int NS>
+template <int NS, bool FA>
 cudaError_t launch_tma(const DecodeLaunch& d, cudaStream_t stream) {
     static bool configured[64] = {};
-    const int smem = kDecodeWarps * NS * kStageBytes + kDecodeWarps * NS * 8 + 1024;
+    // rings, mbarriers (padded to 128 bytes), the fused append's cos/sin and new-row staging, alignment slack
+    const int smem = kDecodeWarps * NS * kStageBytes + 128 + (FA ? (64 + 64 + 2 * kMmaD) * 4 : 0) + 1024;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel<NS, FA>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
-    return launch_pdl(decode_tma_kernel<NS>, grid, dim3(kDecodeThreads), (size_t)smem, stream, d,
+    return launch_pdl(decode_tma_kernel<NS, FA>, grid, dim3(kDecodeThreads), (size_t)smem, stream, d,
                       *reinterpret_cast<const CUtensorMap*>(d.k_map), *reinterpret_cast<const CUtensorMap*>(d.v_map));
 }
 
@@ -665,7 +771,7 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
     const int D = pv.head_dim;
     T* out = reinterpret_cast<T*>(d.out) + ((int64_t)i * d.n_q_heads + hq) * D;
     int n_attend = 0;
-    if (seq >= 0 && seq < pv.max_seqs) n_attend = attend_count(d, i, seq);
+    if (seq >= 0 && seq < pv.max_seqs) n_attend = attend_count(d, i, seq) + (d.fused_append ? 1 : 0);
     const int n_splits = (n_attend + d.chunk_tokens - 1) / d.chunk_tokens;   // <= 128 by the plan
     const int64_t base = ((int64_t)i * d.n_q_heads + hq) * d.max_splits;
     // one thread per split fetches (m, l): the loads of all splits are in flight together
@@ -722,6 +828,32 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
 #pragma unroll 1
             for (int r = 0; r < d.gather.world; ++r) reinterpret_cast<T*>(d.gather.out[r])[off] = val;
         }
+    }
+    if (d.fused_append) {
+        // The decode CTAs worked on their own rotated copies of q: write the rotated row back (the step's
+        // contract), then let the block that arrives last count this step's token into the device lengths --
+        // every block has read the old length by then.
+        if (tid < D / 2 && seq >= 0 && seq < pv.max_seqs) {
+            T* qrow = reinterpret_cast<T*>(const_cast<void*>(d.q)) + ((int64_t)i * d.n_q_heads + hq) * D;
+            float fpos = (float)(n_attend - 1);
+            if (d.rope_scaling != 1.0f) fpos = __fdiv_rn(fpos, d.rope_scaling);
+            float sn, cs;
+            sincosf(__fmul_rn(fpos, d.inv_freq[tid]), &sn, &cs);
+            const float x1 = to_f32(qrow[tid]), x2 = to_f32(qrow[tid + D / 2]);
+            qrow[tid] = from_f32<T>(__fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn)));
+            qrow[tid + D / 2] = from_f32<T>(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn)));
+        }
+        __shared__ int s_last;
+        __syncthreads();
+        if (tid == 0) {
+            const int n_blocks = (int)(gridDim.x * gridDim.y);
+            const int t = atomicAdd(d.append_ticket, 1);
+            s_last = (t == n_blocks - 1);
+            if (s_last) *d.append_ticket = 0;
+        }
+        __syncthreads();
+        if (s_last)
+            for (int s2 = tid; s2 < d.n_seqs; s2 += blockDim.x) pv.lengths[(int64_t)d.layer * pv.max_seqs + s2] += 1;
     }
     if (d.gather.world > 0) {
         // When the last merge block has stored its rows, tell every rank (itself included) that this rank's
@@ -844,19 +976,26 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     // every CTA plus a serial tail), but saves about 5 us at an eighth of it, where the call is latency-bound.
     // So it is chosen only for small calls; SKV_DECODE_FUSE=0/1 overrides.
     d.fuse_merge = d.total_tokens * d.pool.num_kv_heads < 400000 ? 1 : 0;
-    if (d.gather.world > 0 || d.partial_out) d.fuse_merge = 0;   // the gather / the partial output live in the merge kernel
-    if (fuse && (fuse[0] == '0' || fuse[0] == '1') && d.gather.world == 0 && !d.partial_out) d.fuse_merge = fuse[0] == '1';
+    // the gather, the partial output and the fused append's bookkeeping live in the merge kernel
+    const bool needs_merge_kernel = d.gather.world > 0 || d.partial_out || d.fused_append;
+    if (needs_merge_kernel) d.fuse_merge = 0;
+    if (fuse && (fuse[0] == '0' || fuse[0] == '1') && !needs_merge_kernel) d.fuse_merge = fuse[0] == '1';
     const int G = d.n_q_heads / d.pool.num_kv_heads;
     const bool mma_ok = d.dtype == SKV_BF16 && d.pool.head_dim == kMmaD && d.pool.page_size % 16 == 0 && G <= 8 &&
                         !d.force_generic && ((uintptr_t)d.q % 16 == 0);
     if (d.max_splits > 128) return cudaErrorInvalidValue;   // the merge kernel handles one split per thread
     cudaError_t e;
     const char* impl = getenv("SKV_DECODE_IMPL");   // "reg": direct-to-register loads; default: TMA ring when maps exist
-    const bool tma_ok = mma_ok && d.k_map && d.v_map && !(impl && impl[0] == 'r');
+    const bool tma_ok = mma_ok && d.k_map && d.v_map && (d.fused_append || !(impl && impl[0] == 'r'));
+    if (d.fused_append && (!tma_ok || d.seq_ids || d.q_pos || !d.new_k || !d.new_v || !d.inv_freq || !d.append_ticket))
+        return cudaErrorInvalidValue;   // only the TMA kernel implements it; callers check the conditions first
     if (tma_ok) {
         const char* st = getenv("SKV_DECODE_STAGES");
         const int ns = st ? atoi(st) : 2;   // 2 stages -> 3 CTAs per SM (24 stages of 8 KB in flight), the measured best
-        e = ns == 3 ? launch_tma<3>(d, stream) : ns == 4 ? launch_tma<4>(d, stream) : launch_tma<2>(d, stream);
+        if (d.fused_append)
+            e = launch_tma<2, true>(d, stream);
+        else
+            e = ns == 3 ? launch_tma<3, false>(d, stream) : ns == 4 ? launch_tma<4, false>(d, stream) : launch_tma<2, false>(d, stream);
     } else if (mma_ok) {
         dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
         decode_mma_kernel<<<grid, kDecodeThreads, 0, stream>>>(d);

@@ -106,7 +106,7 @@ struct skv_pool {
     int32_t* d_page_table = nullptr;
     int32_t* d_lengths = nullptr;
     int32_t* d_status = nullptr;
-    int32_t* d_tickets = nullptr;        // [max_seqs][num_kv_heads] + 1 (gather), zero between decode calls
+    int32_t* d_tickets = nullptr;        // [max_seqs][num_kv_heads] + 2 (gather, fused append), zero between decode calls
     float* d_inv_freq = nullptr;
     // K and V pools as 2-D bf16 tensors [layers*pages*heads*page_size][head_dim] with [16][64] boxes
     alignas(64) CUtensorMap k_map;
@@ -372,8 +372,8 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
         CUDA_TRY(p, cudaMemset(p->d_lengths, 0, p->lengths.size() * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_status, sizeof(int32_t)));
         CUDA_TRY(p, cudaMemset(p->d_status, 0, sizeof(int32_t)));
-        CUDA_TRY(p, cudaMalloc((void**)&p->d_tickets, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 1) * sizeof(int32_t)));
-        CUDA_TRY(p, cudaMemset(p->d_tickets, 0, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 1) * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_tickets, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 2) * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMemset(p->d_tickets, 0, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 2) * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_inv_freq, (size_t)cfg->head_dim / 2 * sizeof(float)));
         CUDA_TRY(p, p->ring.init());
         CUDA_TRY(p, cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
@@ -951,9 +951,103 @@ int32_t skv_gather_wait(skv_pool* p, const int32_t* local_flags, int32_t world, 
     return SKV_OK;
 }
 
+// One decode step as two launches: the decode kernel rotates q and the new K row itself, stores the new rows and
+// attends them from shared memory; the merge kernel writes the rotated q back and counts the token into the
+// device lengths.  Applies to the bf16 / head_dim 128 / TMA configuration; returns 0 from `applies` otherwise and
+// the caller takes the append + attention pair.  Host-side order follows skv_append: validate, reserve pages
+// all-or-nothing, then mutate.
+static bool fused_step_applies(const skv_pool* p, const void* q, int32_t n_q_heads) {
+    const char* mode = getenv("SKV_STEP_FUSED");   // "0": always the append + attention pair
+    if ((mode && mode[0] == '0') || p->host_only || !p->has_maps || !p->rope_set) return false;
+    if (p->cfg.dtype != SKV_BF16 || p->cfg.head_dim != 128 || p->cfg.page_size % 16 != 0) return false;
+    if (n_q_heads <= 0 || n_q_heads % p->cfg.num_kv_heads != 0 || n_q_heads / p->cfg.num_kv_heads > 8) return false;
+    const char* force = getenv("SKV_DECODE_GENERIC");
+    const char* impl = getenv("SKV_DECODE_IMPL");
+    if ((force && force[0] == '1') || (impl && impl[0] == 'r')) return false;
+    return (uintptr_t)q % 16 == 0;
+}
+
+static int32_t fused_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v, void* out,
+                          int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes, const skv_peer_gather* g,
+                          cudaStream_t stream) {
+    if (layer < 0) return p->fail(SKV_ERR_BAD_ARG, "layer_idx must be a non-negative integer");
+    if (layer >= p->cfg.num_layers)
+        return p->fail(SKV_ERR_BAD_ARG, "layer_idx %d is outside configured layer count %d", layer, p->cfg.num_layers);
+    if (n_seqs <= 0 || n_seqs > p->cfg.max_seqs) return p->fail(SKV_ERR_BAD_ARG, "n_seqs %d out of range", n_seqs);
+    if (!q || !k || !v || (!out && !g)) return p->fail(SKV_ERR_BAD_ARG, "q, k, v and out must be given");
+    const int32_t P = p->cfg.page_size;
+    int64_t total = 0, need_total = 0;
+    for (int32_t s = 0; s < n_seqs; ++s) {
+        if (!valid_seq(p, s)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", s);
+        const int32_t cur = p->len(layer, s);
+        const int32_t need = (cur + 1 + P - 1) / P;
+        if (need > p->cfg.max_pages_per_seq)
+            return p->fail(SKV_ERR_OUT_OF_PAGES, "sequence %d needs %d pages, row holds %d", s, need, p->cfg.max_pages_per_seq);
+        need_total += std::max(0, need - p->n_seq_pages[s]);
+        for (int32_t slot = 0; slot < std::min(need, p->n_seq_pages[s]); ++slot)
+            if (p->pt(s, slot) < 0) return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", s, slot);
+        total += cur + 1;
+    }
+    if (need_total > (int64_t)p->free_pages.size())
+        return p->fail(SKV_ERR_OUT_OF_PAGES, "need %lld pages, %zu free", (long long)need_total, p->free_pages.size());
+    DecodeLaunch D{};
+    decode_plan(P, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
+    const size_t need_ws = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
+    if (!workspace || workspace_bytes < need_ws)
+        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need_ws);
+    std::vector<TableUpdate> ups;
+    for (int32_t s = 0; s < n_seqs; ++s) {
+        int32_t st = grow(p, s, p->len(layer, s) + 1, &ups);
+        if (st != SKV_OK) return st;   // cannot happen after the check above
+    }
+    for (int32_t s = 0; s < n_seqs; ++s) p->len(layer, s) += 1;
+
+    DeviceGuard guard(p);
+    int32_t st = order_transfers(p, stream);
+    if (st != SKV_OK) return st;
+    st = publish_table_updates(p, ups, stream);
+    if (st != SKV_OK) return st;
+    D.pool = p->view();
+    D.layer = layer;
+    D.n_seqs = n_seqs;
+    D.n_q_heads = n_q_heads;
+    D.dtype = p->cfg.dtype;
+    D.q = q;
+    D.out = out;
+    D.eps = eps;
+    D.ws_acc = (float*)workspace;
+    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
+    D.k_map = &p->k_map;
+    D.v_map = &p->v_map;
+    D.tickets = p->d_tickets;
+    D.total_tokens = total;
+    D.fused_append = 1;
+    D.new_k = k;
+    D.new_v = v;
+    D.inv_freq = p->d_inv_freq;
+    D.rope_scaling = p->rope_scaling;
+    D.append_ticket = p->d_tickets + (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads + 1;
+    if (g) {
+        D.out = nullptr;
+        D.gather.world = g->world;
+        D.gather.rank = g->rank;
+        D.gather.epoch = g->epoch;
+        D.gather.ticket = p->d_tickets + (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads;
+        for (int32_t r = 0; r < g->world; ++r) {
+            D.gather.out[r] = g->out_ptrs[r];
+            D.gather.flags[r] = g->flag_ptrs[r];
+        }
+    }
+    CUDA_TRY(p, launch_decode(D, stream));
+    if (g && g->wait_flags) CUDA_TRY(p, launch_gather_wait(g->wait_flags, g->world, g->epoch, p->d_status, stream));
+    return SKV_OK;
+}
+
 int32_t skv_decode_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v, void* out,
                         int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes, void* stream) {
     if (!p) return SKV_ERR_BAD_ARG;
+    if (fused_step_applies(p, q, n_q_heads))
+        return fused_step(p, layer, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, nullptr, (cudaStream_t)stream);
     skv_append_args a{};
     a.layer = layer;
     a.n_seqs = n_seqs;
@@ -979,6 +1073,14 @@ int32_t skv_decode_step_gather(skv_pool* p, int32_t layer, int32_t n_seqs, void*
                                int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
                                const skv_peer_gather* gather, void* stream) {
     if (!p) return SKV_ERR_BAD_ARG;
+    if (gather && fused_step_applies(p, q, n_q_heads)) {
+        if (gather->world < 1 || gather->world > 8 || gather->rank < 0 || gather->rank >= gather->world || !gather->out_ptrs ||
+            !gather->flag_ptrs)
+            return p->fail(SKV_ERR_BAD_ARG, "peer gather needs 1 <= world <= 8, a rank inside it and both pointer arrays");
+        for (int32_t r = 0; r < gather->world; ++r)
+            if (!gather->out_ptrs[r] || !gather->flag_ptrs[r]) return p->fail(SKV_ERR_BAD_ARG, "peer pointer %d is null", r);
+        return fused_step(p, layer, n_seqs, q, k, v, nullptr, n_q_heads, eps, workspace, workspace_bytes, gather, (cudaStream_t)stream);
+    }
     skv_append_args a{};
     a.layer = layer;
     a.n_seqs = n_seqs;
@@ -1183,7 +1285,7 @@ int32_t skv_check_device_status(skv_pool* p, void* stream_, int32_t* flag_out) {
     if (flag != 0) {
         CUDA_TRY(p, cudaMemsetAsync(p->d_status, 0, sizeof flag, stream));
         // a kernel that gave up may have left arrival counters behind
-        CUDA_TRY(p, cudaMemsetAsync(p->d_tickets, 0, ((size_t)p->cfg.max_seqs * p->cfg.num_kv_heads + 1) * sizeof(int32_t), stream));
+        CUDA_TRY(p, cudaMemsetAsync(p->d_tickets, 0, ((size_t)p->cfg.max_seqs * p->cfg.num_kv_heads + 2) * sizeof(int32_t), stream));
         return p->fail(SKV_ERR_DEVICE_FLAG, "device status word 0x%x (1 bad page id, 2 bad length, 4 bad sequence id)", flag);
     }
     return SKV_OK;

@@ -98,6 +98,16 @@ struct DecodeLaunch {
     PeerGatherView gather;
     float* partial_out;          // when set, the merge kernel writes un-normalised [n_seqs][q_heads][head_dim + 2]
                                  // rows (acc..., m, l) instead of the output: the unit of sequence sharding
+    // Fused append (one decode step, identity batch, bf16 TMA kernel only): the device lengths still hold the
+    // count BEFORE this step's token.  Every CTA rotates its own copy of q at position `length`; the CTA whose
+    // chunk contains that position rotates the new K row, stores it and the V row into the page, and attends
+    // the token from registers; the merge kernel writes the rotated q back and bumps the lengths.
+    int32_t fused_append;
+    const void* new_k;           // [n_seqs][kv_heads][head_dim], un-rotated
+    const void* new_v;
+    const float* inv_freq;       // [head_dim / 2]
+    float rope_scaling;
+    int32_t* append_ticket;      // one counter, zero between calls
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
 // chunk length (tokens handled by one CTA) and the number of splits that follow from it

@@ -87,8 +87,8 @@ def test_dense_attention_matches_oracle(dtype, tol, shape):
 
 
 # ---- paged decode ----------------------------------------------------------------------------------------
-def _paged_setup(rng, dtype, n_seqs, Hkv, D, P, lens, n_pages=None, layers=1):
-    pages_per_seq = max(1, max(-(-(t + 1) // P) for t in lens))
+def _paged_setup(rng, dtype, n_seqs, Hkv, D, P, lens, n_pages=None, layers=1, headroom=0):
+    pages_per_seq = max(1, max(-(-(t + 1 + headroom) // P) for t in lens))
     n_pages = n_pages or n_seqs * pages_per_seq + 3
     pool = L.PagedPool(L.PagedKVConfig(num_layers=layers, num_kv_heads=Hkv, head_dim=D, num_pages=n_pages, max_seqs=n_seqs,
                                        max_pages_per_seq=pages_per_seq, page_size=P, dtype=dtype))
@@ -283,7 +283,8 @@ def test_tensor_core_prefill_at_full_sequence_4096(monkeypatch):
     assert parity_errors(out[:, ::8], to_np(ref_all))[0] <= TOL_BF16, "tcgen05 vs CUDA-core at S=4096"
 
 
-def test_decode_step_equals_append_then_attention():
+def test_decode_step_equals_append_then_attention(monkeypatch):
+    monkeypatch.setenv("SKV_STEP_FUSED", "0")     # the two-call form of the step: bit-identical to its parts
     rng = np.random.default_rng(55)
     lens = [5, 16, 300, 1025]
     pool_a, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, len(lens), 8, 128, 16, lens)
@@ -300,6 +301,52 @@ def test_decode_step_equals_append_then_attention():
     out_b = pool_b.decode_step(0, qb, k, v)
     assert torch.equal(qa, qb) and torch.equal(out_a, out_b)
     assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
+
+
+def test_fused_append_step_matches_the_two_launch_step_and_the_oracle(monkeypatch):
+    """The one-kernel step (RoPE of q and of the new K row, the store into the page and the new token's score all
+    inside the decode kernel) against append + attention, over 20 steps that cross page, chunk and empty-sequence
+    boundaries: rotated q and the stored pages bit-equal, outputs within bf16 tolerance of each other and of the
+    oracle on the logical history."""
+    lens = [0, 5, 15, 16, 255, 256, 300, 1023, 2047, 2048]
+    n, Hq, Hkv, D, P = len(lens), 32, 8, 128, 16
+    rng = np.random.default_rng(56)
+    pool_a, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, n, Hkv, D, P, lens, headroom=20)
+    rng = np.random.default_rng(56)
+    pool_b, _, _, _, _ = _paged_setup(rng, torch.bfloat16, n, Hkv, D, P, lens, headroom=20)
+    inv = L.rope_inv_freq(D, 500000.0)
+    for p in (pool_a, pool_b):
+        p.set_rope(inv)
+    from parity import parity_errors
+    launches = []
+    for step in range(20):
+        q = _t(rnd(rng.standard_normal((n, Hq, D), dtype=np.float32)), torch.bfloat16)
+        k = _t(rnd(rng.standard_normal((n, Hkv, D), dtype=np.float32)), torch.bfloat16)
+        v = _t(rnd(rng.standard_normal((n, Hkv, D), dtype=np.float32)), torch.bfloat16)
+        qa, qb = q.clone(), q.clone()
+        monkeypatch.setenv("SKV_STEP_FUSED", "0")
+        out_a = pool_a.decode_step(0, qa, k, v)
+        monkeypatch.setenv("SKV_STEP_FUSED", "1")
+        before = L._lib.lib.skv_launch_count()
+        out_b = pool_b.decode_step(0, qb, k, v)
+        launches.append(L._lib.lib.skv_launch_count() - before)
+        assert torch.equal(qa, qb), f"rotated q differs at step {step}"
+        assert parity_errors(out_b, to_np(out_a))[0] <= TOL_BF16, f"step {step}"
+        assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0))
+    assert max(launches) == 2, "the fused step is the decode kernel and the merge kernel, nothing else"
+    ka, va = pool_a.gather(0, n_seqs=n)
+    kb, vb = pool_b.gather(0, n_seqs=n)
+    final = [t + 20 for t in lens]
+    for i in range(n):
+        assert torch.equal(ka[i, :, :final[i]], kb[i, :, :final[i]]) and torch.equal(va[i, :, :final[i]], vb[i, :, :final[i]]), \
+            f"stored pages of sequence {i} differ"
+    assert pool_b.check_device_status() == 0
+    # last step against the oracle on the logical history read back from the pages
+    k_np, v_np = to_np(kb), to_np(vb)
+    for i in (0, 3, 9):
+        ref = oattn.chunked_grouped_attention(to_np(qb[i])[None, :, None, :], k_np[i:i + 1, :, :final[i]], v_np[i:i + 1, :, :final[i]],
+                                              query_positions=np.array([final[i] - 1], dtype=np.int32))
+        assert_parity(out_b[i], ref[0, :, 0, :], TOL_BF16, f"fused step vs oracle, sequence {i}")
 
 
 def test_fused_gather_path_on_one_gpu_matches_plain_decode():
