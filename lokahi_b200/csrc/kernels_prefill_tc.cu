@@ -73,13 +73,18 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// D[tmem] (+)= A[smem] . B[smem]; issued by one thread.
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[smem] . B[smem].  The whole issuer warp executes the call in uniform control flow, so that the
+// descriptors live in uniform registers; only the lane with `lead` != 0 issues the instruction.  (Measured on
+// B200 with a loop of back-to-back MMAs: issued from inside a one-lane branch an M128 N128 K16 MMA costs 116
+// clocks, issued this way 89; N = 64 costs the same, N = 256 runs at the pipe's full rate of 128.)
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                        uint32_t lead) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(lead)
         : "memory");
 }
 // Arrive on `bar` once every MMA issued so far by this thread has completed.
@@ -168,7 +173,8 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         return;
     }
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // provably warp-uniform for the compiler
     // heavy (late) query tiles first so that the causal triangle balances across SMs
     // (blocks are dispatched x-fastest: all heads' heaviest tiles start first)
     const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;
@@ -236,16 +242,22 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
 
     if (warp == kSoftmaxWarps) {
         // =============================== issuer warp: TMA and MMA ===============================
-        if (lane == 0 && n_tiles > 0) {
-            mbar_expect_tx(bar_q, 2 * kBM * 128);
-            tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, zq, bar_q);
-            tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, zq, bar_q);
-            load_k(0);
-            load_v(0);
-            if (n_tiles > 1) {
-                load_k(1);
-                load_v(1);
+        // The whole warp runs the loop (uniform control flow keeps the MMA descriptors in uniform registers);
+        // lane 0 alone issues the copies, the MMAs and the commits.
+        if (n_tiles > 0) {
+            const uint32_t lead = lane == 0 ? 1u : 0u;
+            if (lead) {
+                mbar_expect_tx(bar_q, 2 * kBM * 128);
+                tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, zq, bar_q);
+                tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, zq, bar_q);
+                load_k(0);
+                load_v(0);
+                if (n_tiles > 1) {
+                    load_k(1);
+                    load_v(1);
+                }
             }
+            __syncwarp();
             auto issue_qk = [&](int jj) {
                 ok = ok && mbar_wait(&bar_k[jj & 1], (uint32_t)((jj >> 1) & 1));
                 if (!ok) return;
@@ -255,9 +267,10 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint32_t blk = (uint32_t)(ks >> 2), in = (uint32_t)(ks & 3) * 32;
                     umma_ss(tmem_base + kColS + (uint32_t)(jj & 1) * kBN, smem_desc(q_addr + blk * (kBM * 128) + in, 16, 1024),
-                            smem_desc(ks_addr + blk * (kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u);
+                            smem_desc(ks_addr + blk * (kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u, lead);
                 }
-                umma_commit(&bar_s[jj & 1]);
+                if (lead) umma_commit(&bar_s[jj & 1]);
+                __syncwarp();
             };
             ok = mbar_wait(bar_q, 0);
             if (ok) issue_qk(0);
@@ -268,21 +281,24 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 if (j + 2 < n_tiles) {
                     ok = ok && mbar_wait(&bar_s[j & 1], (uint32_t)((j >> 1) & 1));
                     if (!ok) break;
-                    load_k(j + 2);
+                    if (lead) load_k(j + 2);
+                    __syncwarp();
                 }
                 // softmax of tile j done: P_j is in shared memory, S_j has been read, PV_{j-1} has completed
                 ok = ok && mbar_wait(bar_p, (uint32_t)(j & 1));
                 if (!ok) break;
                 tc_fence_after();
-                if (j >= 1 && j + 1 < n_tiles) load_v(j + 1);     // V stage (j+1)&1 was consumed by PV_{j-1}
+                if (lead && j >= 1 && j + 1 < n_tiles) load_v(j + 1);     // V stage (j+1)&1 was consumed by PV_{j-1}
+                __syncwarp();
                 ok = mbar_wait(&bar_v[j & 1], (uint32_t)((j >> 1) & 1));
                 if (!ok) break;
                 const uint32_t vs = v_addr + (uint32_t)(j & 1) * kVStage;
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ++ks)
                     umma_ss(tmem_base + kColO, smem_desc(p_addr + (uint32_t)ks * 32, 16, 1024),
-                            smem_desc(vs + (uint32_t)ks * 2048, kBN * 128, 1024), kIdescO, (j > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(bar_o);
+                            smem_desc(vs + (uint32_t)ks * 2048, kBN * 128, 1024), kIdescO, (j > 0 || ks > 0) ? 1u : 0u, lead);
+                if (lead) umma_commit(bar_o);
+                __syncwarp();
             }
             if (!ok) *sh_abort = 1;
         }
