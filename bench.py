@@ -317,7 +317,7 @@ def run_prefill(args):
     q = torch.randn((B, HQ, S, D), generator=gen, device=dev).to(torch.bfloat16)
     k = torch.randn((B, HKV, S, D), generator=gen, device=dev).to(torch.bfloat16)
     v = torch.randn((B, HKV, S, D), generator=gen, device=dev).to(torch.bfloat16)
-    pos = np.arange(S, dtype=np.int32)
+    pos = torch.arange(S, dtype=torch.int32, device=dev)      # positions are an input: resident in HBM like q, k, v
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     K, W = args.steps, args.warmup
     for _ in range(W):
@@ -339,6 +339,7 @@ def run_prefill(args):
     ms = np.array([a.elapsed_time(b) for a, b in evs])
     # end to end: pinned host q, k, v in, out back, every step
     qh, kh, vh = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
+    pos_h = np.arange(S, dtype=np.int32)                      # host positions, copied by the call
     oh = torch.empty_like(qh).pin_memory()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     Ke = max(3, min(K, 20))
@@ -346,7 +347,7 @@ def run_prefill(args):
     e0.record()
     for _ in range(Ke):
         q.copy_(qh, non_blocking=True); k.copy_(kh, non_blocking=True); v.copy_(vh, non_blocking=True)
-        o = L.chunked_grouped_attention(q, k, v, query_positions=pos, causal=True, q_block_size=512, k_block_size=512)
+        o = L.chunked_grouped_attention(q, k, v, query_positions=pos_h, causal=True, q_block_size=512, k_block_size=512)
         oh.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()
     e1.record()

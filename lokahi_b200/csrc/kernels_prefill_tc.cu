@@ -6,26 +6,35 @@
 // out = wv / max(s, eps) so that a row with no allowed key is exactly 0 (:118, :146).
 //
 // One CTA = 128 query rows of one query head: four softmax warps (thread r owns query row r, which is TMEM
-// lane r) plus a fifth warp whose lane 0 issues every TMA copy and every MMA, so that instruction issue to
-// the tensor cores (about 64 clocks per M128 N64 K16 MMA, measured) never sits on a softmax warp's path.
-// Per 64-key tile:
-//   TMA   K tile and V tile -> shared memory (3-D tensor maps [batch*head][token][dim], 128-byte swizzle,
-//         rows past the end of a head are zero-filled by the copy engine);
-//   MMA 1 S[128x64]  = Q[128x128] . K^T        tcgen05.mma kind::f16, both operands K-major from smem,
-//                                              accumulator in TMEM columns [0, 64);
+// lane r) plus a fifth warp that issues every TMA copy and every MMA, so that instruction issue to the
+// tensor cores never sits on a softmax warp's path.  The fifth warp runs its loop in warp-uniform control
+// flow with only lane 0 enabled on the copy / MMA / commit instructions: the descriptors then live in
+// uniform registers.  Measured on B200 with back-to-back MMAs (M128, K16, operands in shared memory): 116
+// clocks per instruction when issued from inside a one-lane branch, 89 issued this way, the same for N = 64
+// and N = 128 (N = 256 runs at the pipe's full rate of 128).  Since N = 64 costs as much as N = 128, the
+// scores of TWO 64-key tiles come from one set of N = 128 instructions.
+// Per pair of 64-key tiles:
+//   TMA   the pair's K tiles -> shared memory, laid out [dim box][tile][64 keys x 128 B] so that they form one
+//         128-row K-major operand; V tile by tile (3-D tensor maps [batch*head][token][dim], 128-byte
+//         swizzle, rows past the end of a head are zero-filled by the copy engine);
+//   MMA 1 S[128x128] = Q[128x128] . K^T        eight tcgen05.mma kind::f16 (N = 128), both operands K-major
+//                                              from smem, accumulator in TMEM columns [0, 128): tile 2m in
+//                                              [0, 64), tile 2m+1 in [64, 128);
+// then per tile:
 //   soft  tcgen05.ld S -> registers, scale, mask by the row's absolute position, running max / sum,
 //         P = exp2(...) rounded to bf16 and written to shared memory in the swizzled K-major layout;
-//   MMA 2 O[128x128] += P[128x64] . V[64x128]  V is the MN-major B operand straight from the TMA box
+//   MMA 2 O[128x128] += P[128x64] . V[64x128]  four MMAs, V is the MN-major B operand straight from the TMA box
 //                                              (two-stage ring); the accumulator stays in TMEM columns
-//                                              [64, 192) for the whole key loop.
+//                                              [128, 256) for the whole key loop.
+//   As soon as the softmax threads hold the pair's second tile in registers they say so (bar_r) and the next
+//   pair's MMA 1 is issued, so it overlaps that tile's softmax.
 //   The running maximum that scales P and O is raised only when a tile's maximum exceeds it by more than
 //   8 in the log2 domain; only then is O read, scaled and written back (tcgen05.ld / tcgen05.st).  The
 //   final division by the row sum makes the stale maximum cancel exactly.
-// Two CTAs fit on an SM (96 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the
-// other's MMAs.  One elected thread issues TMA and MMA; completion travels through mbarriers
-// (tcgen05.commit), every wait is bounded, and on a timeout the CTA records FLAG_WAIT_TIMEOUT in the
-// caller's status word (when given), stops issuing work, frees its TMEM and returns.
-// No cluster launch and no multicast anywhere.
+// Two CTAs fit on an SM (112 KB shared memory each, 256 TMEM columns each), so one CTA's softmax overlaps the
+// other's MMAs.  Completion travels through mbarriers (tcgen05.commit), every wait is bounded, and on a
+// timeout the CTA records FLAG_WAIT_TIMEOUT in the caller's status word (when given), stops issuing work,
+// frees its TMEM and returns.  No cluster launch and no multicast anywhere.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -41,13 +50,13 @@ constexpr int kD = 128;           // head_dim
 constexpr int kSoftmaxWarps = 4;   // one query row per thread
 constexpr int kThreads = (kSoftmaxWarps + 1) * 32;   // plus one warp whose lane 0 issues TMA and MMA
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0;     // S accumulators: two buffers of 64 fp32 columns, [0,64) and [64,128)
+constexpr uint32_t kColS = 0;     // S of a pair of tiles: 64 fp32 columns each, [0,64) and [64,128), written by one N = 128 MMA set
 constexpr uint32_t kColO = 128;   // O accumulator: 128 fp32 columns
 constexpr float kLog2eF = 1.4426950408889634f;
 
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr int kOffQ = 0;                       // 2 boxes [128 rows][64 dims]   = 32 KB
-constexpr int kOffK = kOffQ + 2 * kBM * 128;   // 2 stages x 2 boxes [64 keys][64 dims] = 32 KB
+constexpr int kOffK = kOffQ + 2 * kBM * 128;   // [2 dim boxes][2 tiles of the pair][64 keys x 128 B] = 32 KB
 constexpr int kVStage = 2 * kBN * 128;         // bytes of one K or V stage
 constexpr int kOffV = kOffK + 2 * kVStage;     // 2 stages x 2 boxes [64 keys][64 dims] = 32 KB
 constexpr int kOffP = kOffV + 2 * kVStage;     // [128 rows][64 keys] bf16      = 16 KB
@@ -160,11 +169,12 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
     uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + kOffBar);
-    uint64_t* bar_k = bar_q + 1;       // two stages
+    uint64_t* bar_k = bar_q + 1;       // two stages (the two tiles of a pair)
     uint64_t* bar_v = bar_q + 3;       // two stages
-    uint64_t* bar_s = bar_q + 5;       // two S buffers
-    uint64_t* bar_o = bar_q + 7;
-    uint64_t* bar_p = bar_q + 8;       // softmax threads -> issuer: P of this tile is in shared memory
+    uint64_t* bar_s = bar_q + 5;       // first MMA of a PAIR of tiles done: S of both tiles is in TMEM, both K stages are free
+    uint64_t* bar_o = bar_q + 6;
+    uint64_t* bar_p = bar_q + 7;       // softmax threads -> issuer: P of this tile is in shared memory
+    uint64_t* bar_r = bar_q + 8;       // softmax threads -> issuer: S of the pair's second tile is in registers, S may be overwritten
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 9);
     int32_t* sh_limit = reinterpret_cast<int32_t*>(bar_q + 10);   // max over the tile's rows of the allowed-key count
     int32_t* sh_abort = sh_limit + 1;
@@ -202,8 +212,8 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         mbar_init(&bar_k[1], 1);
         mbar_init(&bar_v[0], 1);
         mbar_init(&bar_v[1], 1);
-        mbar_init(&bar_s[0], 1);
-        mbar_init(&bar_s[1], 1);
+        mbar_init(bar_s, 1);
+        mbar_init(bar_r, kSoftmaxWarps * 32);
         mbar_init(bar_o, 1);
         mbar_init(bar_p, kSoftmaxWarps * 32);
         fence_mbar_init();
@@ -217,11 +227,13 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     const uint32_t tmem_base = *tmem_slot;
     const int n_tiles = (*sh_limit + kBN - 1) / kBN;
 
+    // K lives as [dim box][stage][64 keys x 128 B]: the two stages of a box are contiguous, so that the two tiles
+    // of a pair form one 128-row K-major operand and their scores come from ONE set of N = 128 MMAs.
     auto load_k = [&](int j) {
-        uint8_t* dst = smem + kOffK + (j & 1) * kVStage;
+        uint8_t* dst = smem + kOffK + (j & 1) * (kBN * 128);
         mbar_expect_tx(&bar_k[j & 1], 2 * kBN * 128);
         tma_load_3d(dst, &kmap, 0, j * kBN, zkv, &bar_k[j & 1]);
-        tma_load_3d(dst + kBN * 128, &kmap, 64, j * kBN, zkv, &bar_k[j & 1]);
+        tma_load_3d(dst + 2 * kBN * 128, &kmap, 64, j * kBN, zkv, &bar_k[j & 1]);
     };
     auto load_v = [&](int j) {
         uint8_t* dst = smem + kOffV + (j & 1) * kVStage;
@@ -236,7 +248,7 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t q_addr = smem_u32(smem + kOffQ), k_addr = smem_u32(smem + kOffK);
     const uint32_t v_addr = smem_u32(smem + kOffV), p_addr = smem_u32(smem + kOffP);
-    constexpr uint32_t kIdescS = instr_desc(kBN, 0);
+    constexpr uint32_t kIdescS = instr_desc(2 * kBN, 0);   // a pair of tiles per instruction
     constexpr uint32_t kIdescO = instr_desc(kD, 1);
     bool ok = true;
 
@@ -251,40 +263,51 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, zq, bar_q);
                 tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, zq, bar_q);
                 load_k(0);
+                load_k(1);      // always a whole pair: rows past the end are zero-filled, rows past the limit are masked
                 load_v(0);
-                if (n_tiles > 1) {
-                    load_k(1);
-                    load_v(1);
-                }
+                if (n_tiles > 1) load_v(1);
             }
             __syncwarp();
-            auto issue_qk = [&](int jj) {
-                ok = ok && mbar_wait(&bar_k[jj & 1], (uint32_t)((jj >> 1) & 1));
+            // S of tiles 2m and 2m+1 in one go: eight N = 128 MMAs into columns [0, 128)
+            auto issue_qk_pair = [&](int m) {
+                ok = ok && mbar_wait(&bar_k[0], (uint32_t)(m & 1));
+                ok = ok && mbar_wait(&bar_k[1], (uint32_t)(m & 1));
                 if (!ok) return;
                 tc_fence_after();
-                const uint32_t ks_addr = k_addr + (uint32_t)(jj & 1) * kVStage;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint32_t blk = (uint32_t)(ks >> 2), in = (uint32_t)(ks & 3) * 32;
-                    umma_ss(tmem_base + kColS + (uint32_t)(jj & 1) * kBN, smem_desc(q_addr + blk * (kBM * 128) + in, 16, 1024),
-                            smem_desc(ks_addr + blk * (kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u, lead);
+                    umma_ss(tmem_base + kColS, smem_desc(q_addr + blk * (kBM * 128) + in, 16, 1024),
+                            smem_desc(k_addr + blk * (2 * kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u, lead);
                 }
-                if (lead) umma_commit(&bar_s[jj & 1]);
+                if (lead) umma_commit(bar_s);
                 __syncwarp();
             };
             ok = mbar_wait(bar_q, 0);
-            if (ok) issue_qk(0);
+            if (ok) issue_qk_pair(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                // S[(j+1)&1] was last read by the softmax of tile j-1, whose arrival on bar_p has been seen
-                if (j + 1 < n_tiles) issue_qk(j + 1);
-                // K stage j&1 is free as soon as S_j has been computed: refill it a whole tile ahead of its use
-                if (j + 2 < n_tiles) {
-                    ok = ok && mbar_wait(&bar_s[j & 1], (uint32_t)((j >> 1) & 1));
+                const int m = j >> 1;
+                const bool next_pair = 2 * (m + 1) < n_tiles;
+                if ((j & 1) == 0) {
+                    // both K stages are free once the pair's first MMA has completed: refill them for the next pair
+                    if (next_pair) {
+                        ok = ok && mbar_wait(bar_s, (uint32_t)(m & 1));
+                        if (!ok) break;
+                        if (lead) {
+                            load_k(2 * m + 2);
+                            load_k(2 * m + 3);
+                        }
+                        __syncwarp();
+                    }
+                } else if (next_pair) {
+                    // the softmax threads hold S of the pair's second tile in registers: S may be overwritten
+                    ok = ok && mbar_wait(bar_r, (uint32_t)(m & 1));
                     if (!ok) break;
-                    if (lead) load_k(j + 2);
-                    __syncwarp();
+                    tc_fence_after();
+                    issue_qk_pair(m + 1);
+                    if (!ok) break;
                 }
-                // softmax of tile j done: P_j is in shared memory, S_j has been read, PV_{j-1} has completed
+                // softmax of tile j done: P_j is in shared memory, PV_{j-1} has completed
                 ok = ok && mbar_wait(bar_p, (uint32_t)(j & 1));
                 if (!ok) break;
                 tc_fence_after();
@@ -305,7 +328,7 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     } else {
         // =============================== softmax warps: one query row per thread ===============================
         for (int j = 0; j < n_tiles; ++j) {
-            ok = mbar_wait(&bar_s[j & 1], (uint32_t)((j >> 1) & 1));
+            ok = mbar_wait(bar_s, (uint32_t)((j >> 1) & 1));    // one completion per pair of tiles
             if (!ok) break;
             tc_fence_after();
             const uint32_t s_col = kColS + (uint32_t)(j & 1) * kBN;
@@ -313,6 +336,10 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
             tmem_ld32(lane_addr + s_col, s);
             tmem_ld32(lane_addr + s_col + 32, s + 32);
             tc_wait_ld();
+            if (j & 1) {   // the pair's scores have left tensor memory: the next pair's first MMA may overwrite them
+                tc_fence_before();
+                mbar_arrive(bar_r);
+            }
             const int t0 = j * kBN;
             if (t0 + kBN > limit) {   // only tiles that cross the row's limit pay for the mask
 #pragma unroll
