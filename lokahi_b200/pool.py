@@ -390,6 +390,14 @@ class PagedPool:
     def wait_resident(self, timeout_ms: int = 10000):
         self._check(lib.skv_wait_resident(self._h, timeout_ms))
 
+    def transfers_done(self) -> bool:
+        """True when the copy stream has drained (a poll: never blocks)."""
+        try:
+            self.wait_resident(0)
+            return True
+        except TimeoutError:
+            return False
+
     def check_device_status(self) -> int:
         flag = C.c_int32()
         self._check(lib.skv_check_device_status(self._h, self.stream, C.byref(flag)))

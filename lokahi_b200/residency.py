@@ -24,6 +24,7 @@ class BudgetExceededError(RuntimeError):
 class GroupState(str, Enum):
     RESIDENT = "resident"
     PARKED = "parked"
+    LOADING = "loading"       # device pages reserved, copy back from the host enqueued but not yet confirmed
 
 
 @dataclass
@@ -49,6 +50,7 @@ class KVResidencySnapshot:
     evictions: int
     prefetches: int
     stalls: int               # ensure_resident calls that had to bring at least one group back
+    loading_groups: Tuple[Tuple[int, int], ...] = ()
 
 
 class KVPageResidency:
@@ -71,7 +73,8 @@ class KVPageResidency:
         return self._tick
 
     def _resident_pages(self) -> int:
-        return sum(g.n_slots for g in self._groups.values() if g.state is GroupState.RESIDENT)
+        """Device pages held: resident groups plus those reserved for a copy in flight."""
+        return sum(g.n_slots for g in self._groups.values() if g.state is not GroupState.PARKED)
 
     def track(self, seq: int) -> None:
         """Register (or extend) the groups of a sequence from its current page-table row; new pages are resident."""
@@ -139,18 +142,60 @@ class KVPageResidency:
         with self._lock:
             groups = self._groups_of(seq, first_slot, n_slots)
             parked = [g for g in groups if g.state is GroupState.PARKED]
+            loading = [g for g in groups if g.state is GroupState.LOADING]      # reserved earlier, copy in flight
             keys = {(g.seq, g.index) for g in groups}
             self._make_room(sum(g.n_slots for g in parked), exclude=keys)     # raises before anything moves
             for g in parked:
                 self.pool.prefetch(g.seq, g.first_slot, g.n_slots)
-                g.state = GroupState.RESIDENT
                 self._prefetches += 1
             for g in groups:
+                g.state = GroupState.RESIDENT
                 g.last_used = self._next_tick()
-            if parked:
+            if parked or loading:
                 self._stalls += 1
                 self.pool.sync_transfers()
             return len(parked)
+
+    # -- reserve / commit: the asynchronous half (residency_manager.py:78-150) -------------------------------
+    def is_resident(self, seq: int, group_index: int) -> bool:
+        with self._lock:
+            g = self._groups.get((seq, group_index))
+            return g is not None and g.state is GroupState.RESIDENT
+
+    def state(self, seq: int, group_index: int) -> GroupState:
+        with self._lock:
+            g = self._groups.get((seq, group_index))
+            if g is None:
+                raise KeyError(f"group {(seq, group_index)} is not tracked")
+            return g.state
+
+    def reserve(self, seq: int, group_index: int) -> bool:
+        """Make room for a parked group and enqueue its copy back without waiting for it.  Returns False, with
+        nothing changed, when the budget cannot hold it beside the pinned and loading groups (the reference's
+        ``reserve`` returning False -> "budget_skip", prefetch_scheduler.py:146-156)."""
+        with self._lock:
+            g = self._groups.get((seq, group_index))
+            if g is None:
+                raise KeyError(f"group {(seq, group_index)} is not tracked")
+            if g.state is not GroupState.PARKED:
+                return True
+            try:
+                self._make_room(g.n_slots, exclude={(seq, group_index)})
+            except BudgetExceededError:
+                return False
+            self.pool.prefetch(g.seq, g.first_slot, g.n_slots)
+            g.state = GroupState.LOADING
+            self._prefetches += 1
+            return True
+
+    def commit(self, seq: int, group_index: int) -> None:
+        """The copy of a reserved group has completed: it is resident (and, unpinned, evictable) from now on."""
+        with self._lock:
+            g = self._groups.get((seq, group_index))
+            if g is None or g.state is not GroupState.LOADING:
+                raise KeyError(f"group {(seq, group_index)} has no reservation")
+            g.state = GroupState.RESIDENT
+            g.last_used = self._next_tick()
 
     def pin(self, seq: int, first_slot: int, n_slots: int) -> None:
         with self._lock:
@@ -210,10 +255,11 @@ class KVPageResidency:
             res = [g for g in self._groups.values() if g.state is GroupState.RESIDENT]
             par = [g for g in self._groups.values() if g.state is GroupState.PARKED]
             pin = [g for g in self._groups.values() if g.pin_count > 0]
+            load = [g for g in self._groups.values() if g.state is GroupState.LOADING]
             key = lambda g: (g.seq, g.index)
             return KVResidencySnapshot(
                 budget_pages=self.budget_pages, resident_pages=sum(g.n_slots for g in res),
                 parked_pages=sum(g.n_slots for g in par), pinned_pages=sum(g.n_slots for g in pin),
                 resident_groups=tuple(sorted(map(key, res))), parked_groups=tuple(sorted(map(key, par))),
                 pinned_groups=tuple(sorted(map(key, pin))), evictions=self._evictions, prefetches=self._prefetches,
-                stalls=self._stalls)
+                stalls=self._stalls, loading_groups=tuple(sorted(map(key, load))))

@@ -309,3 +309,44 @@ def test_residency_manager_keeps_results_exact_under_lru_churn():
     snap = res.snapshot()
     assert snap.resident_pages <= snap.budget_pages and snap.stalls >= 6 and snap.pinned_pages == 0
     assert pool.check_device_status() == 0
+
+
+@pytest.mark.gpu
+def test_look_ahead_prefetcher_keeps_results_exact_and_counts_its_hits():
+    """Same churn as above, driven through the prefetcher: while a sequence is attended (pinned) the next one is
+    reserved and copied back on the copy stream; every output equals the all-resident result bit for bit and the
+    counters tell demand loads from look-ahead hits."""
+    rng = np.random.default_rng(23)
+    n, Hq, Hkv, D, P, T = 3, 8, 2, 128, 16, 320
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=2, num_kv_heads=Hkv, head_dim=D, num_pages=64, max_seqs=n,
+                                       max_pages_per_seq=24, page_size=P, dtype=torch.bfloat16, host_pages=64))
+    qs = []
+    for s in range(n):
+        assert pool.alloc_sequence() == s
+        for layer in range(2):
+            k = _t(bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32)), torch.bfloat16)
+            v = _t(bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32)), torch.bfloat16)
+            pool.append(layer, k, v, seq_ids=[s], start_pos=[0])
+        qs.append(_t(bf16_round(rng.standard_normal((1, Hq, D), dtype=np.float32)), torch.bfloat16))
+    expect = [[pool.decode_attention(layer, qs[s], seq_ids=[s]).clone() for layer in range(2)] for s in range(n)]
+    groups = -(-(T // P) // 10)                                  # 20 pages in groups of 10
+    res = L.KVPageResidency(pool, budget_pages=2 * (T // P), group_pages=10)
+    for s in range(n):
+        res.track(s)
+    pf = L.KVPagePrefetcher(res)
+    statuses = []
+    for turn in range(9):
+        s, nxt = turn % n, (turn + 1) % n
+        leases = [pf.acquire(s, g) for g in range(groups)]
+        statuses += [l.cache_status for l in leases]
+        for g in range(groups):                                  # look ahead while this sequence is in use
+            pf.prefetch(nxt, g)
+        for layer in range(2):
+            assert torch.equal(pool.decode_attention(layer, qs[s], seq_ids=[s]), expect[s][layer])
+        for l in leases:
+            l.release()
+    snap = pf.snapshot()
+    assert snap.prefetch_ready_hits + snap.prefetch_waits >= 8 and snap.pages_loaded >= 8 * 10
+    assert "cold_miss" not in statuses[2 * groups:]              # after the first turns the look-ahead covers every group
+    assert res.snapshot().resident_pages <= res.snapshot().budget_pages and res.snapshot().pinned_pages == 0
+    assert pool.check_device_status() == 0
