@@ -489,6 +489,7 @@ def run_longctx(args):
     kn = torch.randn((n_seq, hkv, D), generator=gen, device=dev).to(torch.bfloat16)
     vn = torch.randn((n_seq, hkv, D), generator=gen, device=dev).to(torch.bfloat16)
     out = torch.empty_like(q)
+    q_work = torch.empty_like(q)
 
     def step(timers=None):
         if timers:
@@ -501,8 +502,8 @@ def run_longctx(args):
         if timers:
             timers[1].record()
         for layer in range(layers):
-            pool.append(layer, kn, vn, rope_k=True, q=q.clone(), layout="bhd")
-            pool.decode_attention(layer, q, out=out)
+            q_work.copy_(q)                                  # the step rotates q in place
+            pool.decode_step(layer, q_work, kn, vn, out=out)  # RoPE + append + attention: one library call
         if timers:
             timers[2].record()
 
