@@ -320,8 +320,27 @@ def run_prefill(args):
     pos = torch.arange(S, dtype=torch.int32, device=dev)      # positions are an input: resident in HBM like q, k, v
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     K, W = args.steps, args.warmup
+    if args.kv == "paged":
+        # the same K/V held in a pool of 16-token pages dealt out in a random order: the kernel reads the pages
+        n_pages = S // P
+        pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=HKV, head_dim=D, num_pages=n_pages + 8, max_seqs=1,
+                                           max_pages_per_seq=n_pages, page_size=P, dtype=torch.bfloat16, device=0))
+        assert pool.alloc_sequence() == 0
+        perm = np.random.default_rng(SEED).permutation(n_pages + 8)[:n_pages]
+        pool.set_page_table(0, perm.tolist(), S)
+        kp, vp = pool.layer_views(0)
+        idx = torch.as_tensor(perm, device=dev, dtype=torch.long)
+        kp[idx] = k[0].view(HKV, n_pages, P, D).transpose(0, 1)
+        vp[idx] = v[0].view(HKV, n_pages, P, D).transpose(0, 1)
+        pos2 = pos.view(1, S)
+
+        def call():
+            return pool.prefill_attention(0, q, positions=pos2)
+    else:
+        def call():
+            return L.chunked_grouped_attention(q, k, v, query_positions=pos, causal=True, q_block_size=512, k_block_size=512)
     for _ in range(W):
-        L.chunked_grouped_attention(q, k, v, query_positions=pos, causal=True, q_block_size=512, k_block_size=512)
+        call()
     torch.cuda.synchronize()
     sampler = ClockSampler(0)
     sampler.start()
@@ -331,7 +350,7 @@ def run_prefill(args):
     for a, b in evs:
         flush.zero_()
         a.record()
-        L.chunked_grouped_attention(q, k, v, query_positions=pos, causal=True, q_block_size=512, k_block_size=512)
+        call()
         b.record()
     torch.cuda.synchronize()
     launches = L._lib.lib.skv_launch_count() - l0
@@ -366,7 +385,7 @@ def run_prefill(args):
         "steps": K, "warmup": W, "ms_per_step": float(ms.mean()), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "chunked_gqa_prefill_4096", "batch": B, "q_heads": HQ, "kv_heads": HKV, "head_dim": D,
-                   "seq_len": S, "q_chunk": 512, "k_chunk": 512, "l2": "flushed between timed calls (256 MB write)"},
+                   "seq_len": S, "q_chunk": 512, "k_chunk": 512, "kv": args.kv, "l2": "flushed between timed calls (256 MB write)"},
         "e2e": {"value": B * S / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": int(q.numel()) * 2},
         "gpu_launches": int(launches),
@@ -699,6 +718,8 @@ def main():
     ap.add_argument("--emulate-shard", type=int, default=1, help=argparse.SUPPRESS)
     ap.add_argument("--workload", choices=["decode", "prefill", "decoder", "longctx"], default="decode",
                     help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")
+    ap.add_argument("--kv", choices=["dense", "paged"], default="dense",
+                    help="prefill workload: K/V as dense tensors or as scattered 16-token pages of a pool")
     ap.add_argument("--seqs", type=int, default=N_SEQS,
                     help="number of sequences (default: the workload's 64; smaller values are for profiler captures)")
     args = ap.parse_args()

@@ -1150,7 +1150,15 @@ int32_t skv_prefill_attn_paged(skv_pool* p, int32_t layer, const int32_t* seq_id
     A.layer = layer;
     st = upload_ids(p, seq_ids, n_seqs, stream, &A.seq_ids);
     if (st != SKV_OK) return st;
-    CUDA_TRY(p, launch_attn_generic(A, stream));
+    A.k_map = p->has_maps ? &p->k_map : nullptr;
+    A.v_map = p->has_maps ? &p->v_map : nullptr;
+    // bf16, head_dim 128, 16-token pages and at least 32 query rows: the tensor-core kernel reads the pages
+    // directly through the pool's tensor maps; everything else takes the float32 CUDA-core kernel
+    const char* force = getenv("SKV_PREFILL_GENERIC");
+    cudaError_t e = cudaErrorNotSupported;
+    if (!(force && force[0] == '1')) e = launch_attn_tc(A, stream);
+    if (e == cudaErrorNotSupported) e = launch_attn_generic(A, stream);
+    CUDA_TRY(p, e);
     return SKV_OK;
 }
 

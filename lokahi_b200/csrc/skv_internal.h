@@ -124,6 +124,9 @@ struct DenseAttnLaunch {
     PoolView pool;
     int32_t layer;
     const int32_t* seq_ids;      // device or nullptr
+    // host pointers to the pool's CUtensorMaps ([rows][head_dim] bf16, [16][64] boxes); nullptr when it has none
+    const void* k_map;
+    const void* v_map;
 };
 cudaError_t launch_attn_generic(const DenseAttnLaunch& a, cudaStream_t stream);
 // Tensor-core (tcgen05) causal prefill; returns cudaErrorNotSupported when the shape is outside its cover.

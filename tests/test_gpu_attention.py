@@ -283,6 +283,44 @@ def test_tensor_core_prefill_at_full_sequence_4096(monkeypatch):
     assert parity_errors(out[:, ::8], to_np(ref_all))[0] <= TOL_BF16, "tcgen05 vs CUDA-core at S=4096"
 
 
+def test_tensor_core_prefill_over_pages_matches_oracle_and_the_dense_kernel(monkeypatch):
+    """bf16, head_dim 128, 16-token pages, at least 32 query rows: the tcgen05 kernel reads K/V straight from the
+    scattered pages.  Ragged lengths (one shorter than a key tile, one not a multiple of the page size), default
+    bottom-right positions and explicit ones (with fully masked rows), against the oracle on the logical history
+    and against the float32 CUDA-core kernel."""
+    rng = np.random.default_rng(91)
+    lens = [40, 64, 200, 777, 1030]
+    n, Hq, Hkv, D, P, Lq = len(lens), 8, 2, 128, 16, 40
+    pool, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, n, Hkv, D, P, lens)
+    q = _t(rnd(rng.standard_normal((n, Hq, Lq, D), dtype=np.float32)), torch.bfloat16)
+    before = L._lib.lib.skv_launch_count()
+    out = pool.prefill_attention(0, q)                                   # positions default to Lk - Lq + i
+    assert L._lib.lib.skv_launch_count() - before == 1
+    monkeypatch.setenv("SKV_PREFILL_GENERIC", "1")
+    out_generic = pool.prefill_attention(0, q)
+    monkeypatch.delenv("SKV_PREFILL_GENERIC")
+    from parity import parity_errors
+    assert parity_errors(out, to_np(out_generic))[0] <= TOL_BF16
+    for i, t in enumerate(lens):
+        k_log = opaged.logical_kv(k_ref, table[i], t)[None]
+        v_log = opaged.logical_kv(v_ref, table[i], t)[None]
+        ref = oattn.chunked_grouped_attention(to_np(q[i:i + 1]), k_log, v_log, q_block_size=16, k_block_size=64)
+        assert_parity(out[i:i + 1], ref, TOL_BF16, f"paged tensor-core prefill, sequence {i} (length {t})")
+    # explicit absolute positions: some rows see nothing (-1), some see everything, the rest are scattered
+    pos = rng.integers(-1, 1100, size=(n, Lq)).astype(np.int32)
+    pos[:, 0] = -1
+    pos[:, 1] = 5000
+    out2 = pool.prefill_attention(0, q, positions=_t(pos, torch.int32))
+    assert pool.check_device_status() == 0
+    for i, t in enumerate(lens):
+        k_log = opaged.logical_kv(k_ref, table[i], t)[None]
+        v_log = opaged.logical_kv(v_ref, table[i], t)[None]
+        ref = oattn.chunked_grouped_attention(to_np(q[i:i + 1]), k_log, v_log, query_positions=pos[i:i + 1],
+                                              q_block_size=16, k_block_size=64)
+        assert_parity(out2[i:i + 1], ref, TOL_BF16, f"paged tensor-core prefill with positions, sequence {i}")
+        assert torch.count_nonzero(out2[i, :, 0]) == 0, "a row with no allowed key is exactly 0"
+
+
 def test_decode_step_equals_append_then_attention(monkeypatch):
     monkeypatch.setenv("SKV_STEP_FUSED", "0")     # the two-call form of the step: bit-identical to its parts
     rng = np.random.default_rng(55)
