@@ -960,6 +960,22 @@ void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, i
     if (env && atoi(env) > 0 && atoi(env) >= floor_chunk) chunk = atoi(env);
     chunk = ((chunk + 63) / 64) * 64;                 // 4 warps x 16-token tiles
     if (chunk < 256) chunk = 256;
+    // Few CTAs: avoid a thin last wave.  With 3 CTAs per SM a wave is 444 CTAs; when the estimate (tokens / chunk
+    // plus half a CTA of rounding per sequence and head) lands a little above one or two waves, grow the chunk
+    // until it fits (measured: 4 sequences x 96k tokens x 1 head went from 512 CTAs of 768 tokens to 440 of 896).
+    const char* wq = getenv("SKV_PLAN_WAVES");       // "0": keep the chunk as computed above
+    if (total_tokens_hint > 0 && !(env && atoi(env) > 0) && !(wq && wq[0] == '0')) {
+        const double wave = 444.0, round_up = 0.5 * (double)n_seqs * num_kv_heads;
+        const double work = (double)total_tokens_hint * num_kv_heads;
+        const double est = work / (double)chunk + round_up;
+        for (int w = 1; w <= 2; ++w) {
+            if (est > w * wave && est <= (w + 0.6) * wave && w * wave > round_up) {
+                int64_t fit = (int64_t)(work / (w * wave - round_up)) + 1;
+                fit = ((fit + 63) / 64) * 64;
+                if (fit > chunk && fit <= 2048) chunk = fit;
+            }
+        }
+    }
     if (chunk > 2048) {                               // a warp holds at most 32 tile page ids
         chunk = 2048;
         splits = (max_ctx + chunk - 1) / chunk;
