@@ -12,7 +12,8 @@ src/ollm/deepseek_mlx.py:72-169, 426-549):
         query_positions=position_ids, causal=True, q_block_size=32768,
         k_block_size=1024 if L > 128 else 1000000) -> o_proj
 
-With ``fused_rope=True`` (default) RoPE and the append are one launch (``update_with_rope``); with
+With ``fused_rope=True`` (default) RoPE and the append are one launch (``update_with_rope``), and a cached
+decode step (L == 1) is ONE library call covering RoPE, update and attention (``decode_step_with_rope``); with
 ``False`` RoPE runs first and ``cache.update`` receives rotated K, as in the reference.
 ``use_cache=False`` never touches the cache (llama_mlx.py:762).
 """
@@ -98,16 +99,22 @@ class PagedDecoder:
         if self.hot_path_events is not None:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
-        if cache is not None and self.fused_rope and hasattr(cache, "update_with_rope"):
-            k_hist, v_hist = cache.update_with_rope(q, k, v, layer, kwargs, inv_freq=self.inv_freq_np,
-                                                    scaling_factor=self.rope_scale)
-        else:
-            pos_dev = torch.as_tensor(cache_position, dtype=torch.int32, device=self.device)
-            self._rope_inplace(q, pos_dev)
-            self._rope_inplace(k, pos_dev)
-            k_hist, v_hist = (k, v) if cache is None else cache.update(k, v, layer, kwargs)
-        out = chunked_grouped_attention(q, k_hist, v_hist, query_positions=position_ids, causal=True,
-                                        q_block_size=32768, k_block_size=(1024 if L > 128 else 1000000))
+        out = None
+        if cache is not None and self.fused_rope and L == 1 and past_length > 0 and hasattr(cache, "decode_step_with_rope"):
+            # RoPE, cache update and attention of a cached decode step in one library call (two launches)
+            out = cache.decode_step_with_rope(q, k, v, layer, kwargs, inv_freq=self.inv_freq_np,
+                                              scaling_factor=self.rope_scale)
+        if out is None:
+            if cache is not None and self.fused_rope and hasattr(cache, "update_with_rope"):
+                k_hist, v_hist = cache.update_with_rope(q, k, v, layer, kwargs, inv_freq=self.inv_freq_np,
+                                                        scaling_factor=self.rope_scale)
+            else:
+                pos_dev = torch.as_tensor(cache_position, dtype=torch.int32, device=self.device)
+                self._rope_inplace(q, pos_dev)
+                self._rope_inplace(k, pos_dev)
+                k_hist, v_hist = (k, v) if cache is None else cache.update(k, v, layer, kwargs)
+            out = chunked_grouped_attention(q, k_hist, v_hist, query_positions=position_ids, causal=True,
+                                            q_block_size=32768, k_block_size=(1024 if L > 128 else 1000000))
         if self.hot_path_events is not None:
             ev[1].record()
             self.hot_path_events.append(ev)

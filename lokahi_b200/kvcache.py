@@ -144,6 +144,30 @@ class PagedKVCache:
                              start_pos=[previous] * self.batch_size, rope_k=True, q=query_states)
         return self._finish_update(layer_idx, previous, key_states.shape[2])
 
+    def decode_step_with_rope(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                              layer_idx: int, cache_kwargs: Optional[Dict[str, Any]] = None, *, inv_freq: np.ndarray,
+                              scaling_factor: float = 1.0, eps: float = 1e-12) -> Optional[torch.Tensor]:
+        """The cached decode step of a layer (one new token per sequence) in ONE library call:
+        ``update_with_rope`` followed by the attention call with ``query_positions = [past]``
+        (llama_mlx.py:284-308 for L == 1).  Same validation and bookkeeping as ``update``; ``query_states``
+        is rotated in place; returns ``[B, Hq, 1, D]``, or ``None`` when the step does not apply (more than one
+        token, or sequences that are not the pool's 0..B-1) and the caller should make the two calls."""
+        if key_states.dim() != 4 or key_states.shape[2] != 1 or query_states.dim() != 4 or query_states.shape[2] != 1:
+            return None
+        if self.seq_ids is None or list(self.seq_ids) != list(range(self.batch_size)) or not query_states.is_contiguous():
+            return None
+        previous = self._prepare_update(key_states, value_states, layer_idx, cache_kwargs)
+        rope_key = (inv_freq.tobytes(), float(scaling_factor))
+        if getattr(self, "_rope_key", None) != rope_key:
+            self.pool.set_rope(inv_freq, scaling_factor)
+            self._rope_key = rope_key
+        B, Hq, _, D = query_states.shape
+        Hkv = key_states.shape[1]
+        out = self.pool.decode_step(layer_idx, query_states.view(B, Hq, D), key_states.reshape(B, Hkv, D).contiguous(),
+                                    value_states.reshape(B, Hkv, D).contiguous(), eps=eps)
+        self._finish_update(layer_idx, previous, 1)
+        return out.view(B, Hq, 1, D)
+
     # -- lengths (mlx_kvcache.py:160-181) ----------------------------------------------------------------------
     def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:
         if layer_idx is None:

@@ -350,3 +350,43 @@ def test_look_ahead_prefetcher_keeps_results_exact_and_counts_its_hits():
     assert "cold_miss" not in statuses[2 * groups:]              # after the first turns the look-ahead covers every group
     assert res.snapshot().resident_pages <= res.snapshot().budget_pages and res.snapshot().pinned_pages == 0
     assert pool.check_device_status() == 0
+
+
+@pytest.mark.gpu
+def test_one_call_decode_step_of_the_cache_equals_update_then_attention():
+    """``decode_step_with_rope`` (one library call, two launches) against ``update_with_rope`` + the attention
+    callable on twin caches over several steps: same rotated q, same stored history, same lengths, outputs within
+    bf16 tolerance; a replayed position is still rejected with the reference's message."""
+    rng = np.random.default_rng(31)
+    B, Hq, Hkv, D, T0 = 3, 8, 2, 128, 37
+    cfg = SimpleNamespace(num_hidden_layers=2, max_position_embeddings=256)
+    inv = L.rope_inv_freq(D, 10000.0)
+    caches = [L.PagedKVCache(cfg), L.PagedKVCache(cfg)]
+    k0 = _t(bf16_round(rng.standard_normal((B, Hkv, T0, D), dtype=np.float32)), torch.bfloat16)
+    v0 = _t(bf16_round(rng.standard_normal((B, Hkv, T0, D), dtype=np.float32)), torch.bfloat16)
+    q0 = _t(bf16_round(rng.standard_normal((B, Hq, T0, D), dtype=np.float32)), torch.bfloat16)
+    for c in caches:
+        for layer in range(2):
+            c.update_with_rope(q0.clone(), k0, v0, layer, {"cache_position": list(range(T0))}, inv_freq=inv)
+    from parity import parity_errors
+    for step in range(5):
+        pos = T0 + step
+        q = _t(bf16_round(rng.standard_normal((B, Hq, 1, D), dtype=np.float32)), torch.bfloat16)
+        k = _t(bf16_round(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32)), torch.bfloat16)
+        v = _t(bf16_round(rng.standard_normal((B, Hkv, 1, D), dtype=np.float32)), torch.bfloat16)
+        for layer in range(2):
+            qa, qb = q.clone(), q.clone()
+            kh, vh = caches[0].update_with_rope(qa, k, v, layer, {"cache_position": [pos]}, inv_freq=inv)
+            out_a = L.chunked_grouped_attention(qa, kh, vh, query_positions=np.array([[pos]], dtype=np.int32), causal=True)
+            out_b = caches[1].decode_step_with_rope(qb, k, v, layer, {"cache_position": [pos]}, inv_freq=inv)
+            assert out_b is not None and out_b.shape == (B, Hq, 1, D)
+            assert torch.equal(qa, qb)
+            assert parity_errors(out_b, to_np(out_a))[0] <= TOL_BF16
+            assert caches[0].get_seq_length(layer) == caches[1].get_seq_length(layer) == pos + 1
+    for layer in range(2):
+        ka, va = caches[0].materialize(layer)
+        kb, vb = caches[1].materialize(layer)
+        assert torch.equal(ka, kb) and torch.equal(va, vb)
+    with pytest.raises(ValueError, match="append exactly"):
+        caches[1].decode_step_with_rope(q.clone(), k, v, 0, {"cache_position": [T0]}, inv_freq=inv)
+    assert caches[1].decode_step_with_rope(q0.clone(), k0, v0, 0, {"cache_position": [0]}, inv_freq=inv) is None   # L > 1
