@@ -105,6 +105,13 @@ def chunked_grouped_attention(
     positions = None
     if causal and query_positions is not None:
         positions = _normalize_query_positions(query_positions, B, Lq)
+        if not positions.is_cuda and Lk >= Lq:
+            # Host positions that equal the default arange(Lk - Lq, Lk) (what the decoder passes for every cached
+            # call, llama_mlx.py:777) need no device copy at all: the kernels compute that default themselves.  A
+            # pageable host-to-device copy here would also stall the host until the stream drains, once per layer.
+            default = torch.arange(Lk - Lq, Lk, dtype=torch.int32)
+            if bool((positions == default.unsqueeze(0)).all()):
+                positions = None
 
     paged = isinstance(k, PagedView)
     if paged != isinstance(v, PagedView):

@@ -75,7 +75,112 @@ __global__ void append_kernel(AppendLaunch a) {
     }
 }
 
+// Vectorised append: one block per new token, 16-byte accesses, cos/sin of the token's position computed once
+// per block and shared by all heads (the scalar kernel above recomputes them per head and moves 2 or 4 bytes
+// per access: measured 0.27 ms for 16 k tokens x 32 heads of bf16 where the bytes need about 0.07 ms).
+// Work items: (head slot, 16-byte chunk c of the first half) for K and Q -- the thread loads chunk c of both
+// halves, rotates the pairs and stores both -- and (KV head, 16-byte chunk of the whole row) for V.
+// Same arithmetic per element as rope_pair, so the stored bytes are identical to the scalar kernel's.
+template <typename T>
+__global__ void __launch_bounds__(128) append_vec_kernel(AppendLaunch a) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const PoolView& pv = a.pool;
+    pdl_wait();
+    extern __shared__ float cs[];                // [half] cos, [half] sin
+    const int half = pv.head_dim >> 1;
+    const int tok = blockIdx.x;                  // i * n_new + j
+    const int i = tok / a.n_new;
+    const int j = tok - i * a.n_new;
+    const AppendMeta m = a.meta[i];
+    if (!checked_seq(pv, m.seq)) return;
+    const int pos = m.start + j;
+    const bool need_rope = a.rope_k || a.n_q_heads > 0;
+    if (need_rope) {
+        float fpos = (float)pos;
+        if (a.scaling != 1.0f) fpos = __fdiv_rn(fpos, a.scaling);
+        for (int d = threadIdx.x; d < half; d += blockDim.x) {
+            float sn, c;
+            sincosf(__fmul_rn(fpos, a.inv_freq[d]), &sn, &c);
+            cs[d] = c;
+            cs[half + d] = sn;
+        }
+        __syncthreads();
+    }
+    const int page = checked_page(pv, m.seq, pos / pv.page_size);
+    const int chunks = half / VEC;               // 16-byte chunks per half row
+    const int n_rot = pv.num_kv_heads + a.n_q_heads;
+    // K rows (rotated or copied) and Q rows (rotated)
+    for (int item = threadIdx.x; item < n_rot * chunks; item += blockDim.x) {
+        const int slot = item / chunks, c = item - slot * chunks;
+        const T* src;
+        T* dst;
+        bool rotate;
+        if (slot < pv.num_kv_heads) {
+            if (page < 0) continue;
+            src = reinterpret_cast<const T*>(a.k) + i * a.kv_stride_seq + slot * a.kv_stride_head + j * a.kv_stride_tok;
+            dst = reinterpret_cast<T*>(pv.k_base) + (int64_t)a.layer * (pv.layer_stride_bytes / (int64_t)sizeof(T)) +
+                  row_offset(pv, page, slot, pos % pv.page_size);
+            rotate = a.rope_k != 0;
+        } else {
+            const int64_t qoff = i * a.q_stride_seq + (slot - pv.num_kv_heads) * a.q_stride_head + j * a.q_stride_tok;
+            src = reinterpret_cast<const T*>(a.q_in) + qoff;
+            dst = reinterpret_cast<T*>(a.q_out) + qoff;
+            rotate = true;
+        }
+        uint4 lo = *reinterpret_cast<const uint4*>(src + c * VEC);
+        uint4 hi = *reinterpret_cast<const uint4*>(src + half + c * VEC);
+        if (rotate) {
+            T* x1 = reinterpret_cast<T*>(&lo);
+            T* x2 = reinterpret_cast<T*>(&hi);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                const float f1 = to_f32(x1[e]), f2 = to_f32(x2[e]);
+                const float co = cs[c * VEC + e], sn = cs[half + c * VEC + e];
+                x1[e] = from_f32<T>(__fadd_rn(__fmul_rn(f1, co), __fmul_rn(-f2, sn)));
+                x2[e] = from_f32<T>(__fadd_rn(__fmul_rn(f2, co), __fmul_rn(f1, sn)));
+            }
+        }
+        *reinterpret_cast<uint4*>(dst + c * VEC) = lo;
+        *reinterpret_cast<uint4*>(dst + half + c * VEC) = hi;
+    }
+    // V rows: plain copy
+    if (page >= 0) {
+        for (int item = threadIdx.x; item < pv.num_kv_heads * 2 * chunks; item += blockDim.x) {
+            const int h = item / (2 * chunks), c = item - h * 2 * chunks;
+            const T* src = reinterpret_cast<const T*>(a.v) + i * a.kv_stride_seq + h * a.kv_stride_head + j * a.kv_stride_tok;
+            T* dst = reinterpret_cast<T*>(pv.v_base) + (int64_t)a.layer * (pv.layer_stride_bytes / (int64_t)sizeof(T)) +
+                     row_offset(pv, page, h, pos % pv.page_size);
+            *reinterpret_cast<uint4*>(dst + c * VEC) = *reinterpret_cast<const uint4*>(src + c * VEC);
+        }
+    }
+    if (j == 0 && threadIdx.x == 0) pv.lengths[(int64_t)a.layer * pv.max_seqs + m.seq] = m.start + a.n_new;
+}
+
+// 16-byte accesses need 16-byte aligned rows on both sides.
+static bool append_vectorisable(const AppendLaunch& a, size_t esize) {
+    const int vec = (int)(16 / esize);
+    if (a.pool.head_dim % (2 * vec) != 0) return false;
+    auto ok_ptr = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    auto ok_stride = [vec](int64_t s) { return s % vec == 0; };
+    if (!ok_ptr(a.k) || !ok_ptr(a.v) || !ok_stride(a.kv_stride_seq) || !ok_stride(a.kv_stride_head) || !ok_stride(a.kv_stride_tok))
+        return false;
+    if (a.n_q_heads > 0 && (!ok_ptr(a.q_in) || !ok_ptr(a.q_out) || !ok_stride(a.q_stride_seq) || !ok_stride(a.q_stride_head) ||
+                            !ok_stride(a.q_stride_tok)))
+        return false;
+    const char* force = getenv("SKV_APPEND_SCALAR");
+    return !(force && force[0] == '1');
+}
+
 cudaError_t launch_append(const AppendLaunch& a, cudaStream_t stream) {
+    const size_t esize = a.dtype == SKV_BF16 ? 2 : 4;
+    if (append_vectorisable(a, esize)) {
+        dim3 grid((unsigned)(a.n_seqs * a.n_new));
+        const size_t smem = (size_t)a.pool.head_dim * sizeof(float);
+        cudaError_t e = a.dtype == SKV_BF16 ? launch_pdl(append_vec_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, a)
+                                            : launch_pdl(append_vec_kernel<float>, grid, dim3(128), smem, stream, a);
+        count_launches(1);
+        return e;
+    }
     const int half = a.pool.head_dim / 2;
     int heads_per_block = 128 / half;
     if (heads_per_block < 1) heads_per_block = 1;

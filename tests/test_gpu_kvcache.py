@@ -390,3 +390,40 @@ def test_one_call_decode_step_of_the_cache_equals_update_then_attention():
     with pytest.raises(ValueError, match="append exactly"):
         caches[1].decode_step_with_rope(q.clone(), k, v, 0, {"cache_position": [T0]}, inv_freq=inv)
     assert caches[1].decode_step_with_rope(q0.clone(), k0, v0, 0, {"cache_position": [0]}, inv_freq=inv) is None   # L > 1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float32, 64)])
+def test_vectorised_append_writes_the_same_bytes_as_the_scalar_kernel(monkeypatch, dtype, D):
+    """The 16-byte-access append (one block per token, cos/sin shared by all heads) against the element-wise
+    kernel: stored K/V, rotated q and lengths bit-identical, with ragged starts and several tokens per call."""
+    rng = np.random.default_rng(77)
+    B, Hq, Hkv, P, n_new = 3, 8, 2, 16, 21
+    starts = [0, 5, 30]
+    inv = L.rope_inv_freq(D, 500000.0)
+    results = []
+    for scalar in ("1", "0"):
+        monkeypatch.setenv("SKV_APPEND_SCALAR", scalar)
+        pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=32, max_seqs=B,
+                                           max_pages_per_seq=8, page_size=P, dtype=dtype))
+        pool.set_rope(inv, 2.0)
+        r = np.random.default_rng(78)
+        rnd = bf16_round if dtype == torch.bfloat16 else (lambda a: a)
+        for s in range(B):
+            assert pool.alloc_sequence() == s
+            if starts[s]:
+                k0 = _t(rnd(r.standard_normal((1, Hkv, starts[s], D), dtype=np.float32)), dtype)
+                pool.append(0, k0, k0, seq_ids=[s], start_pos=[0])
+        q = _t(rnd(r.standard_normal((B, Hq, n_new, D), dtype=np.float32)), dtype)
+        k = _t(rnd(r.standard_normal((B, Hkv, n_new, D), dtype=np.float32)), dtype)
+        v = _t(rnd(r.standard_normal((B, Hkv, n_new, D), dtype=np.float32)), dtype)
+        pool.append(0, k, v, start_pos=starts, rope_k=True, q=q)
+        kk, vv = pool.gather(0, n_seqs=B, max_len=max(starts) + n_new)
+        torch.cuda.synchronize()
+        results.append((q.clone(), kk.clone(), vv.clone(), pool.lengths(0).copy()))
+        assert pool.check_device_status() == 0
+    (qa, ka, va, la), (qb, kb, vb, lb) = results
+    assert torch.equal(qa, qb) and np.array_equal(la, lb)
+    for s in range(B):
+        t = starts[s] + n_new
+        assert torch.equal(ka[s, :, :t], kb[s, :, :t]) and torch.equal(va[s, :, :t], vb[s, :, :t])
