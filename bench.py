@@ -577,9 +577,9 @@ def pool_set_lengths(pool, layers, n_seq, length):
 
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per decode launch: measured on the 16-sequence capture
-# case (292.68 MB of traffic for 287.07 MB algorithmic, profiles/decode_tma_kernel_paged_decode_16seq.md)
+# case (293.13 MB of traffic for 287.07 MB algorithmic, profiles/decode_tma_kernel_paged_decode_16seq.md)
 # and scaled to this workload by the algorithmic bytes, which is what the traffic grows with.
-TRAFFIC_RATIO = 292.68 / 287.07
+TRAFFIC_RATIO = 293.13 / 287.07
 
 
 # ------------------------------------------------------------------------------------------------------
