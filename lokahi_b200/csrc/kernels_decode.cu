@@ -767,6 +767,9 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
     const PoolView& pv = d.pool;
     const int hq = blockIdx.x, i = blockIdx.y;
     pdl_wait();
+    // The next kernel in the stream (the following step's split-K kernel, or the gather wait) starts with a
+    // wait of its own for this grid's completion: letting it launch now hides its launch latency.
+    pdl_launch_dependents();
     const int seq = d.seq_ids ? d.seq_ids[i] : i;
     const int D = pv.head_dim;
     T* out = reinterpret_cast<T*>(d.out) + ((int64_t)i * d.n_q_heads + hq) * D;
@@ -911,6 +914,7 @@ __global__ void __launch_bounds__(128) merge_partials_kernel(const float* __rest
 
 // Waits (bounded, about a second) until every rank's flag has reached `epoch`; lane r watches rank r.
 __global__ void gather_wait_kernel(const int32_t* flags, int world, int epoch, int32_t* status) {
+    pdl_wait();   // launched early (programmatic dependent launch); the local merge kernel has completed from here on
     const int r = threadIdx.x;
     if (r < world) {
         const volatile int32_t* f = flags + r;
@@ -1046,9 +1050,9 @@ cudaError_t launch_merge_partials(const float* parts, int32_t n_parts, int64_t p
 }
 
 cudaError_t launch_gather_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, cudaStream_t stream) {
-    gather_wait_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, status);
+    cudaError_t e = launch_pdl(gather_wait_kernel, dim3(1), dim3(32), 0, stream, flags, (int)world, (int)epoch, status);
     count_launches(1);
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace skv
