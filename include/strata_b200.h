@@ -252,6 +252,19 @@ SKV_API int32_t skv_rope_rows(const void* x_in, void* x_out, const int32_t* posi
                       int32_t n_rows, int32_t n_heads, int32_t head_dim, int64_t stride_row, int64_t stride_head,
                       float scaling_factor, int32_t dtype, void* stream);
 
+/* Decoder glue on either side of the hot path (the callers directly above it; float32 arithmetic, one rounding per
+ * output element, storage dtype float32 or bfloat16).
+ * skv_rmsnorm: out = weight * (h * rsqrt(mean(h^2) + eps)) per row of [n_rows][hidden]
+ *   (MLXRMSNorm, src/ollm/llama_mlx.py:77-92; optimized_rmsnorm, src/ollm/metal_optimizations.py:75-97).
+ *   delta == NULL: h = x.  Otherwise h = x + delta, rounded to the storage dtype, and h is also written to
+ *   sum_out (may alias x): the residual add that precedes the norm, fused
+ *   (optimized_rmsnorm_residual, metal_optimizations.py:100-117).
+ * skv_swiglu: out = (gate * sigmoid(gate)) * up over n elements
+ *   (MLXLlamaMLP, llama_mlx.py:345-408; optimized_swiglu, metal_optimizations.py:140-157). */
+SKV_API int32_t skv_rmsnorm(const void* x, const void* delta, void* sum_out, const void* weight, void* out, int64_t n_rows,
+                            int32_t hidden, float eps, int32_t dtype, void* stream);
+SKV_API int32_t skv_swiglu(const void* gate, const void* up, void* out, int64_t n, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

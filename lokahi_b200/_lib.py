@@ -98,6 +98,8 @@ SIGNATURES = {
     "skv_wait_resident": (_i32, [_vp, _i32]),
     "skv_check_device_status": (_i32, [_vp, _vp, _pi32]),
     "skv_rope_rows": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _f, _i32, _vp]),
+    "skv_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f, _i32, _vp]),
+    "skv_swiglu": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
 }
 
 

@@ -21,6 +21,7 @@ SOURCES = [
     "decode_static.cu",
     "kernels_attn_generic.cu",
     "kernels_prefill_tc.cu",
+    "kernels_glue.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,7 +1,7 @@
 """Llama / DeepSeek-style decoder around the B200 hot path.
 
-The linear layers, RMSNorm and the SiLU-gate MLP are plain torch ops (cuBLAS): they are the callers
-of the hot path, not part of it.  What matters here is the call sequence around the cache, which
+The linear layers are torch (cuBLAS); RMSNorm (with the residual add before it) and the SiLU-gate product
+are single launches of the library (``glue.py``): they are the callers of the hot path, not part of it.  What matters here is the call sequence around the cache, which
 follows the reference exactly (MLXLlamaAttention.__call__, src/ollm/llama_mlx.py:220-342;
 MLXLlamaModel.__call__, :740-833; MLXLlamaForCausalLM.__call__, :863-912; DeepSeek twin
 src/ollm/deepseek_mlx.py:72-169, 426-549):
@@ -19,6 +19,7 @@ decode step (L == 1) is ONE library call covering RoPE, update and attention (``
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import Any, Dict, Optional
 
@@ -26,6 +27,7 @@ import torch
 import torch.nn.functional as F
 
 from .attention import chunked_grouped_attention
+from .glue import add_rms_norm, rms_norm, swiglu
 from .generation import greedy_generate
 from .pool import rope_inv_freq, rope_rows
 
@@ -44,11 +46,13 @@ def rope_scaling_factor(config: Any) -> float:
 
 class PagedDecoder:
     def __init__(self, config: Any, weights: Dict[str, torch.Tensor], *, tracer: Optional[Any] = None,
-                 fused_rope: bool = True):
+                 fused_rope: bool = True, fused_glue: Optional[bool] = None):
         self.config = config
         self.w = weights
         self.tracer = tracer
         self.fused_rope = fused_rope
+        # RMSNorm (+ residual add) and SwiGLU as single launches; False (or SKV_FUSED_GLUE=0): plain torch ops
+        self.fused_glue = (os.environ.get("SKV_FUSED_GLUE", "1") != "0") if fused_glue is None else bool(fused_glue)
         self.H = config.hidden_size
         self.Hq = config.num_attention_heads
         # deepseek_mlx.py:235: KV heads default to the attention-head count (MHA)
@@ -69,14 +73,24 @@ class PagedDecoder:
 
     # -- glue (llama_mlx.py:53-92, 345-408) ------------------------------------------------------------
     def _rms_norm(self, x, weight):
+        if self.fused_glue:
+            return rms_norm(x.contiguous(), weight, self.eps)             # one launch
         x32 = x.float()
         var = x32.pow(2).mean(-1, keepdim=True)
         return (weight.float() * (x32 * torch.rsqrt(var + self.eps))).to(x.dtype)
 
+    def _add_norm(self, hidden, delta, weight):
+        """hidden + delta, and the RMSNorm of that sum (the residual add and the norm that follows it)."""
+        if self.fused_glue:
+            return add_rms_norm(hidden.contiguous(), delta.contiguous(), weight, self.eps)   # one launch, sum in place
+        hidden = hidden + delta
+        return hidden, self._rms_norm(hidden, weight)
+
     def _mlp(self, x, b):
         gate = F.linear(x, self.w[f"{b}.mlp.gate_proj.weight"])
         up = F.linear(x, self.w[f"{b}.mlp.up_proj.weight"])
-        return F.linear(F.silu(gate) * up, self.w[f"{b}.mlp.down_proj.weight"])
+        act = swiglu(gate, up) if self.fused_glue else F.silu(gate) * up
+        return F.linear(act, self.w[f"{b}.mlp.down_proj.weight"])
 
     def _rope_inplace(self, x: torch.Tensor, positions: torch.Tensor):
         """x [B, H, L, D] contiguous, one position per token shared by the batch (llama_mlx.py:777)."""
@@ -138,13 +152,17 @@ class PagedDecoder:
         past = cache.get_seq_length() if cache is not None else 0
         cache_position = list(range(past, past + L))            # host values: no device sync to validate them
         position_ids = torch.tensor([cache_position], dtype=torch.int32)
-        for i in range(self.config.num_hidden_layers):
+        # Same block as the reference (norm -> attention -> add -> norm -> MLP -> add, llama_mlx.py:608-658), with
+        # every residual add folded into the norm that follows it.
+        n_layers = self.config.num_hidden_layers
+        x = self._rms_norm(hidden, self.w["model.layers.0.input_layernorm.weight"]) if n_layers else None
+        for i in range(n_layers):
             b = f"model.layers.{i}"
-            x = self._rms_norm(hidden, self.w[f"{b}.input_layernorm.weight"])
-            hidden = hidden + self._attention(i, x, position_ids, cache, cache_position)
-            x = self._rms_norm(hidden, self.w[f"{b}.post_attention_layernorm.weight"])
-            hidden = hidden + self._mlp(x, b)
-        hidden = self._rms_norm(hidden, self.w["model.norm.weight"])
+            hidden, x = self._add_norm(hidden, self._attention(i, x, position_ids, cache, cache_position),
+                                       self.w[f"{b}.post_attention_layernorm.weight"])
+            next_w = self.w[f"model.layers.{i + 1}.input_layernorm.weight"] if i + 1 < n_layers else self.w["model.norm.weight"]
+            hidden, x = self._add_norm(hidden, self._mlp(x, b), next_w)
+        hidden = x if n_layers else self._rms_norm(hidden, self.w["model.norm.weight"])
         head = self.w.get("lm_head.weight")
         if head is None:                                          # tied-embedding fallback (llama_mlx.py:886-890)
             head = self.w["model.embed_tokens.weight"]

@@ -96,7 +96,9 @@ class PagedKVCache:
                 max_pages_per_seq=pages_per_seq, page_size=self._page_size, dtype=key_states.dtype,
                 device=dev, host_pages=self._host_pages))
         if self.seq_ids is None:
-            self.seq_ids = [self.pool.alloc_sequence() for _ in range(B)]
+            # sorted: on a pool of its own the cache then owns sequences 0..B-1 in batch order, which is what the
+            # one-call decode step needs (the allocator hands ids back in LIFO order after a clear)
+            self.seq_ids = sorted(self.pool.alloc_sequence() for _ in range(B))
             self.batch_size = B
 
     # -- update (mlx_kvcache.py:65-125) ----------------------------------------------------------------------

@@ -447,3 +447,31 @@ def test_sequence_sharding_partials_merge_to_the_unsharded_result():
     # world == 1 path of the helper
     one = L.sequence_sharded_decode(pool_for(0, lambda s: lens[s]), 0, qt, qpos, L.SequenceShard(0, 1, 2048, P))
     assert_parity(one, to_np(whole), TOL_BF16, "single-rank sequence sharding")
+
+
+def test_fused_step_is_all_or_nothing_when_pages_run_out():
+    """A step that needs a fresh page for some sequences while the pool has too few free ones fails with
+    OutOfPagesError before anything is launched or changed; after a sequence is freed the same step succeeds."""
+    rng = np.random.default_rng(57)
+    n, Hq, Hkv, D, P = 3, 8, 2, 128, 16
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=4, max_seqs=4,
+                                       max_pages_per_seq=4, page_size=P, dtype=torch.bfloat16))
+    pool.set_rope(L.rope_inv_freq(D, 10000.0))
+    rnd = bf16_round
+    for s in range(n):                                  # 16 tokens each: three full pages, one page left
+        assert pool.alloc_sequence() == s
+        kv = _t(rnd(rng.standard_normal((1, Hkv, P, D), dtype=np.float32)), torch.bfloat16)
+        pool.append(0, kv, kv, seq_ids=[s], start_pos=[0])
+    q = _t(rnd(rng.standard_normal((n, Hq, D), dtype=np.float32)), torch.bfloat16)
+    k = _t(rnd(rng.standard_normal((n, Hkv, D), dtype=np.float32)), torch.bfloat16)
+    v = _t(rnd(rng.standard_normal((n, Hkv, D), dtype=np.float32)), torch.bfloat16)
+    q_before, lens_before, free_before = q.clone(), pool.lengths(0).copy(), pool.counters()["free_pages"]
+    with pytest.raises(L.OutOfPagesError):
+        pool.decode_step(0, q, k, v)                    # needs three pages, one is free
+    torch.cuda.synchronize()
+    assert torch.equal(q, q_before) and np.array_equal(pool.lengths(0), lens_before)
+    assert pool.counters()["free_pages"] == free_before and pool.check_device_status() == 0
+    # two sequences fit: the step runs for 0..1 after sequence 2 gave its page back
+    pool.free_sequence(2)
+    out = pool.decode_step(0, q[:2].contiguous(), k[:2].contiguous(), v[:2].contiguous())
+    assert out.shape == (2, Hq, D) and list(pool.lengths(0)[:2]) == [P + 1, P + 1] and pool.check_device_status() == 0
