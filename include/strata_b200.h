@@ -161,6 +161,11 @@ SKV_API int32_t skv_decode_attn(skv_pool* pool, int32_t layer, const int32_t* se
 SKV_API int32_t skv_decode_step(skv_pool* pool, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
                                 void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
                                 void* stream);
+/* skv_decode_step for an explicit list of live, distinct sequences (host array, n_seqs entries): rows of q, k, v and
+ * out follow the order of the list.  NULL is the identity 0..n_seqs-1. */
+SKV_API int32_t skv_decode_step_seqs(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* q,
+                                     const void* k, const void* v, void* out, int32_t n_q_heads, float eps,
+                                     void* workspace, size_t workspace_bytes, void* stream);
 
 /* K3 with the output all-gather of KV-head sharding fused into the merge kernel (no reference counterpart: the
  * reference is single-device and concatenates its per-KV-head results in place, mlx_ops.py:152).

@@ -89,6 +89,7 @@ SIGNATURES = {
     "skv_merge_partials": (_i32, [_vp, _i32, _i64, _i32, _i32, _f, _vp, _i32, _vp]),
     "skv_gather_wait": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "skv_decode_step": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp]),
+    "skv_decode_step_seqs": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp]),
     "skv_decode_attn_static": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp]),
     "skv_attn_dense": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f, _vp]),
     "skv_prefill_attn_paged": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _f, _vp]),

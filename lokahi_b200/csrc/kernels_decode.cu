@@ -856,7 +856,10 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
         }
         __syncthreads();
         if (s_last)
-            for (int s2 = tid; s2 < d.n_seqs; s2 += blockDim.x) pv.lengths[(int64_t)d.layer * pv.max_seqs + s2] += 1;
+            for (int s2 = tid; s2 < d.n_seqs; s2 += blockDim.x) {
+                const int sq = d.seq_ids ? d.seq_ids[s2] : s2;     // distinct by the host's check
+                if (sq >= 0 && sq < pv.max_seqs) pv.lengths[(int64_t)d.layer * pv.max_seqs + sq] += 1;
+            }
     }
     if (d.gather.world > 0) {
         // When the last merge block has stored its rows, tell every rank (itself included) that this rank's
@@ -1007,7 +1010,7 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     cudaError_t e;
     const char* impl = getenv("SKV_DECODE_IMPL");   // "reg": direct-to-register loads; default: TMA ring when maps exist
     const bool tma_ok = mma_ok && d.k_map && d.v_map && (d.fused_append || !(impl && impl[0] == 'r'));
-    if (d.fused_append && (!tma_ok || d.seq_ids || d.q_pos || !d.new_k || !d.new_v || !d.inv_freq || !d.append_ticket))
+    if (d.fused_append && (!tma_ok || d.q_pos || !d.new_k || !d.new_v || !d.inv_freq || !d.append_ticket))
         return cudaErrorInvalidValue;   // only the TMA kernel implements it; callers check the conditions first
     if (tma_ok) {
         const char* st = getenv("SKV_DECODE_STAGES");

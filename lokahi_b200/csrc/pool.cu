@@ -967,18 +967,26 @@ static bool fused_step_applies(const skv_pool* p, const void* q, int32_t n_q_hea
     return (uintptr_t)q % 16 == 0;
 }
 
-static int32_t fused_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v, void* out,
-                          int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes, const skv_peer_gather* g,
-                          cudaStream_t stream) {
+static int32_t fused_step(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* q, const void* k, const void* v,
+                          void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                          const skv_peer_gather* g, cudaStream_t stream) {
     if (layer < 0) return p->fail(SKV_ERR_BAD_ARG, "layer_idx must be a non-negative integer");
     if (layer >= p->cfg.num_layers)
         return p->fail(SKV_ERR_BAD_ARG, "layer_idx %d is outside configured layer count %d", layer, p->cfg.num_layers);
     if (n_seqs <= 0 || n_seqs > p->cfg.max_seqs) return p->fail(SKV_ERR_BAD_ARG, "n_seqs %d out of range", n_seqs);
     if (!q || !k || !v || (!out && !g)) return p->fail(SKV_ERR_BAD_ARG, "q, k, v and out must be given");
     const int32_t P = p->cfg.page_size;
+    if (seq_ids && (size_t)n_seqs * sizeof(int32_t) > StagingRing::kSlotBytes)
+        return p->fail(SKV_ERR_BAD_ARG, "too many sequences (%d) for one call", n_seqs);
     int64_t total = 0, need_total = 0;
-    for (int32_t s = 0; s < n_seqs; ++s) {
+    std::vector<uint8_t> seen(seq_ids ? p->cfg.max_seqs : 0, 0);
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        const int32_t s = seq_ids ? seq_ids[i] : i;
         if (!valid_seq(p, s)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", s);
+        if (seq_ids) {
+            if (seen[s]) return p->fail(SKV_ERR_BAD_ARG, "sequence %d listed twice", s);
+            seen[s] = 1;
+        }
         const int32_t cur = p->len(layer, s);
         const int32_t need = (cur + 1 + P - 1) / P;
         if (need > p->cfg.max_pages_per_seq)
@@ -996,16 +1004,19 @@ static int32_t fused_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, c
     if (!workspace || workspace_bytes < need_ws)
         return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need_ws);
     std::vector<TableUpdate> ups;
-    for (int32_t s = 0; s < n_seqs; ++s) {
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        const int32_t s = seq_ids ? seq_ids[i] : i;
         int32_t st = grow(p, s, p->len(layer, s) + 1, &ups);
         if (st != SKV_OK) return st;   // cannot happen after the check above
     }
-    for (int32_t s = 0; s < n_seqs; ++s) p->len(layer, s) += 1;
+    for (int32_t i = 0; i < n_seqs; ++i) p->len(layer, seq_ids ? seq_ids[i] : i) += 1;
 
     DeviceGuard guard(p);
     int32_t st = order_transfers(p, stream);
     if (st != SKV_OK) return st;
     st = publish_table_updates(p, ups, stream);
+    if (st != SKV_OK) return st;
+    st = upload_ids(p, seq_ids, n_seqs, stream, &D.seq_ids);
     if (st != SKV_OK) return st;
     D.pool = p->view();
     D.layer = layer;
@@ -1047,7 +1058,7 @@ int32_t skv_decode_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, con
                         int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes, void* stream) {
     if (!p) return SKV_ERR_BAD_ARG;
     if (fused_step_applies(p, q, n_q_heads))
-        return fused_step(p, layer, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, nullptr, (cudaStream_t)stream);
+        return fused_step(p, layer, nullptr, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, nullptr, (cudaStream_t)stream);
     skv_append_args a{};
     a.layer = layer;
     a.n_seqs = n_seqs;
@@ -1069,6 +1080,33 @@ int32_t skv_decode_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, con
     return skv_decode_attn(p, layer, nullptr, n_seqs, q, out, nullptr, n_q_heads, eps, workspace, workspace_bytes, stream);
 }
 
+int32_t skv_decode_step_seqs(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* q, const void* k,
+                             const void* v, void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (!seq_ids) return skv_decode_step(p, layer, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, stream);
+    if (fused_step_applies(p, q, n_q_heads))
+        return fused_step(p, layer, seq_ids, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, nullptr, (cudaStream_t)stream);
+    skv_append_args a{};
+    a.layer = layer;
+    a.n_seqs = n_seqs;
+    a.seq_ids = seq_ids;
+    a.n_new = 1;
+    a.k = k;
+    a.v = v;
+    a.kv_stride_seq = (int64_t)p->cfg.num_kv_heads * p->cfg.head_dim;
+    a.kv_stride_head = p->cfg.head_dim;
+    a.rope_k = 1;
+    a.q_in = q;
+    a.q_out = q;
+    a.n_q_heads = n_q_heads;
+    a.q_stride_seq = (int64_t)n_q_heads * p->cfg.head_dim;
+    a.q_stride_head = p->cfg.head_dim;
+    int32_t st = skv_append(p, &a, stream);
+    if (st != SKV_OK) return st;
+    return skv_decode_attn(p, layer, seq_ids, n_seqs, q, out, nullptr, n_q_heads, eps, workspace, workspace_bytes, stream);
+}
+
 int32_t skv_decode_step_gather(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
                                int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
                                const skv_peer_gather* gather, void* stream) {
@@ -1079,7 +1117,7 @@ int32_t skv_decode_step_gather(skv_pool* p, int32_t layer, int32_t n_seqs, void*
             return p->fail(SKV_ERR_BAD_ARG, "peer gather needs 1 <= world <= 8, a rank inside it and both pointer arrays");
         for (int32_t r = 0; r < gather->world; ++r)
             if (!gather->out_ptrs[r] || !gather->flag_ptrs[r]) return p->fail(SKV_ERR_BAD_ARG, "peer pointer %d is null", r);
-        return fused_step(p, layer, n_seqs, q, k, v, nullptr, n_q_heads, eps, workspace, workspace_bytes, gather, (cudaStream_t)stream);
+        return fused_step(p, layer, nullptr, n_seqs, q, k, v, nullptr, n_q_heads, eps, workspace, workspace_bytes, gather, (cudaStream_t)stream);
     }
     skv_append_args a{};
     a.layer = layer;

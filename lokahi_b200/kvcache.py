@@ -153,10 +153,10 @@ class PagedKVCache:
         ``update_with_rope`` followed by the attention call with ``query_positions = [past]``
         (llama_mlx.py:284-308 for L == 1).  Same validation and bookkeeping as ``update``; ``query_states``
         is rotated in place; returns ``[B, Hq, 1, D]``, or ``None`` when the step does not apply (more than one
-        token, or sequences that are not the pool's 0..B-1) and the caller should make the two calls."""
+        token) and the caller should make the two calls."""
         if key_states.dim() != 4 or key_states.shape[2] != 1 or query_states.dim() != 4 or query_states.shape[2] != 1:
             return None
-        if self.seq_ids is None or list(self.seq_ids) != list(range(self.batch_size)) or not query_states.is_contiguous():
+        if self.seq_ids is None or not query_states.is_contiguous():
             return None
         previous = self._prepare_update(key_states, value_states, layer_idx, cache_kwargs)
         rope_key = (inv_freq.tobytes(), float(scaling_factor))
@@ -166,7 +166,8 @@ class PagedKVCache:
         B, Hq, _, D = query_states.shape
         Hkv = key_states.shape[1]
         out = self.pool.decode_step(layer_idx, query_states.view(B, Hq, D), key_states.reshape(B, Hkv, D).contiguous(),
-                                    value_states.reshape(B, Hkv, D).contiguous(), eps=eps)
+                                    value_states.reshape(B, Hkv, D).contiguous(), eps=eps,
+                                    seq_ids=None if list(self.seq_ids) == list(range(B)) else self.seq_ids)
         self._finish_update(layer_idx, previous, 1)
         return out.view(B, Hq, 1, D)
 

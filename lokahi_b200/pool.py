@@ -315,10 +315,10 @@ class PagedPool:
         return out
 
     def decode_step(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: float = 1e-12,
-                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    out: Optional[torch.Tensor] = None, seq_ids=None) -> torch.Tensor:
         """RoPE-on-write append of one token per sequence plus decode attention in one library call.
         ``q`` ``[n_seqs, q_heads, head_dim]`` is rotated in place; ``k``, ``v`` ``[n_seqs, kv_heads, head_dim]``;
-        sequences are 0..n_seqs-1 and the token goes to each sequence's current length."""
+        the sequences are ``seq_ids`` (distinct; default 0..n_seqs-1) and the token goes to each one's current length."""
         for name, t in (("q", q), ("k", k), ("v", v)):
             self._check_tensor(t, name)
             if t.dim() != 3 or not t.is_contiguous():
@@ -329,8 +329,15 @@ class PagedPool:
         if out is None:
             out = torch.empty_like(q)
         ws = self.workspace(n_seqs, hq)
-        self._check(lib.skv_decode_step(self._h, layer, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                        hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
+        if seq_ids is None:
+            self._check(lib.skv_decode_step(self._h, layer, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                            hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
+        else:
+            ids = i32_array(seq_ids)
+            if len(ids) != n_seqs:
+                raise ValueError("seq_ids must have one entry per row of q")
+            self._check(lib.skv_decode_step_seqs(self._h, layer, ids, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                 out.data_ptr(), hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
         return out
 
     def decode_step_gather(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gather, *,

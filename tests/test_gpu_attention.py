@@ -475,3 +475,41 @@ def test_fused_step_is_all_or_nothing_when_pages_run_out():
     pool.free_sequence(2)
     out = pool.decode_step(0, q[:2].contiguous(), k[:2].contiguous(), v[:2].contiguous())
     assert out.shape == (2, Hq, D) and list(pool.lengths(0)[:2]) == [P + 1, P + 1] and pool.check_device_status() == 0
+
+
+def test_one_call_step_with_a_sequence_list_matches_the_two_calls(monkeypatch):
+    """A subset of the live sequences in a shuffled order: the two-launch step against append + attention with the
+    same list, for five steps; stored pages, lengths (also of the untouched sequences) and rotated q identical,
+    outputs within bf16 tolerance; a repeated id is rejected."""
+    lens = [3, 700, 16, 255, 1024, 90]
+    ids = [4, 1, 5, 2]
+    n, Hq, Hkv, D, P = len(lens), 32, 8, 128, 16
+    rng = np.random.default_rng(58)
+    pool_a, _, _, _, rnd = _paged_setup(rng, torch.bfloat16, n, Hkv, D, P, lens, headroom=8)
+    rng = np.random.default_rng(58)
+    pool_b, _, _, _, _ = _paged_setup(rng, torch.bfloat16, n, Hkv, D, P, lens, headroom=8)
+    inv = L.rope_inv_freq(D, 500000.0)
+    for p in (pool_a, pool_b):
+        p.set_rope(inv)
+    from parity import parity_errors
+    for step in range(5):
+        q = _t(rnd(rng.standard_normal((len(ids), Hq, D), dtype=np.float32)), torch.bfloat16)
+        k = _t(rnd(rng.standard_normal((len(ids), Hkv, D), dtype=np.float32)), torch.bfloat16)
+        v = _t(rnd(rng.standard_normal((len(ids), Hkv, D), dtype=np.float32)), torch.bfloat16)
+        qa, qb = q.clone(), q.clone()
+        pool_a.append(0, k, v, seq_ids=ids, start_pos=[lens[s] + step for s in ids], rope_k=True, q=qa, layout="bhd")
+        out_a = pool_a.decode_attention(0, qa, seq_ids=ids)
+        before = L._lib.lib.skv_launch_count()
+        out_b = pool_b.decode_step(0, qb, k, v, seq_ids=ids)
+        assert L._lib.lib.skv_launch_count() - before == 2
+        assert torch.equal(qa, qb) and parity_errors(out_b, to_np(out_a))[0] <= TOL_BF16
+        assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0))
+    assert list(pool_b.lengths(0)) == [lens[s] + (5 if s in ids else 0) for s in range(n)]
+    ka, va = pool_a.gather(0, n_seqs=n)
+    kb, vb = pool_b.gather(0, n_seqs=n)
+    for s in range(n):
+        t = lens[s] + (5 if s in ids else 0)
+        assert torch.equal(ka[s, :, :t], kb[s, :, :t]) and torch.equal(va[s, :, :t], vb[s, :, :t])
+    with pytest.raises(ValueError, match="listed twice"):
+        pool_b.decode_step(0, qb[:2].contiguous(), k[:2].contiguous(), v[:2].contiguous(), seq_ids=[1, 1])
+    assert pool_b.check_device_status() == 0
