@@ -32,7 +32,10 @@ struct TableUpdate {
 
 // Pinned host slots with matching device slots.  A slot is reused only after the copy that
 // read it has finished (one event per slot), so per-call metadata can be uploaded without
-// blocking the host.
+// blocking the host.  The event covers the upload, not the kernel that reads the device slot afterwards: that
+// kernel is protected by stream order, so a ring must only ever be used with ONE stream (the pool keeps one
+// ring for the compute stream and one for its copy stream; sharing one let 64 later uploads on the other stream
+// overwrite a slot whose kernel had not run yet).
 struct StagingRing {
     static constexpr int kSlots = 64;
     static constexpr size_t kSlotBytes = 64 * 1024;
@@ -41,13 +44,15 @@ struct StagingRing {
     cudaEvent_t ev[kSlots] = {};
     bool pending[kSlots] = {};
     int next = 0;
+    int n_slots = kSlots;
 
-    cudaError_t init() {
-        cudaError_t e = cudaHostAlloc((void**)&host, kSlots * kSlotBytes, cudaHostAllocDefault);
+    cudaError_t init(int slots = kSlots) {
+        n_slots = slots < 1 ? 1 : (slots > kSlots ? kSlots : slots);
+        cudaError_t e = cudaHostAlloc((void**)&host, n_slots * kSlotBytes, cudaHostAllocDefault);
         if (e != cudaSuccess) return e;
-        e = cudaMalloc((void**)&dev, kSlots * kSlotBytes);
+        e = cudaMalloc((void**)&dev, n_slots * kSlotBytes);
         if (e != cudaSuccess) return e;
-        for (int i = 0; i < kSlots; ++i) {
+        for (int i = 0; i < n_slots; ++i) {
             e = cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming);
             if (e != cudaSuccess) return e;
         }
@@ -63,7 +68,7 @@ struct StagingRing {
     cudaError_t upload(const void* src, size_t bytes, cudaStream_t stream, void** dev_out) {
         if (bytes > kSlotBytes) return cudaErrorInvalidValue;
         int s = next;
-        next = (next + 1) % kSlots;
+        next = (next + 1) % n_slots;
         if (pending[s]) {
             cudaError_t e = cudaEventSynchronize(ev[s]);
             if (e != cudaSuccess) return e;
@@ -114,7 +119,8 @@ struct skv_pool {
     bool has_maps = false;
     bool rope_set = false;
     float rope_scaling = 1.0f;
-    StagingRing ring;
+    StagingRing ring;                    // compute stream
+    StagingRing ring_copy;               // copy stream
 
     // host tier
     char* h_tier = nullptr;              // pinned + mapped: [host_pages][num_layers][2][page_bytes]
@@ -205,13 +211,17 @@ struct CopyItem {
     int32_t page, slot;
 };
 __global__ void __launch_bounds__(256) page_copy_kernel(char* __restrict__ k_base, char* __restrict__ v_base, char* __restrict__ tier,
-                                                         const CopyItem* __restrict__ items, int64_t layer_stride, int64_t page_bytes,
-                                                         int num_layers, int to_host) {
-    // One block moves several (layer, K|V) chunks of one page; every thread keeps four 16-byte loads in
+                                                         const CopyItem* __restrict__ items, int n_items, int64_t layer_stride,
+                                                         int64_t page_bytes, int num_layers, int to_host) {
+    // One block moves several (layer, K|V) chunks of one page at a time; every thread keeps four 16-byte loads in
     // flight, which is what the host link needs (loads from mapped host memory are latency-bound otherwise).
-    const CopyItem it = items[blockIdx.x];
+    // The grid is small and strides over the pages: the link (about 52 GB/s measured, either direction) is
+    // saturated by a few hundred blocks, and a grid that filled every SM would keep compute kernels from running
+    // beside the copy.
     const int n = (int)(page_bytes / 16);
     const int n_chunks = num_layers * 2;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const CopyItem it = items[item];
     for (int c0 = blockIdx.y; c0 < n_chunks; c0 += 4 * gridDim.y) {
         const int4* src[4];
         int4* dst[4];
@@ -233,6 +243,7 @@ __global__ void __launch_bounds__(256) page_copy_kernel(char* __restrict__ k_bas
             for (int u = 0; u < 4; ++u)
                 if (c0 + u * (int)gridDim.y < n_chunks) dst[u][i] = v[u];
         }
+    }
     }
 }
 
@@ -376,6 +387,7 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
         CUDA_TRY(p, cudaMemset(p->d_tickets, 0, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 2) * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_inv_freq, (size_t)cfg->head_dim / 2 * sizeof(float)));
         CUDA_TRY(p, p->ring.init());
+        CUDA_TRY(p, p->ring_copy.init(16));
         CUDA_TRY(p, cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
         CUDA_TRY(p, cudaEventCreateWithFlags(&p->ev_compute, cudaEventDisableTiming));
         CUDA_TRY(p, cudaEventCreateWithFlags(&p->ev_copy, cudaEventDisableTiming));
@@ -404,6 +416,7 @@ int32_t skv_destroy(skv_pool* p) {
         DeviceGuard g(p);
         cudaDeviceSynchronize();
         p->ring.destroy();
+        p->ring_copy.destroy();
         if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
         if (p->ev_compute) cudaEventDestroy(p->ev_compute);
         if (p->ev_copy) cudaEventDestroy(p->ev_copy);
@@ -1228,6 +1241,12 @@ int32_t skv_evict(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slots,
     p->bytes_d2h += (int64_t)items.size() * p->cfg.num_layers * 2 * (int64_t)p->page_bytes;
     if (p->host_only || items.empty()) return SKV_OK;
     DeviceGuard g(p);
+    // Page-table entries deferred by earlier prefetches must reach the device before this call's entries: flushed
+    // later, they would overwrite them with stale page ids.
+    if (!p->deferred_updates.empty()) {
+        int32_t st0 = order_transfers(p, stream);
+        if (st0 != SKV_OK) return st0;
+    }
     // the copy must see everything already enqueued on the compute stream
     CUDA_TRY(p, cudaEventRecord(p->ev_compute, stream));
     CUDA_TRY(p, cudaStreamWaitEvent(p->copy_stream, p->ev_compute, 0));
@@ -1235,9 +1254,9 @@ int32_t skv_evict(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slots,
     for (size_t off = 0; off < items.size(); off += per) {
         size_t n = std::min(per, items.size() - off);
         void* dev = nullptr;
-        CUDA_TRY(p, p->ring.upload(items.data() + off, n * sizeof(CopyItem), p->copy_stream, &dev));
-        dim3 grid((unsigned)n, (unsigned)std::min(p->cfg.num_layers * 2, 8));
-        page_copy_kernel<<<grid, 256, 0, p->copy_stream>>>(p->d_k, p->d_v, p->h_tier_dev, (const CopyItem*)dev,
+        CUDA_TRY(p, p->ring_copy.upload(items.data() + off, n * sizeof(CopyItem), p->copy_stream, &dev));
+        dim3 grid((unsigned)std::min<size_t>(n, 32), (unsigned)std::min(p->cfg.num_layers * 2, 8));
+        page_copy_kernel<<<grid, 256, 0, p->copy_stream>>>(p->d_k, p->d_v, p->h_tier_dev, (const CopyItem*)dev, (int)n,
                                                            (int64_t)p->layer_stride, (int64_t)p->page_bytes,
                                                            p->cfg.num_layers, 1);
         CUDA_TRY(p, cudaGetLastError());
@@ -1285,9 +1304,9 @@ int32_t skv_prefetch(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slo
     for (size_t off = 0; off < items.size(); off += per) {
         size_t n = std::min(per, items.size() - off);
         void* dev = nullptr;
-        CUDA_TRY(p, p->ring.upload(items.data() + off, n * sizeof(CopyItem), p->copy_stream, &dev));
-        dim3 grid((unsigned)n, (unsigned)std::min(p->cfg.num_layers * 2, 8));
-        page_copy_kernel<<<grid, 256, 0, p->copy_stream>>>(p->d_k, p->d_v, p->h_tier_dev, (const CopyItem*)dev,
+        CUDA_TRY(p, p->ring_copy.upload(items.data() + off, n * sizeof(CopyItem), p->copy_stream, &dev));
+        dim3 grid((unsigned)std::min<size_t>(n, 32), (unsigned)std::min(p->cfg.num_layers * 2, 8));
+        page_copy_kernel<<<grid, 256, 0, p->copy_stream>>>(p->d_k, p->d_v, p->h_tier_dev, (const CopyItem*)dev, (int)n,
                                                            (int64_t)p->layer_stride, (int64_t)p->page_bytes,
                                                            p->cfg.num_layers, 0);
         CUDA_TRY(p, cudaGetLastError());

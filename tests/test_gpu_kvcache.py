@@ -427,3 +427,76 @@ def test_vectorised_append_writes_the_same_bytes_as_the_scalar_kernel(monkeypatc
     for s in range(B):
         t = starts[s] + n_new
         assert torch.equal(ka[s, :, :t], kb[s, :, :t]) and torch.equal(va[s, :, :t], vb[s, :, :t])
+
+
+@pytest.mark.gpu
+def test_interleaved_parking_and_fetching_without_synchronisation_stays_bit_exact():
+    """Evictions and prefetches of different sequences interleaved without any synchronisation in between, so that
+    many copies are queued behind the compute stream and freed device pages and host slots are reused at once
+    (more than a staging ring's worth of per-call metadata in flight): after the churn every sequence's K/V
+    equals what was written."""
+    rng = np.random.default_rng(41)
+    n, Hkv, D, P, T = 6, 2, 128, 16, 256            # 16 pages per sequence
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=3, num_kv_heads=Hkv, head_dim=D, num_pages=n * 16 + 4, max_seqs=n,
+                                       max_pages_per_seq=16, page_size=P, dtype=torch.bfloat16, host_pages=3 * 16))
+    truth = []
+    for s in range(n):
+        assert pool.alloc_sequence() == s
+        per_layer = []
+        for layer in range(3):
+            k = _t(bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32)), torch.bfloat16)
+            v = _t(bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32)), torch.bfloat16)
+            pool.append(layer, k, v, seq_ids=[s], start_pos=[0])
+            per_layer.append((k.clone(), v.clone()))
+        truth.append(per_layer)
+    parked = []
+    order = rng.permutation(n).tolist()
+    for rnd_ in range(12):                           # at most three sequences' worth of host slots
+        s = order[rnd_ % n]
+        if s in parked:
+            pool.prefetch(s, 0, 16)
+            parked.remove(s)
+        else:
+            if len(parked) == 3:
+                back = parked.pop(0)
+                pool.prefetch(back, 0, 16)           # frees host slots that the eviction below takes straight away
+            pool.evict(s, 0, 16)
+            parked.append(s)
+    for s in list(parked):
+        pool.prefetch(s, 0, 16)
+    pool.sync_transfers()
+    for s in range(n):
+        assert (pool.page_table(s) >= 0).all()
+        for layer in range(3):
+            k, v = pool.gather(layer, seq_ids=[s], max_len=T)
+            assert torch.equal(k, truth[s][layer][0]) and torch.equal(v, truth[s][layer][1]), (s, layer)
+    c = pool.counters()
+    assert c["pages_evicted"] == c["pages_prefetched"] and c["free_host_slots"] == 3 * 16 and pool.check_device_status() == 0
+
+
+@pytest.mark.gpu
+def test_park_after_fetch_without_compute_in_between_leaves_the_device_table_parked():
+    """prefetch then evict of the same pages with no compute call between them: the page-table entries that the
+    prefetch deferred must not overwrite the eviction's; attention afterwards is refused (not resident) and, once
+    fetched again, bit-exact."""
+    rng = np.random.default_rng(43)
+    Hq, Hkv, D, P, T = 8, 2, 128, 16, 64
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=16, max_seqs=2,
+                                       max_pages_per_seq=4, page_size=P, dtype=torch.bfloat16, host_pages=8))
+    assert pool.alloc_sequence() == 0
+    k = _t(bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32)), torch.bfloat16)
+    v = _t(bf16_round(rng.standard_normal((1, Hkv, T, D), dtype=np.float32)), torch.bfloat16)
+    pool.append(0, k, v, seq_ids=[0], start_pos=[0])
+    q = _t(bf16_round(rng.standard_normal((1, Hq, D), dtype=np.float32)), torch.bfloat16)
+    expect = pool.decode_attention(0, q, seq_ids=[0]).clone()
+    pool.evict(0, 0, 4)
+    pool.prefetch(0, 0, 4)
+    pool.evict(0, 0, 4)                                  # deferred entries of the prefetch are still unpublished here
+    with pytest.raises(L.NotResidentError):
+        pool.decode_attention(0, q, seq_ids=[0])
+    pool.sync_transfers()
+    kp, vp = pool.layer_views(0)
+    kp.zero_(); vp.zero_()                               # whatever the device table pointed at is now zeros
+    pool.prefetch(0, 0, 4)
+    assert torch.equal(pool.decode_attention(0, q, seq_ids=[0]), expect)
+    assert pool.check_device_status() == 0
