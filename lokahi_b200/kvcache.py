@@ -314,13 +314,23 @@ class PagedLlamaDiskCache(PagedKVCache):
             raise ValueError("max_layers_in_memory must be positive")
         self.max_layers_in_memory = max_layers_in_memory
 
-    def update(self, key_states, value_states, layer_idx, cache_kwargs=None):
-        result = super().update(key_states, value_states, layer_idx, cache_kwargs)
+    def _finish_update(self, layer_idx: int, previous: int, n_new: int):
+        # every way of appending (update, update_with_rope, decode_step_with_rope) ends here
+        result = super()._finish_update(layer_idx, previous, n_new)
         if self.max_layers_in_memory is not None and len(self._resident) > self.max_layers_in_memory:
             for idx in sorted(self._resident)[: -self.max_layers_in_memory]:
                 if idx != layer_idx:
                     self.save_to_disk(idx)
         return result
+
+
+class PagedQwen3NextDiskCache(PagedKVCache):
+    """Cache for Qwen3-Next models: the base cache plus the layer count the reference records
+    (``config.num_hidden_layers``, 80 when the config has none; MLXQwen3NextDiskCache, mlx_kvcache.py:370-396)."""
+
+    def __init__(self, config: Any, cache_dir: str = "./kvcache", stats: Optional[Any] = None, **kw):
+        super().__init__(config, cache_dir, stats, **kw)
+        self.num_layers = getattr(config, "num_hidden_layers", None) or 80
 
 
 def create_paged_kv_cache(model_id: str, config: Any, cache_dir: str = "./kvcache", stats: Optional[Any] = None,
@@ -329,4 +339,6 @@ def create_paged_kv_cache(model_id: str, config: Any, cache_dir: str = "./kvcach
     if model_id.startswith("llama"):
         kw.setdefault("max_layers_in_memory", None)
         return PagedLlamaDiskCache(config, cache_dir, stats, **kw)
-    return PagedKVCache(config, cache_dir, stats, **kw)
+    if model_id.startswith("qwen"):
+        return PagedQwen3NextDiskCache(config, cache_dir, stats, **kw)
+    return PagedKVCache(config, cache_dir, stats, **kw)          # "gemma" and everything else: the base class

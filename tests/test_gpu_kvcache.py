@@ -103,6 +103,17 @@ def test_layer_window_cache_spills_lowest_layers(tmp_path):
     with pytest.raises(ValueError, match="must be positive"):
         L.PagedLlamaDiskCache(cfg, cache_dir=str(tmp_path), max_layers_in_memory=0)
     assert isinstance(L.create_paged_kv_cache("llama3-1B", cfg, str(tmp_path)), L.PagedLlamaDiskCache)
+    qwen = L.create_paged_kv_cache("qwen3-next-80B", SimpleNamespace(max_position_embeddings=32, num_hidden_layers=None), str(tmp_path))
+    assert isinstance(qwen, L.PagedQwen3NextDiskCache) and qwen.num_layers == 80
+    assert type(L.create_paged_kv_cache("gemma3-12B", cfg, str(tmp_path))) is L.PagedKVCache
+    # the window also applies when the tokens arrive through the RoPE-on-write path
+    cache2 = L.PagedLlamaDiskCache(cfg, cache_dir=str(tmp_path / "w2"), max_layers_in_memory=2)
+    D = 64
+    kk = torch.randn((1, 2, 3, D), device=DEV)
+    qq = torch.randn((1, 4, 3, D), device=DEV)
+    for layer in range(4):
+        cache2.update_with_rope(qq.clone(), kk, kk, layer, {"cache_position": [0, 1, 2]}, inv_freq=L.rope_inv_freq(D, 10000.0))
+    assert sorted(cache2._resident) == [2, 3] and sorted(cache2._disk_offloaded) == [0, 1]
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
