@@ -701,7 +701,8 @@ def run_reference(args):
     return {
         "impl": "reference", "metric": "paged GQA decode tokens/s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": dt / K * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        # same workload at every N (the CPU arm does not shard): the label follows the GPU arm's
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "n_seqs": N_SEQS, "context": [CTX_LO, CTX_HI], "q_heads": HQ, "kv_heads": HKV,
                    "head_dim": D, "page_size": P, "rope_theta": THETA, "layers": 1},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
