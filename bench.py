@@ -291,7 +291,8 @@ def run_ours(args):
                                     "decode step call: append kernel + split-K kernel + merge kernel")
                                    + (" + gather wait" if fused_gather else ""),
                          "algorithmic_bytes_per_launch": algo_bytes, "launch_ms": attn_mean_ms,
-                         "launch_ms_min": float(attn_ms.min()), "traffic": algo_bytes * TRAFFIC_RATIO},
+                         "launch_ms_min": float(attn_ms.min()), "launch_ms_median": float(np.median(attn_ms)),
+                         "launch_ms_p95": float(np.percentile(attn_ms, 95)), "traffic": algo_bytes * TRAFFIC_RATIO},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -391,7 +392,8 @@ def run_prefill(args):
         "gpu_launches": int(launches),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "peak_kind": f"of {kind} (burst)", "flops_per_launch": flops, "flops_counted": "causal-useful 4*Hq*D*S(S+1)/2",
-                     "launch_ms": float(ms.mean()), "launch_ms_min": float(ms.min()), "traffic": None},
+                     "launch_ms": float(ms.mean()), "launch_ms_min": float(ms.min()), "launch_ms_median": float(np.median(ms)),
+                     "launch_ms_p95": float(np.percentile(ms, 95)), "traffic": None},
         "clocks": clocks,
     }
 

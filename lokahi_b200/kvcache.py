@@ -131,16 +131,23 @@ class PagedKVCache:
                              start_pos=[previous] * self.batch_size)
         return self._finish_update(layer_idx, previous, key_states.shape[2])
 
+    def _ensure_rope(self, inv_freq: np.ndarray, scaling_factor: float) -> None:
+        """Hand the RoPE table to the pool when it changes (same array object and factor: nothing to compare)."""
+        if inv_freq is getattr(self, "_rope_arr", None) and scaling_factor == getattr(self, "_rope_scale", None):
+            return
+        rope_key = (inv_freq.tobytes(), float(scaling_factor))
+        if getattr(self, "_rope_key", None) != rope_key:
+            self.pool.set_rope(inv_freq, scaling_factor)
+            self._rope_key = rope_key
+        self._rope_arr, self._rope_scale = inv_freq, scaling_factor
+
     def update_with_rope(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
                          layer_idx: int, cache_kwargs: Optional[Dict[str, Any]] = None, *, inv_freq: np.ndarray,
                          scaling_factor: float = 1.0) -> Tuple[PagedView, PagedView]:
         """``update`` for un-rotated K: RoPE is applied on the way into the pages, and ``query_states``
         is rotated in place by the same launch (apply_rotary_pos_emb_mlx + update, llama_mlx.py:284-297)."""
         previous = self._prepare_update(key_states, value_states, layer_idx, cache_kwargs)
-        rope_key = (inv_freq.tobytes(), float(scaling_factor))
-        if getattr(self, "_rope_key", None) != rope_key:
-            self.pool.set_rope(inv_freq, scaling_factor)
-            self._rope_key = rope_key
+        self._ensure_rope(inv_freq, scaling_factor)
         if key_states.shape[2] > 0:
             self.pool.append(layer_idx, key_states, value_states, seq_ids=self.seq_ids,
                              start_pos=[previous] * self.batch_size, rope_k=True, q=query_states)
@@ -159,10 +166,7 @@ class PagedKVCache:
         if self.seq_ids is None or not query_states.is_contiguous():
             return None
         previous = self._prepare_update(key_states, value_states, layer_idx, cache_kwargs)
-        rope_key = (inv_freq.tobytes(), float(scaling_factor))
-        if getattr(self, "_rope_key", None) != rope_key:
-            self.pool.set_rope(inv_freq, scaling_factor)
-            self._rope_key = rope_key
+        self._ensure_rope(inv_freq, scaling_factor)
         B, Hq, _, D = query_states.shape
         Hkv = key_states.shape[1]
         out = self.pool.decode_step(layer_idx, query_states.view(B, Hq, D), key_states.reshape(B, Hkv, D).contiguous(),
