@@ -719,7 +719,8 @@ def main():
     global N_SEQS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps; default by workload: decode 128, prefill 30, decoder 256, longctx 64 (the configurations' own counts)")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -733,6 +734,8 @@ def main():
     ap.add_argument("--seqs", type=int, default=N_SEQS,
                     help="number of sequences (default: the workload's 64; smaller values are for profiler captures)")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = {"decode": 128, "prefill": 30, "decoder": 256, "longctx": 64}[args.workload]
     N_SEQS = args.seqs
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
