@@ -486,6 +486,53 @@ def run_decoder(args):
     }
 
 
+def run_glue(args):
+    """Secondary workload "decoder_glue": the RMSNorm (with the residual add fused) and SwiGLU launches at the
+    shapes of configs[3]'s prefill (16384 rows, hidden 2048, MLP 5504), bf16: element-wise, HBM roofline.  The
+    tensors (64 MB to 180 MB each) rotate through four sets so that consecutive calls do not hit L2."""
+    import torch
+
+    import lokahi_b200 as L
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rows, hidden, inter, sets = 16384, 2048, 5504, 4
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    mk = lambda *shape: torch.randn(shape, generator=gen, device=dev).to(torch.bfloat16)
+    xs, ds, gs, us = ([mk(rows, n) for _ in range(sets)] for n in (hidden, hidden, inter, inter))
+    w = mk(hidden)
+    K, W = args.steps, args.warmup
+    peak, peak_kind = measured_peak_gbs()
+
+    def timed(fn, bytes_per_call):
+        for i in range(W):
+            fn(i % sets)
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+        for i, (a, b) in enumerate(evs):
+            a.record()
+            fn(i % sets)
+            b.record()
+        torch.cuda.synchronize()
+        ms = np.array([a.elapsed_time(b) for a, b in evs])
+        gbs = bytes_per_call / (ms.mean() * 1e-3) / 1e9
+        return {"launch_ms": float(ms.mean()), "launch_ms_min": float(ms.min()), "algorithmic_bytes": bytes_per_call,
+                "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak, "peak_kind": f"of {peak_kind}"}
+
+    l0 = L._lib.lib.skv_launch_count()
+    norm = timed(lambda i: L.rms_norm(xs[i], w, 1e-6), 2 * rows * hidden * 2 + hidden * 2)
+    add_norm = timed(lambda i: L.add_rms_norm(xs[i], ds[i], w, 1e-6), 4 * rows * hidden * 2 + hidden * 2)
+    swi = timed(lambda i: L.swiglu(gs[i], us[i]), 3 * rows * inter * 2)
+    launches = L._lib.lib.skv_launch_count() - l0
+    return {
+        "metric": "decoder glue GB/s (add + RMSNorm)", "value": add_norm["achieved_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": K,
+        "warmup": W, "ms_per_step": add_norm["launch_ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "decoder_glue", "rows": rows, "hidden": hidden, "mlp": inter,
+                   "l2": "four tensor sets in rotation (each set larger than L2 together with its outputs)"},
+        "rmsnorm": norm, "add_rmsnorm": add_norm, "swiglu": swi, "gpu_launches": int(launches),
+    }
+
+
 def run_longctx(args):
     """Secondary workload "long_context_llama3_8b_kv": one GPU's share of the 8-way KV-head sharding of a
     Llama-3-8B KV path: 32 layers, 1 KV head with its 4 query heads, head_dim 128, bf16, 4 sequences at 96k
@@ -727,7 +774,7 @@ def main():
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how the per-rank attention outputs are gathered")
     ap.add_argument("--emulate-shard", type=int, default=1, help=argparse.SUPPRESS)
-    ap.add_argument("--workload", choices=["decode", "prefill", "decoder", "longctx"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "decoder", "longctx", "glue"], default="decode",
                     help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")
     ap.add_argument("--kv", choices=["dense", "paged"], default="dense",
                     help="prefill workload: K/V as dense tensors or as scattered 16-token pages of a pool")
@@ -735,7 +782,7 @@ def main():
                     help="number of sequences (default: the workload's 64; smaller values are for profiler captures)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"decode": 128, "prefill": 30, "decoder": 256, "longctx": 64}[args.workload]
+        args.steps = {"decode": 128, "prefill": 30, "decoder": 256, "longctx": 64, "glue": 30}[args.workload]
     N_SEQS = args.seqs
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -747,6 +794,8 @@ def main():
         result = run_decoder(args)
     elif args.workload == "longctx":
         result = run_longctx(args)
+    elif args.workload == "glue":
+        result = run_glue(args)
     else:
         result = run_ours(args)
     if result is not None:

@@ -36,7 +36,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // rows 16-byte aligned), one element otherwise.  With `delta`, the row that is normalised is x + delta, and that
 // sum is also written to `sum_out` (the updated residual stream); `sum_out` may alias x.
 template <typename T>
-__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ delta, T* sum_out,
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const T* x /* may alias sum_out */, const T* __restrict__ delta, T* sum_out,
                                                               const T* __restrict__ weight, T* __restrict__ out, int hidden,
                                                               float eps, int vec) {
     constexpr int VEC = 16 / (int)sizeof(T);
@@ -91,6 +91,60 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const T* __restri
     }
 }
 
+// Warp-per-row variant for rows of exactly 32 * CPL 16-byte chunks (hidden = 256 * CPL bf16 or 128 * CPL float32
+// elements): the row lives in registers, the sum of squares is a warp reduction, and a block of eight warps
+// covers eight rows, so short rows do not pay for a block barrier and a block launch each (measured at 16384 rows
+// of 2048 bf16: 0.049 ms per call with one block per row).
+template <typename T, int CPL>
+__global__ void __launch_bounds__(256) rmsnorm_warp_kernel(const T* x /* may alias sum_out */, const T* __restrict__ delta, T* sum_out,
+                                                           const T* __restrict__ weight, T* __restrict__ out, int64_t n_rows,
+                                                           float eps) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    constexpr int hidden = 32 * CPL * VEC;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int64_t base = row * hidden;
+    uint4 v[CPL];
+#pragma unroll
+    for (int k = 0; k < CPL; ++k) v[k] = *reinterpret_cast<const uint4*>(x + base + (int64_t)(k * 32 + lane) * VEC);
+    if (delta) {
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) {
+            const uint4 b = *reinterpret_cast<const uint4*>(delta + base + (int64_t)(k * 32 + lane) * VEC);
+            T* ae = reinterpret_cast<T*>(&v[k]);
+            const T* be = reinterpret_cast<const T*>(&b);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) ae[e] = from_f32<T>(__fadd_rn(to_f32(ae[e]), to_f32(be[e])));
+            *reinterpret_cast<uint4*>(sum_out + base + (int64_t)(k * 32 + lane) * VEC) = v[k];
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < CPL; ++k) {
+        const T* ae = reinterpret_cast<const T*>(&v[k]);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const float f = to_f32(ae[e]);
+            ss = fmaf(f, f, ss);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int k = 0; k < CPL; ++k) {
+        const uint4 w = *reinterpret_cast<const uint4*>(weight + (int64_t)(k * 32 + lane) * VEC);
+        const T* we = reinterpret_cast<const T*>(&w);
+        const T* ae = reinterpret_cast<const T*>(&v[k]);
+        uint4 o;
+        T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) oe[e] = from_f32<T>(to_f32(we[e]) * (to_f32(ae[e]) * inv));
+        *reinterpret_cast<uint4*>(out + base + (int64_t)(k * 32 + lane) * VEC) = o;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out,
                                                      int64_t n, int vec) {
@@ -127,6 +181,25 @@ cudaError_t run_rmsnorm(const void* x, const void* delta, void* sum_out, const v
     constexpr int VEC = 16 / (int)sizeof(T);
     const bool vec = hidden % VEC == 0 && aligned16(x) && aligned16(weight) && aligned16(out) &&
                      (!delta || (aligned16(delta) && aligned16(sum_out)));
+    if (vec && hidden % (32 * VEC) == 0) {
+        const int cpl = hidden / (32 * VEC);
+        const unsigned blocks = (unsigned)((n_rows + 7) / 8);
+        auto launch = [&](auto kernel) {
+            kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(delta),
+                                               reinterpret_cast<T*>(sum_out), reinterpret_cast<const T*>(weight),
+                                               reinterpret_cast<T*>(out), n_rows, eps);
+            count_launches(1);
+            return cudaGetLastError();
+        };
+        switch (cpl) {
+            case 1: return launch(rmsnorm_warp_kernel<T, 1>);
+            case 2: return launch(rmsnorm_warp_kernel<T, 2>);
+            case 4: return launch(rmsnorm_warp_kernel<T, 4>);
+            case 8: return launch(rmsnorm_warp_kernel<T, 8>);
+            case 16: return launch(rmsnorm_warp_kernel<T, 16>);
+            default: break;   // other sizes: one block per row below
+        }
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     static bool configured[64] = {};
     int dev = 0;
