@@ -243,8 +243,10 @@ class PagedKVCache:
         else:
             k = torch.from_numpy(key_np).to(dev)
             v = torch.from_numpy(value_np).to(dev)
+        if k.dtype != self.pool.cfg.dtype:      # e.g. a float32 file written by the reference for a bfloat16 pool
+            k, v = k.to(self.pool.cfg.dtype), v.to(self.pool.cfg.dtype)
         if k.shape[2] > 0:
-            self.pool.append(layer_idx, k, v, seq_ids=self.seq_ids, start_pos=[0] * self.batch_size)
+            self.pool.append(layer_idx, k.contiguous(), v.contiguous(), seq_ids=self.seq_ids, start_pos=[0] * self.batch_size)
         self._resident.add(layer_idx)
         self._layer_lengths[layer_idx] = k.shape[2]
         if self.stats:

@@ -511,3 +511,22 @@ def test_park_after_fetch_without_compute_in_between_leaves_the_device_table_par
     pool.prefetch(0, 0, 4)
     assert torch.equal(pool.decode_attention(0, q, seq_ids=[0]), expect)
     assert pool.check_device_status() == 0
+
+
+@pytest.mark.gpu
+def test_layer_file_in_the_reference_layout_and_float32_loads_into_a_bfloat16_cache(tmp_path):
+    """A layer file as the reference writes it (compressed .npz with float32 ``key`` / ``value`` and ``seen_tokens``,
+    mlx_kvcache.py:183-222) replaces the file of an offloaded layer: the bfloat16 cache reads it back, rounded."""
+    cfg = SimpleNamespace(num_hidden_layers=2, max_position_embeddings=64)
+    cache = L.PagedKVCache(cfg, cache_dir=str(tmp_path))
+    rng = np.random.default_rng(3)
+    k = _t(bf16_round(rng.standard_normal((1, 2, 5, 128), dtype=np.float32)), torch.bfloat16)
+    cache.update(k, k, 0, {"cache_position": list(range(5))})
+    cache.save_to_disk(0)
+    name = cache._disk_offloaded[0]
+    k32 = rng.standard_normal((1, 2, 5, 128), dtype=np.float32)
+    v32 = rng.standard_normal((1, 2, 5, 128), dtype=np.float32)
+    np.savez_compressed(name, key=k32, value=v32, seen_tokens=5)
+    got = cache[0]
+    assert np.array_equal(to_np(got["key"]), bf16_round(k32)) and np.array_equal(to_np(got["value"]), bf16_round(v32))
+    assert cache.get_seq_length(0) == 5 and 0 not in cache._disk_offloaded
