@@ -38,6 +38,18 @@ class PagedView:
     def dtype(self):
         return self.cache.pool.cfg.dtype
 
+    @property
+    def itemsize(self) -> int:
+        return 2 if self.dtype == torch.bfloat16 else 4
+
+    @property
+    def nbytes(self) -> int:
+        """Bytes of the history this view denotes (what a dense tensor of the same shape would hold)."""
+        n = self.itemsize
+        for d in self.shape:
+            n *= int(d)
+        return n
+
     def materialize(self) -> torch.Tensor:
         k, v = self.cache.materialize(self.layer)
         return k if self.which == "key" else v

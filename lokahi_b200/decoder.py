@@ -26,7 +26,7 @@ from typing import Any, Dict, Optional
 import torch
 import torch.nn.functional as F
 
-from .attention import chunked_grouped_attention
+from .attention import PagedView, chunked_grouped_attention
 from .glue import add_rms_norm, rms_norm, swiglu
 from .generation import greedy_generate
 from .pool import rope_inv_freq, rope_rows
@@ -136,7 +136,14 @@ class PagedDecoder:
         out = F.linear(out, self.w[f"{b}.o_proj.weight"])
         if self.tracer is not None:
             torch.cuda.synchronize(self.device)
+            # the reference records the query, the full key / value history and the layer output (llama_mlx.py:318-340)
             self.tracer.record_tensor("query", q, phase=phase, layer=layer)
+            if cache is not None:
+                k_seen, v_seen = PagedView(cache, layer, "key"), PagedView(cache, layer, "value")
+            else:
+                k_seen, v_seen = k, v
+            self.tracer.record_tensor("key", k_seen, phase=phase, layer=layer)
+            self.tracer.record_tensor("value", v_seen, phase=phase, layer=layer)
             self.tracer.record_tensor("attention_output", out, phase=phase, layer=layer)
             self.tracer.record_operation("attention", (time.perf_counter() - started) * 1000.0, phase=phase, layer=layer,
                                          active_memory_bytes=torch.cuda.memory_allocated(self.device),

@@ -2,7 +2,8 @@
 
 The reference has this for weight groups (``PrefetchScheduler``, src/ollm/scheduling/prefetch_scheduler.py:64-257:
 ``prefetch`` reserves budget and loads on a worker thread, ``acquire`` pins a group and reports how it was found
--- ``resident_hit``, ``prefetch_ready``, ``prefetch_wait``, ``cold_miss``, ``prefetch_evicted_reload`` -- a
+-- ``resident_hit``, ``prefetch_ready``, ``prefetch_wait``, ``cold_miss``, ``prefetch_evicted_reload`` (recorded through the tracer's ``record_operation`` with the
+reference's keyword arguments: ``group_id``, ``cache_status``, ``bytes_transferred``, ``bandwidth_bytes_per_second``) -- a
 reservation that does not fit is a ``budget_skip``, and a snapshot carries the counters and the measured stall
 time).  Here the unit is a group of KV page-table slots (``KVPageResidency``) and there is no worker thread: the
 copy back from pinned host memory is a kernel on the pool's copy stream, so "in flight" means enqueued there and
@@ -56,6 +57,9 @@ class KVPagePrefetcher:
         self.pool = residency.pool
         self.tracer = tracer
         self.wait_timeout_ms = int(wait_timeout_ms)
+        c = self.pool.cfg
+        self._page_bytes = (c.num_layers * 2 * c.num_kv_heads * c.page_size * c.head_dim *
+                            (2 if "bfloat16" in str(c.dtype) else 4))       # one page id covers all layers, K and V
         self._inflight: Dict[Tuple[int, int], float] = {}       # group -> time its copy was enqueued
         self._lock = RLock()
         self._resident_hits = self._cold_misses = self._ready_hits = self._waits = self._skips = 0
@@ -86,8 +90,11 @@ class KVPagePrefetcher:
                     n = self._slots(*k)[1]
                     self._pages_loaded += n
                     self._load_ms += (now - t_enq) * 1000.0
-                    self._trace("kv_page_load", (now - t_enq) * 1000.0, phase=phase, group=k,
-                                cache_status=status if k == key else "prefetch", pages=n)
+                    nbytes = n * self._page_bytes
+                    secs = now - t_enq
+                    self._trace("kv_page_load", secs * 1000.0, phase=phase, group_id=f"{k[0]}:{k[1]}",
+                                cache_status=status if k == key else "prefetch", bytes_transferred=nbytes,
+                                bandwidth_bytes_per_second=(nbytes / secs if secs > 0 else None))
                 del self._inflight[k]
         del started
 
@@ -100,7 +107,7 @@ class KVPagePrefetcher:
                 return True
             if not self.residency.reserve(seq, group_index):
                 self._skips += 1
-                self._trace("kv_page_prefetch", 0.0, phase=phase, group=key, cache_status="budget_skip")
+                self._trace("kv_page_prefetch", 0.0, phase=phase, group_id=f"{key[0]}:{key[1]}", cache_status="budget_skip")
                 return False
             self._inflight[key] = time.perf_counter()
             return True
@@ -140,7 +147,7 @@ class KVPagePrefetcher:
         stall = (time.perf_counter() - started) * 1000.0
         with self._lock:
             self._stall_ms += stall
-        self._trace("kv_page_acquire", stall, phase=phase, group=key, cache_status=status)
+        self._trace("kv_page_acquire", stall, phase=phase, group_id=f"{key[0]}:{key[1]}", cache_status=status)
         return KVPageLease(self, seq, group_index, status)
 
     def _demand(self, seq: int, group_index: int, first: int, n: int, phase: str, status: str) -> None:

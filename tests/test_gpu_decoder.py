@@ -208,3 +208,25 @@ def test_fused_glue_decoder_agrees_with_the_torch_glue_decoder():
     from parity import assert_parity_logits
     assert outs[0][1] == outs[1][1] == 43
     assert_parity_logits(outs[0][0], to_np(outs[1][0]), TOL_BF16, "fused glue vs torch glue")
+
+
+def test_reference_style_tracer_sees_query_key_value_and_output_per_layer():
+    """With the library's own ``TensorTracer`` (the reference's record, src/ollm/tracing.py): per layer and call the
+    events query, key, value, attention_output and the timed operation "attention", as the reference's attention
+    layer records them (llama_mlx.py:318-340); key and value describe the whole cached history."""
+    cfg = tiny_config()
+    tr = L.TensorTracer()
+    model = L.PagedDecoder(cfg, _to_torch(od.random_weights(cfg, seed=7, std=0.15), torch.float32), tracer=tr)
+    cache = L.PagedKVCache(cfg, cache_dir=None)
+    model(torch.tensor([[2, 5, 3]]), past_key_values=cache, use_cache=True)
+    model(torch.tensor([[11]]), past_key_values=cache, use_cache=True)
+    per_call = [e for e in tr.events if e.layer == 0]
+    assert [e.name for e in per_call] == ["query", "key", "value", "attention_output", "attention"] * 2
+    assert [e.phase for e in per_call[:5]] == ["prefill"] * 5 and [e.phase for e in per_call[5:]] == ["decode"] * 5
+    D = cfg.hidden_size // cfg.num_attention_heads
+    key_decode = per_call[6]
+    assert key_decode.kind == "tensor" and key_decode.shape == (1, cfg.num_key_value_heads, 4, D)
+    assert key_decode.byte_size == cfg.num_key_value_heads * 4 * D * 4 and "float32" in key_decode.dtype
+    op = per_call[9]
+    assert op.kind == "operation" and op.duration_ms > 0 and op.active_memory_bytes is not None
+    assert {e.layer for e in tr.events} == set(range(cfg.num_hidden_layers))

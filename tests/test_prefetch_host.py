@@ -35,6 +35,16 @@ def test_pipeline_loads_the_next_group_ahead_of_its_use():
     assert res.snapshot().resident_pages == 0
     rec = Recorder()
     pf = L.KVPagePrefetcher(res, tracer=rec)
+    full = L.TensorTracer()                        # the same calls must fit the reference tracer's signature
+    pf2_pool, pf2_res, pf2_seqs = make(budget=8)
+    for s in pf2_seqs:
+        pf2_res.evict(s, 0)
+    with L.KVPagePrefetcher(pf2_res, tracer=full).acquire(pf2_seqs[0], 0, phase="decode"):
+        pass
+    kinds = [(e.name, e.cache_status, e.group_id) for e in full.events]
+    assert ("kv_page_acquire", "cold_miss", f"{pf2_seqs[0]}:0") in kinds
+    load = [e for e in full.events if e.name == "kv_page_load"][0]
+    assert load.kind == "operation" and load.phase == "decode" and load.bytes_transferred == 4 * (1 * 2 * 1 * 4 * 8 * 2)   # pages x (layers, K|V, heads, page, dim, bf16)
     statuses = []
     for i, s in enumerate(seqs):
         with pf.acquire(s, 0, phase="decode") as lease:
