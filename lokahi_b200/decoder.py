@@ -44,15 +44,38 @@ def rope_scaling_factor(config: Any) -> float:
     return 1.0
 
 
+class _DecodeGraphs:
+    """CUDA graphs of a cached decode step for one batch size.  The hot-path call of each layer stays an ordinary
+    library call (it does host-side bookkeeping: lengths, page growth, the split-K plan), so the step is cut at
+    those calls: ``pre`` = embedding, first norm and the first layer's q/k/v projections; ``post[i]`` = layer i's
+    output projection, residual add + norm, MLP, residual add + next norm and the next layer's q/k/v projections
+    (for the last layer: the final norm and the logits).  All tensors are static buffers of the graphs' shared
+    memory pool; the hot path reads q/k/v from them and writes the attention output into ``attn``."""
+
+    def __init__(self):
+        self.ids = None
+        self.attn = None
+        self.qkv = []          # per layer (q, k, v), each [B, H, 1, D]
+        self.pre = None
+        self.post = []
+        self.logits = None
+
+
 class PagedDecoder:
     def __init__(self, config: Any, weights: Dict[str, torch.Tensor], *, tracer: Optional[Any] = None,
-                 fused_rope: bool = True, fused_glue: Optional[bool] = None):
+                 fused_rope: bool = True, fused_glue: Optional[bool] = None, decode_graphs: Optional[bool] = None):
         self.config = config
         self.w = weights
         self.tracer = tracer
         self.fused_rope = fused_rope
         # RMSNorm (+ residual add) and SwiGLU as single launches; False (or SKV_FUSED_GLUE=0): plain torch ops
         self.fused_glue = (os.environ.get("SKV_FUSED_GLUE", "1") != "0") if fused_glue is None else bool(fused_glue)
+        # Cached decode steps replay CUDA graphs for everything between two hot-path calls (see _DecodeGraphs);
+        # False (or SKV_DECODE_GRAPHS=0): every op is launched from Python.  Weights must not be replaced after the
+        # first graphed step.
+        self.decode_graphs = (os.environ.get("SKV_DECODE_GRAPHS", "1") != "0") if decode_graphs is None else bool(decode_graphs)
+        self._graphs: Dict[int, "_DecodeGraphs"] = {}
+        self._eager_decodes: Dict[int, int] = {}
         self.H = config.hidden_size
         self.Hq = config.num_attention_heads
         # deepseek_mlx.py:235: KV heads default to the attention-head count (MHA)
@@ -150,6 +173,72 @@ class PagedDecoder:
                                          peak_memory_bytes=torch.cuda.max_memory_allocated(self.device))
         return out
 
+    # -- graphed decode step ---------------------------------------------------------------------------------
+    def _project_qkv(self, layer: int, x: torch.Tensor):
+        B = x.shape[0]
+        b = f"model.layers.{layer}.self_attn"
+        q = F.linear(x, self.w[f"{b}.q_proj.weight"]).view(B, 1, self.Hq, self.D).transpose(1, 2).contiguous()
+        k = F.linear(x, self.w[f"{b}.k_proj.weight"]).view(B, 1, self.Hkv, self.D).transpose(1, 2).contiguous()
+        v = F.linear(x, self.w[f"{b}.v_proj.weight"]).view(B, 1, self.Hkv, self.D).transpose(1, 2).contiguous()
+        return q, k, v
+
+    def _capture_decode_graphs(self, B: int) -> _DecodeGraphs:
+        g = _DecodeGraphs()
+        n_layers = self.config.num_hidden_layers
+        g.ids = torch.zeros((B, 1), dtype=torch.long, device=self.device)
+        g.attn = torch.zeros((B, self.Hq, 1, self.D), dtype=self.dtype, device=self.device)
+        head = self.w.get("lm_head.weight")
+        if head is None:
+            head = self.w["model.embed_tokens.weight"]
+        mem = torch.cuda.graph_pool_handle()
+        torch.cuda.synchronize(self.device)
+        g.pre = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g.pre, pool=mem):
+            hidden = self.w["model.embed_tokens.weight"][g.ids]
+            x = self._rms_norm(hidden, self.w["model.layers.0.input_layernorm.weight"])
+            g.qkv.append(self._project_qkv(0, x))
+        for i in range(n_layers):
+            b = f"model.layers.{i}"
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=mem):
+                delta = F.linear(g.attn.transpose(1, 2).reshape(B, 1, -1), self.w[f"{b}.self_attn.o_proj.weight"])
+                hidden, x = self._add_norm(hidden, delta, self.w[f"{b}.post_attention_layernorm.weight"])
+                next_w = self.w[f"model.layers.{i + 1}.input_layernorm.weight"] if i + 1 < n_layers else self.w["model.norm.weight"]
+                hidden, x = self._add_norm(hidden, self._mlp(x, b), next_w)
+                if i + 1 < n_layers:
+                    g.qkv.append(self._project_qkv(i + 1, x))
+                else:
+                    g.logits = F.linear(x, head)
+            g.post.append(graph)
+        return g
+
+    def _graphed_decode(self, input_ids: torch.Tensor, cache: Any, past: int) -> torch.Tensor:
+        B = input_ids.shape[0]
+        g = self._graphs.get(B)
+        if g is None:
+            g = self._graphs[B] = self._capture_decode_graphs(B)
+        kwargs = {"cache_position": [past]}
+        g.ids.copy_(input_ids)
+        g.pre.replay()
+        for i, (q, k, v) in enumerate(g.qkv):
+            if self.hot_path_events is not None:
+                ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                ev[0].record()
+            out = cache.decode_step_with_rope(q, k, v, i, kwargs, inv_freq=self.inv_freq_np, scaling_factor=self.rope_scale,
+                                              out=g.attn)
+            if out is None:
+                raise RuntimeError("the cache refused the one-call decode step inside a graphed decode")
+            if self.hot_path_events is not None:
+                ev[1].record()
+                self.hot_path_events.append(ev)
+            g.post[i].replay()
+        return g.logits.clone()
+
+    def _can_graph_decode(self, L: int, cache: Any, past: int) -> bool:
+        return (self.decode_graphs and self.fused_rope and self.fused_glue and self.tracer is None and L == 1 and past > 0
+                and cache is not None and hasattr(cache, "decode_step_with_rope") and self.config.num_hidden_layers > 0
+                and all(cache.get_seq_length(i) == past for i in range(self.config.num_hidden_layers)))
+
     # -- model (llama_mlx.py:740-833, 863-912) ---------------------------------------------------------------
     def __call__(self, input_ids: torch.Tensor, past_key_values: Optional[Any] = None, use_cache: bool = False) -> torch.Tensor:
         input_ids = input_ids.to(self.device)
@@ -157,6 +246,13 @@ class PagedDecoder:
         hidden = self.w["model.embed_tokens.weight"][input_ids]
         cache = past_key_values if use_cache else None
         past = cache.get_seq_length() if cache is not None else 0
+        if self._can_graph_decode(L, cache, past):
+            # the first cached steps of a batch size run from Python (library and cuBLAS set-up must not happen
+            # inside a capture); from the third on the step replays graphs
+            seen = self._eager_decodes.get(B, 0)
+            if seen >= 2:
+                return self._graphed_decode(input_ids, cache, past)
+            self._eager_decodes[B] = seen + 1
         cache_position = list(range(past, past + L))            # host values: no device sync to validate them
         position_ids = torch.tensor([cache_position], dtype=torch.int32)
         # Same block as the reference (norm -> attention -> add -> norm -> MLP -> add, llama_mlx.py:608-658), with

@@ -155,12 +155,13 @@ class PagedKVCache:
 
     def decode_step_with_rope(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
                               layer_idx: int, cache_kwargs: Optional[Dict[str, Any]] = None, *, inv_freq: np.ndarray,
-                              scaling_factor: float = 1.0, eps: float = 1e-12) -> Optional[torch.Tensor]:
+                              scaling_factor: float = 1.0, eps: float = 1e-12,
+                              out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """The cached decode step of a layer (one new token per sequence) in ONE library call:
         ``update_with_rope`` followed by the attention call with ``query_positions = [past]``
         (llama_mlx.py:284-308 for L == 1).  Same validation and bookkeeping as ``update``; ``query_states``
-        is rotated in place; returns ``[B, Hq, 1, D]``, or ``None`` when the step does not apply (more than one
-        token) and the caller should make the two calls."""
+        is rotated in place; returns ``[B, Hq, 1, D]`` (written into ``out`` when given), or ``None`` when the step
+        does not apply (more than one token) and the caller should make the two calls."""
         if key_states.dim() != 4 or key_states.shape[2] != 1 or query_states.dim() != 4 or query_states.shape[2] != 1:
             return None
         if self.seq_ids is None or not query_states.is_contiguous():
@@ -171,6 +172,7 @@ class PagedKVCache:
         Hkv = key_states.shape[1]
         out = self.pool.decode_step(layer_idx, query_states.view(B, Hq, D), key_states.reshape(B, Hkv, D).contiguous(),
                                     value_states.reshape(B, Hkv, D).contiguous(), eps=eps,
+                                    out=None if out is None else out.view(B, Hq, D),
                                     seq_ids=None if list(self.seq_ids) == list(range(B)) else self.seq_ids)
         self._finish_update(layer_idx, previous, 1)
         return out.view(B, Hq, 1, D)

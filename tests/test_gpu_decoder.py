@@ -230,3 +230,33 @@ def test_reference_style_tracer_sees_query_key_value_and_output_per_layer():
     op = per_call[9]
     assert op.kind == "operation" and op.duration_ms > 0 and op.active_memory_bytes is not None
     assert {e.layer for e in tr.events} == set(range(cfg.num_hidden_layers))
+
+
+def test_graphed_decode_steps_equal_the_eager_ones():
+    """Cached decode steps with everything between two hot-path calls replayed from CUDA graphs against the same
+    steps launched op by op: identical logits (the kernels and their inputs are the same), identical cache
+    lengths, for two batch sizes on one model and across the eager-to-graph switch."""
+    cfg = od.make_config(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, intermediate_size=1024,
+                         vocab_size=512, num_hidden_layers=3, rope_theta=10000.0)
+    w = {k: torch.from_numpy(v).to(DEV).to(torch.bfloat16) for k, v in od.random_weights(cfg, seed=9, std=0.05).items()}
+    rng = np.random.default_rng(10)
+    runs = {}
+    for graphs in (False, True):
+        model = L.PagedDecoder(cfg, w, decode_graphs=graphs)
+        outs = []
+        for B in (2, 3):
+            ids = torch.from_numpy(np.random.default_rng(11 + B).integers(0, 512, size=(B, 21))).to(DEV)
+            cache = L.PagedKVCache(cfg)
+            logits = model(ids, past_key_values=cache, use_cache=True)
+            nxt = logits[:, -1].argmax(-1, keepdim=True)
+            for _ in range(6):                      # steps 1-2 run eagerly, 3-6 replay graphs when enabled
+                logits = model(nxt, past_key_values=cache, use_cache=True)
+                outs.append(logits.clone())
+                nxt = logits[:, -1].argmax(-1, keepdim=True)
+            assert cache.get_seq_length() == 27
+        runs[graphs] = outs
+        if graphs:
+            assert sorted(model._graphs) == [2, 3] and len(model._graphs[2].post) == 3
+    for a, b in zip(runs[False], runs[True]):
+        assert torch.equal(a, b)
+    del rng
