@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import os
 import time
+import weakref
 from typing import Any, Dict, Optional
 
 import torch
@@ -59,6 +60,7 @@ class _DecodeGraphs:
         self.pre = None
         self.post = []
         self.logits = None
+        self.bound = {}        # id(cache) -> (pool, per-layer bound hot-path calls)
 
 
 class PagedDecoder:
@@ -217,16 +219,28 @@ class PagedDecoder:
         g = self._graphs.get(B)
         if g is None:
             g = self._graphs[B] = self._capture_decode_graphs(B)
+        # the hot-path calls on the graphs' static buffers, bound once per (cache, pool): one ctypes call per layer
+        bound = g.bound.get(id(cache))
+        ids_now = tuple(cache.seq_ids or ())
+        if bound is None or bound[0]() is not cache or bound[1] is not cache.pool or bound[2] != ids_now:
+            steps = [cache.bind_decode_step(q, k, v, g.attn, inv_freq=self.inv_freq_np, scaling_factor=self.rope_scale)
+                     if hasattr(cache, "bind_decode_step") else None for q, k, v in g.qkv]
+            bound = g.bound[id(cache)] = (weakref.ref(cache), cache.pool, ids_now, None if any(s is None for s in steps) else steps)
+            if len(g.bound) > 8:                    # caches come and go: keep the table small
+                g.bound.pop(next(iter(g.bound)))
+        steps = bound[3]
         kwargs = {"cache_position": [past]}
+        stream = torch.cuda.current_stream(self.device).cuda_stream
         g.ids.copy_(input_ids)
         g.pre.replay()
         for i, (q, k, v) in enumerate(g.qkv):
             if self.hot_path_events is not None:
                 ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                 ev[0].record()
-            out = cache.decode_step_with_rope(q, k, v, i, kwargs, inv_freq=self.inv_freq_np, scaling_factor=self.rope_scale,
-                                              out=g.attn)
-            if out is None:
+            if steps is not None:
+                steps[i](i, past, stream)
+            elif cache.decode_step_with_rope(q, k, v, i, kwargs, inv_freq=self.inv_freq_np, scaling_factor=self.rope_scale,
+                                             out=g.attn) is None:
                 raise RuntimeError("the cache refused the one-call decode step inside a graphed decode")
             if self.hot_path_events is not None:
                 ev[1].record()

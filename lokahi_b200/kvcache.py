@@ -177,6 +177,41 @@ class PagedKVCache:
         self._finish_update(layer_idx, previous, 1)
         return out.view(B, Hq, 1, D)
 
+    def bind_decode_step(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                         out: torch.Tensor, *, inv_freq: np.ndarray, scaling_factor: float = 1.0, eps: float = 1e-12):
+        """``decode_step_with_rope`` for tensors that stay put (static buffers of a CUDA graph): shapes, dtypes and
+        the RoPE table are checked once; the returned ``step(layer, position, stream)`` rejects a position that does
+        not append exactly after the cached sequence, makes the library call and does the bookkeeping of
+        ``update``.  Returns ``None`` when a per-update policy has to run (a layer window), so that the caller keeps
+        using ``decode_step_with_rope``."""
+        if self.pool is None or self.seq_ids is None or type(self)._finish_update is not PagedKVCache._finish_update:
+            return None
+        self._validate_state_shapes(key_states, value_states)
+        B, Hq, L, D = query_states.shape
+        Hkv = key_states.shape[1]
+        c = self.pool.cfg
+        if L != 1 or key_states.shape[2] != 1 or (B, Hkv, D) != (self.batch_size, c.num_kv_heads, c.head_dim):
+            raise ValueError("new key states must match cached batch, head, and feature dimensions")
+        self._ensure_rope(inv_freq, scaling_factor)
+        call = self.pool.decode_step_binder(query_states.view(B, Hq, D), key_states.view(B, Hkv, D), value_states.view(B, Hkv, D),
+                                            out.view(B, Hq, D), eps=eps,
+                                            seq_ids=None if list(self.seq_ids) == list(range(B)) else self.seq_ids)
+        lengths, resident, offloaded = self._layer_lengths, self._resident, self._disk_offloaded
+
+        def step(layer_idx: int, position: int, stream: int) -> None:
+            if layer_idx in offloaded:
+                self._load_layer_from_disk(layer_idx)
+            previous = lengths.get(layer_idx, 0)
+            if position != previous:
+                raise ValueError("cache_position must append exactly after the cached sequence; "
+                                 f"expected {[previous]}, got {[position]}")
+            call(layer_idx, stream)
+            resident.add(layer_idx)
+            lengths[layer_idx] = previous + 1
+            if previous + 1 > self._seen_tokens:
+                self._seen_tokens = previous + 1
+        return step
+
     # -- lengths (mlx_kvcache.py:160-181) ----------------------------------------------------------------------
     def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:
         if layer_idx is None:

@@ -340,6 +340,40 @@ class PagedPool:
                                                  out.data_ptr(), hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
         return out
 
+    def decode_step_binder(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, *, seq_ids=None,
+                           eps: float = 1e-12):
+        """``decode_step`` for buffers that stay put (the static tensors of a CUDA graph): the tensors are checked
+        once, here, and the returned ``call(layer, stream)`` only makes the library call.  The caller keeps the
+        tensors alive and unchanged in shape for as long as it uses the callable."""
+        for name, t in (("q", q), ("k", k), ("v", v), ("out", out)):
+            self._check_tensor(t, name)
+            if t.dim() != 3 or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous rank-3 tensor")
+        n_seqs, hq, _ = q.shape
+        if k.shape != (n_seqs, self.cfg.num_kv_heads, self.cfg.head_dim) or v.shape != k.shape or out.shape != q.shape:
+            raise ValueError("new key states must match cached batch, head, and feature dimensions")
+        ws = self.workspace(n_seqs, hq)
+        h, qp, kp, vp, op, wp, wn = self._h, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel()
+        eps_f = float(eps)
+        if seq_ids is None:
+            fn = lib.skv_decode_step
+
+            def call(layer: int, stream: int):
+                st = fn(h, layer, n_seqs, qp, kp, vp, op, hq, eps_f, wp, wn, stream)
+                if st:
+                    raise_for_status(st, h)
+        else:
+            ids = i32_array(seq_ids)
+            if len(ids) != n_seqs:
+                raise ValueError("seq_ids must have one entry per row of q")
+            fn = lib.skv_decode_step_seqs
+
+            def call(layer: int, stream: int):
+                st = fn(h, layer, ids, n_seqs, qp, kp, vp, op, hq, eps_f, wp, wn, stream)
+                if st:
+                    raise_for_status(st, h)
+        return call
+
     def decode_step_gather(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gather, *,
                            eps: float = 1e-12) -> torch.Tensor:
         """``decode_step`` under KV-head sharding: append, attend, fused output gather and wait in one library call.
