@@ -3,16 +3,18 @@
 
 Workload "paged_decode_llama3_8b_layer": 32 query heads, 8 KV heads, head_dim 128, bf16, page size 16,
 64 sequences with context lengths uniform in [512, 8192], the page table a random permutation of a
-shared pool, K/V ~ N(0,1).  One step = append one token per sequence with RoPE (theta 500000) on write
-(K and Q rotated in the same launch), then attend over the whole paged history.
+shared pool, K/V ~ N(0,1).  One step = append one token per sequence with RoPE (theta 500000) on write,
+then attend over the whole paged history: one library call, two launches.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload prefill [--kv paged] | decoder | longctx | glue      (secondary workloads, 1 GPU)
 
 Prints one JSON line.  `value` is decode tokens/s with inputs resident in HBM; `e2e` is the same step
 driven from pinned host buffers through the public API with the output read back every step;
-`roofline` relates the attention call's algorithmic HBM bytes to the measured copy bandwidth;
+`roofline` relates the step call's algorithmic HBM bytes to the measured copy bandwidth;
 `cpu_baseline` times the NumPy restatement of the reference path on the host.  With N > 1 the KV heads
-(and their query heads) are sharded over the ranks and the outputs are all-gathered with NCCL.
+(and their query heads) are sharded over the ranks and the output slices are gathered by peer stores from the
+merge kernel (`--gather nccl`: by an NCCL all-gather).
 """
 from __future__ import annotations
 
