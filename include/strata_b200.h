@@ -179,7 +179,7 @@ typedef struct skv_peer_gather {
     int32_t rank, world, epoch;
     void* const* out_ptrs;        /* host array, world entries */
     int32_t* const* flag_ptrs;    /* host array, world entries; each points to int32 flags[world] on that rank */
-    const int32_t* wait_flags;    /* this rank's own flag array: when not NULL the call also enqueues skv_gather_wait */
+    const int32_t* wait_flags;    /* this rank's own flag array: when not NULL the merge kernel's last block also waits (bounded) for every rank's slice, so no skv_gather_wait is needed */
 } skv_peer_gather;
 SKV_API int32_t skv_decode_attn_gather(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
                                        const void* q, const int32_t* q_pos, int32_t n_q_heads, float eps,

@@ -862,6 +862,8 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
             }
     }
     if (d.gather.world > 0) {
+        __shared__ int s_wait;
+        if (tid == 0) s_wait = 0;
         // When the last merge block has stored its rows, tell every rank (itself included) that this rank's
         // slice of epoch `epoch` has landed.  fence -> ticket -> fence -> flag keeps the rows ahead of the flag.
         __threadfence_system();
@@ -873,7 +875,23 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
                 __threadfence_system();
                 for (int r = 0; r < d.gather.world; ++r)
                     *reinterpret_cast<volatile int32_t*>(d.gather.flags[r] + d.gather.rank) = d.gather.epoch;
+                s_wait = d.gather.wait_flags != nullptr;
             }
+        }
+        // The consumer's wait, folded into this kernel: the last block watches this rank's own flags (the peers'
+        // kernels on OTHER GPUs write them) for about a second at most; a timeout sets a status bit.  Work enqueued
+        // after this kernel then sees every rank's rows without a separate wait launch.
+        __syncthreads();
+        if (s_wait && tid < d.gather.world) {
+            const volatile int32_t* f = d.gather.wait_flags + tid;
+            const long long start = clock64();
+            while (*f < d.gather.epoch) {
+                if (clock64() - start > 2000000000LL) {
+                    atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
+                    break;
+                }
+            }
+            __threadfence_system();
         }
     }
 }

@@ -913,13 +913,13 @@ int32_t skv_decode_attn_gather(skv_pool* p, int32_t layer, const int32_t* seq_id
     D.gather.world = g->world;
     D.gather.rank = g->rank;
     D.gather.epoch = g->epoch;
+    D.gather.wait_flags = g->wait_flags;   // the wait runs in the merge kernel's last block: no separate launch
     D.gather.ticket = p->d_tickets + (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads;
     for (int32_t r = 0; r < g->world; ++r) {
         D.gather.out[r] = g->out_ptrs[r];
         D.gather.flags[r] = g->flag_ptrs[r];
     }
     CUDA_TRY(p, launch_decode(D, stream));
-    if (g->wait_flags) CUDA_TRY(p, launch_gather_wait(g->wait_flags, g->world, g->epoch, p->d_status, stream));
     return SKV_OK;
 }
 
@@ -1056,6 +1056,7 @@ static int32_t fused_step(skv_pool* p, int32_t layer, const int32_t* seq_ids, in
         D.gather.world = g->world;
         D.gather.rank = g->rank;
         D.gather.epoch = g->epoch;
+        D.gather.wait_flags = g->wait_flags;   // the wait runs in the merge kernel's last block
         D.gather.ticket = p->d_tickets + (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads;
         for (int32_t r = 0; r < g->world; ++r) {
             D.gather.out[r] = g->out_ptrs[r];
@@ -1063,7 +1064,6 @@ static int32_t fused_step(skv_pool* p, int32_t layer, const int32_t* seq_ids, in
         }
     }
     CUDA_TRY(p, launch_decode(D, stream));
-    if (g && g->wait_flags) CUDA_TRY(p, launch_gather_wait(g->wait_flags, g->world, g->epoch, p->d_status, stream));
     return SKV_OK;
 }
 

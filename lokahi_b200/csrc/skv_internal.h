@@ -72,6 +72,8 @@ struct PeerGatherView {
     int32_t* ticket;             // device counter of finished merge blocks (zero between calls)
     void* out[8];                // per rank: base of its gathered buffer [world][n_seqs][q_heads][head_dim]
     int32_t* flags[8];           // per rank: its flag array [world]
+    const int32_t* wait_flags;   // this rank's own flag array: when set, the merge kernel's last block also waits
+                                 // (bounded) until every rank's slice of this epoch has landed here
 };
 
 struct DecodeLaunch {
