@@ -104,6 +104,174 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------------
+SEQ_BLOCK = 64            # tokens per round-robin block of the sequence sharding (four pages)
+
+
+def base_config(n_gpus, parallelism):
+    """The `config` object both arms print (same keys, same values for the same workload)."""
+    return {"workload": WORKLOAD, "n_seqs": N_SEQS, "context": [CTX_LO, CTX_HI], "q_heads": HQ, "kv_heads": HKV,
+            "head_dim": D, "page_size": P, "rope_theta": THETA, "layers": 1, "parallelism": parallelism,
+            "l2": "inputs larger than L2 (KV working set per step >= 1 GB / n_gpus)"}
+
+
+def parallelism_label(world, shard, gather):
+    if world == 1:
+        return "single"
+    if shard == "seq":
+        return f"sequence_shard{world} (round-robin blocks of {SEQ_BLOCK} tokens), cross-rank merge fused into the merge kernel (peer stores)"
+    return f"kv_head_shard{world}, output gather " + ("fused into the merge kernel (peer stores)" if gather == "fused" else "NCCL all-gather")
+
+
+def rank_geometry(r, world, shard_kind):
+    """(kv heads, q heads, per-sequence stored lengths) of rank r."""
+    from lokahi_b200.sharding import InterleavedShard
+    lens0 = workload_lengths()
+    if shard_kind == "seq" and world > 1:
+        sh = InterleavedShard(r, world, SEQ_BLOCK, P)
+        return HKV, HQ, np.array([sh.local_count(int(t)) for t in lens0], dtype=np.int64), sh
+    return HKV // world, HQ // world, lens0, None
+
+
+def rank_tables(r, world, shard_kind, total_steps):
+    """Page-table geometry of rank r's pool: the same on whichever rank computes it."""
+    hkv, hq, lens_local, sh = rank_geometry(r, world, shard_kind)
+    cap = lens_local + total_steps + 2 * P
+    pages_each = (-(-cap // P)).astype(np.int64)
+    n_pages = int(pages_each.sum()) + 16
+    perm = np.random.default_rng(SEED + 1 + 101 * r).permutation(n_pages)   # page table = random permutation of the pool
+    starts = np.concatenate([[0], np.cumsum(pages_each)])
+    return hkv, hq, lens_local, sh, int(pages_each.max()), n_pages, [perm[starts[s]:starts[s + 1]] for s in range(N_SEQS)]
+
+
+def rank_data(r, world, shard_kind, total_steps, dev):
+    """K/V pool contents and per-step inputs of rank r, from a generator seeded by r alone, so that rank 0 can
+    rebuild every rank's data for the parity check."""
+    import torch
+    hkv, hq, _, _, _, n_pages, _ = rank_tables(r, world, shard_kind, total_steps)
+    gen = torch.Generator(device=dev).manual_seed(SEED + 17 * r)
+    kp = torch.empty((n_pages, hkv, P, D), device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+    vp = torch.empty((n_pages, hkv, P, D), device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+    # under sequence sharding every rank sees the same q, k, v rows (all heads): seeded alike
+    gen_in = torch.Generator(device=dev).manual_seed(SEED + 5 + (0 if shard_kind == "seq" else 17 * r))
+    mk = lambda h: torch.randn((total_steps, N_SEQS, h, D), generator=gen_in, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    return kp, vp, mk(hq), mk(hkv), mk(hkv)
+
+
+def build_pool(L, torch, r, world, shard_kind, total_steps, dev, local_rank):
+    hkv, hq, lens_local, sh, pages_per_seq, n_pages, tables = rank_tables(r, world, shard_kind, total_steps)
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=hkv, head_dim=D, num_pages=n_pages, max_seqs=N_SEQS,
+                                       max_pages_per_seq=pages_per_seq, page_size=P, dtype=torch.bfloat16,
+                                       device=local_rank, rope_theta=THETA))
+    for s in range(N_SEQS):
+        assert pool.alloc_sequence() == s
+        pool.set_page_table(s, tables[s].tolist(), int(lens_local[s]))
+    return pool
+
+
+def parity_check(L, torch, dist, args, world, rank, dev, local_rank, total_steps, pool, data, run_step):
+    """One step, outside every timed region, whose result is compared (on rank 0) with the same step on ONE pool
+    that holds all heads and all tokens, and with the NumPy oracle on sampled sequences.  Returns the `parity`
+    object of the JSON line; a mismatch ends the run with a non-zero exit code."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from parity import TOL_BF16, parity_errors, to_np
+    from oracle import attention as oattn
+    from oracle import paged as opaged
+    kp, vp, q_all, k_all, v_all = data
+    lens0 = workload_lengths()
+    q0 = q_all[0].clone()
+    got_local = run_step(q0, k_all[0], v_all[0], False).clone()     # [world, n, hq, D] / [n, HQ, D] / [n, hq, D]
+    torch.cuda.synchronize()
+    if world > 1 and args.shard == "head":
+        got_local = got_local.movedim(0, 1).reshape(N_SEQS, HQ, D)
+    result = None
+    if rank == 0:
+        # the unsharded pool: all heads, all tokens, filled from every rank's regenerated data
+        if world == 1:
+            full, q_full, out_full = pool, q0, got_local
+        else:
+            full = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=HKV, head_dim=D, max_seqs=N_SEQS,
+                                               num_pages=int(sum(-(-(int(t) + 2 * P) // P) for t in lens0)) + 16,
+                                               max_pages_per_seq=int(-(-(lens0.max() + 2 * P) // P)), page_size=P,
+                                               dtype=torch.bfloat16, device=local_rank, rope_theta=THETA))
+            for s in range(N_SEQS):
+                assert full.alloc_sequence() == s
+                full.reserve(s, int(lens0[s]) + 1)
+            if args.shard == "head":
+                hkv = HKV // world
+                hist = None
+                qs, ks, vs = [], [], []
+                for r in range(world):
+                    kp_r, vp_r, q_r, k_r, v_r = data if r == 0 else rank_data(r, world, "head", total_steps, dev)
+                    tables = rank_tables(r, world, "head", total_steps)[6]
+                    qs.append(q_r[0]); ks.append(k_r[0]); vs.append(v_r[0])
+                    for s in range(N_SEQS):                # the rank's heads of sequence s, in token order
+                        T = int(lens0[s])
+                        pg = torch.as_tensor(tables[s][: -(-T // P)] if T else tables[s][:0], device=dev, dtype=torch.long)
+                        kk = kp_r[pg].permute(1, 0, 2, 3).reshape(hkv, -1, D)[:, :T]
+                        vv = vp_r[pg].permute(1, 0, 2, 3).reshape(hkv, -1, D)[:, :T]
+                        if hist is None:
+                            hist = [[torch.empty((HKV, int(t), D), device=dev, dtype=torch.bfloat16) for t in lens0] for _ in range(2)]
+                        hist[0][s][r * hkv:(r + 1) * hkv] = kk
+                        hist[1][s][r * hkv:(r + 1) * hkv] = vv
+                    del kp_r, vp_r
+                q_full = torch.cat(qs, dim=1).contiguous()
+                k_new, v_new = torch.cat(ks, dim=1).contiguous(), torch.cat(vs, dim=1).contiguous()
+            else:
+                from lokahi_b200.sharding import InterleavedShard
+                hist = [[torch.empty((HKV, int(t), D), device=dev, dtype=torch.bfloat16) for t in lens0] for _ in range(2)]
+                for r in range(world):
+                    kp_r, vp_r, q_r, k_r, v_r = data if r == 0 else rank_data(r, world, "seq", total_steps, dev)
+                    tables = rank_tables(r, world, "seq", total_steps)[6]
+                    sh = InterleavedShard(r, world, SEQ_BLOCK, P)
+                    for s in range(N_SEQS):
+                        idx = sh.global_positions(int(lens0[s]))
+                        if not idx:
+                            continue
+                        pg = torch.as_tensor(tables[s][: -(-len(idx) // P)], device=dev, dtype=torch.long)
+                        ix = torch.as_tensor(idx, device=dev, dtype=torch.long)
+                        hist[0][s][:, ix] = kp_r[pg].permute(1, 0, 2, 3).reshape(HKV, -1, D)[:, :len(idx)]
+                        hist[1][s][:, ix] = vp_r[pg].permute(1, 0, 2, 3).reshape(HKV, -1, D)[:, :len(idx)]
+                    del kp_r, vp_r
+                q_full, k_new, v_new = q_all[0].clone(), k_all[0], v_all[0]
+            for s in range(N_SEQS):
+                if int(lens0[s]):
+                    full.append(0, hist[0][s][None], hist[1][s][None], seq_ids=[s], start_pos=[0])
+            del hist
+            out_full = full.decode_step(0, q_full, k_new, v_new)
+            torch.cuda.synchronize()
+        err_unsharded = parity_errors(got_local, to_np(out_full))[0] if world > 1 else 0.0
+        # the oracle on the logical history of sampled sequences: shortest, longest, two drawn at random
+        pick = sorted({int(np.argmin(lens0)), int(np.argmax(lens0)), *np.random.default_rng(SEED + 9).choice(N_SEQS, 2, replace=False).tolist()})
+        err_oracle = 0.0
+        for s in pick:
+            T = int(lens0[s]) + 1
+            kd, vd = full.gather(0, seq_ids=[s], max_len=T)
+            ref = oattn.chunked_grouped_attention(to_np(q_full[s])[None, :, None, :], to_np(kd), to_np(vd),
+                                                  query_positions=np.array([T - 1], dtype=np.int32))
+            err_oracle = max(err_oracle, parity_errors(got_local[s], ref[0, :, 0, :])[0])
+            qr = opaged.rope_rows(to_np(q_all[0][s] if world == 1 or args.shard == "seq" else torch.cat([x[s] for x in qs], 0))[None], np.array([T - 1]), THETA)[0]
+            import ml_dtypes
+            qr = qr.astype(ml_dtypes.bfloat16).astype(np.float32)      # one bf16 step of slack: sincosf vs NumPy cos/sin
+            if not np.all(np.abs(to_np(q_full[s]) - qr) <= np.abs(qr) * 2.0 ** -7 + 1e-30):
+                raise SystemExit(f"parity: rotated q of sequence {s} differs from the oracle's RoPE")
+        result = {"checked": True, "tolerance": TOL_BF16, "vs_oracle_max_norm_err": err_oracle, "sequences": pick,
+                  "vs_unsharded_pool_max_norm_err": err_unsharded if world > 1 else None,
+                  "vs_unsharded_pool_sequences": N_SEQS if world > 1 else 0}
+        if not (err_oracle <= TOL_BF16 and err_unsharded <= TOL_BF16):
+            print(json.dumps({"parity": result, "error": "parity check failed"}), flush=True)
+            raise SystemExit(3)
+    # every rank goes back to the workload's starting lengths (the token written above is overwritten by the first step)
+    _, _, lens_local, _ = rank_geometry(rank, world, args.shard)
+    for s in range(N_SEQS):
+        if pool.length(0, s) != int(lens_local[s]):
+            pool.truncate(0, int(lens_local[s]), seq_ids=[s])
+    torch.cuda.synchronize()
+    if world > 1:
+        ok = torch.tensor([1 if (rank != 0 or result is not None) else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return result
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -122,183 +290,293 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     from lokahi_b200.sharding import HeadShard
-    shard = HeadShard(rank, world, HQ, HKV)          # raises when the KV heads do not divide over the ranks
-    hkv, hq = shard.local_kv_heads, shard.local_q_heads
-    if args.emulate_shard > 1 and world == 1:      # one GPU doing the per-GPU share of an N-way head sharding (tuning aid)
-        hkv, hq = HKV // args.emulate_shard, HQ // args.emulate_shard
-
-    K, W = args.steps, args.warmup
-    total_steps = W + K
+    if args.shard == "head":
+        shard = HeadShard(rank, world, HQ, HKV)        # raises when the KV heads do not divide over the ranks
+    K, W, R = args.steps, args.warmup, max(1, args.repeats)
+    K2 = min(K, 32)
+    total_steps = W + K + 4                                # every timed repeat re-runs the same K steps
+    hkv, hq, lens_local, seq_sh = rank_geometry(rank, world, args.shard)
     lens0 = workload_lengths()
-    rng = np.random.default_rng(SEED + 1)
-    cap = lens0 + 3 * total_steps + 2 * P                   # room for the timed leg, the instrumented pass and the e2e leg
-    pages_per_seq = int(-(-cap.max() // P))
-    pages_each = (-(-cap // P)).astype(np.int64)
-    n_pages = int(pages_each.sum()) + 16
-    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=hkv, head_dim=D, num_pages=n_pages, max_seqs=N_SEQS,
-                                       max_pages_per_seq=pages_per_seq, page_size=P, dtype=torch.bfloat16,
-                                       device=local_rank, rope_theta=THETA))
-    perm = rng.permutation(n_pages)                        # page table = random permutation of the shared pool
-    at = 0
-    for s in range(N_SEQS):
-        assert pool.alloc_sequence() == s
-        pool.set_page_table(s, perm[at:at + pages_each[s]].tolist(), int(lens0[s]))
-        at += int(pages_each[s])
+    pool = build_pool(L, torch, rank, world, args.shard, total_steps, dev, local_rank)
+    data = rank_data(rank, world, args.shard, total_steps, dev)
     kp, vp = pool.layer_views(0)
-    gen = torch.Generator(device=dev).manual_seed(SEED + 17 * rank)
-    kp.normal_(generator=gen)
-    vp.normal_(generator=gen)
-
-    # per-step inputs, resident in HBM (device leg) and in pinned host memory (e2e leg)
-    q_all = torch.randn((total_steps, N_SEQS, hq, D), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    k_all = torch.randn((total_steps, N_SEQS, hkv, D), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    v_all = torch.randn((total_steps, N_SEQS, hkv, D), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    kp.copy_(data[0]); vp.copy_(data[1])
+    data = (kp, vp) + data[2:]
+    _, _, q_all, k_all, v_all = data
     out_buf = torch.empty((N_SEQS, hq, D), device=dev, dtype=torch.bfloat16)
     gathered = torch.empty((world, N_SEQS, hq, D), device=dev, dtype=torch.bfloat16) if world > 1 else None
-    fused_gather = world > 1 and args.gather == "fused"
+    mode = "plain" if world == 1 else ("seq" if args.shard == "seq" else args.gather)
     peer = None
-    if fused_gather:
-        # peer-mapped buffers need torch symmetric memory on every rank; if any rank cannot set them up,
-        # all ranks fall back to the NCCL all-gather together
+    if mode in ("fused", "seq"):
+        # peer-mapped buffers need torch symmetric memory on every rank; without it KV-head sharding falls back to
+        # the NCCL all-gather on all ranks together (sequence sharding has no such fallback here)
         try:
-            peer = L.PeerGather(shard, N_SEQS, D, torch.bfloat16, dev)
+            peer = (L.PeerGather(shard, N_SEQS, D, torch.bfloat16, dev) if mode == "fused"
+                    else L.PeerSeqMerge(rank, world, N_SEQS, HQ, D, torch.bfloat16, dev))
             ok_local = 1
         except Exception as exc:   # noqa: BLE001 - any failure means "no peer mapping here"
-            sys.stderr.write(f"[bench] rank {rank}: fused gather unavailable ({exc}); using NCCL all-gather\n")
+            sys.stderr.write(f"[bench] rank {rank}: peer exchange unavailable ({exc})\n")
             ok_local = 0
         flag = torch.tensor([ok_local], device=dev, dtype=torch.int32)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:
-            fused_gather, peer = False, None
-    state = {"view": gathered}
+            if mode == "seq":
+                raise SystemExit("sequence sharding needs peer-mapped buffers (torch symmetric memory)")
+            mode, peer = "nccl", None
+    state = {"view": out_buf, "step": 0}
 
-    def step_call(q, k, v):
+    def positions_for(step_index):
+        cur = [int(t) + step_index for t in lens0]
+        return cur, [seq_sh.owner(p) == rank for p in cur]
+
+    def step_call(q, k, v, consecutive, step_index=None, out=None):
         """The library call of one decode step: RoPE of q and of the new K row, the append and the attention in the
-        split-K kernel, then the merge kernel (under sharding with the fused gather: its peer stores and the wait)."""
-        if fused_gather:
-            state["view"] = pool.decode_step_gather(0, q, k, v, peer)
+        split-K kernel, then the merge kernel (under sharding: with the exchange between the GPUs inside it)."""
+        if mode == "fused":
+            state["view"] = pool.decode_step(0, q, k, v, exchange=peer, consecutive=consecutive)
+        elif mode == "seq":
+            cur, store = positions_for(state["step"] if step_index is None else step_index)
+            state["view"] = pool.decode_step(0, q, k, v, exchange=peer, positions=cur, store=store, consecutive=consecutive)
         else:
-            pool.decode_step(0, q, k, v, out=out_buf)
+            state["view"] = out_buf if out is None else out
+            pool.decode_step(0, q, k, v, out=state["view"], consecutive=consecutive and mode != "nccl")
+        return state["view"]
 
-    def step(q, k, v):
-        step_call(q, k, v)
-        if world > 1 and not fused_gather:
-            dist.all_gather_into_tensor(gathered, out_buf)
+    def step(q, k, v, consecutive=True, step_index=None, out=None, gathered_out=None):
+        view = step_call(q, k, v, consecutive, step_index, out)
+        if mode == "nccl":
+            state["view"] = gathered if gathered_out is None else gathered_out
+            dist.all_gather_into_tensor(state["view"], view)
+            view = state["view"]
+        return view
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident leg ---------------------------------------------------------------------------
-    for i in range(W):
-        step(q_all[i], k_all[i], v_all[i])
+    def rewind(n_steps_done):
+        """Back to the state after `n_steps_done` steps from the workload's start (lengths only: the pages keep the
+        appended rows, which the next run overwrites with the same bytes)."""
+        for s in range(N_SEQS):
+            want = int(lens0[s]) + n_steps_done if seq_sh is None else seq_sh.local_count(int(lens0[s]) + n_steps_done)
+            if pool.length(0, s) != want:
+                pool.truncate(0, want, seq_ids=[s])
+        state["step"] = n_steps_done
+
+    # ---- parity: one step against an unsharded pool and the oracle, outside every timed region ----------------
+    parity = None
+    if not args.no_parity:
+        parity = parity_check(L, torch, dist, args, world, rank, dev, local_rank, total_steps, pool, data,
+                              lambda q, k, v, c: step(q, k, v, c, 0))
+    rewind(0)
+
+    # ---- device-resident leg ---------------------------------------------------------------------------------
+    # The inputs of step j are tensors of their own, so the calls are bound once (tensor checks and argument
+    # marshalling happen here, not in the loop): bound[j](layer, stream) is one library call.
+    bound = None
+    if mode != "nccl":
+        bound = []
+        for j in range(W + K):
+            kw = {"consecutive": True}
+            if mode == "seq":
+                kw["positions"], kw["store"] = positions_for(j)
+            if mode in ("fused", "seq"):
+                bound.append(pool.decode_step_binder(q_all[j], k_all[j], v_all[j], exchange=peer, **kw))
+            else:
+                bound.append(pool.decode_step_binder(q_all[j], k_all[j], v_all[j], out_buf, **kw))
+
+    def run_steps(first, count, consecutive=True):
+        if bound is not None:
+            stream = torch.cuda.current_stream().cuda_stream
+            for j in range(first, first + count):
+                state["view"] = bound[j](0, stream)
+            state["step"] = first + count
+            return
+        for i in range(count):
+            j = first + i
+            state["step"] = j
+            step(q_all[j], k_all[j], v_all[j], consecutive, j)
+
+    run_steps(0, W)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    launches0 = L._lib.lib.skv_launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for i in range(K):
-        j = W + i
-        step(q_all[j], k_all[j], v_all[j])
-    ev1.record()
-    barrier()
-    launches = L._lib.lib.skv_launch_count() - launches0
+    ms_repeats, launches = [], 0
+    host_us = []
+    for r in range(R):
+        rewind(W)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        launches0 = L._lib.lib.skv_launch_count()
+        ev0.record()
+        t_host = time.perf_counter()
+        run_steps(W, K)
+        host_us.append((time.perf_counter() - t_host) / K * 1e6)      # host time to enqueue a step (no sync inside)
+        ev1.record()
+        barrier()
+        launches = L._lib.lib.skv_launch_count() - launches0
+        ms_repeats.append(ev0.elapsed_time(ev1))
     clocks = sampler.stop() if rank == 0 else None
-    ms_total = ev0.elapsed_time(ev1)
+
     # instrumented pass (not part of `value`): the same steps with CUDA events around the library call only
-    # (split-K kernel + merge kernel, under sharding with the fused gather and its wait), for the roofline
-    K2 = min(K, 32)
+    # (split-K kernel + merge kernel, under sharding with the exchange inside it), for the roofline
+    rewind(W)
     attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K2)]
-    barrier()                                             # rank 0 spent time stopping the clock sampler
+    barrier()
     l_inst0 = L._lib.lib.skv_launch_count()
     for i in range(K2):
         j = W + i
+        state["step"] = j
         attn_ev[i][0].record()
-        step_call(q_all[j], k_all[j], v_all[j])
+        step_call(q_all[j], k_all[j], v_all[j], False, j)
         attn_ev[i][1].record()
-        if world > 1 and not fused_gather:
+        if mode == "nccl":
             dist.all_gather_into_tensor(gathered, out_buf)
     launches_per_call = (L._lib.lib.skv_launch_count() - l_inst0) // K2
     barrier()
     attn_ms = np.array([a.elapsed_time(b) for a, b in attn_ev])
     if K2 > 4:
         attn_ms = attn_ms[2:]                             # the first launches after a barrier absorb rank skew
+    # kernel-only pass under sharding: this rank's share of the step with no exchange at all (what one GPU needs for
+    # its own heads / tokens), so that step time splits into kernels and exchange + skew
+    kernel_only_ms = None
+    if world > 1:
+        rewind(W)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(K):
+            j = W + i
+            if mode == "seq":
+                cur, store = positions_for(j)
+                pool.decode_step(0, q_all[j], k_all[j], v_all[j], positions=cur, store=store, out=out_buf, consecutive=True)
+            else:
+                pool.decode_step(0, q_all[j], k_all[j], v_all[j], out=out_buf, consecutive=True)
+        e1.record()
+        barrier()
+        kernel_only_ms = e0.elapsed_time(e1) / K
     if pool.check_device_status() != 0:
         raise SystemExit("device status flag set during the timed region")
-    lens_timed = lens0[None, :] + W + K + 1 + np.arange(K2)[:, None]      # attended tokens per instrumented step
-    algo_bytes = float(np.mean([algorithmic_bytes(lens_timed[i], hq, hkv) for i in range(K2 - len(attn_ms), K2)]))
+    steps_timed = W + np.arange(K2)[K2 - len(attn_ms):]
+    if seq_sh is None:
+        algo_bytes = float(np.mean([algorithmic_bytes(lens0 + j + 1, hq, hkv) for j in steps_timed]))
+    else:
+        algo_bytes = float(np.mean([algorithmic_bytes(np.array([seq_sh.local_count(int(t) + j + 1) for t in lens0]), hq, hkv)
+                                    for j in steps_timed]))
 
-    # ---- end-to-end leg: pinned host inputs, output read back every step ----------------------------------
+    # ---- end-to-end leg: every step's inputs come from pinned host memory, every step's result goes back ------------
+    # Two device staging buffers: the upload of step s + 1 runs on a copy stream while step s computes, and the
+    # result of step s is read back on a third stream while step s + 1 computes; the host waits for result s - 1
+    # before it enqueues step s + 1, and for the last result before the clock stops.
     Ke = K
+    rewind(W)
     nq, nk = N_SEQS * hq * D, N_SEQS * hkv * D
-    # one pinned staging buffer per step, [q | k | v], so that a step costs one host->device copy
-    qkv_h = torch.cat([q_all[:Ke].reshape(Ke, nq), k_all[:Ke].reshape(Ke, nk), v_all[:Ke].reshape(Ke, nk)], dim=1).cpu().pin_memory()
-    qkv_d = torch.empty((nq + 2 * nk,), device=dev, dtype=torch.bfloat16)
-    q_d = qkv_d[:nq].view(N_SEQS, hq, D)
-    k_d = qkv_d[nq:nq + nk].view(N_SEQS, hkv, D)
-    v_d = qkv_d[nq + nk:].view(N_SEQS, hkv, D)
-    out_h = torch.empty((world if world > 1 else 1, N_SEQS, hq, D), dtype=torch.bfloat16).pin_memory()
+    qkv_h = torch.cat([q_all[W:W + Ke].reshape(Ke, nq), k_all[W:W + Ke].reshape(Ke, nk), v_all[W:W + Ke].reshape(Ke, nk)], dim=1).cpu().pin_memory()
+    qkv_d = [torch.empty((nq + 2 * nk,), device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    views = [(b[:nq].view(N_SEQS, hq, D), b[nq:nq + nk].view(N_SEQS, hkv, D), b[nq + nk:].view(N_SEQS, hkv, D)) for b in qkv_d]
+    res_shape = tuple(state["view"].shape) if mode != "nccl" else tuple(gathered.shape)
+    out_h = [torch.empty(res_shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    # without the fused exchange the step writes a buffer of the caller's: two of them, like the exchange's own pair
+    out_d = [torch.empty_like(out_buf) for _ in range(2)]
+    gat_d = [torch.empty_like(gathered) for _ in range(2)] if mode == "nccl" else [None, None]
+    up, down, main = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev), torch.cuda.current_stream()
+    ev_up = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_step = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_step(i):
-        qkv_d.copy_(qkv_h[i], non_blocking=True)
-        step(q_d, k_d, v_d)
-        out_h.copy_((state["view"] if world > 1 else out_buf).view(out_h.shape), non_blocking=True)
-        torch.cuda.current_stream().synchronize()          # a decode loop consumes the result before the next step
+    def e2e_run(count):
+        with torch.cuda.stream(up):
+            qkv_d[0].copy_(qkv_h[0], non_blocking=True)
+            ev_up[0].record(up)
+        for i in range(count):
+            b = i & 1
+            if i + 1 < count:                                  # next step's inputs, while this step computes
+                with torch.cuda.stream(up):
+                    if i >= 1:
+                        up.wait_event(ev_free[1 - b])          # step i - 1 has finished reading that staging buffer
+                    qkv_d[1 - b].copy_(qkv_h[i + 1], non_blocking=True)
+                    ev_up[1 - b].record(up)
+            main.wait_event(ev_up[b])
+            if i >= 2:
+                main.wait_event(ev_done[b])                     # the result buffer of this parity has been read back
+            view = step(*views[b], False, W + i, out_d[b], gat_d[b])
+            ev_free[b].record(main)
+            ev_step[b].record(main)
+            with torch.cuda.stream(down):
+                down.wait_event(ev_step[b])
+                out_h[b].copy_(view, non_blocking=True)
+                ev_done[b].record(down)
+            if i >= 1:
+                ev_done[1 - b].synchronize()                   # the host consumes result i - 1 here
+        ev_done[(count - 1) & 1].synchronize()
 
-    for i in range(min(W, Ke)):
-        e2e_step(i)
+    e2e_run(min(max(W, 3), Ke))
+    rewind(W)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(Ke):
-        e2e_step(i)
+    t0 = time.perf_counter()
+    e2e_run(Ke)
     e1.record()
+    wall_e2e_ms = (time.perf_counter() - t0) * 1e3
     barrier()
-    ms_e2e = e0.elapsed_time(e1)
+    ms_e2e = max(e0.elapsed_time(e1), 0.0)
     if pool.check_device_status() != 0:
         raise SystemExit("device status flag set during the end-to-end leg")
 
-    # ---- max over ranks --------------------------------------------------------------------------------------
-    stats = torch.tensor([ms_total, ms_e2e, float(attn_ms.mean())], device=dev, dtype=torch.float64)
+    # ---- max over ranks ------------------------------------------------------------------------------------------
+    stats = torch.tensor(ms_repeats + [ms_e2e, float(attn_ms.mean()), kernel_only_ms or 0.0, float(np.median(host_us))],
+                         device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e, attn_mean_ms = [float(x) for x in stats.tolist()]
+    stats = [float(x) for x in stats.tolist()]
+    ms_repeats, (ms_e2e, attn_mean_ms, kernel_only_ms, host_us_per_call) = stats[:R], stats[R:]
+    ms_total = float(np.median(ms_repeats))
 
     result = None
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         achieved = algo_bytes / (attn_mean_ms * 1e-3) / 1e9
         tokens = N_SEQS * K
+        step_desc = {2: "decode step call: split-K kernel with RoPE and the append folded in + merge kernel"
+                        + (" (exchange between the GPUs and its wait inside the merge kernel)" if mode in ("fused", "seq") else ""),
+                     3: "decode step call: append kernel + split-K kernel + merge kernel"}.get(
+                         launches_per_call, f"decode step call: {launches_per_call} launches")
         result = {
             "metric": "paged GQA decode tokens/s", "value": tokens / (ms_total * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "n_seqs": N_SEQS, "context": [CTX_LO, CTX_HI], "q_heads": HQ, "kv_heads": HKV,
-                       "head_dim": D, "page_size": P, "rope_theta": THETA, "layers": 1,
-                       "parallelism": (f"kv_head_shard{world}, output gather " + ("fused into the merge kernel (peer stores)" if fused_gather else "NCCL all-gather")) if world > 1 else "single",
-                       "l2": "inputs larger than L2 (KV working set per step >= 1 GB / n_gpus)"},
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": base_config(world, parallelism_label(world, args.shard, mode)),
+            "repeats": R, "ms_per_step_repeats": [m / K for m in ms_repeats],
+            "timing": "median over `repeats` timed regions of K steps each (every region bracketed by a barrier and a device "
+                      "synchronisation, max over ranks per region); steps are enqueued back to back and a step's split-K "
+                      "kernel overlaps the previous step's merge kernel",
             "e2e": {"value": N_SEQS * Ke / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / Ke,
-                    "h2d_bytes_per_step": int(q_d.numel() + k_d.numel() + v_d.numel()) * 2,
-                    "d2h_bytes_per_step": int(out_h.numel()) * 2},
+                    "h2d_bytes_per_step": int(nq + 2 * nk) * 2, "d2h_bytes_per_step": int(np.prod(res_shape)) * 2,
+                    "pipeline": "upload of step s+1 and read-back of step s-1 overlap step s (three streams); "
+                                "every result is awaited on the host", "host_wall_ms_per_step": wall_e2e_ms / Ke},
             "gpu_launches": int(launches),
+            "host_us_per_call": host_us_per_call,
+            "kernel_only_ms": kernel_only_ms if world > 1 else None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "kernel": ("decode step call: split-K kernel with RoPE and the append folded in + merge kernel"
-                                    if launches_per_call == 2 + (1 if fused_gather else 0) else
-                                    "decode step call: append kernel + split-K kernel + merge kernel")
-                                   + (" + gather wait" if fused_gather else ""),
+                         "kernel": step_desc, "launches_per_call": int(launches_per_call),
                          "algorithmic_bytes_per_launch": algo_bytes, "launch_ms": attn_mean_ms,
                          "launch_ms_min": float(attn_ms.min()), "launch_ms_median": float(np.median(attn_ms)),
-                         "launch_ms_p95": float(np.percentile(attn_ms, 95)), "traffic": algo_bytes * TRAFFIC_RATIO},
+                         "launch_ms_p95": float(np.percentile(attn_ms, 95)), "traffic": algo_bytes * TRAFFIC_RATIO,
+                         "traffic_source": "ncu dram bytes of a 16-sequence capture, scaled by the algorithmic bytes",
+                         "pipelined_frac": algo_bytes / (ms_total / K * 1e-3) / 1e9 / peak},
+            "parity": parity,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
-            result["cpu_baseline"] = cpu_baseline_sample(pool, kp, vp, lens0 + W + K + K2 + min(W, Ke) + Ke, hq, hkv)
+            result["cpu_baseline"] = cpu_baseline_sample(pool, kp, vp, np.array([pool.length(0, s) for s in range(N_SEQS)]), hq, hkv)
+    if peer is not None:
+        peer.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -634,9 +912,9 @@ def pool_set_lengths(pool, layers, n_seq, length):
             done += n
 
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum per decode launch: measured on the 16-sequence capture
-# case (293.13 MB of traffic for 287.07 MB algorithmic, profiles/decode_tma_kernel_paged_decode_16seq.md)
-# and scaled to this workload by the algorithmic bytes, which is what the traffic grows with.
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per decode launch: measured on a 16-sequence capture of the
+# same kernel (293.13 MB of traffic for 287.07 MB algorithmic) and scaled to this workload by the algorithmic
+# bytes, which is what the traffic grows with.
 TRAFFIC_RATIO = 293.13 / 287.07
 
 
@@ -753,9 +1031,8 @@ def run_reference(args):
         "impl": "reference", "metric": "paged GQA decode tokens/s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": dt / K * 1e3, "higher_is_better": True,
         # same workload at every N (the CPU arm does not shard): the label follows the GPU arm's
-        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "n_seqs": N_SEQS, "context": [CTX_LO, CTX_HI], "q_heads": HQ, "kv_heads": HKV,
-                   "head_dim": D, "page_size": P, "rope_theta": THETA, "layers": 1},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": base_config(args.gpus, parallelism_label(args.gpus, args.shard, args.gather)),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": f"full workload step (64 sequences x 1 token) x {K} steps; NumPy restatement of the "
                                    f"reference path, one process per core (requested steps {args.steps})"},
@@ -775,7 +1052,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how the per-rank attention outputs are gathered")
-    ap.add_argument("--emulate-shard", type=int, default=1, help=argparse.SUPPRESS)
+    ap.add_argument("--shard", choices=["head", "seq"], default="head",
+                    help="N > 1: shard by KV head (output gather) or by sequence (round-robin token blocks, cross-rank merge)")
+    ap.add_argument("--repeats", type=int, default=10, help="decode workload: timed regions of K steps; the median is reported")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity step (one unsharded pool + the oracle on rank 0)")
     ap.add_argument("--workload", choices=["decode", "prefill", "decoder", "longctx", "glue"], default="decode",
                     help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")
     ap.add_argument("--kv", choices=["dense", "paged"], default="dense",

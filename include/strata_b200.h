@@ -7,7 +7,9 @@
  * launch; skv_last_error() gives the message of the last failing call on a pool.
  * Device pointers are borrowed for the duration of the call on the given stream;
  * the library never frees caller memory.  `stream` is a cudaStream_t passed as
- * void* (NULL = the legacy default stream).
+ * void* (NULL = the legacy default stream).  Calls that change page tables or lengths publish the
+ * change to the device on the stream they are given; a pool is driven from one stream at a time
+ * (hand it from one stream to another with an event, as with any buffer).
  *
  * Each declaration cites the interface of the reference project (Strata,
  * Python package `ollm`) that it stands in for, as  path:line  inside that project.
@@ -28,7 +30,7 @@ extern "C" {
 #define SKV_API
 #endif
 
-#define SKV_ABI_VERSION 1
+#define SKV_ABI_VERSION 2
 
 /* status codes */
 enum {
@@ -67,8 +69,15 @@ typedef struct skv_config {
 
 /* Pool life cycle.  Stands in for MLXKVCache.__init__ / clear (mlx_kvcache.py:31-63, 271-284).
  * Device layout per layer: K[page][kv_head][page_size][head_dim], V likewise. */
+/* A sequence may hold at most SKV_MAX_TOKENS_PER_SEQ tokens (the split-K plan gives a sequence at most 128
+ * chunks of 2048 tokens): skv_create refuses a pool whose max_pages_per_seq * page_size exceeds it with
+ * SKV_ERR_UNSUPPORTED (on failure *out still holds a handle for skv_last_error; destroy it). */
+#define SKV_MAX_TOKENS_PER_SEQ 262144
 SKV_API int32_t skv_abi_version(void);
 SKV_API int32_t skv_create(const skv_config* cfg, skv_pool** out);
+/* The SKV_* environment switches (A/B aids) are read once, at the first call that needs one; this reads them
+ * again.  No reference counterpart. */
+SKV_API void skv_reload_env(void);
 SKV_API int32_t skv_destroy(skv_pool* pool);
 SKV_API const char* skv_last_error(const skv_pool* pool);
 SKV_API const char* skv_status_string(int32_t status);
@@ -79,11 +88,14 @@ SKV_API int64_t skv_launch_count(void);
 /* Sequences.  The reference keeps one tensor per layer with a batch axis (mlx_kvcache.py:54);
  * here each batch row is a sequence with its own page-table row and per-layer lengths. */
 SKV_API int32_t skv_alloc_sequence(skv_pool* pool, int32_t* seq_out);
-SKV_API int32_t skv_free_sequence(skv_pool* pool, int32_t seq);
-SKV_API int32_t skv_reserve(skv_pool* pool, int32_t seq, int32_t total_tokens);
+/* The three calls below change the device copy of the page table / lengths on `stream`, in order with the
+ * kernels enqueued there before and after them. */
+SKV_API int32_t skv_free_sequence(skv_pool* pool, int32_t seq, void* stream);
+SKV_API int32_t skv_reserve(skv_pool* pool, int32_t seq, int32_t total_tokens, void* stream);
 /* Adopt an externally chosen page-table row (validated: range, no page shared with a live sequence)
  * and set every layer's length to `length`.  No reference counterpart. */
-SKV_API int32_t skv_set_page_table(skv_pool* pool, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t length);
+SKV_API int32_t skv_set_page_table(skv_pool* pool, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t length,
+                                   void* stream);
 
 /* Shorten one layer's history of the listed sequences to `new_length` tokens; pages stay owned.
  * Used when a layer is dropped to a file and later re-appended from position 0
@@ -141,58 +153,99 @@ SKV_API int32_t skv_gather(skv_pool* pool, int32_t layer, const int32_t* seq_ids
  * (online_chunked_grouped_attention_mx with Lq == 1, src/ollm/backends/mlx_ops.py:32-152;
  * call site llama_mlx.py:300-308).  q, out: [n_seqs][n_q_heads][head_dim], pool dtype.
  * q_pos (host, may be NULL = length-1) are absolute query positions: keys 0..q_pos are attended.
- * workspace holds the split-K partials; size from skv_decode_workspace_bytes. */
+ * workspace holds the split-K partials: skv_decode_workspace_bytes bytes, 16-byte aligned (a pointer that is not
+ * is refused with SKV_ERR_BAD_ARG before anything is launched). */
 SKV_API size_t skv_decode_workspace_bytes(const skv_pool* pool, int32_t n_seqs, int32_t n_q_heads);
 SKV_API int32_t skv_decode_attn(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
                         const void* q, void* out, const int32_t* q_pos, int32_t n_q_heads,
                         float eps, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Exchange between GPUs fused into the merge kernel (no reference counterpart: the reference is single-device; it
+ * loops over its KV heads and concatenates their results, mlx_ops.py:81-87, :152, and merges key chunks with the
+ * rule of :125-146).  Every rank passes the same description with its own `rank`:
+ *   SKV_XCHG_HEAD_GATHER  KV-head sharding: rank r holds KV heads [r*Hkv/N, (r+1)*Hkv/N) and their query heads; its
+ *       merge kernel stores each finished row into slot r of every rank's receive buffer and unpacks all slots into
+ *       `out` [world][n_seqs][n_q_heads][head_dim] (n_q_heads = this rank's heads).
+ *   SKV_XCHG_SEQ_MERGE    sequence sharding: every rank holds all heads and a share of every sequence's tokens; the
+ *       un-normalised partial row (acc, m, l) goes to the row's owner (row % world), which merges the `world`
+ *       partials and sends the finished row to every rank; `out` is [n_seqs][n_q_heads][head_dim].
+ * recv_ptrs[r] is rank r's receive buffer as seen from this rank (peer-mapped device memory: CUDA IPC, symmetric
+ * memory ...), skv_exchange_bytes long, 16-byte aligned and zero-filled before the first call.  `epoch` starts at 1
+ * and grows by one per call on every rank alike (the two halves of a buffer alternate by its parity).  Data crosses
+ * NVLink as 16-byte stores whose 8-byte halves each carry the epoch, so the receiver needs no flag and no fence; the
+ * merge kernel of a call waits (bounded, about a second; a timeout sets bit 8 of the pool's status word) for the
+ * rows it unpacks, and work enqueued after the call sees the complete `out`.  head_dim * element size must be a
+ * multiple of 8 and world at most 8. */
+enum { SKV_XCHG_HEAD_GATHER = 1, SKV_XCHG_SEQ_MERGE = 2 };
+typedef struct skv_exchange {
+    int32_t mode, rank, world;
+    uint32_t epoch;
+    void* const* recv_ptrs;       /* host array, world entries */
+    void* out;                    /* this rank's result buffer */
+} skv_exchange;
+SKV_API size_t skv_exchange_bytes(int32_t mode, int32_t world, int32_t n_seqs, int32_t n_q_heads, int32_t head_dim,
+                                  int32_t dtype);
+/* skv_decode_attn with the exchange in place of `out`. */
+SKV_API int32_t skv_decode_attn_xchg(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
+                                     const void* q, const int32_t* q_pos, int32_t n_q_heads, float eps,
+                                     void* workspace, size_t workspace_bytes, const skv_exchange* xchg, void* stream);
+
 /* K1 + K3 in one call for the cached decode step of a layer: rotate q (in place) and the new k with the pool's
  * RoPE table, append k, v at each sequence's current length, then attend
  * (the sequence apply_rotary_pos_emb_mlx -> cache.update -> attention of src/ollm/llama_mlx.py:284-308 for L == 1).
- * Sequences are 0..n_seqs-1; q, out: [n_seqs][n_q_heads][head_dim]; k, v: [n_seqs][kv_heads][head_dim], contiguous.
- * Same workspace as skv_decode_attn.  One host call instead of two halves the per-step host overhead.
  * For bf16, head_dim 128, page_size a multiple of 16 and at most 8 query heads per KV head the whole step is two
  * launches: the split-K kernel rotates q and the new k itself, stores the new rows into their page and attends
- * them from shared memory; the merge kernel writes the rotated q back and counts the token into the device
- * lengths.  The stored pages and the rotated q are bit-identical to the append + attention pair; the output
+ * them from shared memory; the merge kernel writes the rotated q back, sets the device lengths and runs the
+ * exchange.  The stored pages and the rotated q are bit-identical to the append + attention pair; the output
  * differs from it by rounding only (the new token's weight stays in float32).  SKV_STEP_FUSED=0 in the
- * environment selects the pair. */
+ * environment selects the pair.  On any error nothing was launched and the pool's host state is unchanged. */
+typedef struct skv_step_args {
+    int32_t layer, n_seqs;
+    const int32_t* seq_ids;       /* host, n_seqs live distinct sequences; NULL = 0..n_seqs-1.  Row i of q, k, v, out
+                                     belongs to seq_ids[i] */
+    void* q;                      /* row i at q + i * q_row_stride elements: [n_q_heads][head_dim]; rotated in place */
+    const void* k;                /* row i at k + i * k_row_stride: [kv_heads][head_dim], un-rotated */
+    const void* v;
+    void* out;                    /* row i at out + i * out_row_stride: [n_q_heads][head_dim]; ignored with xchg */
+    int64_t q_row_stride, k_row_stride, v_row_stride, out_row_stride;   /* elements; 0 = rows packed back to back.
+                                     With strides q, k and v can be slices of one fused projection output
+                                     [n_seqs][(n_q_heads + 2 * kv_heads) * head_dim] (llama_mlx.py:257-281) */
+    int32_t n_q_heads;
+    float eps;
+    void* workspace;              /* as for skv_decode_attn */
+    size_t workspace_bytes;
+    const skv_exchange* xchg;     /* NULL: the result goes to `out` */
+    float* partial_out;           /* when set (and xchg is NULL): un-normalised float32 rows [n_seqs][n_q_heads][head_dim + 2]
+                                     as skv_decode_partial writes them, instead of `out` */
+    /* Sequence sharding: this pool holds only a share of every sequence's tokens.  positions[i] is the absolute
+     * position of the step's token (its RoPE angle) and store[i] != 0 says that this pool keeps it.  NULL, NULL:
+     * the position is the row's length in this pool and every row is stored (the single-pool case). */
+    const int32_t* positions;     /* host */
+    const uint8_t* store;         /* host */
+    /* SKV_STEP_CONSECUTIVE: the caller states that (1) nothing was enqueued on `stream` since this pool's previous
+     * skv_decode_step* call on it, and (2) q, k, v and the pool's pages were complete before that call was made
+     * (they are not outputs of it).  The split-K kernel then runs ahead of the previous step's merge kernel and its
+     * exchange, and waits for it only where it stores its partials.  The library drops the flag by itself when
+     * the previous call on this pool was not a step on the same stream or when q, k, v overlap what that step
+     * wrote (its rotated q, its output). */
+    uint32_t flags;
+} skv_step_args;
+#define SKV_STEP_CONSECUTIVE 1u
+SKV_API int32_t skv_decode_step_ex(skv_pool* pool, const skv_step_args* args, void* stream);
+/* Short forms of skv_decode_step_ex: packed rows, sequences 0..n_seqs-1 (skv_decode_step), an explicit list
+ * (skv_decode_step_seqs), and the list plus an exchange (skv_decode_step_xchg). */
 SKV_API int32_t skv_decode_step(skv_pool* pool, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
                                 void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
                                 void* stream);
-/* skv_decode_step for an explicit list of live, distinct sequences (host array, n_seqs entries): rows of q, k, v and
- * out follow the order of the list.  NULL is the identity 0..n_seqs-1. */
 SKV_API int32_t skv_decode_step_seqs(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* q,
                                      const void* k, const void* v, void* out, int32_t n_q_heads, float eps,
                                      void* workspace, size_t workspace_bytes, void* stream);
+SKV_API int32_t skv_decode_step_xchg(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* q,
+                                     const void* k, const void* v, int32_t n_q_heads, float eps, void* workspace,
+                                     size_t workspace_bytes, const skv_exchange* xchg, void* stream);
 
-/* K3 with the output all-gather of KV-head sharding fused into the merge kernel (no reference counterpart: the
- * reference is single-device and concatenates its per-KV-head results in place, mlx_ops.py:152).
- * Rank `rank` of `world` (<= 8) stores its [n_seqs][n_q_heads][head_dim] output rows with plain peer stores into
- * slot `rank` of every rank's gathered buffer [world][n_seqs][n_q_heads][head_dim] (out_ptrs[r], peer-mapped device
- * pointers, e.g. from CUDA IPC or symmetric memory) and then writes `epoch` to flag_ptrs[r][rank].  Epochs must
- * grow by one per call and callers alternate between two gathered buffers.  skv_gather_wait enqueues a kernel
- * that waits (bounded, about a second; a timeout sets bit 8 of the pool's status word) until all `world` local
- * flags reached `epoch`; work enqueued after it on the stream sees every rank's rows. */
-typedef struct skv_peer_gather {
-    int32_t rank, world, epoch;
-    void* const* out_ptrs;        /* host array, world entries */
-    int32_t* const* flag_ptrs;    /* host array, world entries; each points to int32 flags[world] on that rank */
-    const int32_t* wait_flags;    /* this rank's own flag array: when not NULL the merge kernel's last block also waits (bounded) for every rank's slice, so no skv_gather_wait is needed */
-} skv_peer_gather;
-SKV_API int32_t skv_decode_attn_gather(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,
-                                       const void* q, const int32_t* q_pos, int32_t n_q_heads, float eps,
-                                       void* workspace, size_t workspace_bytes, const skv_peer_gather* gather,
-                                       void* stream);
-/* skv_decode_step with the fused gather: append (RoPE on write, q rotated in place), attend, gather, wait. */
-SKV_API int32_t skv_decode_step_gather(skv_pool* pool, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
-                                       int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
-                                       const skv_peer_gather* gather, void* stream);
-SKV_API int32_t skv_gather_wait(skv_pool* pool, const int32_t* local_flags, int32_t world, int32_t epoch, void* stream);
-
-/* Sequence sharding (no reference counterpart; the merge is the reference's own chunk-merge rule,
- * src/ollm/backends/mlx_ops.py:125-144, applied across ranks instead of across key blocks).
+/* Sequence sharding without the fused exchange (no reference counterpart; the merge is the reference's own
+ * chunk-merge rule, src/ollm/backends/mlx_ops.py:125-144, applied across ranks instead of across key blocks).
  * skv_decode_partial: K3 over the keys THIS pool holds, writing un-normalised float32 rows
  *   partial_out[n_seqs][n_q_heads][head_dim + 2] = (weighted V sum relative to m, m, l); q_pos are positions in this
  *   pool's own token numbering (a negative position means "none of my keys": l = 0).
@@ -222,10 +275,11 @@ SKV_API int32_t skv_decode_attn_static(skv_pool* pool, int32_t layer, const int3
  * (online_chunked_grouped_attention_mx, mlx_ops.py:32-152; unmasked twin :155-178).
  * q,out [B][Hq][Lq][D], k,v [B][Hkv][Lk][D], contiguous.  positions: device int32 [B][Lq]
  * absolute query positions, or NULL for bottom-right alignment arange(Lk-Lq, Lk) (:69-72).
- * Rows with no allowed key produce 0 (:118, :146). */
+ * Rows with no allowed key produce 0 (:118, :146).  status (device int32, may be NULL): the tensor-core kernel ORs
+ * bit 8 into it when one of its bounded waits ran out (the result is then invalid); the caller zeroes and reads it. */
 SKV_API int32_t skv_attn_dense(const void* q, const void* k, const void* v, void* out, const int32_t* positions,
                        int32_t B, int32_t Hq, int32_t Hkv, int32_t Lq, int32_t Lk, int32_t D,
-                       int32_t dtype, int32_t causal, float eps, void* stream);
+                       int32_t dtype, int32_t causal, float eps, int32_t* status, void* stream);
 
 /* K4 over pages: queries [n_seqs][Hq][Lq][D] against each sequence's first `lengths` tokens of a layer
  * (the attention call of a chunked prefill over the cache, src/ollm/llama_mlx.py:300-308 with L > 1).

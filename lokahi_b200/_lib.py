@@ -16,8 +16,11 @@ OK, ERR_BAD_ARG, ERR_REPLAY, ERR_OUT_OF_PAGES, ERR_NOT_RESIDENT = 0, -1, -2, -3,
 ERR_TIMEOUT, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_FLAG = -5, -6, -7, -8
 F32, BF16 = 0, 1
 PAGE_UNASSIGNED = -1
-ABI_VERSION = 1
+ABI_VERSION = 2
 STATIC_SCRATCH_BYTES = 16 << 20
+MAX_TOKENS_PER_SEQ = 262144
+XCHG_HEAD_GATHER, XCHG_SEQ_MERGE = 1, 2
+STEP_CONSECUTIVE = 1
 
 
 class OutOfPagesError(RuntimeError):
@@ -51,9 +54,23 @@ class SkvAppendArgs(C.Structure):
     ]
 
 
-class SkvPeerGather(C.Structure):
-    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("epoch", C.c_int32),
-                ("out_ptrs", C.POINTER(C.c_void_p)), ("flag_ptrs", C.POINTER(C.c_void_p)), ("wait_flags", C.c_void_p)]
+class SkvExchange(C.Structure):
+    _fields_ = [("mode", C.c_int32), ("rank", C.c_int32), ("world", C.c_int32), ("epoch", C.c_uint32),
+                ("recv_ptrs", C.POINTER(C.c_void_p)), ("out", C.c_void_p)]
+
+
+class SkvStepArgs(C.Structure):
+    _fields_ = [
+        ("layer", C.c_int32), ("n_seqs", C.c_int32),
+        ("seq_ids", C.POINTER(C.c_int32)),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("q_row_stride", C.c_int64), ("k_row_stride", C.c_int64), ("v_row_stride", C.c_int64), ("out_row_stride", C.c_int64),
+        ("n_q_heads", C.c_int32), ("eps", C.c_float),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("xchg", C.POINTER(SkvExchange)), ("partial_out", C.c_void_p),
+        ("positions", C.POINTER(C.c_int32)), ("store", C.POINTER(C.c_uint8)),
+        ("flags", C.c_uint32),
+    ]
 
 
 _i32, _i64, _vp, _f = C.c_int32, C.c_int64, C.c_void_p, C.c_float
@@ -68,9 +85,10 @@ SIGNATURES = {
     "skv_status_string": (C.c_char_p, [_i32]),
     "skv_launch_count": (_i64, []),
     "skv_alloc_sequence": (_i32, [_vp, _pi32]),
-    "skv_free_sequence": (_i32, [_vp, _i32]),
-    "skv_reserve": (_i32, [_vp, _i32, _i32]),
-    "skv_set_page_table": (_i32, [_vp, _i32, _pi32, _i32, _i32]),
+    "skv_reload_env": (None, []),
+    "skv_free_sequence": (_i32, [_vp, _i32, _vp]),
+    "skv_reserve": (_i32, [_vp, _i32, _i32, _vp]),
+    "skv_set_page_table": (_i32, [_vp, _i32, _pi32, _i32, _i32, _vp]),
     "skv_truncate": (_i32, [_vp, _i32, _pi32, _i32, _i32, _vp]),
     "skv_length": (_i32, [_vp, _i32, _i32, _pi32]),
     "skv_lengths": (_i32, [_vp, _i32, _pi32, _i32]),
@@ -83,15 +101,16 @@ SIGNATURES = {
     "skv_gather": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _i32, _vp]),
     "skv_decode_workspace_bytes": (C.c_size_t, [_vp, _i32, _i32]),
     "skv_decode_attn": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp, C.c_size_t, _vp]),
-    "skv_decode_attn_gather": (_i32, [_vp, _i32, _pi32, _i32, _vp, _pi32, _i32, _f, _vp, C.c_size_t, _vp, _vp]),
-    "skv_decode_step_gather": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp, _vp]),
+    "skv_exchange_bytes": (C.c_size_t, [_i32, _i32, _i32, _i32, _i32, _i32]),
+    "skv_decode_attn_xchg": (_i32, [_vp, _i32, _pi32, _i32, _vp, _pi32, _i32, _f, _vp, C.c_size_t, C.POINTER(SkvExchange), _vp]),
+    "skv_decode_step_ex": (_i32, [_vp, C.POINTER(SkvStepArgs), _vp]),
+    "skv_decode_step_xchg": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, C.POINTER(SkvExchange), _vp]),
     "skv_decode_partial": (_i32, [_vp, _i32, _pi32, _i32, _vp, _pi32, _i32, _vp, C.c_size_t, _vp, _vp]),
     "skv_merge_partials": (_i32, [_vp, _i32, _i64, _i32, _i32, _f, _vp, _i32, _vp]),
-    "skv_gather_wait": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "skv_decode_step": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp]),
     "skv_decode_step_seqs": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _f, _vp, C.c_size_t, _vp]),
     "skv_decode_attn_static": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _pi32, _i32, _f, _vp]),
-    "skv_attn_dense": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f, _vp]),
+    "skv_attn_dense": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f, _vp, _vp]),
     "skv_prefill_attn_paged": (_i32, [_vp, _i32, _pi32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _f, _vp]),
     "skv_evict": (_i32, [_vp, _i32, _i32, _i32, _vp]),
     "skv_prefetch": (_i32, [_vp, _i32, _i32, _i32, _vp]),

@@ -158,9 +158,36 @@ def chunked_grouped_attention(
         pos_ptr = positions.data_ptr()
     st = lib.skv_attn_dense(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), pos_ptr, B, Hq, Hkv, Lq, Lk, D,
                             _lib.BF16 if q.dtype == torch.bfloat16 else _lib.F32, 1 if causal else 0, float(eps),
-                            torch.cuda.current_stream(q.device).cuda_stream)
+                            _dense_status_word(q.device).data_ptr(), torch.cuda.current_stream(q.device).cuda_stream)
     raise_for_status(st)
     return out
+
+
+_DENSE_STATUS = {}
+
+
+def _dense_status_word(device: torch.device) -> torch.Tensor:
+    """One int32 per device that the dense tensor-core kernel ORs bit 8 into when a bounded wait ran out."""
+    key = torch.device(device).index or 0
+    word = _DENSE_STATUS.get(key)
+    if word is None:
+        word = _DENSE_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return word
+
+
+def check_dense_attention_status(device=None) -> int:
+    """Read and clear the status word of the dense attention calls made on ``device`` (synchronises it).  Raises
+    DeviceFlagError when a kernel gave up on a bounded wait: the outputs of the calls since the last check are
+    then not to be trusted.  The paged calls report through ``PagedPool.check_device_status`` instead."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _DENSE_STATUS.get(device.index or 0)
+    if word is None:
+        return 0
+    flag = int(word.item())
+    if flag:
+        word.zero_()
+        raise _lib.DeviceFlagError(f"dense attention status word 0x{flag:x} (8: a bounded wait ran out)")
+    return 0
 
 
 def chunked_grouped_attention_no_mask(

@@ -58,7 +58,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in _sources():
         obj = os.path.join(HERE, "build", os.path.basename(src) + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("SKV_NVCC_EXTRA", "").split(), "-I", os.path.join(ROOT, "include"), "-I", CSRC,
+               "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

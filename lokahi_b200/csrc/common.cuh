@@ -61,7 +61,7 @@ __device__ __forceinline__ int64_t row_offset(const PoolView& pv, int32_t page, 
 #ifdef __CUDACC__
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-    static const bool enabled = [] { const char* e = getenv("SKV_PDL"); return !(e && e[0] == '0'); }();
+    const bool enabled = switches().pdl != 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

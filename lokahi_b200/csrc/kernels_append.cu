@@ -167,8 +167,7 @@ static bool append_vectorisable(const AppendLaunch& a, size_t esize) {
     if (a.n_q_heads > 0 && (!ok_ptr(a.q_in) || !ok_ptr(a.q_out) || !ok_stride(a.q_stride_seq) || !ok_stride(a.q_stride_head) ||
                             !ok_stride(a.q_stride_tok)))
         return false;
-    const char* force = getenv("SKV_APPEND_SCALAR");
-    return !(force && force[0] == '1');
+    return !switches().append_scalar;
 }
 
 cudaError_t launch_append(const AppendLaunch& a, cudaStream_t stream) {

@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_generic_kernel(DecodeLa
     const float scale = rsqrtf((float)D);
 
     float q[DPL], acc[DPL];
-    const T* qrow = reinterpret_cast<const T*>(d.q) + ((int64_t)i * d.n_q_heads + hq) * D;
+    const T* qrow = reinterpret_cast<const T*>(d.q) + (int64_t)i * d.q_stride + (int64_t)hq * D;
 #pragma unroll
     for (int e = 0; e < DPL; ++e) {
         const int dd = lane + 32 * e;
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_mma_kernel(DecodeLaunch
     // Q fragments: row g of the group, 16-byte units c, 4+c, 8+c, 12+c of the head dimension.
     uint32_t qa[8][2];
     {
-        const char* qrow = reinterpret_cast<const char*>(d.q) + (((int64_t)i * d.n_q_heads + h * G + g) * kMmaD) * 2;
+        const char* qrow = reinterpret_cast<const char*>(d.q) + ((int64_t)i * d.q_stride + (int64_t)(h * G + g) * kMmaD) * 2;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             uint4 r = make_uint4(0, 0, 0, 0);
@@ -342,14 +342,41 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_mma_kernel(DecodeLaunch
 // ---------------------------------------------------------------------------------------------
 constexpr int kStageBytes = 8192;   // one 16-token tile: K (2 boxes x 2 KB) + V (2 boxes x 2 KB)
 
+// Per-row metadata of a one-call step: from the kernel parameters, or from the uploaded copy for large batches.
+__device__ __forceinline__ int row_seq(const StepRows& r, int n, int i) { return r.dev ? r.dev[i] : r.seq[i]; }
+__device__ __forceinline__ int row_len(const StepRows& r, int n, int i) { return r.dev ? r.dev[n + i] : r.len[i]; }
+__device__ __forceinline__ uint32_t row_pos(const StepRows& r, int n, int i) {
+    return r.dev ? (uint32_t)r.dev[2 * n + i] : r.pos[i];
+}
+
+// FA (the one-call decode step): sequence id, stored length and token position of a row come from `rows`, so the
+// kernel depends on nothing that an earlier kernel of the stream wrote except q, the new K/V rows and the pages.
+// With d.early_start the caller has vouched for those (see skv_step_args), the wait for the previous kernel moves
+// from the top to just before the partials are stored, and the whole K/V stream of this step overlaps the previous
+// step's merge kernel and its exchange.
 template <int NS, bool FA>
-__global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch d, const __grid_constant__ CUtensorMap kmap,
-                                                                    const __grid_constant__ CUtensorMap vmap) {
+__global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid_constant__ DecodeLaunch d,
+                                                                    const __grid_constant__ CUtensorMap kmap,
+                                                                    const __grid_constant__ CUtensorMap vmap,
+                                                                    const __grid_constant__ StepRows rows) {
     extern __shared__ uint8_t smem_raw[];
     const PoolView& pv = d.pool;
     const int split = blockIdx.x, h = blockIdx.y, i = blockIdx.z;
-    pdl_wait();
-    const int seq = d.seq_ids ? d.seq_ids[i] : i;
+    const bool late_wait = FA && d.early_start;
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&kmap);
+        prefetch_tensormap(&vmap);
+    }
+    if (!late_wait) pdl_wait();
+    int seq, len_old = 0;
+    uint32_t pos_raw = 0;
+    if constexpr (FA) {
+        seq = row_seq(rows, d.n_seqs, i);
+        len_old = row_len(rows, d.n_seqs, i);
+        pos_raw = row_pos(rows, d.n_seqs, i);
+    } else {
+        seq = d.seq_ids ? d.seq_ids[i] : i;
+    }
     if (!checked_seq(pv, seq)) return;
     const int t0 = split * d.chunk_tokens;
     // The page id of this lane's tile does not depend on the sequence length: fetch it now, next to the
@@ -359,25 +386,39 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
         const int slot = (t0 + ((int)(threadIdx.x >> 5) + kDecodeWarps * (int)(threadIdx.x & 31)) * 16) / pv.page_size;
         if (slot < pv.max_pages_per_seq) raw_page = pv.page_table[(int64_t)seq * pv.max_pages_per_seq + slot];
     }
-    // With the fused append the device length does not count this step's token yet: it sits at position
-    // len_old, is attended from registers by the CTA whose chunk contains it, and t1 bounds the tokens that
-    // are read from the pages.
-    const int len_old = attend_count(d, i, seq);
-    const int n_attend = FA ? len_old + 1 : len_old;
+    // In a step the row's length does not count this step's token yet: it sits at position len_old of the pages,
+    // is attended from shared memory by the CTA whose chunk contains it, and t1 bounds the tokens read from pages.
+    if constexpr (!FA) len_old = attend_count(d, i, seq);
+    const bool stores = FA && !(pos_raw & kRowNoStore);
+    const int n_attend = len_old + (stores ? 1 : 0);
     const int G = d.n_q_heads / pv.num_kv_heads;
     if (t0 >= n_attend) {
         if (split == 0 && d.fuse_merge) {   // nothing to attend: the output row is exactly 0 (mlx_ops.py:118, :146)
-            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(d.out) + ((int64_t)i * d.n_q_heads + h * G) * kMmaD;
+            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(d.out) + (int64_t)i * d.out_stride + (int64_t)h * G * kMmaD;
             for (int idx = threadIdx.x; idx < G * kMmaD; idx += kDecodeThreads) orow[idx] = __float2bfloat16_rn(0.f);
         }
         return;
     }
     const int t1 = min(len_old, t0 + d.chunk_tokens);
-    const bool owner = FA && len_old >= t0 && len_old < t0 + d.chunk_tokens;
+    const bool owner = stores && len_old >= t0 && len_old < t0 + d.chunk_tokens;
     const int n_splits = (n_attend + d.chunk_tokens - 1) / d.chunk_tokens;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int P = pv.page_size;
+
+    // Q fragments: row g, 16-byte units 2c and 2c+1 of each 128-byte half (the K lane mapping).  The loads are
+    // issued here, beside the page ids, and used after the first tiles have been requested.
+    uint4 qr[4];
+    {
+        const char* qrow = reinterpret_cast<const char*>(d.q) + ((int64_t)i * d.q_stride + (int64_t)(h * G + g) * kMmaD) * 2;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            qr[u] = make_uint4(0, 0, 0, 0);
+            if (g < G) qr[u] = *reinterpret_cast<const uint4*>(qrow + (8 * (u >> 1) + 2 * c + (u & 1)) * 16);
+        }
+    }
+    float my_inv_freq = 0.f;
+    if (FA && threadIdx.x < kMmaD / 2) my_inv_freq = d.inv_freq[threadIdx.x];
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* ring = smem + warp * NS * kStageBytes;
@@ -389,26 +430,18 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     }
     __syncwarp();
 
-    // Q fragments: row g, 16-byte units 2c and 2c+1 of each 128-byte half (the K lane mapping)
     uint32_t qa[8][2];
     float* fa_cos = reinterpret_cast<float*>(smem + kDecodeWarps * NS * kStageBytes + 128);   // [64]
     float* fa_sin = fa_cos + 64;                                                             // [64]
     float* fa_k = fa_sin + 64;                                                               // [128] rotated new K row
     float* fa_v = fa_k + kMmaD;                                                              // [128] new V row
-    auto load_q = [&]() {
-        const char* qrow = reinterpret_cast<const char*>(d.q) + (((int64_t)i * d.n_q_heads + h * G + g) * kMmaD) * 2;
-        uint4 r[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            r[u] = make_uint4(0, 0, 0, 0);
-            if (g < G) r[u] = *reinterpret_cast<const uint4*>(qrow + (8 * (u >> 1) + 2 * c + (u & 1)) * 16);
-        }
+    auto finish_q = [&]() {
         if constexpr (FA) {
             // unit u (first half) pairs with unit u + 2 (second half): dims 8 * (2c + u) + e and 64 more
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-                uint32_t* lo = reinterpret_cast<uint32_t*>(&r[u]);
-                uint32_t* hi = reinterpret_cast<uint32_t*>(&r[u + 2]);
+                uint32_t* lo = reinterpret_cast<uint32_t*>(&qr[u]);
+                uint32_t* hi = reinterpret_cast<uint32_t*>(&qr[u + 2]);
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo[w]));
@@ -426,13 +459,12 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            qa[2 * u][0] = r[u].x;
-            qa[2 * u][1] = r[u].y;
-            qa[2 * u + 1][0] = r[u].z;
-            qa[2 * u + 1][1] = r[u].w;
+            qa[2 * u][0] = qr[u].x;
+            qa[2 * u][1] = qr[u].y;
+            qa[2 * u + 1][0] = qr[u].z;
+            qa[2 * u + 1][1] = qr[u].w;
         }
     };
-    if constexpr (!FA) load_q();
     const int n_tiles = (t1 - t0 + 15) >> 4;
     const int n_my = n_tiles > warp ? (n_tiles - warp + kDecodeWarps - 1) / kDecodeWarps : 0;
     int my_page = -1;
@@ -476,20 +508,19 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
 
     for (int k = 0; k < NS && k < n_my; ++k) issue(k);
     if constexpr (FA) {
-        // While the first tiles are in flight: cos/sin of this step's position (the append kernel's arithmetic,
+        // While the first tiles are in flight: cos/sin of the token's position (the append kernel's arithmetic,
         // llama_mlx.py:132-136, :172-182), and in the owning CTA the new token's rows.
         const int tid = threadIdx.x;
         if (tid < kMmaD / 2) {
-            float fpos = (float)len_old;
+            float fpos = (float)(pos_raw & ~kRowNoStore);
             if (d.rope_scaling != 1.0f) fpos = __fdiv_rn(fpos, d.rope_scaling);
             float sn, cs;
-            sincosf(__fmul_rn(fpos, d.inv_freq[tid]), &sn, &cs);
+            sincosf(__fmul_rn(fpos, my_inv_freq), &sn, &cs);
             fa_cos[tid] = cs;
             fa_sin[tid] = sn;
             if (owner) {
-                const int64_t src = ((int64_t)i * pv.num_kv_heads + h) * kMmaD;
-                const __nv_bfloat16* ks = reinterpret_cast<const __nv_bfloat16*>(d.new_k) + src;
-                const __nv_bfloat16* vs = reinterpret_cast<const __nv_bfloat16*>(d.new_v) + src;
+                const __nv_bfloat16* ks = reinterpret_cast<const __nv_bfloat16*>(d.new_k) + (int64_t)i * d.k_stride + (int64_t)h * kMmaD;
+                const __nv_bfloat16* vs = reinterpret_cast<const __nv_bfloat16*>(d.new_v) + (int64_t)i * d.v_stride + (int64_t)h * kMmaD;
                 const float x1 = __bfloat162float(ks[tid]), x2 = __bfloat162float(ks[tid + 64]);
                 const __nv_bfloat16 k1 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn)));
                 const __nv_bfloat16 k2 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn)));
@@ -511,14 +542,15 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
             }
         }
         __syncthreads();
-        load_q();
     }
+    finish_q();
     bool dead = false;
     int k = 0;
     for (; k < n_my; ++k) {
         const int page = __shfl_sync(0xffffffffu, my_page, k);
         const int stage = k % NS;
-        if (!mbar_wait(&wbar[stage], (k / NS) & 1)) {
+        // every lane runs its own bounded wait; the verdict is made warp-uniform before anything branches on it
+        if (!__all_sync(0xffffffffu, mbar_wait(&wbar[stage], (k / NS) & 1))) {
             dead = true;
             break;
         }
@@ -606,6 +638,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
         if (lane == 0) atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
         // copies already issued for later tiles still target this CTA's shared memory: wait for them (bounded)
         for (int kk = k + 1; kk < n_my && kk < k + NS; ++kk) mbar_wait(&wbar[kk % NS], (kk / NS) & 1);
+        __syncwarp();
         l_run = 0.f;
         m_run = -INFINITY;
 #pragma unroll
@@ -666,7 +699,10 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
             *reinterpret_cast<float4*>(dst + 4) = make_float4(o[hh][4][b], o[hh][5][b], o[hh][6][b], o[hh][7][b]);
         }
     __syncthreads();
-    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(d.out) + ((int64_t)i * d.n_q_heads + h * G) * kMmaD;
+    // The partials go into the workspace that the previous step's merge kernel may still be reading: this is
+    // the first point that has to wait for it.
+    if (late_wait) pdl_wait();
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(d.out) + (int64_t)i * d.out_stride + (int64_t)h * G * kMmaD;
     for (int idx = threadIdx.x; idx < G * kMmaD; idx += kDecodeThreads) {
         const int r = idx >> 7, dd = idx & 127;
         float M = -INFINITY;
@@ -741,6 +777,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(DecodeLaunch
     }
 }
 
+const StepRows& empty_rows() {
+    static const StepRows r{};
+    return r;
+}
+
 template <int NS, bool FA>
 cudaError_t launch_tma(const DecodeLaunch& d, cudaStream_t stream) {
     static bool configured[64] = {};
@@ -755,31 +796,66 @@ cudaError_t launch_tma(const DecodeLaunch& d, cudaStream_t stream) {
     }
     dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
     return launch_pdl(decode_tma_kernel<NS, FA>, grid, dim3(kDecodeThreads), (size_t)smem, stream, d,
-                      *reinterpret_cast<const CUtensorMap*>(d.k_map), *reinterpret_cast<const CUtensorMap*>(d.v_map));
+                      *reinterpret_cast<const CUtensorMap*>(d.k_map), *reinterpret_cast<const CUtensorMap*>(d.v_map),
+                      d.rows ? *d.rows : empty_rows());
+}
+
+// ---------------------------------------------------------------------------------------------
+// Self-validating 16-byte words for the exchange between GPUs: {payload0, epoch, payload1, epoch}.  Each 8-byte
+// half is a naturally aligned unit that arrives whole, so a reader that sees the call's epoch beside a payload word
+// has that word; nothing else (fence, ticket, flag) orders the two sides.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_word(void* p, uint32_t d0, uint32_t d1, uint32_t epoch) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(epoch), "r"(d1), "r"(epoch) : "memory");
+}
+// Bounded (about a second of SM clocks) wait for one word of this call's epoch.
+__device__ __forceinline__ bool poll_word(const void* p, uint32_t epoch, uint32_t& d0, uint32_t& d1) {
+    const long long start = clock64();
+    for (;;) {
+        uint32_t x, y, z, w;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(p) : "memory");
+        if (y == epoch && w == epoch) {
+            d0 = x;
+            d1 = z;
+            return true;
+        }
+        if (clock64() - start > 2000000000LL) return false;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
 // K3r: merge the partials of one (sequence, query head) with the reference's chunk-merge rule and
-// write out = wv / max(s, eps) in the storage dtype.  grid (n_q_heads, n_seqs).
+// write out = wv / max(s, eps) in the storage dtype.  grid (n_q_heads, n_seqs).  The same block also runs the
+// row's share of the exchange between GPUs (ExchangeView) and, for a one-call step, writes the rotated q back and
+// sets the sequence's device length.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
+__global__ void __launch_bounds__(128) decode_reduce_kernel(const __grid_constant__ DecodeLaunch d,
+                                                            const __grid_constant__ StepRows rows) {
     const PoolView& pv = d.pool;
     const int hq = blockIdx.x, i = blockIdx.y;
     pdl_wait();
-    // The next kernel in the stream (the following step's split-K kernel, or the gather wait) starts with a
-    // wait of its own for this grid's completion: letting it launch now hides its launch latency.
+    // The next kernel in the stream (the following step's split-K kernel) either waits for this grid at its top or
+    // touches nothing this grid reads or writes until it does: letting it launch now hides its launch latency and,
+    // in the second case, its whole K/V stream.
     pdl_launch_dependents();
-    const int seq = d.seq_ids ? d.seq_ids[i] : i;
     const int D = pv.head_dim;
-    T* out = reinterpret_cast<T*>(d.out) + ((int64_t)i * d.n_q_heads + hq) * D;
-    int n_attend = 0;
-    if (seq >= 0 && seq < pv.max_seqs) n_attend = attend_count(d, i, seq) + (d.fused_append ? 1 : 0);
+    int seq, n_attend = 0;
+    uint32_t pos_raw = 0;
+    if (d.fused_append) {
+        seq = row_seq(rows, d.n_seqs, i);
+        pos_raw = row_pos(rows, d.n_seqs, i);
+        n_attend = row_len(rows, d.n_seqs, i) + ((pos_raw & kRowNoStore) ? 0 : 1);
+    } else {
+        seq = d.seq_ids ? d.seq_ids[i] : i;
+        if (seq >= 0 && seq < pv.max_seqs) n_attend = attend_count(d, i, seq);
+    }
     const int n_splits = (n_attend + d.chunk_tokens - 1) / d.chunk_tokens;   // <= 128 by the plan
     const int64_t base = ((int64_t)i * d.n_q_heads + hq) * d.max_splits;
     // one thread per split fetches (m, l): the loads of all splits are in flight together
-    __shared__ float sm_m[128], sm_w[128];
+    __shared__ float sm_w[128];
     __shared__ float sm_red[8];
+    __shared__ __align__(16) uint32_t sm_row[260];   // the finished row (storage dtype) or the partial row (float bits)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float m = -INFINITY, l = 0.f;
     if (tid < n_splits) {
@@ -794,10 +870,7 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
     __syncthreads();
     M = fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3]));
     const float w = l > 0.f ? expf(m - M) : 0.f;
-    if (tid < 128) {
-        sm_w[tid] = w;
-        sm_m[tid] = w * l;
-    }
+    sm_w[tid] = w;
     float L = w * l;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
@@ -805,6 +878,8 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
     __syncthreads();
     L = (sm_red[4] + sm_red[5]) + (sm_red[6] + sm_red[7]);
     const float inv = 1.0f / fmaxf(L, d.eps);
+    const int mode = d.xchg.mode;
+    T* out = reinterpret_cast<T*>(d.out) + (int64_t)i * d.out_stride + (int64_t)hq * D;
     for (int dd = tid; dd < D; dd += blockDim.x) {
         float a = 0.f;
         for (int s0 = 0; s0 < n_splits; s0 += 8) {   // eight independent loads per thread in flight
@@ -814,31 +889,32 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) a += (s0 + j < n_splits ? sm_w[s0 + j] : 0.f) * v[j];
         }
-        if (d.partial_out) {   // un-normalised partial for a cross-rank merge: (acc, m, l) relative to M
+        if (d.partial_out) {   // un-normalised partial for a merge done elsewhere: (acc, m, l) relative to M
             float* prow = d.partial_out + ((int64_t)i * d.n_q_heads + hq) * (D + 2);
             prow[dd] = a;
             if (dd == 0) {
                 prow[D] = M;
                 prow[D + 1] = L;
             }
-            continue;
-        }
-        const T val = from_f32<T>(a * inv);
-        if (d.gather.world == 0) {
-            out[dd] = val;
-        } else {   // the same row into every rank's gathered buffer, slot [rank][i][hq]
-            const int64_t off = (((int64_t)d.gather.rank * d.n_seqs + i) * d.n_q_heads + hq) * D + dd;
-#pragma unroll 1
-            for (int r = 0; r < d.gather.world; ++r) reinterpret_cast<T*>(d.gather.out[r])[off] = val;
+        } else if (mode == 0) {
+            out[dd] = from_f32<T>(a * inv);
+        } else if (mode == 1) {
+            reinterpret_cast<T*>(sm_row)[dd] = from_f32<T>(a * inv);
+        } else {
+            sm_row[dd] = __float_as_uint(a);
+            if (dd == 0) {
+                sm_row[D] = __float_as_uint(M);
+                sm_row[D + 1] = __float_as_uint(L);
+            }
         }
     }
-    if (d.fused_append) {
+    if (d.fused_append && seq >= 0 && seq < pv.max_seqs) {
         // The decode CTAs worked on their own rotated copies of q: write the rotated row back (the step's
-        // contract), then let the block that arrives last count this step's token into the device lengths --
-        // every block has read the old length by then.
-        if (tid < D / 2 && seq >= 0 && seq < pv.max_seqs) {
-            T* qrow = reinterpret_cast<T*>(const_cast<void*>(d.q)) + ((int64_t)i * d.n_q_heads + hq) * D;
-            float fpos = (float)(n_attend - 1);
+        // contract).  Every CTA of the split-K kernel has finished, and nothing reads the device length of a row
+        // during a step (the kernels take it from `rows`), so one block per sequence can set it here.
+        if (tid < D / 2) {
+            T* qrow = reinterpret_cast<T*>(const_cast<void*>(d.q)) + (int64_t)i * d.q_stride + (int64_t)hq * D;
+            float fpos = (float)(pos_raw & ~kRowNoStore);
             if (d.rope_scaling != 1.0f) fpos = __fdiv_rn(fpos, d.rope_scaling);
             float sn, cs;
             sincosf(__fmul_rn(fpos, d.inv_freq[tid]), &sn, &cs);
@@ -846,54 +922,88 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeLaunch d) {
             qrow[tid] = from_f32<T>(__fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn)));
             qrow[tid + D / 2] = from_f32<T>(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn)));
         }
-        __shared__ int s_last;
-        __syncthreads();
-        if (tid == 0) {
-            const int n_blocks = (int)(gridDim.x * gridDim.y);
-            const int t = atomicAdd(d.append_ticket, 1);
-            s_last = (t == n_blocks - 1);
-            if (s_last) *d.append_ticket = 0;
-        }
-        __syncthreads();
-        if (s_last)
-            for (int s2 = tid; s2 < d.n_seqs; s2 += blockDim.x) {
-                const int sq = d.seq_ids ? d.seq_ids[s2] : s2;     // distinct by the host's check
-                if (sq >= 0 && sq < pv.max_seqs) pv.lengths[(int64_t)d.layer * pv.max_seqs + sq] += 1;
-            }
+        if (hq == 0 && tid == 0 && !(pos_raw & kRowNoStore)) pv.lengths[(int64_t)d.layer * pv.max_seqs + seq] = n_attend;
     }
-    if (d.gather.world > 0) {
-        __shared__ int s_wait;
-        if (tid == 0) s_wait = 0;
-        // When the last merge block has stored its rows, tell every rank (itself included) that this rank's
-        // slice of epoch `epoch` has landed.  fence -> ticket -> fence -> flag keeps the rows ahead of the flag.
-        __threadfence_system();
-        __syncthreads();
-        if (tid == 0) {
-            const int n_blocks = (int)(gridDim.x * gridDim.y);
-            if (atomicAdd(d.gather.ticket, 1) == n_blocks - 1) {
-                *d.gather.ticket = 0;
-                __threadfence_system();
-                for (int r = 0; r < d.gather.world; ++r)
-                    *reinterpret_cast<volatile int32_t*>(d.gather.flags[r] + d.gather.rank) = d.gather.epoch;
-                s_wait = d.gather.wait_flags != nullptr;
+    if (mode == 0) return;
+
+    // ---- exchange between GPUs --------------------------------------------------------------------------------
+    const uint32_t ep = d.xchg.epoch;
+    const int world = d.xchg.world, rank = d.xchg.rank;
+    const int W = (D * (int)sizeof(T)) >> 3;                       // 16-byte words of a finished row
+    const int64_t row = (int64_t)i * d.n_q_heads + hq;
+    const int64_t n_rows = (int64_t)d.n_seqs * d.n_q_heads;
+    bool ok = true;
+    __syncthreads();                                               // sm_row is complete
+    if (mode == 1) {
+        // finished row -> slot `rank` of every rank's buffer [world][n_rows][W]
+        for (int task = tid; task < W * world; task += 128) {
+            const int wd = task % W, p = task / W;
+            uint4* dst = reinterpret_cast<uint4*>(d.xchg.recv[p]) + ((int64_t)rank * n_rows + row) * W + wd;
+            st_word(dst, sm_row[2 * wd], sm_row[2 * wd + 1], ep);
+        }
+        // the same row of every rank's slot in this rank's buffer -> out[world][n_seqs][q_heads][D]
+        for (int task = tid; task < W * world && ok; task += 128) {
+            const int wd = task % W, s = task / W;
+            const uint4* src = reinterpret_cast<const uint4*>(d.xchg.recv[rank]) + ((int64_t)s * n_rows + row) * W + wd;
+            uint32_t d0 = 0, d1 = 0;
+            ok = poll_word(src, ep, d0, d1);
+            uint2* o = reinterpret_cast<uint2*>(reinterpret_cast<T*>(d.xchg.out) + ((int64_t)s * n_rows + row) * D) + wd;
+            *o = make_uint2(d0, d1);
+        }
+    } else {
+        // Buffer of a rank: region A [world][rows_owned][Wp] receives the partial rows this rank owns (row % world
+        // == rank, slot row / world); region B [n_rows][W] receives every finished row from its owner.
+        const int Wp = (D + 2) >> 1;
+        const int64_t rows_owned = (n_rows + world - 1) / world;
+        const int owner = (int)(row % world);
+        const int64_t slot = row / world;
+        const int64_t b_off = (int64_t)world * rows_owned * Wp;    // in 16-byte words
+        for (int wd = tid; wd < Wp; wd += 128) {
+            uint4* dst = reinterpret_cast<uint4*>(d.xchg.recv[owner]) + ((int64_t)rank * rows_owned + slot) * Wp + wd;
+            st_word(dst, sm_row[2 * wd], sm_row[2 * wd + 1], ep);
+        }
+        if (rank == owner) {
+            __shared__ float sm_part[8][260];
+            for (int task = tid; task < Wp * world && ok; task += 128) {
+                const int wd = task % Wp, s = task / Wp;
+                const uint4* src = reinterpret_cast<const uint4*>(d.xchg.recv[rank]) + ((int64_t)s * rows_owned + slot) * Wp + wd;
+                uint32_t d0 = 0, d1 = 0;
+                ok = poll_word(src, ep, d0, d1);
+                sm_part[s][2 * wd] = __uint_as_float(d0);
+                sm_part[s][2 * wd + 1] = __uint_as_float(d1);
+            }
+            __syncthreads();
+            // the chunk-merge rule across ranks (mlx_ops.py:125-146), every thread on the same eight (m, l) pairs
+            float Mx = -INFINITY;
+            for (int s = 0; s < world; ++s)
+                if (sm_part[s][D + 1] > 0.f) Mx = fmaxf(Mx, sm_part[s][D]);
+            float Lx = 0.f, wr[8];
+            for (int s = 0; s < world; ++s) {
+                wr[s] = sm_part[s][D + 1] > 0.f ? expf(sm_part[s][D] - Mx) : 0.f;
+                Lx += wr[s] * sm_part[s][D + 1];
+            }
+            const float invx = 1.0f / fmaxf(Lx, d.eps);
+            for (int dd = tid; dd < D; dd += 128) {
+                float a = 0.f;
+                for (int s = 0; s < world; ++s) a += wr[s] * sm_part[s][dd];
+                reinterpret_cast<T*>(sm_row)[dd] = from_f32<T>(a * invx);
+            }
+            __syncthreads();
+            for (int task = tid; task < W * world; task += 128) {
+                const int wd = task % W, p = task / W;
+                uint4* dst = reinterpret_cast<uint4*>(d.xchg.recv[p]) + b_off + row * W + wd;
+                st_word(dst, sm_row[2 * wd], sm_row[2 * wd + 1], ep);
             }
         }
-        // The consumer's wait, folded into this kernel: the last block watches this rank's own flags (the peers'
-        // kernels on OTHER GPUs write them) for about a second at most; a timeout sets a status bit.  Work enqueued
-        // after this kernel then sees every rank's rows without a separate wait launch.
-        __syncthreads();
-        if (s_wait && tid < d.gather.world) {
-            const volatile int32_t* f = d.gather.wait_flags + tid;
-            const long long start = clock64();
-            while (*f < d.gather.epoch) {
-                if (clock64() - start > 2000000000LL) {
-                    atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
-                    break;
-                }
-            }
-            __threadfence_system();
+        T* orow = reinterpret_cast<T*>(d.xchg.out) + row * D;
+        for (int wd = tid; wd < W && ok; wd += 128) {
+            const uint4* src = reinterpret_cast<const uint4*>(d.xchg.recv[rank]) + b_off + row * W + wd;
+            uint32_t d0 = 0, d1 = 0;
+            ok = poll_word(src, ep, d0, d1);
+            reinterpret_cast<uint2*>(orow)[wd] = make_uint2(d0, d1);
         }
     }
+    if (!ok) atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
 }
 
 // Merge of partial rows (acc[D], m, l) from several key ranges of the same query rows (sequence sharding, or any
@@ -933,23 +1043,6 @@ __global__ void __launch_bounds__(128) merge_partials_kernel(const float* __rest
     }
 }
 
-// Waits (bounded, about a second) until every rank's flag has reached `epoch`; lane r watches rank r.
-__global__ void gather_wait_kernel(const int32_t* flags, int world, int epoch, int32_t* status) {
-    pdl_wait();   // launched early (programmatic dependent launch); the local merge kernel has completed from here on
-    const int r = threadIdx.x;
-    if (r < world) {
-        const volatile int32_t* f = flags + r;
-        const long long start = clock64();
-        while (*f < epoch) {
-            if (clock64() - start > 2000000000LL) {
-                if (status) atomicOr(status, FLAG_WAIT_TIMEOUT);
-                break;
-            }
-        }
-    }
-    __threadfence_system();
-}
-
 template <typename T>
 cudaError_t launch_generic(const DecodeLaunch& d, cudaStream_t stream) {
     dim3 grid((unsigned)d.max_splits, (unsigned)d.n_q_heads, (unsigned)d.n_seqs);
@@ -981,15 +1074,14 @@ void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, i
     int64_t floor_chunk = (max_ctx + splits - 1) / splits;
     int64_t chunk = total_tokens_hint > 0 ? (num_kv_heads * total_tokens_hint) / target : 0;
     if (chunk < floor_chunk) chunk = floor_chunk;
-    const char* env = getenv("SKV_DECODE_CHUNK");
-    if (env && atoi(env) > 0 && atoi(env) >= floor_chunk) chunk = atoi(env);
+    const Switches& sw = switches();
+    if (sw.chunk > 0 && sw.chunk >= floor_chunk) chunk = sw.chunk;
     chunk = ((chunk + 63) / 64) * 64;                 // 4 warps x 16-token tiles
     if (chunk < 256) chunk = 256;
     // Few CTAs: avoid a thin last wave.  With 3 CTAs per SM a wave is 444 CTAs; when the estimate (tokens / chunk
     // plus half a CTA of rounding per sequence and head) lands a little above one or two waves, grow the chunk
     // until it fits (measured: 4 sequences x 96k tokens x 1 head went from 512 CTAs of 768 tokens to 440 of 896).
-    const char* wq = getenv("SKV_PLAN_WAVES");       // "0": keep the chunk as computed above
-    if (total_tokens_hint > 0 && !(env && atoi(env) > 0) && !(wq && wq[0] == '0')) {
+    if (total_tokens_hint > 0 && sw.chunk <= 0 && sw.plan_waves) {   // SKV_PLAN_WAVES=0 keeps the chunk as computed above
         const double wave = 444.0, round_up = 0.5 * (double)n_seqs * num_kv_heads;
         const double work = (double)total_tokens_hint * num_kv_heads;
         const double est = work / (double)chunk + round_up;
@@ -1011,28 +1103,27 @@ void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, i
 
 cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     DecodeLaunch d = d_in;
-    const char* fuse = getenv("SKV_DECODE_FUSE");
+    const Switches& sw = switches();
     // Measured on B200: the in-kernel merge (last-arriving CTA) costs about 2 us more per call than the
     // separate merge launch at the full 64-sequence workload and at a quarter of it (device-wide fences in
     // every CTA plus a serial tail), but saves about 5 us at an eighth of it, where the call is latency-bound.
     // So it is chosen only for small calls; SKV_DECODE_FUSE=0/1 overrides.
     d.fuse_merge = d.total_tokens * d.pool.num_kv_heads < 400000 ? 1 : 0;
     // the gather, the partial output and the fused append's bookkeeping live in the merge kernel
-    const bool needs_merge_kernel = d.gather.world > 0 || d.partial_out || d.fused_append;
+    const bool needs_merge_kernel = d.xchg.mode != 0 || d.partial_out || d.fused_append;
     if (needs_merge_kernel) d.fuse_merge = 0;
-    if (fuse && (fuse[0] == '0' || fuse[0] == '1') && !needs_merge_kernel) d.fuse_merge = fuse[0] == '1';
+    if (sw.fuse >= 0 && !needs_merge_kernel) d.fuse_merge = sw.fuse;
     const int G = d.n_q_heads / d.pool.num_kv_heads;
     const bool mma_ok = d.dtype == SKV_BF16 && d.pool.head_dim == kMmaD && d.pool.page_size % 16 == 0 && G <= 8 &&
-                        !d.force_generic && ((uintptr_t)d.q % 16 == 0);
-    if (d.max_splits > 128) return cudaErrorInvalidValue;   // the merge kernel handles one split per thread
+                        !d.force_generic && ((uintptr_t)d.q % 16 == 0) && (d.q_stride * 2) % 16 == 0;
+    if (d.max_splits > 128) return cudaErrorInvalidValue;   // the merge kernel handles one split per thread; skv_create rejects such pools
     cudaError_t e;
-    const char* impl = getenv("SKV_DECODE_IMPL");   // "reg": direct-to-register loads; default: TMA ring when maps exist
-    const bool tma_ok = mma_ok && d.k_map && d.v_map && (d.fused_append || !(impl && impl[0] == 'r'));
-    if (d.fused_append && (!tma_ok || d.q_pos || !d.new_k || !d.new_v || !d.inv_freq || !d.append_ticket))
+    // SKV_DECODE_IMPL=reg: direct-to-register loads; default: the TMA ring when the pool has tensor maps
+    const bool tma_ok = mma_ok && d.k_map && d.v_map && (d.fused_append || !sw.impl_reg) && (d.q_stride * 2) % 16 == 0;
+    if (d.fused_append && (!tma_ok || d.q_pos || !d.new_k || !d.new_v || !d.inv_freq || !d.rows))
         return cudaErrorInvalidValue;   // only the TMA kernel implements it; callers check the conditions first
     if (tma_ok) {
-        const char* st = getenv("SKV_DECODE_STAGES");
-        const int ns = st ? atoi(st) : 2;   // 2 stages -> 3 CTAs per SM (24 stages of 8 KB in flight), the measured best
+        const int ns = sw.stages;   // 2 stages -> 3 CTAs per SM (24 stages of 8 KB in flight), the measured best
         if (d.fused_append)
             e = launch_tma<2, true>(d, stream);
         else
@@ -1054,8 +1145,9 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
     count_launches(2);
     dim3 rgrid((unsigned)d.n_q_heads, (unsigned)d.n_seqs);
     const int threads = 128;
-    return d.dtype == SKV_BF16 ? launch_pdl(decode_reduce_kernel<__nv_bfloat16>, rgrid, dim3(threads), 0, stream, d)
-                               : launch_pdl(decode_reduce_kernel<float>, rgrid, dim3(threads), 0, stream, d);
+    const StepRows& rows = d.rows ? *d.rows : empty_rows();
+    return d.dtype == SKV_BF16 ? launch_pdl(decode_reduce_kernel<__nv_bfloat16>, rgrid, dim3(threads), 0, stream, d, rows)
+                               : launch_pdl(decode_reduce_kernel<float>, rgrid, dim3(threads), 0, stream, d, rows);
 }
 
 cudaError_t launch_merge_partials(const float* parts, int32_t n_parts, int64_t part_stride, int32_t n_rows, int32_t head_dim,
@@ -1068,12 +1160,6 @@ cudaError_t launch_merge_partials(const float* parts, int32_t n_parts, int64_t p
                                                                reinterpret_cast<float*>(out));
     count_launches(1);
     return cudaGetLastError();
-}
-
-cudaError_t launch_gather_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, cudaStream_t stream) {
-    cudaError_t e = launch_pdl(gather_wait_kernel, dim3(1), dim3(32), 0, stream, flags, (int)world, (int)epoch, status);
-    count_launches(1);
-    return e;
 }
 
 }  // namespace skv

@@ -611,7 +611,7 @@ cudaError_t launch_attn_tc(const DenseAttnLaunch& a, cudaStream_t stream) {
     TcParams p{};
     p.positions = a.positions;
     p.out = a.out;
-    p.status = paged ? a.pool.status : nullptr;
+    p.status = paged ? a.pool.status : a.status;
     p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk; p.causal = a.causal;
     p.eps = a.eps;
     p.pool = a.pool;

@@ -18,11 +18,57 @@
 #include "tma.cuh"
 
 #include <atomic>
+#include <mutex>
 
 using namespace skv;
 
 static std::atomic<long long> g_launches{0};
 void skv::count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+std::mutex g_switch_mutex;
+skv::Switches g_switches;
+std::atomic<bool> g_switches_ready{false};
+
+int env_int(const char* name, int unset) {
+    const char* e = getenv(name);
+    return (e && *e) ? atoi(e) : unset;
+}
+bool env_is(const char* name, char c) {
+    const char* e = getenv(name);
+    return e && e[0] == c;
+}
+void read_switches() {
+    skv::Switches w{};
+    w.step_fused = !env_is("SKV_STEP_FUSED", '0');
+    w.decode_generic = env_is("SKV_DECODE_GENERIC", '1');
+    w.impl_reg = env_is("SKV_DECODE_IMPL", 'r');
+    w.stages = env_int("SKV_DECODE_STAGES", 2);
+    w.chunk = env_int("SKV_DECODE_CHUNK", 0);
+    w.plan_waves = !env_is("SKV_PLAN_WAVES", '0');
+    w.fuse = env_is("SKV_DECODE_FUSE", '0') ? 0 : (env_is("SKV_DECODE_FUSE", '1') ? 1 : -1);
+    w.prefill_generic = env_is("SKV_PREFILL_GENERIC", '1');
+    w.append_scalar = env_is("SKV_APPEND_SCALAR", '1');
+    w.pdl = !env_is("SKV_PDL", '0');
+    g_switches = w;
+}
+}  // namespace
+
+const skv::Switches& skv::switches() {
+    if (!g_switches_ready.load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(g_switch_mutex);
+        if (!g_switches_ready.load(std::memory_order_relaxed)) {
+            read_switches();
+            g_switches_ready.store(true, std::memory_order_release);
+        }
+    }
+    return g_switches;
+}
+void skv::reload_switches() {
+    std::lock_guard<std::mutex> lock(g_switch_mutex);
+    read_switches();
+    g_switches_ready.store(true, std::memory_order_release);
+}
 
 namespace {
 
@@ -129,6 +175,21 @@ struct skv_pool {
     cudaEvent_t ev_compute = nullptr, ev_copy = nullptr;
     bool copy_pending = false;           // copies enqueued on copy_stream not yet ordered before compute
     std::vector<TableUpdate> deferred_updates;   // page-table entries to publish once prefetch copies are ordered
+
+    // scratch of the one-call decode step, kept between calls so that a step allocates nothing on the host
+    std::vector<TableUpdate> step_ups;
+    std::vector<uint32_t> seen_stamp;            // [max_seqs] generation stamps for the duplicate check
+    uint32_t stamp = 0;
+    std::vector<int32_t> step_store;             // [n_seqs] 0/1: the row's token is stored by this pool
+    StepRows rows{};
+    // What this pool's last step wrote besides pages and partials (the rotated q rows, the output), on which stream,
+    // and the library-wide launch count right after it: a following step may start early only when it comes
+    // directly after it and reads none of that.
+    bool last_step_valid = false;
+    cudaStream_t last_step_stream = nullptr;
+    long long last_step_mark = 0;
+    const char* last_w_lo[2] = {nullptr, nullptr};
+    const char* last_w_hi[2] = {nullptr, nullptr};
 
     std::string err;
 
@@ -324,6 +385,8 @@ extern "C" {
 
 int32_t skv_abi_version(void) { return SKV_ABI_VERSION; }
 
+void skv_reload_env(void) { reload_switches(); }
+
 int64_t skv_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 
 const char* skv_status_string(int32_t s) {
@@ -354,6 +417,14 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
     skv_pool* p = new (std::nothrow) skv_pool();
     if (!p) return SKV_ERR_BAD_ARG;
     p->cfg = *cfg;
+    if ((int64_t)cfg->max_pages_per_seq * cfg->page_size > SKV_MAX_TOKENS_PER_SEQ) {
+        // the split-K plan gives one sequence at most 128 chunks of 2048 tokens (a warp keeps 32 tile page ids, the
+        // merge kernel takes one chunk per thread); a longer row would make every decode call fail at launch
+        *out = p;
+        p->host_only = true;
+        return p->fail(SKV_ERR_UNSUPPORTED, "max_pages_per_seq * page_size = %lld exceeds %d tokens per sequence",
+                       (long long)cfg->max_pages_per_seq * cfg->page_size, SKV_MAX_TOKENS_PER_SEQ);
+    }
     p->host_only = cfg->device < 0;
     p->esize = dtype_size(cfg->dtype);
     p->page_bytes = (size_t)cfg->num_kv_heads * cfg->page_size * cfg->head_dim * p->esize;
@@ -363,6 +434,7 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
     p->lengths.assign((size_t)cfg->num_layers * cfg->max_seqs, 0);
     p->live.assign(cfg->max_seqs, 0);
     p->page_owner.assign(cfg->num_pages, -1);
+    p->seen_stamp.assign(cfg->max_seqs, 0);
     for (int32_t i = cfg->num_pages - 1; i >= 0; --i) p->free_pages.push_back(i);
     for (int32_t i = cfg->max_seqs - 1; i >= 0; --i) p->free_seqs.push_back(i);
     for (int32_t i = cfg->host_pages - 1; i >= 0; --i) p->free_host.push_back(i);
@@ -443,7 +515,8 @@ int32_t skv_alloc_sequence(skv_pool* p, int32_t* seq_out) {
     return SKV_OK;
 }
 
-int32_t skv_free_sequence(skv_pool* p, int32_t seq) {
+int32_t skv_free_sequence(skv_pool* p, int32_t seq, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
     if (!p) return SKV_ERR_BAD_ARG;
     if (!valid_seq(p, seq)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", seq);
     std::vector<TableUpdate> ups;
@@ -471,12 +544,12 @@ int32_t skv_free_sequence(skv_pool* p, int32_t seq) {
                                              [&](const TableUpdate& u) { return u.seq == seq; }),
                               p->deferred_updates.end());
     DeviceGuard g(p);
-    int32_t st = publish_table_updates(p, ups, nullptr);
+    int32_t st = publish_table_updates(p, ups, stream);
     if (st != SKV_OK) return st;
-    return publish_length_updates(p, lups, nullptr);
+    return publish_length_updates(p, lups, stream);
 }
 
-int32_t skv_reserve(skv_pool* p, int32_t seq, int32_t total_tokens) {
+int32_t skv_reserve(skv_pool* p, int32_t seq, int32_t total_tokens, void* stream_) {
     if (!p) return SKV_ERR_BAD_ARG;
     if (!valid_seq(p, seq)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", seq);
     if (total_tokens < 0) return p->fail(SKV_ERR_BAD_ARG, "total_tokens must be non-negative");
@@ -484,10 +557,11 @@ int32_t skv_reserve(skv_pool* p, int32_t seq, int32_t total_tokens) {
     int32_t st = grow(p, seq, total_tokens, &ups);
     if (st != SKV_OK) return st;
     DeviceGuard g(p);
-    return publish_table_updates(p, ups, nullptr);
+    return publish_table_updates(p, ups, (cudaStream_t)stream_);
 }
 
-int32_t skv_set_page_table(skv_pool* p, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t length) {
+int32_t skv_set_page_table(skv_pool* p, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t length, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
     if (!p || (!pages && n_pages > 0)) return SKV_ERR_BAD_ARG;
     if (!valid_seq(p, seq)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", seq);
     if (n_pages < 0 || n_pages > p->cfg.max_pages_per_seq)
@@ -522,9 +596,9 @@ int32_t skv_set_page_table(skv_pool* p, int32_t seq, const int32_t* pages, int32
         lups.push_back({l * p->cfg.max_seqs + seq, length});
     }
     DeviceGuard g(p);
-    int32_t st = publish_table_updates(p, ups, nullptr);
+    int32_t st = publish_table_updates(p, ups, stream);
     if (st != SKV_OK) return st;
-    return publish_length_updates(p, lups, nullptr);
+    return publish_length_updates(p, lups, stream);
 }
 
 int32_t skv_truncate(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, int32_t new_length, void* stream_) {
@@ -804,6 +878,7 @@ int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32
     if (!q || !out) return p->fail(SKV_ERR_BAD_ARG, "q and out must be given");
     int32_t st = order_transfers(p, stream);
     if (st != SKV_OK) return st;
+    p->last_step_valid = false;
     d->pool = p->view();
     d->layer = layer;
     d->n_seqs = n_seqs;
@@ -815,8 +890,9 @@ int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32
     if (st != SKV_OK) return st;
     d->q = q;
     d->out = out;
+    d->q_stride = d->out_stride = (int64_t)n_q_heads * p->cfg.head_dim;
     d->eps = eps;
-    d->force_generic = 0;
+    d->force_generic = switches().decode_generic;
     d->k_map = p->has_maps ? &p->k_map : nullptr;
     d->v_map = p->has_maps ? &p->v_map : nullptr;
     d->tickets = p->d_tickets;
@@ -825,6 +901,94 @@ int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32
 }
 
 }  // namespace skv
+
+namespace {
+
+// 16-byte words of one parity half of an exchange buffer (see ExchangeView).
+size_t exchange_words(int32_t mode, int32_t world, int64_t n_rows, int32_t head_dim, size_t esize) {
+    const size_t W = (size_t)head_dim * esize / 8;
+    if (mode == SKV_XCHG_HEAD_GATHER) return (size_t)world * n_rows * W;
+    const size_t Wp = ((size_t)head_dim + 2) / 2;
+    const size_t rows_owned = ((size_t)n_rows + world - 1) / world;
+    return (size_t)world * rows_owned * Wp + (size_t)n_rows * W;
+}
+
+int32_t fill_exchange(skv_pool* p, const skv_exchange* x, int32_t n_seqs, int32_t n_q_heads, ExchangeView* v) {
+    if (x->mode != SKV_XCHG_HEAD_GATHER && x->mode != SKV_XCHG_SEQ_MERGE)
+        return p->fail(SKV_ERR_BAD_ARG, "exchange mode %d is neither head gather nor sequence merge", x->mode);
+    if (x->world < 1 || x->world > 8 || x->rank < 0 || x->rank >= x->world || !x->recv_ptrs || !x->out)
+        return p->fail(SKV_ERR_BAD_ARG, "exchange needs 1 <= world <= 8, a rank inside it, the receive pointers and out");
+    if (x->epoch == 0) return p->fail(SKV_ERR_BAD_ARG, "exchange epochs start at 1");
+    if (((size_t)p->cfg.head_dim * p->esize) % 8 != 0)
+        return p->fail(SKV_ERR_UNSUPPORTED, "the exchange needs head_dim * element size to be a multiple of 8 bytes");
+    if ((uintptr_t)x->out % 16 != 0) return p->fail(SKV_ERR_BAD_ARG, "exchange out must be 16-byte aligned");
+    const size_t half = exchange_words(x->mode, x->world, (int64_t)n_seqs * n_q_heads, p->cfg.head_dim, p->esize) * 16;
+    v->mode = x->mode;
+    v->world = x->world;
+    v->rank = x->rank;
+    v->epoch = x->epoch;
+    v->out = x->out;
+    for (int32_t r = 0; r < x->world; ++r) {
+        if (!x->recv_ptrs[r] || (uintptr_t)x->recv_ptrs[r] % 16 != 0)
+            return p->fail(SKV_ERR_BAD_ARG, "receive pointer %d is null or not 16-byte aligned", r);
+        v->recv[r] = (char*)x->recv_ptrs[r] + (size_t)(x->epoch & 1u) * half;
+    }
+    return SKV_OK;
+}
+
+int32_t check_workspace(skv_pool* p, const void* workspace, size_t workspace_bytes, size_t need) {
+    if (!workspace || workspace_bytes < need)
+        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need);
+    if ((uintptr_t)workspace % 16 != 0) return p->fail(SKV_ERR_BAD_ARG, "workspace must be 16-byte aligned");
+    return SKV_OK;
+}
+
+// Decode attention over what the pool holds: the shared body of skv_decode_attn, skv_decode_attn_xchg and
+// skv_decode_partial, and the second half of a step that cannot take the one-kernel form.
+int32_t attn_impl(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q, int64_t q_stride,
+                  void* out, int64_t out_stride, const int32_t* q_pos, int32_t n_q_heads, float eps, void* workspace,
+                  size_t workspace_bytes, const skv_exchange* xchg, float* partial_out, cudaStream_t stream) {
+    // a misaligned workspace is refused whatever else the call would do (the merge kernel reads it with 8- and
+    // 16-byte loads), bookkeeping-only pools included
+    if (workspace && (uintptr_t)workspace % 16 != 0) return p->fail(SKV_ERR_BAD_ARG, "workspace must be 16-byte aligned");
+    DeviceGuard guard(p);
+    DecodeLaunch D{};
+    int64_t total = 0;
+    int32_t launchable = 0;
+    // `q` doubles as the non-null output argument of the shared front half when the result goes elsewhere
+    void* out_arg = out ? out : const_cast<void*>(q);
+    if (!p->host_only && !out && !xchg && !partial_out) return p->fail(SKV_ERR_BAD_ARG, "q and out must be given");
+    if (!p->host_only) {   // argument checks that must not depend on what the front half enqueues
+        if (n_q_heads > 0 && n_seqs > 0 && n_seqs <= p->cfg.max_seqs) {
+            int32_t chunk = 0, splits = 0;
+            decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, 0, &chunk, &splits);
+            const size_t least = (size_t)n_seqs * n_q_heads * 1 * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
+            int32_t st0 = check_workspace(p, workspace, workspace_bytes, least);
+            if (st0 != SKV_OK) return st0;
+        }
+    }
+    int32_t st = prepare_decode(p, layer, seq_ids, n_seqs, q_pos, n_q_heads, q, out_arg, eps, stream, &D, &total, &launchable);
+    if (st != SKV_OK || !launchable) return st;
+    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
+    const size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
+    st = check_workspace(p, workspace, workspace_bytes, need);
+    if (st != SKV_OK) return st;
+    D.ws_acc = (float*)workspace;
+    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
+    D.total_tokens = total;
+    D.out = out;
+    if (q_stride) D.q_stride = q_stride;
+    if (out_stride) D.out_stride = out_stride;
+    D.partial_out = partial_out;
+    if (xchg) {
+        st = fill_exchange(p, xchg, n_seqs, n_q_heads, &D.xchg);
+        if (st != SKV_OK) return st;
+    }
+    CUDA_TRY(p, launch_decode(D, stream));
+    return SKV_OK;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -836,115 +1000,36 @@ size_t skv_decode_workspace_bytes(const skv_pool* p, int32_t n_seqs, int32_t n_q
     return (size_t)n_seqs * n_q_heads * splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
 }
 
-int32_t skv_decode_attn(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q, void* out,
-                        const int32_t* q_pos, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
-                        void* stream_) {
-    if (!p) return SKV_ERR_BAD_ARG;
-    cudaStream_t stream = (cudaStream_t)stream_;
-    if (n_q_heads <= 0 || n_q_heads % p->cfg.num_kv_heads != 0)
-        return p->fail(SKV_ERR_BAD_ARG, "query heads must be divisible by key/value heads");
-    std::vector<int32_t> upto;
-    if (q_pos) {
-        upto.resize(n_seqs > 0 ? n_seqs : 0);
-        for (int32_t i = 0; i < n_seqs; ++i) upto[i] = std::max(0, q_pos[i] + 1);
-    }
-    int32_t st = check_readable(p, layer, seq_ids, n_seqs, q_pos ? upto.data() : nullptr);
-    if (st != SKV_OK) return st;
-    if (p->host_only) return SKV_OK;
-    if (!q || !out) return p->fail(SKV_ERR_BAD_ARG, "q and out must be given");
-    int64_t total = 0;
-    for (int32_t i = 0; i < n_seqs; ++i) total += p->len(layer, seq_ids ? seq_ids[i] : i);
-    DecodeLaunch D{};
-    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
-    size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
-    if (!workspace || workspace_bytes < need)
-        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need);
-    DeviceGuard g(p);
-    st = order_transfers(p, stream);
-    if (st != SKV_OK) return st;
-    D.pool = p->view();
-    D.layer = layer;
-    D.n_seqs = n_seqs;
-    D.n_q_heads = n_q_heads;
-    D.dtype = p->cfg.dtype;
-    st = upload_ids(p, seq_ids, n_seqs, stream, &D.seq_ids);
-    if (st != SKV_OK) return st;
-    st = upload_ids(p, q_pos, n_seqs, stream, &D.q_pos);
-    if (st != SKV_OK) return st;
-    D.q = q;
-    D.out = out;
-    D.eps = eps;
-    D.ws_acc = (float*)workspace;
-    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
-    const char* force = getenv("SKV_DECODE_GENERIC");
-    D.force_generic = (force && force[0] == '1') ? 1 : 0;
-    D.k_map = p->has_maps ? &p->k_map : nullptr;
-    D.v_map = p->has_maps ? &p->v_map : nullptr;
-    D.tickets = p->d_tickets;
-    D.total_tokens = total;
-    CUDA_TRY(p, launch_decode(D, stream));
-    return SKV_OK;
+size_t skv_exchange_bytes(int32_t mode, int32_t world, int32_t n_seqs, int32_t n_q_heads, int32_t head_dim, int32_t dtype) {
+    if ((mode != SKV_XCHG_HEAD_GATHER && mode != SKV_XCHG_SEQ_MERGE) || world < 1 || world > 8 || n_seqs <= 0 ||
+        n_q_heads <= 0 || head_dim <= 0 || (dtype != SKV_F32 && dtype != SKV_BF16))
+        return 0;
+    return 2 * 16 * exchange_words(mode, world, (int64_t)n_seqs * n_q_heads, head_dim, dtype_size(dtype));
 }
 
-int32_t skv_decode_attn_gather(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q,
-                               const int32_t* q_pos, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
-                               const skv_peer_gather* g, void* stream_) {
-    if (!p || !g) return SKV_ERR_BAD_ARG;
-    if (g->world < 1 || g->world > 8 || g->rank < 0 || g->rank >= g->world || !g->out_ptrs || !g->flag_ptrs)
-        return p->fail(SKV_ERR_BAD_ARG, "peer gather needs 1 <= world <= 8, a rank inside it and both pointer arrays");
-    for (int32_t r = 0; r < g->world; ++r)
-        if (!g->out_ptrs[r] || !g->flag_ptrs[r]) return p->fail(SKV_ERR_BAD_ARG, "peer pointer %d is null", r);
-    cudaStream_t stream = (cudaStream_t)stream_;
-    DeviceGuard guard(p);
-    DecodeLaunch D{};
-    int64_t total = 0;
-    int32_t launchable = 0;
-    // q doubles as the non-null `out` argument of the shared front half; the merge kernel never writes it here
-    int32_t st = prepare_decode(p, layer, seq_ids, n_seqs, q_pos, n_q_heads, q, const_cast<void*>(q), eps, stream, &D, &total, &launchable);
-    if (st != SKV_OK || !launchable) return st;
-    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
-    size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
-    if (!workspace || workspace_bytes < need)
-        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need);
-    D.ws_acc = (float*)workspace;
-    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
-    D.total_tokens = total;
-    D.out = nullptr;
-    D.gather.world = g->world;
-    D.gather.rank = g->rank;
-    D.gather.epoch = g->epoch;
-    D.gather.wait_flags = g->wait_flags;   // the wait runs in the merge kernel's last block: no separate launch
-    D.gather.ticket = p->d_tickets + (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads;
-    for (int32_t r = 0; r < g->world; ++r) {
-        D.gather.out[r] = g->out_ptrs[r];
-        D.gather.flags[r] = g->flag_ptrs[r];
-    }
-    CUDA_TRY(p, launch_decode(D, stream));
-    return SKV_OK;
+int32_t skv_decode_attn(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q, void* out,
+                        const int32_t* q_pos, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+    if (!p) return SKV_ERR_BAD_ARG;
+    if (!p->host_only && (!q || !out)) return p->fail(SKV_ERR_BAD_ARG, "q and out must be given");
+    return attn_impl(p, layer, seq_ids, n_seqs, q, 0, out, 0, q_pos, n_q_heads, eps, workspace, workspace_bytes, nullptr,
+                     nullptr, (cudaStream_t)stream);
+}
+
+int32_t skv_decode_attn_xchg(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q,
+                             const int32_t* q_pos, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                             const skv_exchange* x, void* stream) {
+    if (!p || !x) return SKV_ERR_BAD_ARG;
+    return attn_impl(p, layer, seq_ids, n_seqs, q, 0, nullptr, 0, q_pos, n_q_heads, eps, workspace, workspace_bytes, x,
+                     nullptr, (cudaStream_t)stream);
 }
 
 int32_t skv_decode_partial(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, const void* q, const int32_t* q_pos,
-                           int32_t n_q_heads, void* workspace, size_t workspace_bytes, float* partial_out, void* stream_) {
+                           int32_t n_q_heads, void* workspace, size_t workspace_bytes, float* partial_out, void* stream) {
     if (!p) return SKV_ERR_BAD_ARG;
     if (!partial_out && !p->host_only) return p->fail(SKV_ERR_BAD_ARG, "partial_out must be given");
-    cudaStream_t stream = (cudaStream_t)stream_;
-    DeviceGuard guard(p);
-    DecodeLaunch D{};
-    int64_t total = 0;
-    int32_t launchable = 0;
-    int32_t st = prepare_decode(p, layer, seq_ids, n_seqs, q_pos, n_q_heads, q, partial_out, 0.f, stream, &D, &total, &launchable);
-    if (st != SKV_OK || !launchable) return st;
-    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
-    size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
-    if (!workspace || workspace_bytes < need)
-        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need);
-    D.ws_acc = (float*)workspace;
-    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
-    D.total_tokens = total;
-    D.out = nullptr;
-    D.partial_out = partial_out;
-    CUDA_TRY(p, launch_decode(D, stream));
-    return SKV_OK;
+    return attn_impl(p, layer, seq_ids, n_seqs, q, 0, nullptr, 0, q_pos, n_q_heads, 0.f, workspace, workspace_bytes, nullptr,
+                     partial_out, (cudaStream_t)stream);
 }
 
 int32_t skv_merge_partials(const float* parts, int32_t n_parts, int64_t part_stride, int32_t n_rows, int32_t head_dim, float eps,
@@ -956,204 +1041,305 @@ int32_t skv_merge_partials(const float* parts, int32_t n_parts, int64_t part_str
                ? SKV_OK : SKV_ERR_CUDA;
 }
 
-int32_t skv_gather_wait(skv_pool* p, const int32_t* local_flags, int32_t world, int32_t epoch, void* stream_) {
-    if (!p || !local_flags || world < 1 || world > 8) return SKV_ERR_BAD_ARG;
-    if (p->host_only) return SKV_OK;
-    DeviceGuard guard(p);
-    CUDA_TRY(p, launch_gather_wait(local_flags, world, epoch, p->d_status, (cudaStream_t)stream_));
-    return SKV_OK;
-}
+}  // extern "C"
 
-// One decode step as two launches: the decode kernel rotates q and the new K row itself, stores the new rows and
-// attends them from shared memory; the merge kernel writes the rotated q back and counts the token into the
-// device lengths.  Applies to the bf16 / head_dim 128 / TMA configuration; returns 0 from `applies` otherwise and
-// the caller takes the append + attention pair.  Host-side order follows skv_append: validate, reserve pages
-// all-or-nothing, then mutate.
-static bool fused_step_applies(const skv_pool* p, const void* q, int32_t n_q_heads) {
-    const char* mode = getenv("SKV_STEP_FUSED");   // "0": always the append + attention pair
-    if ((mode && mode[0] == '0') || p->host_only || !p->has_maps || !p->rope_set) return false;
+namespace {
+
+// Whether the one-kernel step (RoPE, store and attention inside the split-K kernel) covers this call; otherwise
+// the caller takes the append + attention pair.
+bool fused_step_applies(const skv_pool* p, const skv_step_args& a, int64_t q_stride) {
+    const Switches& sw = switches();
+    if (!sw.step_fused || p->host_only || !p->has_maps || !p->rope_set) return false;
     if (p->cfg.dtype != SKV_BF16 || p->cfg.head_dim != 128 || p->cfg.page_size % 16 != 0) return false;
-    if (n_q_heads <= 0 || n_q_heads % p->cfg.num_kv_heads != 0 || n_q_heads / p->cfg.num_kv_heads > 8) return false;
-    const char* force = getenv("SKV_DECODE_GENERIC");
-    const char* impl = getenv("SKV_DECODE_IMPL");
-    if ((force && force[0] == '1') || (impl && impl[0] == 'r')) return false;
-    return (uintptr_t)q % 16 == 0;
+    if (a.n_q_heads <= 0 || a.n_q_heads % p->cfg.num_kv_heads != 0 || a.n_q_heads / p->cfg.num_kv_heads > 8) return false;
+    if (sw.decode_generic || sw.impl_reg) return false;
+    return (uintptr_t)a.q % 16 == 0 && (q_stride * 2) % 16 == 0;
 }
 
-static int32_t fused_step(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* q, const void* k, const void* v,
-                          void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
-                          const skv_peer_gather* g, cudaStream_t stream) {
+bool overlaps(const char* lo, const char* hi, const char* a, const char* b) { return lo && a < hi && lo < b; }
+
+// Undo of grow(): the pages go back on the free stack in the order that restores it exactly.
+void ungrow(skv_pool* p, const std::vector<TableUpdate>& ups) {
+    for (auto it = ups.rbegin(); it != ups.rend(); ++it) {
+        p->free_pages.push_back(it->value);
+        p->page_owner[it->value] = -1;
+        p->pt(it->seq, it->slot) = SKV_PAGE_UNASSIGNED;
+        p->n_seq_pages[it->seq] -= 1;
+    }
+}
+
+int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
+    const int32_t layer = a.layer, n_seqs = a.n_seqs;
     if (layer < 0) return p->fail(SKV_ERR_BAD_ARG, "layer_idx must be a non-negative integer");
     if (layer >= p->cfg.num_layers)
         return p->fail(SKV_ERR_BAD_ARG, "layer_idx %d is outside configured layer count %d", layer, p->cfg.num_layers);
     if (n_seqs <= 0 || n_seqs > p->cfg.max_seqs) return p->fail(SKV_ERR_BAD_ARG, "n_seqs %d out of range", n_seqs);
-    if (!q || !k || !v || (!out && !g)) return p->fail(SKV_ERR_BAD_ARG, "q, k, v and out must be given");
-    const int32_t P = p->cfg.page_size;
-    if (seq_ids && (size_t)n_seqs * sizeof(int32_t) > StagingRing::kSlotBytes)
+    if (a.n_q_heads <= 0 || a.n_q_heads % p->cfg.num_kv_heads != 0)
+        return p->fail(SKV_ERR_BAD_ARG, "query heads must be divisible by key/value heads");
+    if (a.workspace && (uintptr_t)a.workspace % 16 != 0) return p->fail(SKV_ERR_BAD_ARG, "workspace must be 16-byte aligned");
+    if (!p->host_only && (!a.q || !a.k || !a.v || (!a.out && !a.xchg && !a.partial_out)))
+        return p->fail(SKV_ERR_BAD_ARG, "q, k, v and out must be given");
+    if (a.partial_out && a.xchg) return p->fail(SKV_ERR_BAD_ARG, "partial_out and xchg exclude each other");
+    if ((a.positions == nullptr) != (a.store == nullptr))
+        return p->fail(SKV_ERR_BAD_ARG, "positions and store are given together or not at all");
+    const int32_t P = p->cfg.page_size, Dh = p->cfg.head_dim, Hkv = p->cfg.num_kv_heads;
+    const int64_t q_stride = a.q_row_stride ? a.q_row_stride : (int64_t)a.n_q_heads * Dh;
+    const int64_t out_stride = a.out_row_stride ? a.out_row_stride : (int64_t)a.n_q_heads * Dh;
+    const int64_t k_stride = a.k_row_stride ? a.k_row_stride : (int64_t)Hkv * Dh;
+    const int64_t v_stride = a.v_row_stride ? a.v_row_stride : (int64_t)Hkv * Dh;
+    if (q_stride < (int64_t)a.n_q_heads * Dh || out_stride < (int64_t)a.n_q_heads * Dh || k_stride < (int64_t)Hkv * Dh ||
+        v_stride < (int64_t)Hkv * Dh)
+        return p->fail(SKV_ERR_BAD_ARG, "a row stride is shorter than the row");
+
+    if (!fused_step_applies(p, a, q_stride)) {
+        // the append + attention pair (float32 pools, other head sizes, bookkeeping-only pools, SKV_STEP_FUSED=0)
+        if (a.positions) return p->fail(SKV_ERR_UNSUPPORTED, "a sequence-sharded step needs the bf16 / head_dim 128 kernel");
+        skv_append_args ap{};
+        ap.layer = layer;
+        ap.n_seqs = n_seqs;
+        ap.seq_ids = a.seq_ids;
+        ap.n_new = 1;
+        ap.k = a.k;
+        ap.v = a.v;
+        ap.kv_stride_seq = k_stride;
+        ap.kv_stride_head = Dh;
+        ap.rope_k = 1;
+        ap.q_in = a.q;
+        ap.q_out = a.q;
+        ap.n_q_heads = a.n_q_heads;
+        ap.q_stride_seq = q_stride;
+        ap.q_stride_head = Dh;
+        if (k_stride != v_stride) return p->fail(SKV_ERR_UNSUPPORTED, "k and v need the same row stride outside the one-kernel step");
+        // the attention half can still refuse (workspace): check what does not depend on the append first
+        if (!p->host_only) {
+            const size_t least = (size_t)n_seqs * a.n_q_heads * ((size_t)Dh + 2) * sizeof(float);
+            int32_t st0 = check_workspace(p, a.workspace, a.workspace_bytes, least);
+            if (st0 != SKV_OK) return st0;
+        }
+        int32_t st = skv_append(p, &ap, stream);
+        if (st != SKV_OK) return st;
+        return attn_impl(p, layer, a.seq_ids, n_seqs, a.q, q_stride, a.partial_out ? nullptr : a.out, out_stride, nullptr,
+                         a.n_q_heads, a.eps, a.workspace, a.workspace_bytes, a.xchg, a.partial_out, stream);
+    }
+
+    // ---- validation: nothing is changed or enqueued before all of it has passed -------------------------------
+    const bool inline_rows = n_seqs <= kInlineRows;
+    if (!inline_rows && (size_t)n_seqs * 3 * sizeof(int32_t) > StagingRing::kSlotBytes)
         return p->fail(SKV_ERR_BAD_ARG, "too many sequences (%d) for one call", n_seqs);
     int64_t total = 0, need_total = 0;
-    std::vector<uint8_t> seen(seq_ids ? p->cfg.max_seqs : 0, 0);
+    if (a.seq_ids && ++p->stamp == 0) {   // generation counter wrapped: start over
+        std::fill(p->seen_stamp.begin(), p->seen_stamp.end(), 0u);
+        p->stamp = 1;
+    }
     for (int32_t i = 0; i < n_seqs; ++i) {
-        const int32_t s = seq_ids ? seq_ids[i] : i;
+        const int32_t s = a.seq_ids ? a.seq_ids[i] : i;
         if (!valid_seq(p, s)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", s);
-        if (seq_ids) {
-            if (seen[s]) return p->fail(SKV_ERR_BAD_ARG, "sequence %d listed twice", s);
-            seen[s] = 1;
+        if (a.seq_ids) {
+            if (p->seen_stamp[s] == p->stamp) return p->fail(SKV_ERR_BAD_ARG, "sequence %d listed twice", s);
+            p->seen_stamp[s] = p->stamp;
         }
         const int32_t cur = p->len(layer, s);
-        const int32_t need = (cur + 1 + P - 1) / P;
+        const int32_t stores = a.store ? (a.store[i] ? 1 : 0) : 1;
+        if (a.positions && a.positions[i] < 0) return p->fail(SKV_ERR_BAD_ARG, "position of row %d is negative", i);
+        const int32_t need = (cur + stores + P - 1) / P;
         if (need > p->cfg.max_pages_per_seq)
             return p->fail(SKV_ERR_OUT_OF_PAGES, "sequence %d needs %d pages, row holds %d", s, need, p->cfg.max_pages_per_seq);
         need_total += std::max(0, need - p->n_seq_pages[s]);
         for (int32_t slot = 0; slot < std::min(need, p->n_seq_pages[s]); ++slot)
             if (p->pt(s, slot) < 0) return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", s, slot);
-        total += cur + 1;
+        total += cur + stores;
     }
     if (need_total > (int64_t)p->free_pages.size())
         return p->fail(SKV_ERR_OUT_OF_PAGES, "need %lld pages, %zu free", (long long)need_total, p->free_pages.size());
     DecodeLaunch D{};
-    decode_plan(P, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
-    const size_t need_ws = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
-    if (!workspace || workspace_bytes < need_ws)
-        return p->fail(SKV_ERR_BAD_ARG, "workspace holds %zu bytes, %zu needed", workspace_bytes, need_ws);
-    std::vector<TableUpdate> ups;
-    for (int32_t i = 0; i < n_seqs; ++i) {
-        const int32_t s = seq_ids ? seq_ids[i] : i;
-        int32_t st = grow(p, s, p->len(layer, s) + 1, &ups);
-        if (st != SKV_OK) return st;   // cannot happen after the check above
+    decode_plan(P, p->cfg.max_pages_per_seq, n_seqs, Hkv, total, &D.chunk_tokens, &D.max_splits);
+    if (D.max_splits > 128) return p->fail(SKV_ERR_UNSUPPORTED, "a sequence would need %d split-K chunks, 128 is the limit", D.max_splits);
+    const size_t need_ws = (size_t)n_seqs * a.n_q_heads * D.max_splits * ((size_t)Dh + 2) * sizeof(float);
+    int32_t st = check_workspace(p, a.workspace, a.workspace_bytes, need_ws);
+    if (st != SKV_OK) return st;
+    if (a.xchg) {
+        st = fill_exchange(p, a.xchg, n_seqs, a.n_q_heads, &D.xchg);
+        if (st != SKV_OK) return st;
     }
-    for (int32_t i = 0; i < n_seqs; ++i) p->len(layer, seq_ids ? seq_ids[i] : i) += 1;
 
     DeviceGuard guard(p);
-    int32_t st = order_transfers(p, stream);
+    // May the split-K kernel run ahead of the previous kernel in the stream?  Only when the caller says that this
+    // call directly follows this pool's previous step, when no other call of the library launched anything in
+    // between, and when q, k, v do not overlap what that step's merge kernel wrote.
+    const char* q_lo = (const char*)a.q;
+    const char* q_hi = q_lo + ((int64_t)(n_seqs - 1) * q_stride + (int64_t)a.n_q_heads * Dh) * 2;
+    const char* k_lo = (const char*)a.k;
+    const char* k_hi = k_lo + ((int64_t)(n_seqs - 1) * k_stride + (int64_t)Hkv * Dh) * 2;
+    const char* v_lo = (const char*)a.v;
+    const char* v_hi = v_lo + ((int64_t)(n_seqs - 1) * v_stride + (int64_t)Hkv * Dh) * 2;
+    bool early = (a.flags & SKV_STEP_CONSECUTIVE) && p->last_step_valid && p->last_step_stream == stream &&
+                 p->last_step_mark == g_launches.load(std::memory_order_relaxed) && !p->copy_pending &&
+                 p->deferred_updates.empty();
+    for (int w = 0; early && w < 2; ++w)
+        if (overlaps(p->last_w_lo[w], p->last_w_hi[w], q_lo, q_hi) || overlaps(p->last_w_lo[w], p->last_w_hi[w], k_lo, k_hi) ||
+            overlaps(p->last_w_lo[w], p->last_w_hi[w], v_lo, v_hi))
+            early = false;
+    p->last_step_valid = false;
+
+    // ---- fallible work that does not depend on the new state ------------------------------------------------
+    st = order_transfers(p, stream);
     if (st != SKV_OK) return st;
+    // ---- mutate, then enqueue; a failure from here on puts the host state back -----------------------------------
+    std::vector<TableUpdate>& ups = p->step_ups;
+    ups.clear();
+    p->step_store.resize(n_seqs);
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        const int32_t s = a.seq_ids ? a.seq_ids[i] : i;
+        const int32_t stores = a.store ? (a.store[i] ? 1 : 0) : 1;
+        p->step_store[i] = stores;
+        if (stores) grow(p, s, p->len(layer, s) + 1, &ups);   // cannot fail after the checks above
+    }
+    StepRows& R = p->rows;
+    std::vector<int32_t> big;   // only for calls beyond the inline capacity
+    if (!inline_rows) big.resize((size_t)3 * n_seqs);
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        const int32_t s = a.seq_ids ? a.seq_ids[i] : i;
+        const int32_t cur = p->len(layer, s);
+        const uint32_t pos = (uint32_t)(a.positions ? a.positions[i] : cur) | (p->step_store[i] ? 0u : kRowNoStore);
+        if (inline_rows) {
+            R.seq[i] = s;
+            R.len[i] = cur;
+            R.pos[i] = pos;
+        } else {
+            big[i] = s;
+            big[(size_t)n_seqs + i] = cur;
+            big[(size_t)2 * n_seqs + i] = (int32_t)pos;
+        }
+    }
+    for (int32_t i = 0; i < n_seqs; ++i) p->len(layer, a.seq_ids ? a.seq_ids[i] : i) += p->step_store[i];
+    auto roll_back = [&]() {
+        for (int32_t i = 0; i < n_seqs; ++i) p->len(layer, a.seq_ids ? a.seq_ids[i] : i) -= p->step_store[i];
+        ungrow(p, ups);
+    };
     st = publish_table_updates(p, ups, stream);
-    if (st != SKV_OK) return st;
-    st = upload_ids(p, seq_ids, n_seqs, stream, &D.seq_ids);
-    if (st != SKV_OK) return st;
+    if (st != SKV_OK) {
+        roll_back();
+        return st;
+    }
+    R.dev = nullptr;
+    if (!inline_rows) {
+        void* dev = nullptr;
+        cudaError_t e = p->ring.upload(big.data(), big.size() * sizeof(int32_t), stream, &dev);
+        if (e != cudaSuccess) {
+            roll_back();
+            return p->cuda_fail(e, "upload of the step's rows");
+        }
+        R.dev = (const int32_t*)dev;
+        early = false;
+    }
+    if (!ups.empty()) early = false;   // the page-table update sits between the two kernels anyway
     D.pool = p->view();
     D.layer = layer;
     D.n_seqs = n_seqs;
-    D.n_q_heads = n_q_heads;
+    D.n_q_heads = a.n_q_heads;
     D.dtype = p->cfg.dtype;
-    D.q = q;
-    D.out = out;
-    D.eps = eps;
-    D.ws_acc = (float*)workspace;
-    D.ws_ml = D.ws_acc + (size_t)n_seqs * n_q_heads * D.max_splits * p->cfg.head_dim;
+    D.q = a.q;
+    D.out = a.out;
+    D.q_stride = q_stride;
+    D.out_stride = out_stride;
+    D.eps = a.eps;
+    D.ws_acc = (float*)a.workspace;
+    D.ws_ml = D.ws_acc + (size_t)n_seqs * a.n_q_heads * D.max_splits * Dh;
     D.k_map = &p->k_map;
     D.v_map = &p->v_map;
     D.tickets = p->d_tickets;
     D.total_tokens = total;
     D.fused_append = 1;
-    D.new_k = k;
-    D.new_v = v;
+    D.new_k = a.k;
+    D.new_v = a.v;
+    D.k_stride = k_stride;
+    D.v_stride = v_stride;
     D.inv_freq = p->d_inv_freq;
     D.rope_scaling = p->rope_scaling;
-    D.append_ticket = p->d_tickets + (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads + 1;
-    if (g) {
-        D.out = nullptr;
-        D.gather.world = g->world;
-        D.gather.rank = g->rank;
-        D.gather.epoch = g->epoch;
-        D.gather.wait_flags = g->wait_flags;   // the wait runs in the merge kernel's last block
-        D.gather.ticket = p->d_tickets + (size_t)p->cfg.max_seqs * p->cfg.num_kv_heads;
-        for (int32_t r = 0; r < g->world; ++r) {
-            D.gather.out[r] = g->out_ptrs[r];
-            D.gather.flags[r] = g->flag_ptrs[r];
-        }
+    D.early_start = early ? 1 : 0;
+    D.rows = &R;
+    if (a.xchg || a.partial_out) D.out = nullptr;
+    D.partial_out = a.partial_out;
+    cudaError_t e = launch_decode(D, stream);
+    if (e != cudaSuccess) {
+        roll_back();
+        return p->cuda_fail(e, "launch of the decode step");
     }
-    CUDA_TRY(p, launch_decode(D, stream));
+    // what the merge kernel of this step writes besides pages and partials
+    p->last_w_lo[0] = q_lo;
+    p->last_w_hi[0] = q_hi;
+    if (a.xchg) {
+        const size_t rows_total = (size_t)n_seqs * a.n_q_heads * (a.xchg->mode == SKV_XCHG_HEAD_GATHER ? a.xchg->world : 1);
+        p->last_w_lo[1] = (const char*)a.xchg->out;
+        p->last_w_hi[1] = p->last_w_lo[1] + rows_total * Dh * 2;
+    } else if (a.partial_out) {
+        p->last_w_lo[1] = (const char*)a.partial_out;
+        p->last_w_hi[1] = p->last_w_lo[1] + (size_t)n_seqs * a.n_q_heads * (Dh + 2) * sizeof(float);
+    } else {
+        p->last_w_lo[1] = (const char*)a.out;
+        p->last_w_hi[1] = p->last_w_lo[1] + ((int64_t)(n_seqs - 1) * out_stride + (int64_t)a.n_q_heads * Dh) * 2;
+    }
+    p->last_step_stream = stream;
+    p->last_step_mark = g_launches.load(std::memory_order_relaxed);
+    p->last_step_valid = true;
     return SKV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t skv_decode_step_ex(skv_pool* p, const skv_step_args* a, void* stream) {
+    if (!p || !a) return SKV_ERR_BAD_ARG;
+    return step_impl(p, *a, (cudaStream_t)stream);
 }
 
 int32_t skv_decode_step(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v, void* out,
                         int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes, void* stream) {
-    if (!p) return SKV_ERR_BAD_ARG;
-    if (fused_step_applies(p, q, n_q_heads))
-        return fused_step(p, layer, nullptr, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, nullptr, (cudaStream_t)stream);
-    skv_append_args a{};
-    a.layer = layer;
-    a.n_seqs = n_seqs;
-    a.n_new = 1;
-    a.k = k;
-    a.v = v;
-    a.kv_stride_seq = (int64_t)p->cfg.num_kv_heads * p->cfg.head_dim;
-    a.kv_stride_head = p->cfg.head_dim;
-    a.kv_stride_tok = 0;
-    a.rope_k = 1;
-    a.q_in = q;
-    a.q_out = q;
-    a.n_q_heads = n_q_heads;
-    a.q_stride_seq = (int64_t)n_q_heads * p->cfg.head_dim;
-    a.q_stride_head = p->cfg.head_dim;
-    a.q_stride_tok = 0;
-    int32_t st = skv_append(p, &a, stream);
-    if (st != SKV_OK) return st;
-    return skv_decode_attn(p, layer, nullptr, n_seqs, q, out, nullptr, n_q_heads, eps, workspace, workspace_bytes, stream);
+    return skv_decode_step_seqs(p, layer, nullptr, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, stream);
 }
 
 int32_t skv_decode_step_seqs(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* q, const void* k,
                              const void* v, void* out, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
                              void* stream) {
     if (!p) return SKV_ERR_BAD_ARG;
-    if (!seq_ids) return skv_decode_step(p, layer, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, stream);
-    if (fused_step_applies(p, q, n_q_heads))
-        return fused_step(p, layer, seq_ids, n_seqs, q, k, v, out, n_q_heads, eps, workspace, workspace_bytes, nullptr, (cudaStream_t)stream);
-    skv_append_args a{};
+    skv_step_args a{};
     a.layer = layer;
     a.n_seqs = n_seqs;
     a.seq_ids = seq_ids;
-    a.n_new = 1;
+    a.q = q;
     a.k = k;
     a.v = v;
-    a.kv_stride_seq = (int64_t)p->cfg.num_kv_heads * p->cfg.head_dim;
-    a.kv_stride_head = p->cfg.head_dim;
-    a.rope_k = 1;
-    a.q_in = q;
-    a.q_out = q;
+    a.out = out;
     a.n_q_heads = n_q_heads;
-    a.q_stride_seq = (int64_t)n_q_heads * p->cfg.head_dim;
-    a.q_stride_head = p->cfg.head_dim;
-    int32_t st = skv_append(p, &a, stream);
-    if (st != SKV_OK) return st;
-    return skv_decode_attn(p, layer, seq_ids, n_seqs, q, out, nullptr, n_q_heads, eps, workspace, workspace_bytes, stream);
+    a.eps = eps;
+    a.workspace = workspace;
+    a.workspace_bytes = workspace_bytes;
+    return step_impl(p, a, (cudaStream_t)stream);
 }
 
-int32_t skv_decode_step_gather(skv_pool* p, int32_t layer, int32_t n_seqs, void* q, const void* k, const void* v,
-                               int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
-                               const skv_peer_gather* gather, void* stream) {
-    if (!p) return SKV_ERR_BAD_ARG;
-    if (gather && fused_step_applies(p, q, n_q_heads)) {
-        if (gather->world < 1 || gather->world > 8 || gather->rank < 0 || gather->rank >= gather->world || !gather->out_ptrs ||
-            !gather->flag_ptrs)
-            return p->fail(SKV_ERR_BAD_ARG, "peer gather needs 1 <= world <= 8, a rank inside it and both pointer arrays");
-        for (int32_t r = 0; r < gather->world; ++r)
-            if (!gather->out_ptrs[r] || !gather->flag_ptrs[r]) return p->fail(SKV_ERR_BAD_ARG, "peer pointer %d is null", r);
-        return fused_step(p, layer, nullptr, n_seqs, q, k, v, nullptr, n_q_heads, eps, workspace, workspace_bytes, gather, (cudaStream_t)stream);
-    }
-    skv_append_args a{};
+int32_t skv_decode_step_xchg(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_seqs, void* q, const void* k,
+                             const void* v, int32_t n_q_heads, float eps, void* workspace, size_t workspace_bytes,
+                             const skv_exchange* xchg, void* stream) {
+    if (!p || !xchg) return SKV_ERR_BAD_ARG;
+    skv_step_args a{};
     a.layer = layer;
     a.n_seqs = n_seqs;
-    a.n_new = 1;
+    a.seq_ids = seq_ids;
+    a.q = q;
     a.k = k;
     a.v = v;
-    a.kv_stride_seq = (int64_t)p->cfg.num_kv_heads * p->cfg.head_dim;
-    a.kv_stride_head = p->cfg.head_dim;
-    a.rope_k = 1;
-    a.q_in = q;
-    a.q_out = q;
     a.n_q_heads = n_q_heads;
-    a.q_stride_seq = (int64_t)n_q_heads * p->cfg.head_dim;
-    a.q_stride_head = p->cfg.head_dim;
-    int32_t st = skv_append(p, &a, stream);
-    if (st != SKV_OK) return st;
-    return skv_decode_attn_gather(p, layer, nullptr, n_seqs, q, nullptr, n_q_heads, eps, workspace, workspace_bytes, gather, stream);
+    a.eps = eps;
+    a.workspace = workspace;
+    a.workspace_bytes = workspace_bytes;
+    a.xchg = xchg;
+    return step_impl(p, a, (cudaStream_t)stream);
 }
 
 int32_t skv_attn_dense(const void* q, const void* k, const void* v, void* out, const int32_t* positions, int32_t B,
                        int32_t Hq, int32_t Hkv, int32_t Lq, int32_t Lk, int32_t D, int32_t dtype, int32_t causal,
-                       float eps, void* stream_) {
+                       float eps, int32_t* status, void* stream_) {
     // shape rules of mlx_ops.py:51-67
     if (!q || !k || !v || !out) return SKV_ERR_BAD_ARG;
     if (B <= 0 || Hq <= 0 || Lq < 0 || Lk < 0 || D <= 0) return SKV_ERR_BAD_ARG;
@@ -1167,10 +1353,10 @@ int32_t skv_attn_dense(const void* q, const void* k, const void* v, void* out, c
     A.B = B; A.Hq = Hq; A.Hkv = Hkv; A.Lq = Lq; A.Lk = Lk; A.D = D; A.dtype = dtype; A.causal = causal;
     A.eps = eps;
     A.pool.k_base = nullptr;
+    A.status = status;
     cudaStream_t stream = (cudaStream_t)stream_;
-    const char* force = getenv("SKV_PREFILL_GENERIC");
     cudaError_t e = cudaErrorNotSupported;
-    if (!(force && force[0] == '1')) e = launch_attn_tc(A, stream);
+    if (!switches().prefill_generic) e = launch_attn_tc(A, stream);
     if (e == cudaErrorNotSupported) e = launch_attn_generic(A, stream);
     return e == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
 }
@@ -1205,9 +1391,8 @@ int32_t skv_prefill_attn_paged(skv_pool* p, int32_t layer, const int32_t* seq_id
     A.v_map = p->has_maps ? &p->v_map : nullptr;
     // bf16, head_dim 128, 16-token pages and at least 32 query rows: the tensor-core kernel reads the pages
     // directly through the pool's tensor maps; everything else takes the float32 CUDA-core kernel
-    const char* force = getenv("SKV_PREFILL_GENERIC");
     cudaError_t e = cudaErrorNotSupported;
-    if (!(force && force[0] == '1')) e = launch_attn_tc(A, stream);
+    if (!switches().prefill_generic) e = launch_attn_tc(A, stream);
     if (e == cudaErrorNotSupported) e = launch_attn_generic(A, stream);
     CUDA_TRY(p, e);
     return SKV_OK;

@@ -63,17 +63,38 @@ struct GatherLaunch {
 };
 cudaError_t launch_gather(const GatherLaunch& g, cudaStream_t stream);
 
-// Output gather fused into the merge kernel: every rank stores its output rows straight into all ranks'
-// gathered buffers over NVLink (plain peer stores) and then raises its flag on each peer.
-struct PeerGatherView {
-    int32_t world;               // 0: no gather, the merge kernel writes `out`
-    int32_t rank;
-    int32_t epoch;               // value written to the flags when this call's rows have landed
-    int32_t* ticket;             // device counter of finished merge blocks (zero between calls)
-    void* out[8];                // per rank: base of its gathered buffer [world][n_seqs][q_heads][head_dim]
-    int32_t* flags[8];           // per rank: its flag array [world]
-    const int32_t* wait_flags;   // this rank's own flag array: when set, the merge kernel's last block also waits
-                                 // (bounded) until every rank's slice of this epoch has landed here
+// Exchange fused into the merge kernel.  Every 8-byte unit that crosses NVLink carries its own flag (4 bytes of
+// payload + the call's epoch), so a receiver validates what it reads by itself: no fence, no ticket and no separate
+// flag write sit between a peer store and the moment the peer may consume it.  Two units travel per 16-byte store.
+//   mode 1 (KV-head sharding): a merge block stores its finished output row into slot `rank` of every rank's
+//     receive buffer, then polls the same row of all `world` slots of its own buffer and unpacks them into the
+//     plain gathered output `out` [world][n_seqs][q_heads][head_dim].
+//   mode 2 (sequence sharding): a merge block sends its un-normalised partial row (acc[D], m, l) to the row's
+//     owner (row % world); the owner's block merges the `world` partials with the chunk-merge rule
+//     (mlx_ops.py:125-146) and broadcasts the finished row; every block unpacks it into `out`
+//     [n_seqs][q_heads][head_dim].
+struct ExchangeView {
+    int32_t mode;                // 0: none, 1: head gather, 2: sequence-shard merge
+    int32_t world, rank;
+    uint32_t epoch;              // > 0, grows by one per call; receive buffers alternate by its parity
+    void* recv[8];               // per rank: base of its receive buffer of THIS call's parity (peer-mapped)
+    void* out;                   // local result buffer (plain layout)
+};
+
+// Per-row metadata of a one-call decode step, carried in the kernel parameters: the split-K kernel of a step
+// reads nothing that the previous step's merge kernel wrote until it stores its partials, so its start-up and its
+// K/V streaming overlap that merge kernel (and the exchange wait inside it).  Calls with more rows than fit here
+// upload the same three arrays and pass them through `dev`.
+#ifndef SKV_INLINE_ROWS
+#define SKV_INLINE_ROWS 256
+#endif
+constexpr int kInlineRows = SKV_INLINE_ROWS;
+constexpr uint32_t kRowNoStore = 0x80000000u;   // bit 31 of pos: this pool does not store the step's token
+struct StepRows {
+    const int32_t* dev;           // nullptr, or device [3][n_seqs]: seq, len, pos
+    int32_t seq[kInlineRows];     // sequence id of row i
+    int32_t len[kInlineRows];     // tokens of row i held by this pool before the step
+    uint32_t pos[kInlineRows];    // absolute position of the step's token (RoPE angle) | kRowNoStore
 };
 
 struct DecodeLaunch {
@@ -83,6 +104,7 @@ struct DecodeLaunch {
     const int32_t* q_pos;        // device or nullptr (length - 1)
     const void* q;
     void* out;
+    int64_t q_stride, out_stride;   // elements between the rows of consecutive sequences (heads are contiguous)
     float eps;
     float* ws_acc;               // [n_seqs][n_q_heads][max_splits][head_dim]
     float* ws_ml;                // [n_seqs][n_q_heads][max_splits][2]
@@ -97,19 +119,22 @@ struct DecodeLaunch {
     int32_t* tickets;
     int32_t fuse_merge;          // 0: leave the merge to decode_reduce_kernel
     int64_t total_tokens;        // host's sum of the attended lengths (drives the plan and the merge choice)
-    PeerGatherView gather;
+    ExchangeView xchg;
     float* partial_out;          // when set, the merge kernel writes un-normalised [n_seqs][q_heads][head_dim + 2]
                                  // rows (acc..., m, l) instead of the output: the unit of sequence sharding
-    // Fused append (one decode step, identity batch, bf16 TMA kernel only): the device lengths still hold the
-    // count BEFORE this step's token.  Every CTA rotates its own copy of q at position `length`; the CTA whose
-    // chunk contains that position rotates the new K row, stores it and the V row into the page, and attends
-    // the token from registers; the merge kernel writes the rotated q back and bumps the lengths.
+    // One-call decode step (bf16 TMA kernel only): per-row sequence id, stored length and token position come
+    // from `rows`.  Every CTA rotates its own copy of q at the token's position; the CTA whose chunk contains
+    // the row's length rotates the new K row, stores it and the V row into the page and attends the token from
+    // shared memory; the merge kernel writes the rotated q back and sets the device lengths.
     int32_t fused_append;
-    const void* new_k;           // [n_seqs][kv_heads][head_dim], un-rotated
+    const void* new_k;           // row i at new_k + i * k_stride elements: [kv_heads][head_dim], un-rotated
     const void* new_v;
+    int64_t k_stride, v_stride;
     const float* inv_freq;       // [head_dim / 2]
     float rope_scaling;
-    int32_t* append_ticket;      // one counter, zero between calls
+    int32_t early_start;         // 1: the split-K kernel of a step may run ahead of the previous kernel in the stream
+                                 // up to the point where it stores its partials (the caller vouched for its inputs)
+    const StepRows* rows;        // host pointer; copied into the kernel parameters at launch
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
 // chunk length (tokens handled by one CTA) and the number of splits that follow from it
@@ -129,6 +154,7 @@ struct DenseAttnLaunch {
     // host pointers to the pool's CUtensorMaps ([rows][head_dim] bf16, [16][64] boxes); nullptr when it has none
     const void* k_map;
     const void* v_map;
+    int32_t* status;             // dense calls: optional device word for FLAG_WAIT_TIMEOUT (paged calls use the pool's)
 };
 cudaError_t launch_attn_generic(const DenseAttnLaunch& a, cudaStream_t stream);
 // Tensor-core (tcgen05) causal prefill; returns cudaErrorNotSupported when the shape is outside its cover.
@@ -157,7 +183,22 @@ int32_t pool_device(const skv_pool* pool);
 
 cudaError_t launch_merge_partials(const float* parts, int32_t n_parts, int64_t part_stride, int32_t n_rows, int32_t head_dim,
                                   float eps, void* out, int32_t dtype, cudaStream_t stream);
-cudaError_t launch_gather_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, cudaStream_t stream);
+
+// Process-wide A/B switches, read from the environment once (and again on skv_reload_env).
+struct Switches {
+    int step_fused;        // SKV_STEP_FUSED != "0"
+    int decode_generic;    // SKV_DECODE_GENERIC == "1"
+    int impl_reg;          // SKV_DECODE_IMPL starts with 'r'
+    int stages;            // SKV_DECODE_STAGES (2 when unset)
+    int chunk;             // SKV_DECODE_CHUNK (0 when unset)
+    int plan_waves;        // SKV_PLAN_WAVES != "0"
+    int fuse;              // SKV_DECODE_FUSE: -1 unset, 0, 1
+    int prefill_generic;   // SKV_PREFILL_GENERIC == "1"
+    int append_scalar;     // SKV_APPEND_SCALAR == "1"
+    int pdl;               // SKV_PDL != "0"
+};
+const Switches& switches();
+void reload_switches();
 
 // process-wide count of kernel launches issued by this library
 void count_launches(int n);

@@ -114,15 +114,17 @@ class PagedPool:
         self._check(lib.skv_alloc_sequence(self._h, C.byref(out)))
         return out.value
 
+    # The next three publish their change to the device copy of the tables on the current stream of the pool's
+    # device, like every compute call, so a pool driven from a side stream stays ordered.
     def free_sequence(self, seq: int):
-        self._check(lib.skv_free_sequence(self._h, seq))
+        self._check(lib.skv_free_sequence(self._h, seq, self.stream))
 
     def reserve(self, seq: int, total_tokens: int):
-        self._check(lib.skv_reserve(self._h, seq, total_tokens))
+        self._check(lib.skv_reserve(self._h, seq, total_tokens, self.stream))
 
     def set_page_table(self, seq: int, pages: Sequence[int], length: int):
         arr = i32_array(pages)
-        self._check(lib.skv_set_page_table(self._h, seq, arr, len(arr), length))
+        self._check(lib.skv_set_page_table(self._h, seq, arr, len(arr), length, self.stream))
 
     def truncate(self, layer: int, new_length: int, seq_ids=None, n_seqs: Optional[int] = None):
         """Shorten a layer's history of the given sequences to ``new_length`` tokens (pages are kept)."""
@@ -280,23 +282,23 @@ class PagedPool:
                                         i32_array(q_pos), hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
         return out
 
-    def decode_attention_gather(self, layer: int, q: torch.Tensor, gather, *, seq_ids=None, q_pos=None,
-                                eps: float = 1e-12, wait: bool = True) -> torch.Tensor:
-        """``decode_attention`` under KV-head sharding with the all-gather fused into the merge kernel:
-        this rank's rows go by peer stores into every rank's gathered buffer (``gather`` is a
-        ``sharding.PeerGather``).  Returns this rank's gathered view ``[world, n_seqs, local_q_heads, head_dim]``;
-        with ``wait`` a kernel that waits for all ranks' rows is enqueued first."""
+    def decode_attention_xchg(self, layer: int, q: torch.Tensor, exchange, *, seq_ids=None, q_pos=None,
+                              eps: float = 1e-12) -> torch.Tensor:
+        """``decode_attention`` with the exchange between GPUs fused into the merge kernel (``exchange`` is a
+        ``sharding.PeerGather`` under KV-head sharding or a ``sharding.PeerSeqMerge`` under sequence sharding).
+        Returns the exchange's local result view, complete for anything enqueued after the call."""
         self._check_tensor(q, "q")
         if q.dim() != 3 or not q.is_contiguous():
             raise ValueError("q must be a contiguous [n_seqs, q_heads, head_dim] tensor")
         n_seqs, hq, _ = q.shape
-        if tuple(gather.shape) != (gather.shard.world, n_seqs, hq, self.cfg.head_dim):
-            raise ValueError("gather buffers do not match q")
-        desc, view = gather.begin(wait)
+        exchange.check(n_seqs, hq, self.cfg.head_dim)
+        desc, view = exchange.begin()
         ws = self.workspace(n_seqs, hq)
-        self._check(lib.skv_decode_attn_gather(self._h, layer, i32_array(seq_ids), n_seqs, q.data_ptr(), i32_array(q_pos), hq,
-                                               float(eps), ws.data_ptr(), ws.numel(), C.byref(desc), self.stream))
+        self._check(lib.skv_decode_attn_xchg(self._h, layer, i32_array(seq_ids), n_seqs, q.data_ptr(), i32_array(q_pos), hq,
+                                             float(eps), ws.data_ptr(), ws.numel(), C.byref(desc), self.stream))
         return view
+
+    decode_attention_gather = decode_attention_xchg
 
     def decode_partial(self, layer: int, q: torch.Tensor, *, seq_ids=None, q_pos=None,
                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -314,76 +316,118 @@ class PagedPool:
                                            ws.data_ptr(), ws.numel(), out.data_ptr(), self.stream))
         return out
 
-    def decode_step(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: float = 1e-12,
-                    out: Optional[torch.Tensor] = None, seq_ids=None) -> torch.Tensor:
-        """RoPE-on-write append of one token per sequence plus decode attention in one library call.
-        ``q`` ``[n_seqs, q_heads, head_dim]`` is rotated in place; ``k``, ``v`` ``[n_seqs, kv_heads, head_dim]``;
-        the sequences are ``seq_ids`` (distinct; default 0..n_seqs-1) and the token goes to each one's current length."""
-        for name, t in (("q", q), ("k", k), ("v", v)):
+    def _step_args(self, q, k, v, out, seq_ids, eps, exchange, positions, store, consecutive):
+        """Checked argument block of ``skv_decode_step_ex``; returns (block, objects that must outlive the call)."""
+        for name, t in (("q", q), ("k", k), ("v", v)) + ((("out", out),) if out is not None else ()):
             self._check_tensor(t, name)
-            if t.dim() != 3 or not t.is_contiguous():
-                raise ValueError(f"{name} must be a contiguous rank-3 tensor")
+            if t.dim() != 3 or t.stride(2) != 1 or t.stride(1) != t.shape[2]:
+                raise ValueError(f"{name} must be [n_seqs, heads, head_dim] with the heads of a row packed")
         n_seqs, hq, _ = q.shape
         if k.shape != (n_seqs, self.cfg.num_kv_heads, self.cfg.head_dim) or v.shape != k.shape:
             raise ValueError("new key states must match cached batch, head, and feature dimensions")
-        if out is None:
+        if out is not None and out.shape != q.shape:
+            raise ValueError("out must have q's shape")
+        a = _lib.SkvStepArgs()
+        keep = []
+        a.n_seqs, a.n_q_heads, a.eps = n_seqs, hq, float(eps)
+        a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+        a.q_row_stride, a.k_row_stride, a.v_row_stride = q.stride(0), k.stride(0), v.stride(0)
+        if out is not None:
+            a.out, a.out_row_stride = out.data_ptr(), out.stride(0)
+        if seq_ids is not None:
+            ids = i32_array(seq_ids)
+            if len(ids) != n_seqs:
+                raise ValueError("seq_ids must have one entry per row of q")
+            a.seq_ids = ids
+            keep.append(ids)
+        if (positions is None) != (store is None):
+            raise ValueError("positions and store are given together or not at all")
+        if positions is not None:
+            pos = i32_array(positions)
+            st = (C.c_uint8 * n_seqs)(*[1 if x else 0 for x in store])
+            if len(pos) != n_seqs:
+                raise ValueError("positions must have one entry per row of q")
+            a.positions, a.store = pos, st
+            keep += [pos, st]
+        ws = self.workspace(n_seqs, hq)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        a.flags = _lib.STEP_CONSECUTIVE if consecutive else 0
+        if exchange is not None:
+            exchange.check(n_seqs, hq, self.cfg.head_dim)
+        return a, keep
+
+    def decode_step(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: float = 1e-12,
+                    out: Optional[torch.Tensor] = None, seq_ids=None, exchange=None, positions=None, store=None,
+                    consecutive: bool = False, partial: bool = False) -> torch.Tensor:
+        """RoPE-on-write append of one token per sequence plus decode attention in one library call.
+        ``q`` ``[n_seqs, q_heads, head_dim]`` is rotated in place; ``k``, ``v`` ``[n_seqs, kv_heads, head_dim]``; rows
+        may be strided slices of one fused projection output as long as the heads of a row are packed.  The
+        sequences are ``seq_ids`` (distinct; default 0..n_seqs-1) and the token goes to each one's current length.
+        ``exchange`` (``sharding.PeerGather`` / ``PeerSeqMerge``) fuses the exchange between GPUs into the merge
+        kernel and the call returns its local result view.  ``positions`` / ``store``: sequence sharding (the
+        token's absolute position per row, and whether this pool keeps it).  ``consecutive=True`` states that
+        nothing was enqueued on the stream since this pool's previous step and that q, k, v were complete before
+        it: the step then overlaps the previous step's merge kernel (see ``skv_step_args`` in the header).
+        ``partial=True`` returns un-normalised float32 rows ``[n_seqs, q_heads, head_dim + 2]`` (what ``decode_partial``
+        writes) instead of the output, for a merge done elsewhere."""
+        if partial:
+            if exchange is not None:
+                raise ValueError("partial and exchange exclude each other")
+            part = torch.empty((q.shape[0], q.shape[1], q.shape[2] + 2), dtype=torch.float32, device=q.device)
+        elif out is None and exchange is None:
             out = torch.empty_like(q)
-        ws = self.workspace(n_seqs, hq)
-        if seq_ids is None:
-            self._check(lib.skv_decode_step(self._h, layer, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                            hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
-        else:
-            ids = i32_array(seq_ids)
-            if len(ids) != n_seqs:
-                raise ValueError("seq_ids must have one entry per row of q")
-            self._check(lib.skv_decode_step_seqs(self._h, layer, ids, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                                 out.data_ptr(), hq, float(eps), ws.data_ptr(), ws.numel(), self.stream))
-        return out
+        a, keep = self._step_args(q, k, v, None if (exchange is not None or partial) else out, seq_ids, eps, exchange,
+                                  positions, store, consecutive)
+        a.layer = layer
+        view = out
+        if partial:
+            a.partial_out = part.data_ptr()
+            view = part
+        if exchange is not None:
+            desc, view = exchange.begin()
+            a.xchg = C.pointer(desc)
+        self._check(lib.skv_decode_step_ex(self._h, C.byref(a), self.stream))
+        del keep
+        return view
 
-    def decode_step_binder(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, *, seq_ids=None,
-                           eps: float = 1e-12):
-        """``decode_step`` for buffers that stay put (the static tensors of a CUDA graph): the tensors are checked
-        once, here, and the returned ``call(layer, stream)`` only makes the library call.  The caller keeps the
-        tensors alive and unchanged in shape for as long as it uses the callable."""
-        for name, t in (("q", q), ("k", k), ("v", v), ("out", out)):
-            self._check_tensor(t, name)
-            if t.dim() != 3 or not t.is_contiguous():
-                raise ValueError(f"{name} must be a contiguous rank-3 tensor")
-        n_seqs, hq, _ = q.shape
-        if k.shape != (n_seqs, self.cfg.num_kv_heads, self.cfg.head_dim) or v.shape != k.shape or out.shape != q.shape:
-            raise ValueError("new key states must match cached batch, head, and feature dimensions")
-        ws = self.workspace(n_seqs, hq)
-        h, qp, kp, vp, op, wp, wn = self._h, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel()
-        eps_f = float(eps)
-        if seq_ids is None:
-            fn = lib.skv_decode_step
-
+    def decode_step_binder(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+                           seq_ids=None, eps: float = 1e-12, exchange=None, positions=None, store=None,
+                           consecutive: bool = False):
+        """``decode_step`` for buffers that stay put (the static tensors of a CUDA graph, the buffers of a decode
+        loop): the tensors are checked once, here, and the returned ``call(layer, stream)`` only makes the
+        library call (with an exchange it returns the step's result view).  The caller keeps the tensors alive and
+        unchanged in shape for as long as it uses the callable."""
+        if out is None and exchange is None:
+            raise ValueError("out or exchange is needed")
+        a, keep = self._step_args(q, k, v, None if exchange is not None else out, seq_ids, eps, exchange, positions, store,
+                                  consecutive)
+        h, fn, ref = self._h, lib.skv_decode_step_ex, C.byref(a)
+        if exchange is None:
             def call(layer: int, stream: int):
-                st = fn(h, layer, n_seqs, qp, kp, vp, op, hq, eps_f, wp, wn, stream)
+                a.layer = layer
+                st = fn(h, ref, stream)
                 if st:
                     raise_for_status(st, h)
+                return out
         else:
-            ids = i32_array(seq_ids)
-            if len(ids) != n_seqs:
-                raise ValueError("seq_ids must have one entry per row of q")
-            fn = lib.skv_decode_step_seqs
+            begin = exchange.begin
 
             def call(layer: int, stream: int):
-                st = fn(h, layer, ids, n_seqs, qp, kp, vp, op, hq, eps_f, wp, wn, stream)
+                a.layer = layer
+                desc, view = begin()
+                a.xchg = C.pointer(desc)
+                st = fn(h, ref, stream)
                 if st:
                     raise_for_status(st, h)
+                return view
+        call._keep = (a, keep, q, k, v, out)
         return call
 
     def decode_step_gather(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gather, *,
-                           eps: float = 1e-12) -> torch.Tensor:
-        """``decode_step`` under KV-head sharding: append, attend, fused output gather and wait in one library call.
+                           eps: float = 1e-12, seq_ids=None, consecutive: bool = False) -> torch.Tensor:
+        """``decode_step`` under KV-head sharding: append, attend and the output gather in one library call.
         Returns this rank's gathered view ``[world, n_seqs, local_q_heads, head_dim]``."""
-        n_seqs, hq, _ = q.shape
-        desc, view = gather.begin(True)
-        ws = self.workspace(n_seqs, hq)
-        self._check(lib.skv_decode_step_gather(self._h, layer, n_seqs, q.data_ptr(), k.data_ptr(), v.data_ptr(), hq, float(eps),
-                                               ws.data_ptr(), ws.numel(), C.byref(desc), self.stream))
-        return view
+        return self.decode_step(layer, q, k, v, eps=eps, seq_ids=seq_ids, exchange=gather, consecutive=consecutive)
 
     def decode_attention_static(self, layer: int, q: torch.Tensor, *, seq_ids=None, q_pos=None, eps: float = 1e-12,
                                 out: Optional[torch.Tensor] = None) -> torch.Tensor:

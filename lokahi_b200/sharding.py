@@ -76,71 +76,99 @@ def gather_head_outputs(out_local: torch.Tensor, shard: HeadShard, group: Option
     return moved.reshape(shape)
 
 
-class PeerGather:
-    """Buffers for the output gather that is fused into the decode merge kernel.
+class PeerExchange:
+    """Receive buffers and result buffers of the exchange that the decode merge kernel runs between GPUs.
 
-    Every rank holds two gathered buffers ``[world, n_seqs, local_q_heads, head_dim]`` (used alternately) and
-    a flag array ``[world]``; all of them are peer-mapped (torch symmetric memory over NVLink), so a rank's
-    merge kernel can store its rows straight into every rank's buffer and raise its flag there.  With
-    ``world == 1`` plain device tensors are used, which exercises the same kernel path on one GPU.
-    K/V never cross GPUs; only the outputs do.
+    Every rank holds one receive buffer (two halves used alternately, by epoch parity) that all ranks can store
+    into: torch symmetric memory over NVLink, peer-mapped at construction (a collective: every rank of ``group``
+    must build the same object at the same point).  Rows cross as 16-byte stores whose 8-byte halves carry the
+    call's epoch, so the receiving kernel validates each word by itself.  The result lands in a plain local tensor
+    (two of them, alternating, so that one can still be read while the next step fills the other).  With
+    ``world == 1`` ordinary device memory is used, which runs the same kernel code on one GPU.  K/V never cross
+    GPUs; only output rows (or partial rows) do.
     """
+
+    def __init__(self, mode: int, rank: int, world: int, n_seqs: int, n_q_heads: int, head_dim: int, dtype: torch.dtype,
+                 device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        import ctypes as C
+        from . import _lib
+        self.mode, self.rank, self.world = mode, rank, world
+        self.n_seqs, self.n_q_heads, self.head_dim = n_seqs, n_q_heads, head_dim
+        self.epoch = 0
+        code = _lib.BF16 if dtype == torch.bfloat16 else _lib.F32
+        nbytes = int(_lib.lib.skv_exchange_bytes(mode, world, n_seqs, n_q_heads, head_dim, code))
+        if nbytes == 0:
+            raise ValueError("exchange: unsupported mode, world size (1..8) or shape")
+        self.out_shape = ((world, n_seqs, n_q_heads, head_dim) if mode == _lib.XCHG_HEAD_GATHER
+                          else (n_seqs, n_q_heads, head_dim))
+        self._outs = [torch.zeros(self.out_shape, dtype=dtype, device=device) for _ in range(2)]
+        if world == 1:
+            self.recv = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            self.recv_ptrs = [self.recv.data_ptr()]
+        else:
+            import os
+            # plain peer mappings are all this needs: no NVLink multicast object is bound to the buffers
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            group = group or dist.group.WORLD
+            self.recv = symm.empty(nbytes, dtype=torch.uint8, device=device)
+            self.recv.zero_()
+            handle = symm.rendezvous(self.recv, group.group_name)
+            self.recv_ptrs = [int(p) for p in handle.buffer_ptrs]
+            self._handle = handle
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)          # every rank's buffer is zero before anybody stores into it
+        self._group = group
+        # the argument block is built once: a decode step must not pay for marshalling `world` pointers
+        self._ptr_arr = (C.c_void_p * world)(*self.recv_ptrs)
+        self._desc = _lib.SkvExchange(mode=mode, rank=rank, world=world, epoch=0,
+                                      recv_ptrs=C.cast(self._ptr_arr, C.POINTER(C.c_void_p)), out=0)
+        self._out_ptrs = [t.data_ptr() for t in self._outs]
+
+    def check(self, n_seqs: int, n_q_heads: int, head_dim: int):
+        if (n_seqs, n_q_heads, head_dim) != (self.n_seqs, self.n_q_heads, self.head_dim):
+            raise ValueError("exchange buffers do not match q")
+
+    def begin(self):
+        """Advance to the next epoch; returns (argument block for the library call, local result view)."""
+        self.epoch += 1
+        parity = self.epoch & 1
+        d = self._desc
+        d.epoch = self.epoch
+        d.out = self._out_ptrs[parity]
+        return d, self._outs[parity]
+
+    def close(self):
+        """Collective: all ranks stop using the buffers before any rank lets go of its own."""
+        if self.world > 1 and self.recv is not None:
+            torch.cuda.synchronize(self.recv.device)
+            dist.barrier(group=self._group)
+        self.recv = None
+        self._handle = None
+
+
+class PeerGather(PeerExchange):
+    """Output all-gather of KV-head sharding, fused into the merge kernel: result ``[world, n_seqs, local_q_heads,
+    head_dim]``; slot r holds rank r's query heads (concatenating the slots along the head axis restores the
+    reference's head order, src/ollm/backends/mlx_ops.py:152)."""
 
     def __init__(self, shard: HeadShard, n_seqs: int, head_dim: int, dtype: torch.dtype, device: torch.device,
                  group: Optional[dist.ProcessGroup] = None):
-        self.shard = shard
-        self.shape = (shard.world, n_seqs, shard.local_q_heads, head_dim)
-        self.epoch = 0
-        esize = torch.empty((), dtype=dtype).element_size()
-        self.slab_bytes = int(torch.Size(self.shape).numel()) * esize
-        if shard.world == 1:
-            self.buf = torch.zeros((2,) + self.shape, dtype=dtype, device=device)
-            self.flags = torch.zeros((1,), dtype=torch.int32, device=device)
-            self.buf_ptrs = [self.buf.data_ptr()]
-            self.flag_ptrs = [self.flags.data_ptr()]
-        else:
-            import torch.distributed._symmetric_memory as symm
-            group = group or dist.group.WORLD
-            self.buf = symm.empty((2,) + self.shape, dtype=dtype, device=device)
-            self.flags = symm.empty((shard.world,), dtype=torch.int32, device=device)
-            self.buf.zero_()
-            self.flags.zero_()
-            hb = symm.rendezvous(self.buf, group.group_name)
-            hf = symm.rendezvous(self.flags, group.group_name)
-            self.buf_ptrs = [int(p) for p in hb.buffer_ptrs]
-            self.flag_ptrs = [int(p) for p in hf.buffer_ptrs]
-            self._handles = (hb, hf)
-            torch.cuda.synchronize(device)
-            dist.barrier(group=group)
-
-    def _descriptors(self):
-        # the two argument blocks (one per buffer parity) are built once: a decode step must not pay for
-        # marshalling 2 x world pointers every time
-        import ctypes as C
         from . import _lib
-        if not hasattr(self, "_desc"):
-            world = self.shard.world
-            self._keep, self._desc = [], []
-            flag_arr = (C.c_void_p * world)(*self.flag_ptrs)
-            for parity in (0, 1):
-                out_arr = (C.c_void_p * world)(*[p + parity * self.slab_bytes for p in self.buf_ptrs])
-                d = _lib.SkvPeerGather(rank=self.shard.rank, world=world, epoch=0,
-                                       out_ptrs=C.cast(out_arr, C.POINTER(C.c_void_p)),
-                                       flag_ptrs=C.cast(flag_arr, C.POINTER(C.c_void_p)), wait_flags=self.flags.data_ptr())
-                self._keep.append((out_arr, flag_arr))
-                self._desc.append(d)
-            self._views = [self.buf[0], self.buf[1]]
-        return self._desc
+        super().__init__(_lib.XCHG_HEAD_GATHER, shard.rank, shard.world, n_seqs, shard.local_q_heads, head_dim, dtype, device, group)
+        self.shard = shard
+        self.shape = self.out_shape
 
-    def begin(self, wait: bool = True):
-        """Advance to the next epoch; returns (argument block for the library call, local gathered view)."""
-        desc = self._descriptors()
-        self.epoch += 1
-        parity = self.epoch & 1
-        d = desc[parity]
-        d.epoch = self.epoch
-        d.wait_flags = self.flags.data_ptr() if wait else None
-        return d, self._views[parity]
+
+class PeerSeqMerge(PeerExchange):
+    """Cross-rank merge of sequence sharding, fused into the merge kernel: each rank's un-normalised partial row goes
+    to the row's owner, the owner applies the reference's chunk-merge rule (mlx_ops.py:125-146) and sends the
+    finished row to everyone; result ``[n_seqs, q_heads, head_dim]``, identical on all ranks."""
+
+    def __init__(self, rank: int, world: int, n_seqs: int, n_q_heads: int, head_dim: int, dtype: torch.dtype,
+                 device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        from . import _lib
+        super().__init__(_lib.XCHG_SEQ_MERGE, rank, world, n_seqs, n_q_heads, head_dim, dtype, device, group)
 
 
 @dataclass(frozen=True)
@@ -175,6 +203,52 @@ class SequenceShard:
     def local_position(self, position: int) -> int:
         """A global query position in this rank's own token numbering (negative: none of its keys are allowed)."""
         return position - self.rank * self.span
+
+
+@dataclass(frozen=True)
+class InterleavedShard:
+    """Round-robin split of every sequence's tokens over the ranks in blocks of ``block`` tokens (a multiple of the
+    page size): block j of a sequence lives on rank ``j % world``.  Unlike the contiguous split it balances ragged
+    batches (a short sequence is spread over all ranks too).  A rank keeps its tokens in their global order, so the
+    keys a query at position p may see are the first ``local_count(p + 1)`` tokens of the rank."""
+
+    rank: int
+    world: int
+    block: int = 16
+    page_size: int = 16
+
+    def __post_init__(self):
+        if self.world <= 0 or not 0 <= self.rank < self.world:
+            raise ValueError("rank must lie in [0, world)")
+        if self.block <= 0 or self.block % self.page_size:
+            raise ValueError("block must be a positive multiple of the page size")
+
+    def owner(self, position: int) -> int:
+        return (position // self.block) % self.world
+
+    def local_count(self, length: int, rank: Optional[int] = None) -> int:
+        """Tokens among global positions [0, length) that live on ``rank`` (default: this rank)."""
+        r = self.rank if rank is None else rank
+        cycle = self.block * self.world
+        full, rest = divmod(length, cycle)
+        return full * self.block + min(max(rest - r * self.block, 0), self.block)
+
+    def local_range(self, length: int):
+        return None, self.local_count(length)
+
+    def local_position(self, position: int) -> int:
+        """A global query position as the index of the last local key it may see (-1: none)."""
+        return self.local_count(position + 1) - 1
+
+    def global_positions(self, length: int):
+        """Global positions of this rank's tokens of a sequence of ``length`` tokens, in local order."""
+        out = []
+        cycle = self.block * self.world
+        start = self.rank * self.block
+        while start < length:
+            out.extend(range(start, min(start + self.block, length)))
+            start += cycle
+        return out
 
 
 def sequence_sharded_decode(pool, layer: int, q: torch.Tensor, q_pos_global, seq_shard: SequenceShard, *,

@@ -136,16 +136,16 @@ def test_paged_decode_matches_oracle_on_ragged_lengths(dtype, tol, D, Hq, Hkv):
     assert_parity(out3, ref3, tol, "paged decode with sequence ids")
 
 
-def test_paged_decode_kernels_agree_and_empty_sequences_give_zero(monkeypatch):
+def test_paged_decode_kernels_agree_and_empty_sequences_give_zero(skv_switch):
     rng = np.random.default_rng(3)
     lens = [0, 5, 48, 333]
     pool, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, len(lens), 8, 128, 16, lens)
     q = _t(rnd(rng.standard_normal((len(lens), 32, 128), dtype=np.float32)), torch.bfloat16)
     a = pool.decode_attention(0, q)
     assert not to_np(a[0]).any()
-    monkeypatch.setenv("SKV_DECODE_GENERIC", "1")
+    skv_switch("SKV_DECODE_GENERIC", "1")
     b = pool.decode_attention(0, q)
-    monkeypatch.delenv("SKV_DECODE_GENERIC")
+    skv_switch("SKV_DECODE_GENERIC", None)
     assert_parity(a, to_np(b), TOL_BF16, "tensor-core vs CUDA-core decode")
     ref = opaged.paged_decode_attention(to_np(q), k_ref, v_ref, table, np.array(lens), out_dtype=np.float32)
     assert_parity(b, ref, TOL_BF16, "CUDA-core decode")
@@ -239,7 +239,7 @@ def test_tensor_core_prefill_matches_oracle(shape, causal):
     assert_parity(out, ref, TOL_BF16, "tcgen05 prefill")
 
 
-def test_tensor_core_prefill_absolute_positions_and_masked_rows(monkeypatch):
+def test_tensor_core_prefill_absolute_positions_and_masked_rows(skv_switch):
     rng = np.random.default_rng(77)
     B, Hq, Hkv, Lq, Lk, D = 2, 4, 2, 96, 300, 128
     q = bf16_round(rng.standard_normal((B, Hq, Lq, D), dtype=np.float32))
@@ -251,12 +251,12 @@ def test_tensor_core_prefill_absolute_positions_and_masked_rows(monkeypatch):
     ref = oattn.chunked_grouped_attention(q, k, v, query_positions=pos, k_block_size=64)
     assert_parity(out, ref, TOL_BF16, "tcgen05 prefill, per-row positions")
     assert not to_np(out[0, :, 0]).any(), "a row with no allowed key is exactly 0"
-    monkeypatch.setenv("SKV_PREFILL_GENERIC", "1")
+    skv_switch("SKV_PREFILL_GENERIC", "1")
     gen = L.chunked_grouped_attention(_t(q, torch.bfloat16), _t(k, torch.bfloat16), _t(v, torch.bfloat16), query_positions=pos)
     assert_parity(out, to_np(gen), TOL_BF16, "tcgen05 vs CUDA-core prefill")
 
 
-def test_tensor_core_prefill_at_full_sequence_4096(monkeypatch):
+def test_tensor_core_prefill_at_full_sequence_4096(skv_switch):
     """The stand-alone chunked-GQA configuration (32 query heads, 8 KV heads, head_dim 128, sequence 4096, bf16):
     oracle parity on a sample of heads / row blocks, agreement with the CUDA-core kernel on all of it, and
     causality (changing future V leaves earlier rows untouched)."""
@@ -276,14 +276,14 @@ def test_tensor_core_prefill_at_full_sequence_4096(monkeypatch):
     v2[:, :, 3000:] += 1000.0
     out2 = L.chunked_grouped_attention(q, k, v2, query_positions=pos, causal=True)
     assert torch.equal(out[:, :, :3000], out2[:, :, :3000]) and not torch.equal(out[:, :, 3000:], out2[:, :, 3000:])
-    monkeypatch.setenv("SKV_PREFILL_GENERIC", "1")
+    skv_switch("SKV_PREFILL_GENERIC", "1")
     ref_all = L.chunked_grouped_attention(q[:, ::8], k[:, ::2], v[:, ::2], query_positions=pos, causal=True)
     # both sides are bf16-rounded, so element-wise they may sit two roundings apart: normalised error only
     from parity import parity_errors
     assert parity_errors(out[:, ::8], to_np(ref_all))[0] <= TOL_BF16, "tcgen05 vs CUDA-core at S=4096"
 
 
-def test_tensor_core_prefill_over_pages_matches_oracle_and_the_dense_kernel(monkeypatch):
+def test_tensor_core_prefill_over_pages_matches_oracle_and_the_dense_kernel(skv_switch):
     """bf16, head_dim 128, 16-token pages, at least 32 query rows: the tcgen05 kernel reads K/V straight from the
     scattered pages.  Ragged lengths (one shorter than a key tile, one not a multiple of the page size), default
     bottom-right positions and explicit ones (with fully masked rows), against the oracle on the logical history
@@ -296,9 +296,9 @@ def test_tensor_core_prefill_over_pages_matches_oracle_and_the_dense_kernel(monk
     before = L._lib.lib.skv_launch_count()
     out = pool.prefill_attention(0, q)                                   # positions default to Lk - Lq + i
     assert L._lib.lib.skv_launch_count() - before == 1
-    monkeypatch.setenv("SKV_PREFILL_GENERIC", "1")
+    skv_switch("SKV_PREFILL_GENERIC", "1")
     out_generic = pool.prefill_attention(0, q)
-    monkeypatch.delenv("SKV_PREFILL_GENERIC")
+    skv_switch("SKV_PREFILL_GENERIC", None)
     from parity import parity_errors
     assert parity_errors(out, to_np(out_generic))[0] <= TOL_BF16
     for i, t in enumerate(lens):
@@ -321,8 +321,8 @@ def test_tensor_core_prefill_over_pages_matches_oracle_and_the_dense_kernel(monk
         assert torch.count_nonzero(out2[i, :, 0]) == 0, "a row with no allowed key is exactly 0"
 
 
-def test_decode_step_equals_append_then_attention(monkeypatch):
-    monkeypatch.setenv("SKV_STEP_FUSED", "0")     # the two-call form of the step: bit-identical to its parts
+def test_decode_step_equals_append_then_attention(skv_switch):
+    skv_switch("SKV_STEP_FUSED", "0")     # the two-call form of the step: bit-identical to its parts
     rng = np.random.default_rng(55)
     lens = [5, 16, 300, 1025]
     pool_a, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, len(lens), 8, 128, 16, lens)
@@ -341,7 +341,7 @@ def test_decode_step_equals_append_then_attention(monkeypatch):
     assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
 
 
-def test_fused_append_step_matches_the_two_launch_step_and_the_oracle(monkeypatch):
+def test_fused_append_step_matches_the_two_launch_step_and_the_oracle(skv_switch):
     """The one-kernel step (RoPE of q and of the new K row, the store into the page and the new token's score all
     inside the decode kernel) against append + attention, over 20 steps that cross page, chunk and empty-sequence
     boundaries: rotated q and the stored pages bit-equal, outputs within bf16 tolerance of each other and of the
@@ -362,9 +362,9 @@ def test_fused_append_step_matches_the_two_launch_step_and_the_oracle(monkeypatc
         k = _t(rnd(rng.standard_normal((n, Hkv, D), dtype=np.float32)), torch.bfloat16)
         v = _t(rnd(rng.standard_normal((n, Hkv, D), dtype=np.float32)), torch.bfloat16)
         qa, qb = q.clone(), q.clone()
-        monkeypatch.setenv("SKV_STEP_FUSED", "0")
+        skv_switch("SKV_STEP_FUSED", "0")
         out_a = pool_a.decode_step(0, qa, k, v)
-        monkeypatch.setenv("SKV_STEP_FUSED", "1")
+        skv_switch("SKV_STEP_FUSED", "1")
         before = L._lib.lib.skv_launch_count()
         out_b = pool_b.decode_step(0, qb, k, v)
         launches.append(L._lib.lib.skv_launch_count() - before)
@@ -388,7 +388,8 @@ def test_fused_append_step_matches_the_two_launch_step_and_the_oracle(monkeypatc
 
 
 def test_fused_gather_path_on_one_gpu_matches_plain_decode():
-    """world == 1 runs the same merge-kernel code (peer stores, ticket, flag, wait kernel) against local buffers."""
+    """world == 1 runs the same merge-kernel code (stores into the receive buffer, polling, unpacking) against
+    local buffers."""
     rng = np.random.default_rng(71)
     lens = [1, 40, 777, 2050, 0]
     pool, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, len(lens), 8, 128, 16, lens)
@@ -396,10 +397,10 @@ def test_fused_gather_path_on_one_gpu_matches_plain_decode():
     expect = pool.decode_attention(0, q)
     gather = L.PeerGather(L.HeadShard(0, 1, 32, 8), len(lens), 128, torch.bfloat16, torch.device(DEV))
     for _ in range(3):     # epochs 1..3 alternate between the two gathered buffers
-        view = pool.decode_attention_gather(0, q, gather)
+        view = pool.decode_attention_xchg(0, q, gather)
         torch.cuda.synchronize()
         assert torch.equal(view[0], expect)
-    assert int(gather.flags[0]) == 3 and pool.check_device_status() == 0
+    assert gather.epoch == 3 and pool.check_device_status() == 0
 
 
 def test_sequence_sharding_partials_merge_to_the_unsharded_result():

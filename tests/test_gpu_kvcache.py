@@ -405,7 +405,7 @@ def test_one_call_decode_step_of_the_cache_equals_update_then_attention():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float32, 64)])
-def test_vectorised_append_writes_the_same_bytes_as_the_scalar_kernel(monkeypatch, dtype, D):
+def test_vectorised_append_writes_the_same_bytes_as_the_scalar_kernel(skv_switch, dtype, D):
     """The 16-byte-access append (one block per token, cos/sin shared by all heads) against the element-wise
     kernel: stored K/V, rotated q and lengths bit-identical, with ragged starts and several tokens per call."""
     rng = np.random.default_rng(77)
@@ -414,7 +414,7 @@ def test_vectorised_append_writes_the_same_bytes_as_the_scalar_kernel(monkeypatc
     inv = L.rope_inv_freq(D, 500000.0)
     results = []
     for scalar in ("1", "0"):
-        monkeypatch.setenv("SKV_APPEND_SCALAR", scalar)
+        skv_switch("SKV_APPEND_SCALAR", scalar)
         pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=32, max_seqs=B,
                                            max_pages_per_seq=8, page_size=P, dtype=dtype))
         pool.set_rope(inv, 2.0)

@@ -1,0 +1,333 @@
+"""The one-call decode step (RoPE + append + attention + exchange) through the C ABI: every form of it against the
+append + attention pair, the oracle, and itself (packed vs strided rows, early start vs ordinary launch, exchange
+vs plain output, inline vs uploaded row metadata, default vs side stream)."""
+import numpy as np
+import pytest
+import torch
+
+import lokahi_b200 as L
+from oracle import attention as oattn
+from oracle import paged as opaged
+from parity import TOL_BF16, assert_parity, bf16_round, parity_errors, to_np
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+HQ, HKV, D, P, THETA = 32, 8, 128, 16, 500000.0
+
+
+def _t(a, dtype=torch.bfloat16):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV).to(dtype)
+
+
+def _pool(seed, lens, headroom, *, hkv=HKV, n_pages=None, assign=True):
+    """Pool with `len(lens)` sequences of the given lengths, pages dealt from a seeded permutation and filled with
+    bf16-rounded N(0,1); identical for identical arguments."""
+    rng = np.random.default_rng(seed)
+    n = len(lens)
+    pps = max(1, max(-(-(t + 1 + headroom) // P) for t in lens))
+    n_pages = n_pages or n * pps + 3
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=hkv, head_dim=D, num_pages=n_pages, max_seqs=n,
+                                       max_pages_per_seq=pps, page_size=P, dtype=torch.bfloat16, rope_theta=THETA))
+    perm = rng.permutation(n_pages)
+    k_ref = bf16_round(rng.standard_normal((n_pages, hkv, P, D), dtype=np.float32))
+    v_ref = bf16_round(rng.standard_normal((n_pages, hkv, P, D), dtype=np.float32))
+    table = np.full((n, pps), -1, np.int32)
+    for s in range(n):
+        assert pool.alloc_sequence() == s
+        if assign:
+            table[s] = perm[s * pps:(s + 1) * pps]
+            pool.set_page_table(s, table[s].tolist(), lens[s])
+    kp, vp = pool.layer_views(0)
+    kp.copy_(_t(k_ref)); vp.copy_(_t(v_ref))
+    return pool, k_ref, v_ref, table
+
+
+def _inputs(seed, steps, n, hq=HQ, hkv=HKV):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    mk = lambda *s: torch.randn(s, generator=g, device=DEV).to(torch.bfloat16)
+    return mk(steps, n, hq, D), mk(steps, n, hkv, D), mk(steps, n, hkv, D)
+
+
+def _same_pages(pool_a, pool_b, n, final):
+    ka, va = pool_a.gather(0, n_seqs=n)
+    kb, vb = pool_b.gather(0, n_seqs=n)
+    for i in range(n):
+        assert torch.equal(ka[i, :, :final[i]], kb[i, :, :final[i]]) and torch.equal(va[i, :, :final[i]], vb[i, :, :final[i]]), \
+            f"stored pages of sequence {i} differ"
+
+
+LENS = [0, 5, 15, 16, 255, 256, 300, 1023, 2047, 2048]
+
+
+@pytest.mark.parametrize("mode", ["head_gather", "seq_merge"])
+def test_step_with_exchange_on_one_gpu_equals_the_plain_step(mode):
+    """world == 1 runs the whole exchange code of the merge kernel (self-validating stores into the receive
+    buffer, polling, unpacking; for the sequence merge also the owner's merge and its broadcast) against this GPU's
+    own memory: 20 steps across page, chunk and empty-sequence boundaries, result view, rotated q, lengths and
+    stored pages bit-equal to the plain step."""
+    n, steps = len(LENS), 20
+    pool_a, *_ = _pool(56, LENS, steps)
+    pool_b, *_ = _pool(56, LENS, steps)
+    if mode == "head_gather":
+        ex = L.PeerGather(L.HeadShard(0, 1, HQ, HKV), n, D, torch.bfloat16, torch.device(DEV))
+    else:
+        ex = L.PeerSeqMerge(0, 1, n, HQ, D, torch.bfloat16, torch.device(DEV))
+    q_all, k_all, v_all = _inputs(7, steps, n)
+    for s in range(steps):
+        qa, qb = q_all[s].clone(), q_all[s].clone()
+        before = L._lib.lib.skv_launch_count()
+        out_a = pool_a.decode_step(0, qa, k_all[s], v_all[s])
+        view = pool_b.decode_step(0, qb, k_all[s], v_all[s], exchange=ex)
+        assert L._lib.lib.skv_launch_count() - before == 4, "two launches per step, with or without the exchange"
+        got = view[0] if mode == "head_gather" else view
+        assert torch.equal(got, out_a), f"step {s}"
+        assert torch.equal(qa, qb)
+        assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0))
+    _same_pages(pool_a, pool_b, n, [t + steps for t in LENS])
+    assert pool_a.check_device_status() == 0 and pool_b.check_device_status() == 0
+    # attention without the append through the same exchange
+    q = q_all[0]
+    view = pool_b.decode_attention_xchg(0, q, ex)
+    assert torch.equal(view[0] if mode == "head_gather" else view, pool_a.decode_attention(0, q))
+    # a sequence list in another order
+    ids = [7, 2, 9]
+    qa, qb = q_all[1, :3].clone(), q_all[1, :3].clone()
+    k3, v3 = k_all[1, :3].contiguous(), v_all[1, :3].contiguous()
+    if mode == "head_gather":
+        ex3 = L.PeerGather(L.HeadShard(0, 1, HQ, HKV), 3, D, torch.bfloat16, torch.device(DEV))
+    else:
+        ex3 = L.PeerSeqMerge(0, 1, 3, HQ, D, torch.bfloat16, torch.device(DEV))
+    out_a = pool_a.decode_step(0, qa, k3, v3, seq_ids=ids)
+    view = pool_b.decode_step(0, qb, k3, v3, seq_ids=ids, exchange=ex3)
+    assert torch.equal(view[0] if mode == "head_gather" else view, out_a)
+    assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
+
+
+def test_consecutive_steps_that_start_early_are_bit_identical():
+    """With `consecutive=True` and inputs that were complete beforehand the split-K kernel of a step runs ahead of
+    the previous step's merge kernel.  40 steps enqueued back to back without a host wait, against the same steps
+    launched the ordinary way: outputs, rotated q, lengths and pages bit-equal.  Then steps whose q IS the previous
+    step's rotated q (the library has to notice and fall back) give what the ordinary launch gives."""
+    n, steps = len(LENS), 40
+    pool_a, *_ = _pool(57, LENS, steps + 8)
+    pool_b, *_ = _pool(57, LENS, steps + 8)
+    q_all, k_all, v_all = _inputs(8, steps, n)
+    qa_all, qb_all = q_all.clone(), q_all.clone()
+    out_a, out_b = torch.empty_like(q_all), torch.empty_like(q_all)
+    torch.cuda.synchronize()
+    for s in range(steps):
+        pool_a.decode_step(0, qa_all[s], k_all[s], v_all[s], out=out_a[s])
+    for s in range(steps):
+        pool_b.decode_step(0, qb_all[s], k_all[s], v_all[s], out=out_b[s], consecutive=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b) and torch.equal(qa_all, qb_all)
+    assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0))
+    _same_pages(pool_a, pool_b, n, [t + steps for t in LENS])
+    # aliasing: the rotated q of one step is the input of the next
+    qa, qb = q_all[0].clone(), q_all[0].clone()
+    oa, ob = torch.empty_like(qa), torch.empty_like(qb)
+    torch.cuda.synchronize()
+    for s in range(4):
+        pool_a.decode_step(0, qa, k_all[s], v_all[s], out=oa)
+    for s in range(4):
+        pool_b.decode_step(0, qb, k_all[s], v_all[s], out=ob, consecutive=True)
+    torch.cuda.synchronize()
+    assert torch.equal(qa, qb) and torch.equal(oa, ob)
+    # with the exchange (world == 1) as well; its two result buffers alternate, so the last two views stay intact
+    ex = L.PeerGather(L.HeadShard(0, 1, HQ, HKV), n, D, torch.bfloat16, torch.device(DEV))
+    views = []
+    qa_all, qb_all = q_all.clone(), q_all.clone()
+    torch.cuda.synchronize()
+    for s in range(4):
+        pool_a.decode_step(0, qa_all[s], k_all[s], v_all[s], out=out_a[s])
+    for s in range(4):
+        views.append(pool_b.decode_step(0, qb_all[s], k_all[s], v_all[s], exchange=ex, consecutive=True))
+    torch.cuda.synchronize()
+    for s in (2, 3):
+        assert torch.equal(views[s][0], out_a[s])
+    assert pool_a.check_device_status() == 0 and pool_b.check_device_status() == 0
+
+
+def test_step_takes_strided_rows_of_one_fused_projection_output():
+    """q, k and v as slices of one [n, (Hq + 2 Hkv) * D] buffer (the output of one fused QKV projection) and a
+    strided output: identical to the packed call, and the bytes between the rows are left alone."""
+    lens = [3, 16, 700, 1024, 90]
+    n = len(lens)
+    pool_a, *_ = _pool(58, lens, 8)
+    pool_b, *_ = _pool(58, lens, 8)
+    g = torch.Generator(device=DEV).manual_seed(9)
+    width = (HQ + 2 * HKV) * D
+    for s in range(3):
+        fused = torch.randn((n, width), generator=g, device=DEV).to(torch.bfloat16)
+        keep = fused.clone()
+        q = fused[:, :HQ * D].view(n, HQ, D)
+        k = fused[:, HQ * D:(HQ + HKV) * D].view(n, HKV, D)
+        v = fused[:, (HQ + HKV) * D:].view(n, HKV, D)
+        assert not q.is_contiguous()
+        qa, ka, va = q.contiguous(), k.contiguous(), v.contiguous()
+        out_wide = torch.full((n, HQ * D + 64), 3.0, device=DEV, dtype=torch.bfloat16)
+        out_a = pool_a.decode_step(0, qa, ka, va)
+        pool_b.decode_step(0, q, k, v, out=out_wide[:, :HQ * D].view(n, HQ, D))
+        assert torch.equal(out_wide[:, :HQ * D].reshape(n, HQ, D), out_a) and bool((out_wide[:, HQ * D:] == 3.0).all())
+        assert torch.equal(q, qa), "rotated in place inside the fused buffer"
+        assert torch.equal(fused[:, HQ * D:], keep[:, HQ * D:]), "k and v slices are read only"
+    _same_pages(pool_a, pool_b, n, [t + 3 for t in lens])
+    assert pool_b.check_device_status() == 0
+
+
+def test_step_grows_pages_through_the_allocator_and_matches_the_oracle():
+    """Sequences that start empty and grow by steps only: every 16th step a sequence takes a fresh page from the
+    allocator (a page-table update between the two kernels).  Page tables equal the allocator model, lengths equal,
+    last outputs equal the oracle on the logical history."""
+    n, steps = 5, 40
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=HKV, head_dim=D, num_pages=n * 4, max_seqs=n,
+                                       max_pages_per_seq=4, page_size=P, dtype=torch.bfloat16, rope_theta=THETA))
+    model = opaged.PagePoolModel(1, n * 4, P, n, 4)
+    for s in range(n):
+        assert pool.alloc_sequence() == model.alloc_sequence() == s
+    q_all, k_all, v_all = _inputs(10, steps, n)
+    hist_k = np.zeros((n, HKV, steps, D), np.float32)
+    hist_v = np.zeros((n, HKV, steps, D), np.float32)
+    for s in range(steps):
+        q = q_all[s].clone()
+        out = pool.decode_step(0, q, k_all[s], v_all[s])
+        for i in range(n):
+            model.append(0, i, s, 1)
+        hist_k[:, :, s] = bf16_round(opaged.rope_rows(to_np(k_all[s]), np.full(n, s), THETA))
+        hist_v[:, :, s] = to_np(v_all[s])
+    torch.cuda.synchronize()
+    for i in range(n):
+        assert np.array_equal(pool.page_table(i), model.page_table[i, :model.num_seq_pages[i]])
+    assert list(pool.lengths(0)) == [steps] * n and pool.check_device_status() == 0
+    # the kernel's sincosf and NumPy's cos/sin may differ in the last float32 bit, which now and then moves a bf16
+    # rounding: the rotated q agrees with the oracle's RoPE to one bf16 step
+    qr = bf16_round(opaged.rope_rows(to_np(q_all[steps - 1]), np.full(n, steps - 1), THETA))
+    assert np.all(np.abs(to_np(q) - qr) <= np.abs(qr) * 2.0 ** -7 + 1e-30), "rotated q against the oracle's RoPE"
+    qr = to_np(q)
+    for i in range(n):
+        ref = oattn.chunked_grouped_attention(qr[i][None, :, None, :], hist_k[i:i + 1], hist_v[i:i + 1],
+                                              query_positions=np.array([steps - 1], dtype=np.int32))
+        assert_parity(out[i], ref[0, :, 0, :], TOL_BF16, f"sequence {i}")
+    kd, vd = pool.gather(0, n_seqs=n)
+    assert np.array_equal(to_np(vd), hist_v), "stored V bytes"
+    assert np.all(np.abs(to_np(kd) - hist_k) <= np.abs(hist_k) * 2.0 ** -7 + 1e-30), "stored (rotated) K against the oracle's RoPE"
+
+
+@pytest.mark.parametrize("split", ["interleaved", "contiguous"])
+def test_sequence_sharded_step_on_three_pools_merges_to_the_unsharded_step(split):
+    """Three pools on one GPU stand in for three ranks that each hold a share of every sequence's tokens.  Each
+    step every pool rotates q at the token's global position, the owner of that position stores the token, all
+    write un-normalised partial rows, and the merge of the three equals the step on one pool that holds everything
+    (bf16 tolerance: the partial sums are formed in a different order) and the oracle."""
+    R, steps = 3, 20
+    lens = [0, 5, 40, 100, 517, 1400]
+    n = len(lens)
+    if split == "interleaved":
+        shards = [L.InterleavedShard(r, R, 32, P) for r in range(R)]
+        pos_of = lambda sh, t: sh.global_positions(t)
+        count = lambda sh, t: sh.local_count(t)
+    else:
+        shards = [L.SequenceShard(r, R, 512, P) for r in range(R)]
+        pos_of = lambda sh, t: list(range(sh.local_range(t)[0], sh.local_range(t)[0] + sh.local_range(t)[1]))
+        count = lambda sh, t: sh.local_range(t)[1]
+    rng = np.random.default_rng(77)
+    cap = max(lens) + steps
+    k_hist = [bf16_round(rng.standard_normal((HKV, cap, D), dtype=np.float32)) for _ in lens]
+    v_hist = [bf16_round(rng.standard_normal((HKV, cap, D), dtype=np.float32)) for _ in lens]
+
+    def make(positions_of):
+        pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=HKV, head_dim=D, num_pages=n * 100, max_seqs=n,
+                                           max_pages_per_seq=100, page_size=P, dtype=torch.bfloat16, rope_theta=THETA))
+        for s in range(n):
+            assert pool.alloc_sequence() == s
+            idx = positions_of(s)
+            if idx:
+                pool.append(0, _t(k_hist[s][None, :, idx]), _t(v_hist[s][None, :, idx]), seq_ids=[s], start_pos=[0])
+        return pool
+
+    whole = make(lambda s: list(range(lens[s])))
+    parts_pools = [make(lambda s, sh=sh: pos_of(sh, lens[s])) for sh in shards]
+    q_all, k_all, v_all = _inputs(11, steps, n)
+    for st in range(steps):
+        cur = [t + st for t in lens]
+        q_ref = q_all[st].clone()
+        ref = whole.decode_step(0, q_ref, k_all[st], v_all[st])
+        parts = []
+        for sh, pool in zip(shards, parts_pools):
+            q = q_all[st].clone()
+            store = [sh.owner(p) == sh.rank for p in cur]
+            parts.append(pool.decode_step(0, q, k_all[st], v_all[st], positions=cur, store=store, partial=True))
+            assert torch.equal(q, q_ref), "every rank rotates q at the global position"
+            assert list(pool.lengths(0)) == [count(sh, t + 1) for t in cur]
+        merged = L.merge_partials(torch.stack(parts).contiguous())
+        assert parity_errors(merged, to_np(ref))[0] <= TOL_BF16, f"step {st}"
+    for pool in parts_pools:
+        assert pool.check_device_status() == 0
+    # the union of the shards' pages is the unsharded history, byte for byte
+    kw, vw = whole.gather(0, n_seqs=n)
+    for sh, pool in zip(shards, parts_pools):
+        kl, vl = pool.gather(0, n_seqs=n)
+        for s in range(n):
+            idx = pos_of(sh, lens[s] + steps)
+            assert torch.equal(kl[s, :, :len(idx)], kw[s][:, idx]) and torch.equal(vl[s, :, :len(idx)], vw[s][:, idx])
+    # last step against the oracle on the logical history
+    final = [t + steps for t in lens]
+    k_np, v_np = to_np(kw), to_np(vw)
+    for i in (0, 3, 5):
+        o = oattn.chunked_grouped_attention(to_np(q_ref[i])[None, :, None, :], k_np[i:i + 1, :, :final[i]], v_np[i:i + 1, :, :final[i]],
+                                            query_positions=np.array([final[i] - 1], dtype=np.int32))
+        assert_parity(merged[i], o[0, :, 0, :], TOL_BF16, f"merged step vs oracle, sequence {i}")
+
+
+def test_step_with_more_rows_than_the_kernel_parameters_hold():
+    """300 sequences: the per-row metadata no longer fits the kernel parameters and is uploaded instead; same
+    results as the append + attention pair."""
+    n = 300
+    rng = np.random.default_rng(5)
+    lens = [int(x) for x in rng.integers(0, 70, size=n)]
+    pool_a, *_ = _pool(59, lens, 4, hkv=2)
+    pool_b, *_ = _pool(59, lens, 4, hkv=2)
+    q_all, k_all, v_all = _inputs(12, 2, n, hq=8, hkv=2)
+    for s in range(2):
+        qa, qb = q_all[s].clone(), q_all[s].clone()
+        pool_a.append(0, k_all[s], v_all[s], start_pos=[t + s for t in lens], rope_k=True, q=qa, layout="bhd")
+        out_a = pool_a.decode_attention(0, qa)
+        out_b = pool_b.decode_step(0, qb, k_all[s], v_all[s])
+        assert torch.equal(qa, qb) and parity_errors(out_b, to_np(out_a))[0] <= TOL_BF16
+    assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0))
+    _same_pages(pool_a, pool_b, n, [t + 2 for t in lens])
+    assert pool_b.check_device_status() == 0
+
+
+def test_pool_driven_from_a_side_stream():
+    """Everything, set-up included, enqueued on a non-default (non-blocking) torch stream: table and length changes
+    are published on that stream, so the kernels behind them see them.  Results equal the default-stream run."""
+    lens = [5, 300, 1023]
+    n, steps = len(lens), 6
+    q_all, k_all, v_all = _inputs(13, steps, n)
+    pool_a, *_ = _pool(60, lens, steps)
+    ref = [pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(steps)]
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=DEV)
+    with torch.cuda.stream(side):
+        pool_b, *_ = _pool(60, lens, steps)
+        got = [pool_b.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(steps)]
+        pool_b.free_sequence(1)
+        assert pool_b.alloc_sequence() == 1
+        pool_b.reserve(1, 40)
+        kv = torch.zeros((1, HKV, 33, D), device=DEV, dtype=torch.bfloat16)
+        pool_b.append(0, kv, kv, seq_ids=[1], start_pos=[0])
+        tail = pool_b.decode_step(0, q_all[0, 1:2].clone(), k_all[0, 1:2].contiguous(), v_all[0, 1:2].contiguous(), seq_ids=[1])
+        assert pool_b.check_device_status() == 0
+    side.synchronize()
+    for s in range(steps):
+        assert torch.equal(ref[s], got[s])
+    assert list(pool_b.lengths(0)) == [lens[0] + steps, 34, lens[2] + steps] and bool(torch.isfinite(tail.float()).all())
+
+
+def test_dense_attention_reports_through_its_status_word():
+    g = torch.Generator(device=DEV).manual_seed(3)
+    q = torch.randn((1, 8, 256, 128), generator=g, device=DEV).to(torch.bfloat16)
+    k = torch.randn((1, 2, 256, 128), generator=g, device=DEV).to(torch.bfloat16)
+    out = L.chunked_grouped_attention(q, k, k)
+    assert L.check_dense_attention_status(DEV) == 0 and bool(torch.isfinite(out.float()).all())

@@ -154,3 +154,71 @@ def test_truncate_and_config_validation():
         L.PagedKVConfig(num_layers=0, num_kv_heads=1, head_dim=8, num_pages=1, max_seqs=1, max_pages_per_seq=1)
     with pytest.raises(ValueError, match="even"):
         L.PagedKVConfig(num_layers=1, num_kv_heads=1, head_dim=7, num_pages=1, max_seqs=1, max_pages_per_seq=1)
+
+
+def test_misaligned_workspace_is_refused_before_anything_is_launched():
+    """The merge kernel reads the workspace with 8- and 16-byte loads: a pointer that is not 16-byte aligned is an
+    argument error from every entry point that takes one, not a device fault."""
+    import ctypes as C
+    from lokahi_b200 import _lib
+    pool, _ = make()
+    s = pool.alloc_sequence()
+    pool.append(0, None, None, n_new=3, seq_ids=[s], start_pos=[0])
+    before = _lib.lib.skv_launch_count()
+    odd = 0x1004                          # never dereferenced: the call is refused first
+    ids = _lib.i32_array([s])
+    assert _lib.lib.skv_decode_attn(pool._h, 0, ids, 1, 0x2000, 0x3000, None, 2, 1e-12, odd, 1 << 20, None) == _lib.ERR_BAD_ARG
+    assert b"16-byte aligned" in _lib.lib.skv_last_error(pool._h)
+    assert _lib.lib.skv_decode_partial(pool._h, 0, ids, 1, 0x2000, None, 2, odd, 1 << 20, 0x3000, None) == _lib.ERR_BAD_ARG
+    x = _lib.SkvExchange(mode=_lib.XCHG_HEAD_GATHER, rank=0, world=1, epoch=1)
+    assert _lib.lib.skv_decode_attn_xchg(pool._h, 0, ids, 1, 0x2000, None, 2, 1e-12, odd, 1 << 20, C.byref(x), None) == _lib.ERR_BAD_ARG
+    a = _lib.SkvStepArgs(layer=0, n_seqs=1, q=0x2000, k=0x2000, v=0x2000, out=0x3000, n_q_heads=2, eps=1e-12,
+                         workspace=odd, workspace_bytes=1 << 20)
+    a.seq_ids = ids
+    assert _lib.lib.skv_decode_step_ex(pool._h, C.byref(a), None) == _lib.ERR_BAD_ARG
+    assert b"16-byte aligned" in _lib.lib.skv_last_error(pool._h)
+    assert _lib.lib.skv_launch_count() == before and pool.length(0, s) == 3
+
+
+def test_pools_beyond_the_token_limit_per_sequence_are_refused_at_creation():
+    """The split-K plan gives a sequence at most 128 chunks of 2048 tokens; a page-table row that could hold more
+    used to be accepted and then failed at every decode launch."""
+    from lokahi_b200 import _lib
+    ok = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=1, head_dim=8, num_pages=4, max_seqs=1,
+                                     max_pages_per_seq=_lib.MAX_TOKENS_PER_SEQ // 16, page_size=16, device=-1))
+    assert _lib.lib.skv_decode_workspace_bytes(ok._h, 1, 1) == 128 * (8 + 2) * 4
+    with pytest.raises(NotImplementedError, match="exceeds 262144 tokens per sequence"):
+        L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=1, head_dim=8, num_pages=4, max_seqs=1,
+                                    max_pages_per_seq=_lib.MAX_TOKENS_PER_SEQ // 16 + 1, page_size=16, device=-1))
+
+
+def test_step_bookkeeping_on_a_host_only_pool_and_exchange_sizes():
+    """The one-call step does the same host bookkeeping as append (lengths, page growth, replay-free), rejects a
+    repeated sequence and half-given sharding arguments; exchange buffer sizes follow the documented layout."""
+    import ctypes as C
+    from lokahi_b200 import _lib
+    pool, model = make()
+    pool.set_rope(L.rope_inv_freq(8, 10000.0))
+    for _ in range(3):
+        assert pool.alloc_sequence() == model.alloc_sequence()
+    a = _lib.SkvStepArgs(layer=1, n_seqs=2, n_q_heads=4, eps=1e-12)
+    a.seq_ids = _lib.i32_array([2, 0])
+    for step in range(6):                 # crosses a page boundary (page_size 4)
+        assert _lib.lib.skv_decode_step_ex(pool._h, C.byref(a), None) == _lib.OK
+        for s in (2, 0):
+            model.append(1, s, step, 1)
+        same_state(pool, model)
+    a.seq_ids = _lib.i32_array([1, 1])
+    assert _lib.lib.skv_decode_step_ex(pool._h, C.byref(a), None) == _lib.ERR_BAD_ARG
+    assert b"listed twice" in _lib.lib.skv_last_error(pool._h)
+    a.seq_ids = _lib.i32_array([1, 0])
+    a.positions = _lib.i32_array([5, 6])
+    assert _lib.lib.skv_decode_step_ex(pool._h, C.byref(a), None) == _lib.ERR_BAD_ARG
+    assert b"together" in _lib.lib.skv_last_error(pool._h)
+    same_state(pool, model)
+    # head gather: 2 halves x world x rows x (D * esize / 8) 16-byte words
+    assert _lib.lib.skv_exchange_bytes(_lib.XCHG_HEAD_GATHER, 8, 64, 4, 128, _lib.BF16) == 2 * 8 * 256 * 32 * 16
+    # sequence merge: world x ceil(rows / world) x (D + 2) / 2 partial words + rows x finished-row words
+    assert _lib.lib.skv_exchange_bytes(_lib.XCHG_SEQ_MERGE, 8, 64, 32, 128, _lib.BF16) == 2 * 16 * (8 * 256 * 65 + 2048 * 32)
+    assert _lib.lib.skv_exchange_bytes(3, 8, 64, 32, 128, _lib.BF16) == 0
+    assert _lib.lib.skv_exchange_bytes(_lib.XCHG_HEAD_GATHER, 9, 64, 32, 128, _lib.BF16) == 0
