@@ -488,7 +488,24 @@ def run_ours(args):
     ev_step = [torch.cuda.Event() for _ in range(2)]
     ev_done = [torch.cuda.Event() for _ in range(2)]
 
+    # the step calls on the two staging buffers, bound once (under sequence sharding one per step: positions differ)
+    e2e_bound = None
+    if mode != "nccl":
+        e2e_bound = []
+        for i in range(Ke):
+            if mode != "seq" and i >= 2:
+                e2e_bound.append(e2e_bound[i & 1])
+                continue
+            kw = {}
+            if mode == "seq":
+                kw["positions"], kw["store"] = positions_for(W + i)
+            if mode in ("fused", "seq"):
+                e2e_bound.append(pool.decode_step_binder(*views[i & 1], exchange=peer, **kw))
+            else:
+                e2e_bound.append(pool.decode_step_binder(*views[i & 1], out_d[i & 1], **kw))
+
     def e2e_run(count):
+        main_ptr = main.cuda_stream
         with torch.cuda.stream(up):
             qkv_d[0].copy_(qkv_h[0], non_blocking=True)
             ev_up[0].record(up)
@@ -503,7 +520,10 @@ def run_ours(args):
             main.wait_event(ev_up[b])
             if i >= 2:
                 main.wait_event(ev_done[b])                     # the result buffer of this parity has been read back
-            view = step(*views[b], False, W + i, out_d[b], gat_d[b])
+            if e2e_bound is not None:
+                view = e2e_bound[i](0, main_ptr)
+            else:
+                view = step(*views[b], False, W + i, out_d[b], gat_d[b])
             ev_free[b].record(main)
             ev_step[b].record(main)
             with torch.cuda.stream(down):

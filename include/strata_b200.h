@@ -224,10 +224,13 @@ typedef struct skv_step_args {
     const uint8_t* store;         /* host */
     /* SKV_STEP_CONSECUTIVE: the caller states that (1) nothing was enqueued on `stream` since this pool's previous
      * skv_decode_step* call on it, and (2) q, k, v and the pool's pages were complete before that call was made
-     * (they are not outputs of it).  The split-K kernel then runs ahead of the previous step's merge kernel and its
-     * exchange, and waits for it only where it stores its partials.  The library drops the flag by itself when
-     * the previous call on this pool was not a step on the same stream or when q, k, v overlap what that step
-     * wrote (its rotated q, its output). */
+     * (they are not outputs of it).  When that previous call was a step of the same layer over the same sequences in
+     * the same order, the split-K kernel of this step then runs beside the previous step's kernels: it starts while
+     * that step's last blocks drain, waits (bounded) for a per-(sequence, head) flag before it reads the one page row
+     * that step stored, and waits for that step's merge kernel and exchange only where it stores its own partials.
+     * The library drops the flag by itself when the previous call on this pool was not such a step on the same
+     * stream, when a page-table update has to run between the two, or when q, k, v overlap what that step wrote
+     * (its rotated q, its output).  SKV_STEP_EARLY=0 in the environment drops it always. */
     uint32_t flags;
 } skv_step_args;
 #define SKV_STEP_CONSECUTIVE 1u

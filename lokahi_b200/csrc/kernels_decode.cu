@@ -405,6 +405,31 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int P = pv.page_size;
+    if constexpr (FA) {
+        // The kernels of a step launch their dependents at once: the merge kernel's blocks are resident by the time
+        // this grid drains, and a following step that may start early fills the SMs this grid's tail leaves idle.
+        pdl_launch_dependents();
+        // Started beside the previous step: the newest token of this row (position len_old - 1) may still be on its
+        // way into the page.  The CTA whose chunk holds it waits for that step's flag (bounded) before any of its
+        // tiles are requested; every other CTA reads pages that were complete long before.
+        if (late_wait && (pos_raw & kRowWaitPrev) && len_old > 0 && len_old - 1 >= t0 && len_old - 1 < t0 + d.chunk_tokens) {
+            if (threadIdx.x == 0) {
+                const int32_t* flag = d.chain_flags + (int64_t)seq * pv.num_kv_heads + h;
+                const long long start = clock64();
+                int32_t seen;
+                for (;;) {
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                    if (seen - d.chain_wait >= 0) break;
+                    if (clock64() - start > 2000000000LL) {
+                        atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
+                        break;
+                    }
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");   // the row is read by the TMA unit (async proxy)
+            }
+            __syncthreads();
+        }
+    }
 
     // Q fragments: row g, 16-byte units 2c and 2c+1 of each 128-byte half (the K lane mapping).  The loads are
     // issued here, beside the page ids, and used after the first tiles have been requested.
@@ -512,7 +537,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid
         // llama_mlx.py:132-136, :172-182), and in the owning CTA the new token's rows.
         const int tid = threadIdx.x;
         if (tid < kMmaD / 2) {
-            float fpos = (float)(pos_raw & ~kRowNoStore);
+            float fpos = (float)(pos_raw & kRowPosMask);
             if (d.rope_scaling != 1.0f) fpos = __fdiv_rn(fpos, d.rope_scaling);
             float sn, cs;
             sincosf(__fmul_rn(fpos, my_inv_freq), &sn, &cs);
@@ -538,10 +563,15 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid
                     kdst[tid + 64] = k2;
                     vdst[tid] = v1;
                     vdst[tid + 64] = v2;
+                    __threadfence();   // ahead of the flag below, for a following step that runs beside this one
                 }
             }
         }
         __syncthreads();
+        if (owner && d.chain_flags && tid == 0) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(d.chain_flags + (int64_t)seq * pv.num_kv_heads + h), "r"(d.chain_epoch) : "memory");
+        }
     }
     finish_q();
     bool dead = false;
@@ -633,7 +663,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid
             issue(k + NS);
         }
     }
-    pdl_launch_dependents();   // the merge kernel may begin launching while this CTA combines and stores
+    if constexpr (!FA) pdl_launch_dependents();   // the merge kernel may begin launching while this CTA combines and stores
     if (dead) {
         if (lane == 0) atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
         // copies already issued for later tiles still target this CTA's shared memory: wait for them (bounded)
@@ -834,11 +864,12 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(const __grid_constan
                                                             const __grid_constant__ StepRows rows) {
     const PoolView& pv = d.pool;
     const int hq = blockIdx.x, i = blockIdx.y;
-    pdl_wait();
     // The next kernel in the stream (the following step's split-K kernel) either waits for this grid at its top or
-    // touches nothing this grid reads or writes until it does: letting it launch now hides its launch latency and,
-    // in the second case, its whole K/V stream.
+    // touches nothing this grid reads or writes until it does (and takes care of the one page row the split-K kernel
+    // ahead of this grid may still be storing): letting it launch now hides its launch latency and, in the second
+    // case, lets its K/V stream begin while that kernel's last blocks drain.
     pdl_launch_dependents();
+    pdl_wait();
     const int D = pv.head_dim;
     int seq, n_attend = 0;
     uint32_t pos_raw = 0;
@@ -914,7 +945,7 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(const __grid_constan
         // during a step (the kernels take it from `rows`), so one block per sequence can set it here.
         if (tid < D / 2) {
             T* qrow = reinterpret_cast<T*>(const_cast<void*>(d.q)) + (int64_t)i * d.q_stride + (int64_t)hq * D;
-            float fpos = (float)(pos_raw & ~kRowNoStore);
+            float fpos = (float)(pos_raw & kRowPosMask);
             if (d.rope_scaling != 1.0f) fpos = __fdiv_rn(fpos, d.rope_scaling);
             float sn, cs;
             sincosf(__fmul_rn(fpos, d.inv_freq[tid]), &sn, &cs);

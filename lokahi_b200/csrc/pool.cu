@@ -50,6 +50,7 @@ void read_switches() {
     w.prefill_generic = env_is("SKV_PREFILL_GENERIC", '1');
     w.append_scalar = env_is("SKV_APPEND_SCALAR", '1');
     w.pdl = !env_is("SKV_PDL", '0');
+    w.step_early = !env_is("SKV_STEP_EARLY", '0');
     g_switches = w;
 }
 }  // namespace
@@ -157,7 +158,8 @@ struct skv_pool {
     int32_t* d_page_table = nullptr;
     int32_t* d_lengths = nullptr;
     int32_t* d_status = nullptr;
-    int32_t* d_tickets = nullptr;        // [max_seqs][num_kv_heads] + 2 (gather, fused append), zero between decode calls
+    int32_t* d_tickets = nullptr;        // [max_seqs][num_kv_heads] + 2, zero between decode calls
+    int32_t* d_chain_flags = nullptr;    // [max_seqs][num_kv_heads]: epoch of the last step that stored a token there
     float* d_inv_freq = nullptr;
     // K and V pools as 2-D bf16 tensors [layers*pages*heads*page_size][head_dim] with [16][64] boxes
     alignas(64) CUtensorMap k_map;
@@ -188,6 +190,10 @@ struct skv_pool {
     bool last_step_valid = false;
     cudaStream_t last_step_stream = nullptr;
     long long last_step_mark = 0;
+    int32_t last_step_layer = -1;
+    std::vector<int32_t> last_step_seqs;         // the rows of that step, in order
+    std::vector<int32_t> last_step_store;        // and whether it stored a token for each
+    int32_t chain_epoch = 0;                     // grows by one per one-kernel step
     const char* last_w_lo[2] = {nullptr, nullptr};
     const char* last_w_hi[2] = {nullptr, nullptr};
 
@@ -457,6 +463,8 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
         CUDA_TRY(p, cudaMemset(p->d_status, 0, sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_tickets, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 2) * sizeof(int32_t)));
         CUDA_TRY(p, cudaMemset(p->d_tickets, 0, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 2) * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_chain_flags, (size_t)cfg->max_seqs * cfg->num_kv_heads * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMemset(p->d_chain_flags, 0, (size_t)cfg->max_seqs * cfg->num_kv_heads * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_inv_freq, (size_t)cfg->head_dim / 2 * sizeof(float)));
         CUDA_TRY(p, p->ring.init());
         CUDA_TRY(p, p->ring_copy.init(16));
@@ -499,6 +507,7 @@ int32_t skv_destroy(skv_pool* p) {
         cudaFree(p->d_lengths);
         cudaFree(p->d_status);
         cudaFree(p->d_tickets);
+        cudaFree(p->d_chain_flags);
         cudaFree(p->d_inv_freq);
     }
     delete p;
@@ -1140,7 +1149,8 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
         }
         const int32_t cur = p->len(layer, s);
         const int32_t stores = a.store ? (a.store[i] ? 1 : 0) : 1;
-        if (a.positions && a.positions[i] < 0) return p->fail(SKV_ERR_BAD_ARG, "position of row %d is negative", i);
+        if (a.positions && (a.positions[i] < 0 || (uint32_t)a.positions[i] > kRowPosMask))
+            return p->fail(SKV_ERR_BAD_ARG, "position of row %d is outside [0, 2^30)", i);
         const int32_t need = (cur + stores + P - 1) / P;
         if (need > p->cfg.max_pages_per_seq)
             return p->fail(SKV_ERR_OUT_OF_PAGES, "sequence %d needs %d pages, row holds %d", s, need, p->cfg.max_pages_per_seq);
@@ -1172,9 +1182,14 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     const char* k_hi = k_lo + ((int64_t)(n_seqs - 1) * k_stride + (int64_t)Hkv * Dh) * 2;
     const char* v_lo = (const char*)a.v;
     const char* v_hi = v_lo + ((int64_t)(n_seqs - 1) * v_stride + (int64_t)Hkv * Dh) * 2;
-    bool early = (a.flags & SKV_STEP_CONSECUTIVE) && p->last_step_valid && p->last_step_stream == stream &&
+    bool early = (a.flags & SKV_STEP_CONSECUTIVE) && switches().step_early && p->last_step_valid && p->last_step_stream == stream &&
                  p->last_step_mark == g_launches.load(std::memory_order_relaxed) && !p->copy_pending &&
-                 p->deferred_updates.empty();
+                 p->deferred_updates.empty() && inline_rows && p->last_step_layer == layer &&
+                 (int32_t)p->last_step_seqs.size() == n_seqs;
+    // ... and it then runs beside that step's split-K kernel too, which is only sound for the same rows of the same
+    // layer: the one page row that kernel may still be storing is guarded by a flag per (sequence, head)
+    for (int32_t i = 0; early && i < n_seqs; ++i)
+        if (p->last_step_seqs[i] != (a.seq_ids ? a.seq_ids[i] : i)) early = false;
     for (int w = 0; early && w < 2; ++w)
         if (overlaps(p->last_w_lo[w], p->last_w_hi[w], q_lo, q_hi) || overlaps(p->last_w_lo[w], p->last_w_hi[w], k_lo, k_hi) ||
             overlaps(p->last_w_lo[w], p->last_w_hi[w], v_lo, v_hi))
@@ -1200,7 +1215,8 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     for (int32_t i = 0; i < n_seqs; ++i) {
         const int32_t s = a.seq_ids ? a.seq_ids[i] : i;
         const int32_t cur = p->len(layer, s);
-        const uint32_t pos = (uint32_t)(a.positions ? a.positions[i] : cur) | (p->step_store[i] ? 0u : kRowNoStore);
+        const uint32_t pos = (uint32_t)(a.positions ? a.positions[i] : cur) | (p->step_store[i] ? 0u : kRowNoStore) |
+                             ((early && p->last_step_store[i]) ? kRowWaitPrev : 0u);
         if (inline_rows) {
             R.seq[i] = s;
             R.len[i] = cur;
@@ -1257,6 +1273,9 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     D.inv_freq = p->d_inv_freq;
     D.rope_scaling = p->rope_scaling;
     D.early_start = early ? 1 : 0;
+    D.chain_flags = p->d_chain_flags;
+    D.chain_wait = p->chain_epoch;
+    D.chain_epoch = ++p->chain_epoch;
     D.rows = &R;
     if (a.xchg || a.partial_out) D.out = nullptr;
     D.partial_out = a.partial_out;
@@ -1281,6 +1300,10 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     }
     p->last_step_stream = stream;
     p->last_step_mark = g_launches.load(std::memory_order_relaxed);
+    p->last_step_layer = layer;
+    p->last_step_seqs.resize(n_seqs);
+    for (int32_t i = 0; i < n_seqs; ++i) p->last_step_seqs[i] = a.seq_ids ? a.seq_ids[i] : i;
+    p->last_step_store.assign(p->step_store.begin(), p->step_store.end());
     p->last_step_valid = true;
     return SKV_OK;
 }

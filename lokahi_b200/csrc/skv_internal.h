@@ -90,6 +90,9 @@ struct ExchangeView {
 #endif
 constexpr int kInlineRows = SKV_INLINE_ROWS;
 constexpr uint32_t kRowNoStore = 0x80000000u;   // bit 31 of pos: this pool does not store the step's token
+constexpr uint32_t kRowWaitPrev = 0x40000000u;  // bit 30 of pos: the previous step (which may still be running) stored this
+                                                // row's last token here: wait for its flag before reading that page row
+constexpr uint32_t kRowPosMask = 0x3fffffffu;
 struct StepRows {
     const int32_t* dev;           // nullptr, or device [3][n_seqs]: seq, len, pos
     int32_t seq[kInlineRows];     // sequence id of row i
@@ -132,8 +135,13 @@ struct DecodeLaunch {
     int64_t k_stride, v_stride;
     const float* inv_freq;       // [head_dim / 2]
     float rope_scaling;
-    int32_t early_start;         // 1: the split-K kernel of a step may run ahead of the previous kernel in the stream
-                                 // up to the point where it stores its partials (the caller vouched for its inputs)
+    int32_t early_start;         // 1: the split-K kernel of a step may run beside the previous step's kernels up to the
+                                 // point where it stores its partials (the caller vouched for its inputs); rows marked
+                                 // kRowWaitPrev wait for chain_flags[seq][head] >= chain_wait before they read the page
+                                 // row that step stored
+    int32_t* chain_flags;        // [max_seqs][kv_heads]: epoch of the last step whose CTA stored a token for (seq, head)
+    int32_t chain_epoch;         // this step's epoch, written to chain_flags by every storing CTA
+    int32_t chain_wait;          // epoch of the previous step
     const StepRows* rows;        // host pointer; copied into the kernel parameters at launch
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
@@ -196,6 +204,7 @@ struct Switches {
     int prefill_generic;   // SKV_PREFILL_GENERIC == "1"
     int append_scalar;     // SKV_APPEND_SCALAR == "1"
     int pdl;               // SKV_PDL != "0"
+    int step_early;        // SKV_STEP_EARLY != "0"
 };
 const Switches& switches();
 void reload_switches();
