@@ -4,6 +4,7 @@ surface of the Strata / ``ollm`` runtime.  Importing the package needs the built
 from ._lib import DeviceFlagError, NotResidentError, OutOfPagesError
 from .attention import PagedView, check_dense_attention_status, chunked_grouped_attention, chunked_grouped_attention_no_mask
 from .backend import B200Backend, BackendError, register
+from .batching import BatchedDecodeLoop, DecodeRequest
 from .decoder import PagedDecoder
 from .generation import greedy_generate
 from .tracing import TensorTracer, TraceEvent
@@ -17,7 +18,7 @@ from .pool import PagedKVConfig, PagedPool, merge_partials, rope_inv_freq, rope_
 register()
 
 __all__ = [
-    "B200Backend", "BudgetExceededError", "InterleavedShard", "PeerExchange", "PeerSeqMerge", "check_dense_attention_status", "TensorTracer", "TraceEvent", "add_rms_norm", "rms_norm", "swiglu", "GroupState", "KVPageLease", "KVPagePrefetcher", "KVPrefetchSnapshot", "KVPageResidency", "HeadShard", "PeerGather", "SequenceShard", "gather_head_outputs", "merge_partials", "sequence_sharded_decode", "BackendError", "DeviceFlagError", "NotResidentError", "OutOfPagesError", "PagedKVCache", "PagedQwen3NextDiskCache",
+    "B200Backend", "BatchedDecodeLoop", "DecodeRequest", "BudgetExceededError", "InterleavedShard", "PeerExchange", "PeerSeqMerge", "check_dense_attention_status", "TensorTracer", "TraceEvent", "add_rms_norm", "rms_norm", "swiglu", "GroupState", "KVPageLease", "KVPagePrefetcher", "KVPrefetchSnapshot", "KVPageResidency", "HeadShard", "PeerGather", "SequenceShard", "gather_head_outputs", "merge_partials", "sequence_sharded_decode", "BackendError", "DeviceFlagError", "NotResidentError", "OutOfPagesError", "PagedKVCache", "PagedQwen3NextDiskCache",
     "PagedDecoder", "PagedKVConfig", "PagedLlamaDiskCache", "PagedPool", "PagedView", "chunked_grouped_attention",
     "chunked_grouped_attention_no_mask", "create_paged_kv_cache", "greedy_generate", "register",
     "rope_inv_freq", "rope_rows",

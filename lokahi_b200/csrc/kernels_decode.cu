@@ -409,17 +409,18 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid
         // The kernels of a step launch their dependents at once: the merge kernel's blocks are resident by the time
         // this grid drains, and a following step that may start early fills the SMs this grid's tail leaves idle.
         pdl_launch_dependents();
-        // Started beside the previous step: the newest token of this row (position len_old - 1) may still be on its
-        // way into the page.  The CTA whose chunk holds it waits for that step's flag (bounded) before any of its
-        // tiles are requested; every other CTA reads pages that were complete long before.
+        // Started beside earlier steps: the newest token of this row (position len_old - 1) may still be on its
+        // way into the page.  The CTA whose chunk holds it waits (bounded) until the step that stores it has
+        // published the row's length, before any of its tiles are requested; every other CTA reads pages that were
+        // complete long before.
         if (late_wait && (pos_raw & kRowWaitPrev) && len_old > 0 && len_old - 1 >= t0 && len_old - 1 < t0 + d.chunk_tokens) {
             if (threadIdx.x == 0) {
-                const int32_t* flag = d.chain_flags + (int64_t)seq * pv.num_kv_heads + h;
+                const int32_t* flag = d.stored_len + ((int64_t)d.layer * pv.max_seqs + seq) * pv.num_kv_heads + h;
                 const long long start = clock64();
                 int32_t seen;
                 for (;;) {
                     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-                    if (seen - d.chain_wait >= 0) break;
+                    if (seen >= len_old) break;
                     if (clock64() - start > 2000000000LL) {
                         atomicOr(pv.status, FLAG_WAIT_TIMEOUT);
                         break;
@@ -563,14 +564,15 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid
                     kdst[tid + 64] = k2;
                     vdst[tid] = v1;
                     vdst[tid + 64] = v2;
-                    __threadfence();   // ahead of the flag below, for a following step that runs beside this one
+                    __threadfence();   // ahead of the flag below, for a later step that runs beside this one
                 }
             }
         }
         __syncthreads();
-        if (owner && d.chain_flags && tid == 0) {
+        if (owner && d.stored_len && tid == 0) {
             asm volatile("fence.proxy.async;" ::: "memory");
-            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(d.chain_flags + (int64_t)seq * pv.num_kv_heads + h), "r"(d.chain_epoch) : "memory");
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(d.stored_len + ((int64_t)d.layer * pv.max_seqs + seq) * pv.num_kv_heads + h),
+                         "r"(len_old + 1) : "memory");
         }
     }
     finish_q();

@@ -159,7 +159,7 @@ struct skv_pool {
     int32_t* d_lengths = nullptr;
     int32_t* d_status = nullptr;
     int32_t* d_tickets = nullptr;        // [max_seqs][num_kv_heads] + 2, zero between decode calls
-    int32_t* d_chain_flags = nullptr;    // [max_seqs][num_kv_heads]: epoch of the last step that stored a token there
+    int32_t* d_stored_len = nullptr;     // [num_layers][max_seqs][num_kv_heads]: see DecodeLaunch::stored_len
     float* d_inv_freq = nullptr;
     // K and V pools as 2-D bf16 tensors [layers*pages*heads*page_size][head_dim] with [16][64] boxes
     alignas(64) CUtensorMap k_map;
@@ -190,10 +190,10 @@ struct skv_pool {
     bool last_step_valid = false;
     cudaStream_t last_step_stream = nullptr;
     long long last_step_mark = 0;
-    int32_t last_step_layer = -1;
-    std::vector<int32_t> last_step_seqs;         // the rows of that step, in order
-    std::vector<int32_t> last_step_store;        // and whether it stored a token for each
-    int32_t chain_epoch = 0;                     // grows by one per one-kernel step
+    // [num_layers][max_seqs]: the length a one-kernel step left behind when it stored the row's newest token, -1 once
+    // anything else has changed the row.  A later step that may run beside that one waits for the device-side copy
+    // (d_stored_len) only where this says that a step wrote it.
+    std::vector<int32_t> step_len;
     const char* last_w_lo[2] = {nullptr, nullptr};
     const char* last_w_hi[2] = {nullptr, nullptr};
 
@@ -265,12 +265,17 @@ __global__ void apply_table_updates_kernel(int32_t* __restrict__ table, const Ta
 struct LengthUpdate {
     int32_t index, value;
 };
+// Lengths set from the host (free, truncate, adopted page tables) may shrink a row: the per-head "stored length"
+// words that steps publish are cleared with them, so that a stale larger value can never satisfy a later wait.
 __global__ void apply_length_updates_kernel(int32_t* __restrict__ lengths, const LengthUpdate* __restrict__ ups, int n,
-                                            int total) {
+                                            int total, int32_t* __restrict__ stored_len, int heads) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     LengthUpdate u = ups[i];
-    if (u.index >= 0 && u.index < total) lengths[u.index] = u.value;
+    if (u.index >= 0 && u.index < total) {
+        lengths[u.index] = u.value;
+        for (int h = 0; h < heads; ++h) stored_len[(int64_t)u.index * heads + h] = 0;
+    }
 }
 
 // 16-byte vector copy of whole pages between the device pools and the mapped host tier.
@@ -337,7 +342,8 @@ int32_t publish_length_updates(skv_pool* p, const std::vector<LengthUpdate>& ups
         void* dev = nullptr;
         CUDA_TRY(p, p->ring.upload(ups.data() + off, n * sizeof(LengthUpdate), stream, &dev));
         apply_length_updates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
-            p->d_lengths, (const LengthUpdate*)dev, (int)n, p->cfg.num_layers * p->cfg.max_seqs);
+            p->d_lengths, (const LengthUpdate*)dev, (int)n, p->cfg.num_layers * p->cfg.max_seqs, p->d_stored_len,
+            p->cfg.num_kv_heads);
         CUDA_TRY(p, cudaGetLastError());
         count_launches(1);
     }
@@ -441,6 +447,7 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
     p->live.assign(cfg->max_seqs, 0);
     p->page_owner.assign(cfg->num_pages, -1);
     p->seen_stamp.assign(cfg->max_seqs, 0);
+    p->step_len.assign((size_t)cfg->num_layers * cfg->max_seqs, -1);
     for (int32_t i = cfg->num_pages - 1; i >= 0; --i) p->free_pages.push_back(i);
     for (int32_t i = cfg->max_seqs - 1; i >= 0; --i) p->free_seqs.push_back(i);
     for (int32_t i = cfg->host_pages - 1; i >= 0; --i) p->free_host.push_back(i);
@@ -463,8 +470,9 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
         CUDA_TRY(p, cudaMemset(p->d_status, 0, sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_tickets, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 2) * sizeof(int32_t)));
         CUDA_TRY(p, cudaMemset(p->d_tickets, 0, ((size_t)cfg->max_seqs * cfg->num_kv_heads + 2) * sizeof(int32_t)));
-        CUDA_TRY(p, cudaMalloc((void**)&p->d_chain_flags, (size_t)cfg->max_seqs * cfg->num_kv_heads * sizeof(int32_t)));
-        CUDA_TRY(p, cudaMemset(p->d_chain_flags, 0, (size_t)cfg->max_seqs * cfg->num_kv_heads * sizeof(int32_t)));
+        const size_t n_flags = (size_t)cfg->num_layers * cfg->max_seqs * cfg->num_kv_heads;
+        CUDA_TRY(p, cudaMalloc((void**)&p->d_stored_len, n_flags * sizeof(int32_t)));
+        CUDA_TRY(p, cudaMemset(p->d_stored_len, 0, n_flags * sizeof(int32_t)));
         CUDA_TRY(p, cudaMalloc((void**)&p->d_inv_freq, (size_t)cfg->head_dim / 2 * sizeof(float)));
         CUDA_TRY(p, p->ring.init());
         CUDA_TRY(p, p->ring_copy.init(16));
@@ -507,7 +515,7 @@ int32_t skv_destroy(skv_pool* p) {
         cudaFree(p->d_lengths);
         cudaFree(p->d_status);
         cudaFree(p->d_tickets);
-        cudaFree(p->d_chain_flags);
+        cudaFree(p->d_stored_len);
         cudaFree(p->d_inv_freq);
     }
     delete p;
@@ -544,6 +552,7 @@ int32_t skv_free_sequence(skv_pool* p, int32_t seq, void* stream_) {
     p->n_seq_pages[seq] = 0;
     for (int32_t l = 0; l < p->cfg.num_layers; ++l) {
         p->len(l, seq) = 0;
+        p->step_len[(size_t)l * p->cfg.max_seqs + seq] = -1;
         lups.push_back({l * p->cfg.max_seqs + seq, 0});
     }
     p->live[seq] = 0;
@@ -602,6 +611,7 @@ int32_t skv_set_page_table(skv_pool* p, int32_t seq, const int32_t* pages, int32
     p->n_seq_pages[seq] = n_pages;
     for (int32_t l = 0; l < p->cfg.num_layers; ++l) {
         p->len(l, seq) = length;
+        p->step_len[(size_t)l * p->cfg.max_seqs + seq] = -1;
         lups.push_back({l * p->cfg.max_seqs + seq, length});
     }
     DeviceGuard g(p);
@@ -625,6 +635,7 @@ int32_t skv_truncate(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t
     for (int32_t i = 0; i < n_seqs; ++i) {
         int32_t s = seq_ids ? seq_ids[i] : i;
         p->len(layer, s) = new_length;
+        p->step_len[(size_t)layer * p->cfg.max_seqs + s] = -1;
         lups.push_back({layer * p->cfg.max_seqs + s, new_length});
     }
     DeviceGuard g(p);
@@ -749,7 +760,10 @@ int32_t skv_append(skv_pool* p, const skv_append_args* a, void* stream_) {
         int32_t st = grow(p, meta[i].seq, meta[i].start + a->n_new, &ups);
         if (st != SKV_OK) return st;   // cannot happen after the check above
     }
-    for (int32_t i = 0; i < a->n_seqs; ++i) p->len(a->layer, meta[i].seq) = meta[i].start + a->n_new;
+    for (int32_t i = 0; i < a->n_seqs; ++i) {
+        p->len(a->layer, meta[i].seq) = meta[i].start + a->n_new;
+        p->step_len[(size_t)a->layer * p->cfg.max_seqs + meta[i].seq] = -1;
+    }
     if (p->host_only) return SKV_OK;
 
     DeviceGuard g(p);
@@ -1184,12 +1198,7 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     const char* v_hi = v_lo + ((int64_t)(n_seqs - 1) * v_stride + (int64_t)Hkv * Dh) * 2;
     bool early = (a.flags & SKV_STEP_CONSECUTIVE) && switches().step_early && p->last_step_valid && p->last_step_stream == stream &&
                  p->last_step_mark == g_launches.load(std::memory_order_relaxed) && !p->copy_pending &&
-                 p->deferred_updates.empty() && inline_rows && p->last_step_layer == layer &&
-                 (int32_t)p->last_step_seqs.size() == n_seqs;
-    // ... and it then runs beside that step's split-K kernel too, which is only sound for the same rows of the same
-    // layer: the one page row that kernel may still be storing is guarded by a flag per (sequence, head)
-    for (int32_t i = 0; early && i < n_seqs; ++i)
-        if (p->last_step_seqs[i] != (a.seq_ids ? a.seq_ids[i] : i)) early = false;
+                 p->deferred_updates.empty() && inline_rows;
     for (int w = 0; early && w < 2; ++w)
         if (overlaps(p->last_w_lo[w], p->last_w_hi[w], q_lo, q_hi) || overlaps(p->last_w_lo[w], p->last_w_hi[w], k_lo, k_hi) ||
             overlaps(p->last_w_lo[w], p->last_w_hi[w], v_lo, v_hi))
@@ -1215,8 +1224,10 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     for (int32_t i = 0; i < n_seqs; ++i) {
         const int32_t s = a.seq_ids ? a.seq_ids[i] : i;
         const int32_t cur = p->len(layer, s);
+        // the row's newest token came from a step (possibly still running when this one starts early): guarded
+        const bool guarded = cur > 0 && p->step_len[(size_t)layer * p->cfg.max_seqs + s] == cur;
         const uint32_t pos = (uint32_t)(a.positions ? a.positions[i] : cur) | (p->step_store[i] ? 0u : kRowNoStore) |
-                             ((early && p->last_step_store[i]) ? kRowWaitPrev : 0u);
+                             (guarded ? kRowWaitPrev : 0u);
         if (inline_rows) {
             R.seq[i] = s;
             R.len[i] = cur;
@@ -1227,9 +1238,18 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
             big[(size_t)2 * n_seqs + i] = (int32_t)pos;
         }
     }
-    for (int32_t i = 0; i < n_seqs; ++i) p->len(layer, a.seq_ids ? a.seq_ids[i] : i) += p->step_store[i];
+    for (int32_t i = 0; i < n_seqs; ++i) {
+        const int32_t s = a.seq_ids ? a.seq_ids[i] : i;
+        if (p->step_store[i]) p->step_len[(size_t)layer * p->cfg.max_seqs + s] = (p->len(layer, s) += 1);
+    }
     auto roll_back = [&]() {
-        for (int32_t i = 0; i < n_seqs; ++i) p->len(layer, a.seq_ids ? a.seq_ids[i] : i) -= p->step_store[i];
+        for (int32_t i = 0; i < n_seqs; ++i) {
+            const int32_t s = a.seq_ids ? a.seq_ids[i] : i;
+            if (p->step_store[i]) {
+                p->len(layer, s) -= 1;
+                p->step_len[(size_t)layer * p->cfg.max_seqs + s] = -1;
+            }
+        }
         ungrow(p, ups);
     };
     st = publish_table_updates(p, ups, stream);
@@ -1273,9 +1293,7 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     D.inv_freq = p->d_inv_freq;
     D.rope_scaling = p->rope_scaling;
     D.early_start = early ? 1 : 0;
-    D.chain_flags = p->d_chain_flags;
-    D.chain_wait = p->chain_epoch;
-    D.chain_epoch = ++p->chain_epoch;
+    D.stored_len = p->d_stored_len;
     D.rows = &R;
     if (a.xchg || a.partial_out) D.out = nullptr;
     D.partial_out = a.partial_out;
@@ -1300,10 +1318,6 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     }
     p->last_step_stream = stream;
     p->last_step_mark = g_launches.load(std::memory_order_relaxed);
-    p->last_step_layer = layer;
-    p->last_step_seqs.resize(n_seqs);
-    for (int32_t i = 0; i < n_seqs; ++i) p->last_step_seqs[i] = a.seq_ids ? a.seq_ids[i] : i;
-    p->last_step_store.assign(p->step_store.begin(), p->step_store.end());
     p->last_step_valid = true;
     return SKV_OK;
 }

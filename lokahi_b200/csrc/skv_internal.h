@@ -90,8 +90,8 @@ struct ExchangeView {
 #endif
 constexpr int kInlineRows = SKV_INLINE_ROWS;
 constexpr uint32_t kRowNoStore = 0x80000000u;   // bit 31 of pos: this pool does not store the step's token
-constexpr uint32_t kRowWaitPrev = 0x40000000u;  // bit 30 of pos: the previous step (which may still be running) stored this
-                                                // row's last token here: wait for its flag before reading that page row
+constexpr uint32_t kRowWaitPrev = 0x40000000u;  // bit 30 of pos: the row's newest token was stored by an earlier step that
+                                                // may still be running: wait for its flag before reading that page row
 constexpr uint32_t kRowPosMask = 0x3fffffffu;
 struct StepRows {
     const int32_t* dev;           // nullptr, or device [3][n_seqs]: seq, len, pos
@@ -137,11 +137,10 @@ struct DecodeLaunch {
     float rope_scaling;
     int32_t early_start;         // 1: the split-K kernel of a step may run beside the previous step's kernels up to the
                                  // point where it stores its partials (the caller vouched for its inputs); rows marked
-                                 // kRowWaitPrev wait for chain_flags[seq][head] >= chain_wait before they read the page
-                                 // row that step stored
-    int32_t* chain_flags;        // [max_seqs][kv_heads]: epoch of the last step whose CTA stored a token for (seq, head)
-    int32_t chain_epoch;         // this step's epoch, written to chain_flags by every storing CTA
-    int32_t chain_wait;          // epoch of the previous step
+                                 // kRowWaitPrev wait until stored_len[layer][seq][head] has reached the row's length
+                                 // before they read the page row of its newest token
+    int32_t* stored_len;         // [layers][max_seqs][kv_heads]: tokens of (layer, seq, head) in place, as published by
+                                 // the CTA of a step that stored the last of them
     const StepRows* rows;        // host pointer; copied into the kernel parameters at launch
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);

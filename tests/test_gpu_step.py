@@ -331,3 +331,63 @@ def test_dense_attention_reports_through_its_status_word():
     k = torch.randn((1, 2, 256, 128), generator=g, device=DEV).to(torch.bfloat16)
     out = L.chunked_grouped_attention(q, k, k)
     assert L.check_dense_attention_status(DEV) == 0 and bool(torch.isfinite(out.float()).all())
+
+
+def test_consecutive_steps_across_layers_and_after_a_truncation():
+    """A decode step of a multi-layer cache is one step per layer, back to back, for every token: early start has to
+    hold across layers (a step of layer l may start while the steps of layers l-1 and l-2 are still running, and the
+    row it must wait for was stored a whole round of layers ago).  Then the rows are cut back and regrown: the
+    stored-length words the steps publish must not satisfy a wait with a value from before the cut."""
+    layers, n, tokens = 3, 6, 12
+    lens = [0, 7, 15, 16, 700, 2047]
+    pps = -(-(max(lens) + 2 * tokens + 4) // P)
+
+    def make():
+        rng = np.random.default_rng(91)
+        pool = L.PagedPool(L.PagedKVConfig(num_layers=layers, num_kv_heads=HKV, head_dim=D, num_pages=n * pps + 2, max_seqs=n,
+                                           max_pages_per_seq=pps, page_size=P, dtype=torch.bfloat16, rope_theta=THETA))
+        perm = rng.permutation(n * pps + 2)
+        for s in range(n):
+            assert pool.alloc_sequence() == s
+            pool.set_page_table(s, perm[s * pps:(s + 1) * pps].tolist(), lens[s])
+        g = torch.Generator(device=DEV).manual_seed(17)
+        for layer in range(layers):
+            kp, vp = pool.layer_views(layer)
+            kp.normal_(generator=g); vp.normal_(generator=g)
+        return pool
+
+    pool_a, pool_b = make(), make()
+    g = torch.Generator(device=DEV).manual_seed(18)
+    mk = lambda h: torch.randn((tokens, layers, n, h, D), generator=g, device=DEV).to(torch.bfloat16)
+    q_all, k_all, v_all = mk(HQ), mk(HKV), mk(HKV)
+    qa, qb = q_all.clone(), q_all.clone()
+    out_a, out_b = torch.empty_like(q_all), torch.empty_like(q_all)
+
+    def run(pool, q, out, first, count, consecutive):
+        for t in range(first, first + count):
+            for layer in range(layers):
+                pool.decode_step(layer, q[t, layer], k_all[t, layer], v_all[t, layer], out=out[t, layer], consecutive=consecutive)
+
+    torch.cuda.synchronize()
+    run(pool_a, qa, out_a, 0, tokens, False)
+    run(pool_b, qb, out_b, 0, tokens, True)
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b) and torch.equal(qa, qb)
+    # cut every layer back to the starting lengths and grow again with other inputs
+    for pool in (pool_a, pool_b):
+        for layer in range(layers):
+            for s in range(n):
+                pool.truncate(layer, lens[s], seq_ids=[s])
+    q2 = torch.randn((tokens, layers, n, HQ, D), generator=g, device=DEV).to(torch.bfloat16)
+    qa, qb = q2.clone(), q2.clone()
+    torch.cuda.synchronize()
+    run(pool_a, qa, out_a, 0, tokens, False)
+    run(pool_b, qb, out_b, 0, tokens, True)
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b) and torch.equal(qa, qb)
+    for layer in range(layers):
+        assert np.array_equal(pool_a.lengths(layer), pool_b.lengths(layer))
+        ka, va = pool_a.gather(layer, n_seqs=n)
+        kb, vb = pool_b.gather(layer, n_seqs=n)
+        assert torch.equal(ka, kb) and torch.equal(va, vb)
+    assert pool_a.check_device_status() == 0 and pool_b.check_device_status() == 0
