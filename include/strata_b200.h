@@ -326,6 +326,11 @@ SKV_API int32_t skv_rope_rows(const void* x_in, void* x_out, const int32_t* posi
 SKV_API int32_t skv_rmsnorm(const void* x, const void* delta, void* sum_out, const void* weight, void* out, int64_t n_rows,
                             int32_t hidden, float eps, int32_t dtype, void* stream);
 SKV_API int32_t skv_swiglu(const void* gate, const void* up, void* out, int64_t n, int32_t dtype, void* stream);
+/* skv_swiglu over [n_rows][cols] with a row stride (in elements) per operand: gate and up can be the two halves of one
+ * fused gate/up projection output [n_rows][2 * cols] (the reference projects them separately, llama_mlx.py:398-406). */
+SKV_API int32_t skv_swiglu_rows(const void* gate, const void* up, void* out, int64_t n_rows, int32_t cols,
+                                int64_t gate_row_stride, int64_t up_row_stride, int64_t out_row_stride, int32_t dtype,
+                                void* stream);
 
 #ifdef __cplusplus
 }

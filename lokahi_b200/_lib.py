@@ -120,6 +120,7 @@ SIGNATURES = {
     "skv_rope_rows": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _f, _i32, _vp]),
     "skv_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f, _i32, _vp]),
     "skv_swiglu": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "skv_swiglu_rows": (_i32, [_vp, _vp, _vp, _i64, _i32, _i64, _i64, _i64, _i32, _vp]),
 }
 
 

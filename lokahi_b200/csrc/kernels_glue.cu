@@ -173,6 +173,40 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gate,
     }
 }
 
+// SwiGLU over rows with their own strides: gate and up may be the two halves of one fused projection output
+// [n_rows][2 * cols] (row stride 2 * cols), out a packed [n_rows][cols].  One block walks rows; 16-byte accesses when
+// everything is 16-byte aligned.
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out,
+                                                          int64_t n_rows, int cols, int64_t gate_stride, int64_t up_stride,
+                                                          int64_t out_stride, int vec) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const int per_row = vec ? cols / VEC : cols;
+    const int64_t total = n_rows * per_row;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int64_t r = idx / per_row;
+        const int c = (int)(idx - r * per_row);
+        if (vec) {
+            const uint4 g = *reinterpret_cast<const uint4*>(gate + r * gate_stride + (int64_t)c * VEC);
+            const uint4 u = *reinterpret_cast<const uint4*>(up + r * up_stride + (int64_t)c * VEC);
+            const T* ge = reinterpret_cast<const T*>(&g);
+            const T* ue = reinterpret_cast<const T*>(&u);
+            uint4 o;
+            T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                const float gf = to_f32(ge[e]);
+                oe[e] = from_f32<T>((gf * (1.0f / (1.0f + expf(-gf)))) * to_f32(ue[e]));
+            }
+            *reinterpret_cast<uint4*>(out + r * out_stride + (int64_t)c * VEC) = o;
+        } else {
+            const float gf = to_f32(gate[r * gate_stride + c]);
+            out[r * out_stride + c] = from_f32<T>((gf * (1.0f / (1.0f + expf(-gf)))) * to_f32(up[r * up_stride + c]));
+        }
+    }
+}
+
 bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 template <typename T>
@@ -230,11 +264,41 @@ cudaError_t run_swiglu(const void* gate, const void* up, void* out, int64_t n, c
     return cudaGetLastError();
 }
 
+template <typename T>
+cudaError_t run_swiglu_rows(const void* gate, const void* up, void* out, int64_t n_rows, int32_t cols, int64_t gs, int64_t us,
+                            int64_t os, cudaStream_t stream) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const bool vec = cols % VEC == 0 && gs % VEC == 0 && us % VEC == 0 && os % VEC == 0 && aligned16(gate) && aligned16(up) &&
+                     aligned16(out);
+    const int64_t items = n_rows * (vec ? cols / VEC : cols);
+    int64_t blocks = (items + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    swiglu_rows_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const T*>(gate), reinterpret_cast<const T*>(up),
+                                                               reinterpret_cast<T*>(out), n_rows, cols, gs, us, os, vec ? 1 : 0);
+    count_launches(1);
+    return cudaGetLastError();
+}
+
 }  // namespace
 
 }  // namespace skv
 
 extern "C" {
+
+int32_t skv_swiglu_rows(const void* gate, const void* up, void* out, int64_t n_rows, int32_t cols, int64_t gate_row_stride,
+                        int64_t up_row_stride, int64_t out_row_stride, int32_t dtype, void* stream) {
+    if (!gate || !up || !out || n_rows < 0 || cols <= 0 || gate_row_stride < cols || up_row_stride < cols || out_row_stride < cols)
+        return SKV_ERR_BAD_ARG;
+    if (dtype != SKV_F32 && dtype != SKV_BF16) return SKV_ERR_BAD_ARG;
+    if (n_rows == 0) return SKV_OK;
+    cudaError_t e = dtype == SKV_BF16
+                        ? skv::run_swiglu_rows<__nv_bfloat16>(gate, up, out, n_rows, cols, gate_row_stride, up_row_stride,
+                                                              out_row_stride, (cudaStream_t)stream)
+                        : skv::run_swiglu_rows<float>(gate, up, out, n_rows, cols, gate_row_stride, up_row_stride, out_row_stride,
+                                                      (cudaStream_t)stream);
+    return e == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
 
 int32_t skv_rmsnorm(const void* x, const void* delta, void* sum_out, const void* weight, void* out, int64_t n_rows, int32_t hidden,
                     float eps, int32_t dtype, void* stream) {

@@ -95,6 +95,12 @@ class PagedDecoder:
         # when set to a list, (start, end) CUDA events around the hot path (RoPE + cache update + attention)
         # of every layer call are appended to it
         self.hot_path_events = None
+        # One projection for q, k and v and one for gate and up (the reference projects them separately,
+        # llama_mlx.py:257-281, 398-406): the weights are concatenated once, q / k / v and gate / up are strided
+        # slices of the one GEMM output, and the hot path and the SwiGLU launch read them in place.
+        self.fused_proj = os.environ.get("SKV_FUSED_PROJ", "1") != "0"
+        self._w_qkv: Dict[int, torch.Tensor] = {}
+        self._w_gate_up: Dict[int, torch.Tensor] = {}
 
     # -- glue (llama_mlx.py:53-92, 345-408) ------------------------------------------------------------
     def _rms_norm(self, x, weight):
@@ -111,7 +117,34 @@ class PagedDecoder:
         hidden = hidden + delta
         return hidden, self._rms_norm(hidden, weight)
 
+    def _qkv_weight(self, layer: int) -> torch.Tensor:
+        w = self._w_qkv.get(layer)
+        if w is None:
+            b = f"model.layers.{layer}.self_attn"
+            w = self._w_qkv[layer] = torch.cat([self.w[f"{b}.q_proj.weight"], self.w[f"{b}.k_proj.weight"],
+                                                self.w[f"{b}.v_proj.weight"]], dim=0).contiguous()
+        return w
+
+    def _qkv(self, layer: int, hidden: torch.Tensor):
+        """q, k, v as ``[B, heads, L, D]`` views of one projection output ``[B, L, (Hq + 2 Hkv) * D]``."""
+        B, L, _ = hidden.shape
+        if not self.fused_proj:
+            b = f"model.layers.{layer}.self_attn"
+            return (F.linear(hidden, self.w[f"{b}.q_proj.weight"]).view(B, L, self.Hq, self.D).transpose(1, 2).contiguous(),
+                    F.linear(hidden, self.w[f"{b}.k_proj.weight"]).view(B, L, self.Hkv, self.D).transpose(1, 2).contiguous(),
+                    F.linear(hidden, self.w[f"{b}.v_proj.weight"]).view(B, L, self.Hkv, self.D).transpose(1, 2).contiguous())
+        qkv = F.linear(hidden, self._qkv_weight(layer)).view(B, L, self.Hq + 2 * self.Hkv, self.D).transpose(1, 2)
+        return qkv[:, :self.Hq], qkv[:, self.Hq:self.Hq + self.Hkv], qkv[:, self.Hq + self.Hkv:]
+
     def _mlp(self, x, b):
+        if self.fused_proj and self.fused_glue:
+            w = self._w_gate_up.get(b)
+            if w is None:
+                w = self._w_gate_up[b] = torch.cat([self.w[f"{b}.mlp.gate_proj.weight"], self.w[f"{b}.mlp.up_proj.weight"]],
+                                                   dim=0).contiguous()
+            gu = F.linear(x, w)
+            inter = gu.shape[-1] // 2
+            return F.linear(swiglu(gu[..., :inter], gu[..., inter:]), self.w[f"{b}.mlp.down_proj.weight"])
         gate = F.linear(x, self.w[f"{b}.mlp.gate_proj.weight"])
         up = F.linear(x, self.w[f"{b}.mlp.up_proj.weight"])
         act = swiglu(gate, up) if self.fused_glue else F.silu(gate) * up
@@ -131,9 +164,7 @@ class PagedDecoder:
         past_length = cache.get_seq_length(layer) if cache is not None else 0
         phase = "decode" if past_length > 0 else ("prefill" if cache is not None else "forward")
         started = time.perf_counter()
-        q = F.linear(hidden, self.w[f"{b}.q_proj.weight"]).view(B, L, self.Hq, self.D).transpose(1, 2).contiguous()
-        k = F.linear(hidden, self.w[f"{b}.k_proj.weight"]).view(B, L, self.Hkv, self.D).transpose(1, 2).contiguous()
-        v = F.linear(hidden, self.w[f"{b}.v_proj.weight"]).view(B, L, self.Hkv, self.D).transpose(1, 2).contiguous()
+        q, k, v = self._qkv(layer, hidden)         # strided views of one projection output when fused_proj is on
         kwargs = {"cache_position": cache_position}
         if self.hot_path_events is not None:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
@@ -144,6 +175,9 @@ class PagedDecoder:
             out = cache.decode_step_with_rope(q, k, v, layer, kwargs, inv_freq=self.inv_freq_np,
                                               scaling_factor=self.rope_scale)
         if out is None:
+            q = q.contiguous()                     # rotated in place below and read by the dense / paged prefill kernels
+            if cache is None or not (self.fused_rope and hasattr(cache, "update_with_rope")):
+                k, v = k.contiguous(), v.contiguous()
             if cache is not None and self.fused_rope and hasattr(cache, "update_with_rope"):
                 k_hist, v_hist = cache.update_with_rope(q, k, v, layer, kwargs, inv_freq=self.inv_freq_np,
                                                         scaling_factor=self.rope_scale)
@@ -177,12 +211,7 @@ class PagedDecoder:
 
     # -- graphed decode step ---------------------------------------------------------------------------------
     def _project_qkv(self, layer: int, x: torch.Tensor):
-        B = x.shape[0]
-        b = f"model.layers.{layer}.self_attn"
-        q = F.linear(x, self.w[f"{b}.q_proj.weight"]).view(B, 1, self.Hq, self.D).transpose(1, 2).contiguous()
-        k = F.linear(x, self.w[f"{b}.k_proj.weight"]).view(B, 1, self.Hkv, self.D).transpose(1, 2).contiguous()
-        v = F.linear(x, self.w[f"{b}.v_proj.weight"]).view(B, 1, self.Hkv, self.D).transpose(1, 2).contiguous()
-        return q, k, v
+        return self._qkv(layer, x)
 
     def _capture_decode_graphs(self, B: int) -> _DecodeGraphs:
         g = _DecodeGraphs()

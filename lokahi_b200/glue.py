@@ -65,8 +65,30 @@ def add_rms_norm(hidden_states: torch.Tensor, delta: torch.Tensor, weight: torch
     return hidden_states, out
 
 
+def _row_stride(t: torch.Tensor) -> Optional[int]:
+    """Row stride of ``t`` seen as [rows, cols] (last dimension packed, leading dimensions collapsible), else None."""
+    if t.dim() < 2 or t.stride(-1) != 1:
+        return None
+    stride = t.stride(-2)
+    for d in range(t.dim() - 2, 0, -1):
+        if t.stride(d - 1) != t.stride(d) * t.shape[d]:
+            return None
+    return stride
+
+
 def swiglu(gate: torch.Tensor, up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``silu(gate) * up`` element-wise."""
+    """``silu(gate) * up`` element-wise.  ``gate`` and ``up`` may be strided row slices of one fused projection output
+    (last dimension packed); the result is packed."""
+    if not (gate.is_contiguous() and up.is_contiguous()):
+        gs, us = _row_stride(gate), _row_stride(up)
+        if gs is None or us is None or gate.shape != up.shape or not gate.is_cuda or gate.dtype != up.dtype:
+            raise ValueError("gate and up must be contiguous, or row slices with a packed last dimension")
+        if out is None:
+            out = torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
+        cols = gate.shape[-1]
+        raise_for_status(lib.skv_swiglu_rows(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel() // cols, cols, gs, us,
+                                             cols, _code(gate), torch.cuda.current_stream(gate.device).cuda_stream))
+        return out
     _check(gate, up)
     if gate.shape != up.shape:
         raise ValueError("gate and up must have the same shape")

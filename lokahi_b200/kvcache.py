@@ -30,6 +30,11 @@ def _positions_to_list(cache_position) -> List[int]:
     return [int(x) for x in np.asarray(cache_position).reshape(-1).tolist()]
 
 
+def _rows_packed(t: torch.Tensor) -> bool:
+    """``[B, H, 1, D]`` whose heads lie back to back inside each batch row (contiguous, or a slice of a wider row)."""
+    return t.dim() == 4 and t.shape[2] == 1 and t.stride(3) == 1 and t.stride(1) == t.shape[3]
+
+
 class PagedKVCache:
     def __init__(self, config: Any, cache_dir: Optional[str] = None, stats: Optional[Any] = None, *,
                  pool: Optional[PagedPool] = None, device: Optional[int] = None, page_size: int = 16,
@@ -164,18 +169,17 @@ class PagedKVCache:
         does not apply (more than one token) and the caller should make the two calls."""
         if key_states.dim() != 4 or key_states.shape[2] != 1 or query_states.dim() != 4 or query_states.shape[2] != 1:
             return None
-        if self.seq_ids is None or not query_states.is_contiguous():
+        if self.seq_ids is None or not all(_rows_packed(t) for t in (query_states, key_states, value_states)):
             return None
         previous = self._prepare_update(key_states, value_states, layer_idx, cache_kwargs)
         self._ensure_rope(inv_freq, scaling_factor)
         B, Hq, _, D = query_states.shape
-        Hkv = key_states.shape[1]
-        out = self.pool.decode_step(layer_idx, query_states.view(B, Hq, D), key_states.reshape(B, Hkv, D).contiguous(),
-                                    value_states.reshape(B, Hkv, D).contiguous(), eps=eps,
-                                    out=None if out is None else out.view(B, Hq, D),
+        # [B, H, 1, D] -> [B, H, D] without a copy: the tensors may be strided slices of one fused projection output
+        out = self.pool.decode_step(layer_idx, query_states[:, :, 0], key_states[:, :, 0], value_states[:, :, 0], eps=eps,
+                                    out=None if out is None else out[:, :, 0],
                                     seq_ids=None if list(self.seq_ids) == list(range(B)) else self.seq_ids)
         self._finish_update(layer_idx, previous, 1)
-        return out.view(B, Hq, 1, D)
+        return out.unsqueeze(2)
 
     def bind_decode_step(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
                          out: torch.Tensor, *, inv_freq: np.ndarray, scaling_factor: float = 1.0, eps: float = 1e-12):
@@ -193,8 +197,7 @@ class PagedKVCache:
         if L != 1 or key_states.shape[2] != 1 or (B, Hkv, D) != (self.batch_size, c.num_kv_heads, c.head_dim):
             raise ValueError("new key states must match cached batch, head, and feature dimensions")
         self._ensure_rope(inv_freq, scaling_factor)
-        call = self.pool.decode_step_binder(query_states.view(B, Hq, D), key_states.view(B, Hkv, D), value_states.view(B, Hkv, D),
-                                            out.view(B, Hq, D), eps=eps,
+        call = self.pool.decode_step_binder(query_states[:, :, 0], key_states[:, :, 0], value_states[:, :, 0], out[:, :, 0], eps=eps,
                                             seq_ids=None if list(self.seq_ids) == list(range(B)) else self.seq_ids)
         lengths, resident, offloaded = self._layer_lengths, self._resident, self._disk_offloaded
 
