@@ -834,86 +834,148 @@ def run_glue(args):
 
 
 def run_longctx(args):
-    """Secondary workload "long_context_llama3_8b_kv": one GPU's share of the 8-way KV-head sharding of a
-    Llama-3-8B KV path: 32 layers, 1 KV head with its 4 query heads, head_dim 128, bf16, 4 sequences at 96k
-    (98304) tokens of N(0,1) K/V.  Every step parks the oldest 25 % of each sequence's pages in pinned host
-    memory, brings them back, then appends one token and attends in all 32 layers.  Two rooflines: HBM for the
-    attention bytes, the host link for the parked bytes."""
+    """Secondary workload "long_context_llama3_8b_kv": the KV path of a Llama-3-8B at 96k context sharded one KV head
+    per GPU: 32 layers, 1 KV head with its 4 query heads per rank, head_dim 128, bf16, 4 sequences of 98304 tokens of
+    N(0,1) K/V.  `--gpus N` runs N of the 8 shards (8 = the whole configuration); with N > 1 every layer's output rows
+    are gathered by the merge kernel.  Every decode step parks the oldest 25 % of each sequence's pages in pinned host
+    memory and brings them back, appends one token and attends in all 32 layers.  Two schedules are timed:
+      serial    park and fetch all four sequences, wait, then attend all four;
+      pingpong  two half-batches: while one half's pages travel, the other half is attended (its pages are all
+                resident), then the halves swap -- every sequence is parked, fetched and attended once per step.
+    Two rooflines: HBM for the attention bytes (timed with nothing travelling), the host link for the parked bytes."""
     import torch
+    import torch.distributed as dist
 
     import lokahi_b200 as L
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    layers, n_seq, hkv, hq, T0 = 32, 4, 1, 4, 98304
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    layers, n_seq, hkv, hq, T0 = 32, 4, 1, 4, args.context
     K, W = max(1, min(args.steps, 64)), max(1, min(args.warmup, 3))
-    pages_per_seq = -(-(T0 + K + W + 16) // P)
+    room = 3 * (K + W) + 16
+    pages_per_seq = -(-(T0 + room) // P)
     park = (T0 // P) // 4
     pool = L.PagedPool(L.PagedKVConfig(num_layers=layers, num_kv_heads=hkv, head_dim=D, num_pages=n_seq * pages_per_seq + 8,
                                        max_seqs=n_seq, max_pages_per_seq=pages_per_seq, page_size=P, dtype=torch.bfloat16,
-                                       device=0, host_pages=n_seq * park + 8, rope_theta=THETA))
+                                       device=local_rank, host_pages=n_seq * park + 8, rope_theta=THETA))
     for s_ in range(n_seq):
         assert pool.alloc_sequence() == s_
-        pool.reserve(s_, T0 + K + W + 16)
-    gen = torch.Generator(device=dev).manual_seed(SEED)
+        pool.reserve(s_, T0 + room)
+    gen = torch.Generator(device=dev).manual_seed(SEED + 17 * rank)
     pool_set_lengths(pool, layers, n_seq, T0)        # declares the history (writes zeros) ...
     for layer in range(layers):                      # ... which is then filled with N(0,1) K/V in place
         kp, vp = pool.layer_views(layer)
         kp.normal_(generator=gen)
         vp.normal_(generator=gen)
-    q = torch.randn((n_seq, hq, D), generator=gen, device=dev).to(torch.bfloat16)
+    # one q per layer: the step rotates it in place, which keeps its norm, so the buffers are simply reused
+    q = torch.randn((layers, n_seq, hq, D), generator=gen, device=dev).to(torch.bfloat16)
     kn = torch.randn((n_seq, hkv, D), generator=gen, device=dev).to(torch.bfloat16)
     vn = torch.randn((n_seq, hkv, D), generator=gen, device=dev).to(torch.bfloat16)
-    out = torch.empty_like(q)
-    q_work = torch.empty_like(q)
+    halves = ([0, 1], [2, 3])
+    peers = {}
+    if world > 1:
+        shard = L.HeadShard(rank, world, hq * world, hkv * world)
+        for n in (n_seq, 2):
+            peers[n] = L.PeerGather(shard, n, D, torch.bfloat16, dev)
+    outs = {n_seq: torch.empty((n_seq, hq, D), device=dev, dtype=torch.bfloat16), 2: torch.empty((2, hq, D), device=dev, dtype=torch.bfloat16)}
 
-    def step(timers=None):
-        if timers:
-            timers[0].record()
-        for s_ in range(n_seq):
+    def bind(rows):
+        n = len(rows)
+        sel = slice(rows[0], rows[-1] + 1)
+        ids = None if n == n_seq else rows
+        if world > 1:
+            return [pool.decode_step_binder(q[layer, sel], kn[sel], vn[sel], exchange=peers[n], seq_ids=ids, consecutive=True)
+                    for layer in range(layers)]
+        return [pool.decode_step_binder(q[layer, sel], kn[sel], vn[sel], outs[n], seq_ids=ids, consecutive=True)
+                for layer in range(layers)]
+
+    calls = {"all": bind(list(range(n_seq))), 0: bind(halves[0]), 1: bind(halves[1])}
+
+    def attend(which):
+        stream = torch.cuda.current_stream().cuda_stream
+        for layer, call in enumerate(calls[which]):
+            call(layer, stream)                      # RoPE + append + attention (+ gather): one library call per layer
+
+    def move(rows):
+        for s_ in rows:
             pool.evict(s_, 0, park)
-        for s_ in range(n_seq):
+        for s_ in rows:
             pool.prefetch(s_, 0, park)
-        pool.sync_transfers()
-        if timers:
-            timers[1].record()
-        for layer in range(layers):
-            q_work.copy_(q)                                  # the step rotates q in place
-            pool.decode_step(layer, q_work, kn, vn, out=out)  # RoPE + append + attention: one library call
-        if timers:
-            timers[2].record()
 
-    for _ in range(W):
-        step()
-    torch.cuda.synchronize()
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
-    l0 = L._lib.lib.skv_launch_count()
-    c0 = pool.counters()
-    for i in range(K):
-        step(evs[i])
-    torch.cuda.synchronize()
-    launches = L._lib.lib.skv_launch_count() - l0
-    c1 = pool.counters()
+    def step_serial():
+        move(range(n_seq))
+        pool.sync_transfers()
+        attend("all")
+
+    def step_pingpong():
+        for h in (0, 1):
+            move(halves[h])                          # this half's pages travel ...
+            attend(1 - h)                            # ... while the other half, all resident, is attended
+            pool.sync_transfers()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, count):
+        for _ in range(W):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0 = pool.counters()
+        l0 = L._lib.lib.skv_launch_count()
+        e0.record()
+        for _ in range(count):
+            fn()
+        e1.record()
+        barrier()
+        c1 = pool.counters()
+        ms = e0.elapsed_time(e1) / count
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, (c1["bytes_d2h"] - c0["bytes_d2h"]) / count, (c1["bytes_h2d"] - c0["bytes_h2d"]) / count, L._lib.lib.skv_launch_count() - l0
+
+    attn_ms, _, _, _ = timed(lambda: attend("all"), K)               # nothing travels: the HBM roofline of the attention
+    copy_ms, d2h, h2d, _ = timed(lambda: (move(range(n_seq)), pool.sync_transfers()), max(2, K // 8))
+    serial_ms, _, _, _ = timed(step_serial, K)
+    ping_ms, d2h_p, h2d_p, launches = timed(step_pingpong, K)
     if pool.check_device_status() != 0:
         raise SystemExit("device status flag set")
-    xfer_ms = np.array([e[0].elapsed_time(e[1]) for e in evs])
-    attn_ms = np.array([e[1].elapsed_time(e[2]) for e in evs])
-    d2h = (c1["bytes_d2h"] - c0["bytes_d2h"]) / K
-    h2d = (c1["bytes_h2d"] - c0["bytes_h2d"]) / K
-    attn_bytes = float(np.mean([layers * n_seq * (T0 + W + i + 1) * hkv * D * 2 * 2 for i in range(K)]))
+    tokens_now = pool.length(0, 0)
+    attn_bytes = float(layers * n_seq * (tokens_now - K // 2) * hkv * D * 2 * 2)
     peak, kind = measured_peak_gbs()
-    step_ms = float((xfer_ms + attn_ms).mean())
+    for pe in peers.values():
+        pe.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return None
     return {
-        "metric": "long-context decode tokens/s per GPU (1 of 8 KV heads)", "value": n_seq / (step_ms * 1e-3), "unit": "tokens/s",
-        "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "metric": "long-context decode tokens/s (4 sequences x 96k, one KV head per GPU)", "value": n_seq / (ping_ms * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ping_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "long_context_llama3_8b_kv", "layers": layers, "sequences": n_seq, "context": T0, "kv_heads_local": hkv,
-                   "q_heads_local": hq, "head_dim": D, "page_size": P, "parked_fraction": 0.25},
-        "attention": {"ms_per_step": float(attn_ms.mean()), "algorithmic_bytes": attn_bytes,
-                      "achieved_gbs": attn_bytes / (attn_ms.mean() * 1e-3) / 1e9,
-                      "frac_of_hbm_peak": attn_bytes / (attn_ms.mean() * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}"},
-        "transfers": {"ms_per_step": float(xfer_ms.mean()), "d2h_bytes_per_step": d2h, "h2d_bytes_per_step": h2d,
-                      "achieved_gbs_each_way": (d2h + h2d) / 2 / (xfer_ms.mean() * 1e-3 / 2) / 1e9,
-                      "note": "evict then prefetch of the same pages, serial on one copy stream; host-link bound"},
+                   "q_heads_local": hq, "head_dim": D, "page_size": P, "parked_fraction": 0.25, "shards_running": world, "shards_total": 8,
+                   "schedule": "pingpong (two half-batches: one travels while the other is attended)"},
+        "schedules": {"serial_ms_per_step": serial_ms, "pingpong_ms_per_step": ping_ms, "attention_only_ms": attn_ms, "copies_only_ms": copy_ms,
+                      "overlap_hidden_ms": serial_ms - ping_ms},
+        "attention": {"ms_per_step": attn_ms, "algorithmic_bytes_per_gpu": attn_bytes,
+                      "achieved_gbs_per_gpu": attn_bytes / (attn_ms * 1e-3) / 1e9,
+                      "frac_of_hbm_peak": attn_bytes / (attn_ms * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}",
+                      "us_per_layer_step": attn_ms / layers * 1e3},
+        "transfers": {"ms_per_step": copy_ms, "d2h_bytes_per_step_per_gpu": d2h, "h2d_bytes_per_step_per_gpu": h2d,
+                      "gbs_each_way_per_gpu": (d2h + h2d) / 2 / (copy_ms * 1e-3 / 2) / 1e9,
+                      "gbs_each_way_all_gpus": world * (d2h + h2d) / 2 / (copy_ms * 1e-3 / 2) / 1e9,
+                      "note": "evict then fetch of the same pages on one copy stream; the two directions do not overlap through mapped host memory"},
         "gpu_launches": int(launches),
     }
 
@@ -1080,6 +1142,7 @@ def main():
                     help="decode: the headline paged-decode workload; prefill: the 4096-token chunked-GQA op (1 GPU)")
     ap.add_argument("--kv", choices=["dense", "paged"], default="dense",
                     help="prefill workload: K/V as dense tensors or as scattered 16-token pages of a pool")
+    ap.add_argument("--context", type=int, default=98304, help="longctx workload: tokens per sequence (96k = 98304)")
     ap.add_argument("--seqs", type=int, default=N_SEQS,
                     help="number of sequences (default: the workload's 64; smaller values are for profiler captures)")
     args = ap.parse_args()

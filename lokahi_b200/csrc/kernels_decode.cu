@@ -826,7 +826,8 @@ cudaError_t launch_tma(const DecodeLaunch& d, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
+    // the grid covers the longest sequence of the call, the workspace stride (max_splits) the longest possible one
+    dim3 grid((unsigned)(d.grid_splits > 0 ? d.grid_splits : d.max_splits), (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
     return launch_pdl(decode_tma_kernel<NS, FA>, grid, dim3(kDecodeThreads), (size_t)smem, stream, d,
                       *reinterpret_cast<const CUtensorMap*>(d.k_map), *reinterpret_cast<const CUtensorMap*>(d.v_map),
                       d.rows ? *d.rows : empty_rows());
@@ -1078,7 +1079,7 @@ __global__ void __launch_bounds__(128) merge_partials_kernel(const float* __rest
 
 template <typename T>
 cudaError_t launch_generic(const DecodeLaunch& d, cudaStream_t stream) {
-    dim3 grid((unsigned)d.max_splits, (unsigned)d.n_q_heads, (unsigned)d.n_seqs);
+    dim3 grid((unsigned)(d.grid_splits > 0 ? d.grid_splits : d.max_splits), (unsigned)d.n_q_heads, (unsigned)d.n_seqs);
     const int dpl = (d.pool.head_dim + 31) / 32;
     switch (dpl) {
         case 1: decode_generic_kernel<T, 1><<<grid, kDecodeThreads, 0, stream>>>(d); break;
@@ -1095,43 +1096,32 @@ cudaError_t launch_generic(const DecodeLaunch& d, cudaStream_t stream) {
 
 void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, int32_t num_kv_heads,
                  int64_t total_tokens_hint, int32_t* chunk_tokens, int32_t* max_splits) {
-    // Aim at a little over two waves of 3 CTAs per SM on 148 SMs (about 1000 CTAs): measured on B200 with the
-    // work of 1, 1/2, 1/4 and 1/8 of the 64-sequence workload, the best chunk was the one that gives each
-    // CTA total_tokens * kv_heads / ~1000 tokens (2048, ~1000, ~512, ~256); smaller chunks pay the per-CTA
-    // start-up (lengths -> page ids -> first copy) too often, larger ones leave SMs idle in the last wave.
-    // `splits` bounds the partials per sequence, and with them the workspace, independently of the lengths.
-    const int64_t target = 1000;
+    // `splits` bounds the partials per sequence, and with them the workspace, independently of the lengths: a chunk
+    // is never shorter than 256 tokens and a sequence never has more than 128 of them.
     const int64_t max_ctx = (int64_t)max_pages_per_seq * page_size;
-    int64_t splits = (2 * target + (int64_t)n_seqs * num_kv_heads - 1) / ((int64_t)n_seqs * num_kv_heads);
+    int64_t splits = (max_ctx + 255) / 256;
     splits = splits < 1 ? 1 : (splits > 128 ? 128 : splits);
     int64_t floor_chunk = (max_ctx + splits - 1) / splits;
-    int64_t chunk = total_tokens_hint > 0 ? (num_kv_heads * total_tokens_hint) / target : 0;
-    if (chunk < floor_chunk) chunk = floor_chunk;
+    floor_chunk = ((floor_chunk + 63) / 64) * 64;         // 4 warps x 16-token tiles
+    if (floor_chunk < 256) floor_chunk = 256;
+    // Aim at about 192 CTAs of up to 1536 tokens.  Measured on B200 with steps enqueued back to back: at 3 CTAs per
+    // SM the grid of a step then leaves room for the next step's CTAs beside it (its start-up hides behind this
+    // step's tail), the merge kernel has few partials to read, and 192 CTAs x 64 KB in flight already saturate HBM.
+    // Per-GPU shares of the 64-sequence workload: 1/8 33.9 -> 29.0 us per step, 1/4 54.9 -> 49.2; four sequences of
+    // 96k tokens with one KV head: 52 -> 32 us per layer step (2048-token chunks: 30 us, but ragged batches lose
+    // with them: their last, partly filled chunks leave SMs idle).
     const Switches& sw = switches();
-    if (sw.chunk > 0 && sw.chunk >= floor_chunk) chunk = sw.chunk;
-    chunk = ((chunk + 63) / 64) * 64;                 // 4 warps x 16-token tiles
-    if (chunk < 256) chunk = 256;
-    // Few CTAs: avoid a thin last wave.  With 3 CTAs per SM a wave is 444 CTAs; when the estimate (tokens / chunk
-    // plus half a CTA of rounding per sequence and head) lands a little above one or two waves, grow the chunk
-    // until it fits (measured: 4 sequences x 96k tokens x 1 head went from 512 CTAs of 768 tokens to 440 of 896).
-    if (total_tokens_hint > 0 && sw.chunk <= 0 && sw.plan_waves) {   // SKV_PLAN_WAVES=0 keeps the chunk as computed above
-        const double wave = 444.0, round_up = 0.5 * (double)n_seqs * num_kv_heads;
-        const double work = (double)total_tokens_hint * num_kv_heads;
-        const double est = work / (double)chunk + round_up;
-        for (int w = 1; w <= 2; ++w) {
-            if (est > w * wave && est <= (w + 0.6) * wave && w * wave > round_up) {
-                int64_t fit = (int64_t)(work / (w * wave - round_up)) + 1;
-                fit = ((fit + 63) / 64) * 64;
-                if (fit > chunk && fit <= 2048) chunk = fit;
-            }
-        }
+    int64_t chunk = floor_chunk;
+    if (total_tokens_hint > 0) {
+        chunk = ((num_kv_heads * total_tokens_hint + 191) / 192 + 63) / 64 * 64;
+        const int64_t cap = floor_chunk > 1536 ? floor_chunk : 1536;
+        if (chunk > cap) chunk = cap;
+        if (chunk < floor_chunk) chunk = floor_chunk;
+        if (sw.chunk > 0 && sw.chunk >= floor_chunk) chunk = ((sw.chunk + 63) / 64) * 64;   // SKV_DECODE_CHUNK
     }
-    if (chunk > 2048) {                               // a warp holds at most 32 tile page ids
-        chunk = 2048;
-        splits = (max_ctx + chunk - 1) / chunk;
-    }
+    if (chunk > 2048) chunk = 2048;                       // a warp holds at most 32 tile page ids
     *chunk_tokens = (int32_t)chunk;
-    *max_splits = (int32_t)splits;
+    *max_splits = (int32_t)splits;                        // >= ceil(max_ctx / chunk) for every chunk chosen above
 }
 
 cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
@@ -1162,7 +1152,7 @@ cudaError_t launch_decode(const DecodeLaunch& d_in, cudaStream_t stream) {
         else
             e = ns == 3 ? launch_tma<3, false>(d, stream) : ns == 4 ? launch_tma<4, false>(d, stream) : launch_tma<2, false>(d, stream);
     } else if (mma_ok) {
-        dim3 grid((unsigned)d.max_splits, (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
+        dim3 grid((unsigned)(d.grid_splits > 0 ? d.grid_splits : d.max_splits), (unsigned)d.pool.num_kv_heads, (unsigned)d.n_seqs);
         decode_mma_kernel<<<grid, kDecodeThreads, 0, stream>>>(d);
         e = cudaGetLastError();
     } else if (d.dtype == SKV_BF16) {

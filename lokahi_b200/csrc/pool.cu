@@ -45,7 +45,6 @@ void read_switches() {
     w.impl_reg = env_is("SKV_DECODE_IMPL", 'r');
     w.stages = env_int("SKV_DECODE_STAGES", 2);
     w.chunk = env_int("SKV_DECODE_CHUNK", 0);
-    w.plan_waves = !env_is("SKV_PLAN_WAVES", '0');
     w.fuse = env_is("SKV_DECODE_FUSE", '0') ? 0 : (env_is("SKV_DECODE_FUSE", '1') ? 1 : -1);
     w.prefill_generic = env_is("SKV_PREFILL_GENERIC", '1');
     w.append_scalar = env_is("SKV_APPEND_SCALAR", '1');
@@ -176,6 +175,7 @@ struct skv_pool {
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev_compute = nullptr, ev_copy = nullptr;
     bool copy_pending = false;           // copies enqueued on copy_stream not yet ordered before compute
+    std::vector<uint8_t> copy_busy;      // [max_seqs] 1: pages of this sequence are among those copies
     std::vector<TableUpdate> deferred_updates;   // page-table entries to publish once prefetch copies are ordered
 
     // scratch of the one-call decode step, kept between calls so that a step allocates nothing on the host
@@ -360,6 +360,7 @@ int32_t order_transfers(skv_pool* p, cudaStream_t stream) {
         CUDA_TRY(p, cudaEventRecord(p->ev_copy, p->copy_stream));
         CUDA_TRY(p, cudaStreamWaitEvent(stream, p->ev_copy, 0));
         p->copy_pending = false;
+        std::fill(p->copy_busy.begin(), p->copy_busy.end(), (uint8_t)0);
     }
     if (!p->deferred_updates.empty()) {
         int32_t st = publish_table_updates(p, p->deferred_updates, stream);
@@ -367,6 +368,19 @@ int32_t order_transfers(skv_pool* p, cudaStream_t stream) {
         p->deferred_updates.clear();
     }
     return SKV_OK;
+}
+
+// A call that only reads (or appends inside pages it already owns) needs the pending copies ordered before it only
+// when one of its sequences is among them: attention over other sequences runs beside an eviction or a copy back.
+// A call that takes fresh pages always orders: a page freed by an eviction may still be read by its copy.
+int32_t order_transfers_for(skv_pool* p, cudaStream_t stream, const int32_t* seq_ids, int32_t n_seqs, bool takes_pages) {
+    if (p->host_only || !p->copy_pending) return order_transfers(p, stream);
+    bool involved = takes_pages;
+    for (int32_t i = 0; !involved && i < n_seqs; ++i) {
+        const int32_t s = seq_ids ? seq_ids[i] : i;
+        involved = s >= 0 && s < p->cfg.max_seqs && p->copy_busy[s];
+    }
+    return involved ? order_transfers(p, stream) : SKV_OK;
 }
 
 // Grows a sequence's page-table row to cover `total_tokens`; all-or-nothing.
@@ -447,6 +461,7 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
     p->live.assign(cfg->max_seqs, 0);
     p->page_owner.assign(cfg->num_pages, -1);
     p->seen_stamp.assign(cfg->max_seqs, 0);
+    p->copy_busy.assign(cfg->max_seqs, 0);
     p->step_len.assign((size_t)cfg->num_layers * cfg->max_seqs, -1);
     for (int32_t i = cfg->num_pages - 1; i >= 0; --i) p->free_pages.push_back(i);
     for (int32_t i = cfg->max_seqs - 1; i >= 0; --i) p->free_seqs.push_back(i);
@@ -899,7 +914,7 @@ int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32
     }
     if (p->host_only) return SKV_OK;
     if (!q || !out) return p->fail(SKV_ERR_BAD_ARG, "q and out must be given");
-    int32_t st = order_transfers(p, stream);
+    int32_t st = order_transfers_for(p, stream, seq_ids, n_seqs, false);
     if (st != SKV_OK) return st;
     p->last_step_valid = false;
     d->pool = p->view();
@@ -993,6 +1008,11 @@ int32_t attn_impl(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_
     int32_t st = prepare_decode(p, layer, seq_ids, n_seqs, q_pos, n_q_heads, q, out_arg, eps, stream, &D, &total, &launchable);
     if (st != SKV_OK || !launchable) return st;
     decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
+    {
+        int32_t longest = 0;
+        for (int32_t i = 0; i < n_seqs; ++i) longest = std::max(longest, p->len(layer, seq_ids ? seq_ids[i] : i));
+        D.grid_splits = std::max(1, (longest + D.chunk_tokens - 1) / D.chunk_tokens);
+    }
     const size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
     st = check_workspace(p, workspace, workspace_bytes, need);
     if (st != SKV_OK) return st;
@@ -1150,6 +1170,7 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     if (!inline_rows && (size_t)n_seqs * 3 * sizeof(int32_t) > StagingRing::kSlotBytes)
         return p->fail(SKV_ERR_BAD_ARG, "too many sequences (%d) for one call", n_seqs);
     int64_t total = 0, need_total = 0;
+    int32_t longest = 0;
     if (a.seq_ids && ++p->stamp == 0) {   // generation counter wrapped: start over
         std::fill(p->seen_stamp.begin(), p->seen_stamp.end(), 0u);
         p->stamp = 1;
@@ -1172,12 +1193,14 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
         for (int32_t slot = 0; slot < std::min(need, p->n_seq_pages[s]); ++slot)
             if (p->pt(s, slot) < 0) return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", s, slot);
         total += cur + stores;
+        longest = std::max(longest, cur + stores);
     }
     if (need_total > (int64_t)p->free_pages.size())
         return p->fail(SKV_ERR_OUT_OF_PAGES, "need %lld pages, %zu free", (long long)need_total, p->free_pages.size());
     DecodeLaunch D{};
     decode_plan(P, p->cfg.max_pages_per_seq, n_seqs, Hkv, total, &D.chunk_tokens, &D.max_splits);
     if (D.max_splits > 128) return p->fail(SKV_ERR_UNSUPPORTED, "a sequence would need %d split-K chunks, 128 is the limit", D.max_splits);
+    D.grid_splits = std::max(1, (longest + D.chunk_tokens - 1) / D.chunk_tokens);
     const size_t need_ws = (size_t)n_seqs * a.n_q_heads * D.max_splits * ((size_t)Dh + 2) * sizeof(float);
     int32_t st = check_workspace(p, a.workspace, a.workspace_bytes, need_ws);
     if (st != SKV_OK) return st;
@@ -1197,8 +1220,7 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     const char* v_lo = (const char*)a.v;
     const char* v_hi = v_lo + ((int64_t)(n_seqs - 1) * v_stride + (int64_t)Hkv * Dh) * 2;
     bool early = (a.flags & SKV_STEP_CONSECUTIVE) && switches().step_early && p->last_step_valid && p->last_step_stream == stream &&
-                 p->last_step_mark == g_launches.load(std::memory_order_relaxed) && !p->copy_pending &&
-                 p->deferred_updates.empty() && inline_rows;
+                 p->last_step_mark == g_launches.load(std::memory_order_relaxed) && inline_rows;
     for (int w = 0; early && w < 2; ++w)
         if (overlaps(p->last_w_lo[w], p->last_w_hi[w], q_lo, q_hi) || overlaps(p->last_w_lo[w], p->last_w_hi[w], k_lo, k_hi) ||
             overlaps(p->last_w_lo[w], p->last_w_hi[w], v_lo, v_hi))
@@ -1206,8 +1228,10 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     p->last_step_valid = false;
 
     // ---- fallible work that does not depend on the new state ------------------------------------------------
-    st = order_transfers(p, stream);
+    const bool copies_were_pending = p->copy_pending;
+    st = order_transfers_for(p, stream, a.seq_ids, n_seqs, need_total > 0);
     if (st != SKV_OK) return st;
+    if (copies_were_pending && !p->copy_pending) early = false;   // a wait for the copy stream now sits ahead of the step
     // ---- mutate, then enqueue; a failure from here on puts the host state back -----------------------------------
     std::vector<TableUpdate>& ups = p->step_ups;
     ups.clear();
@@ -1485,6 +1509,7 @@ int32_t skv_evict(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slots,
         count_launches(1);
     }
     p->copy_pending = true;   // freed pages may be rewritten only after the copy: order_transfers enforces it
+    p->copy_busy[seq] = 1;
     return publish_table_updates(p, ups, stream);
 }
 
@@ -1535,6 +1560,7 @@ int32_t skv_prefetch(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slo
         count_launches(1);
     }
     p->copy_pending = true;
+    p->copy_busy[seq] = 1;
     return SKV_OK;
 }
 

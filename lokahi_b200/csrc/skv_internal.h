@@ -112,6 +112,7 @@ struct DecodeLaunch {
     float* ws_acc;               // [n_seqs][n_q_heads][max_splits][head_dim]
     float* ws_ml;                // [n_seqs][n_q_heads][max_splits][2]
     int32_t max_splits, chunk_tokens;
+    int32_t grid_splits;         // chunks of the longest sequence of this call (0: launch max_splits of them)
     int32_t force_generic;       // 1: take the CUDA-core kernel even where the tensor-core one applies
     // tensor maps (host pointers to CUtensorMap) of the K and V pools viewed as [rows][head_dim] bf16 with
     // [16][64] boxes; nullptr when the pool has none, and then the direct-load kernel runs
@@ -198,7 +199,6 @@ struct Switches {
     int impl_reg;          // SKV_DECODE_IMPL starts with 'r'
     int stages;            // SKV_DECODE_STAGES (2 when unset)
     int chunk;             // SKV_DECODE_CHUNK (0 when unset)
-    int plan_waves;        // SKV_PLAN_WAVES != "0"
     int fuse;              // SKV_DECODE_FUSE: -1 unset, 0, 1
     int prefill_generic;   // SKV_PREFILL_GENERIC == "1"
     int append_scalar;     // SKV_APPEND_SCALAR == "1"
