@@ -176,6 +176,8 @@ struct skv_pool {
     cudaEvent_t ev_compute = nullptr, ev_copy = nullptr;
     bool copy_pending = false;           // copies enqueued on copy_stream not yet ordered before compute
     std::vector<uint8_t> copy_busy;      // [max_seqs] 1: pages of this sequence are among those copies
+    std::vector<int32_t> n_parked;       // [max_seqs] page-table entries of the sequence that point into the host tier:
+                                         // the residency checks of the hot calls scan a row only when this is not 0
     std::vector<TableUpdate> deferred_updates;   // page-table entries to publish once prefetch copies are ordered
 
     // scratch of the one-call decode step, kept between calls so that a step allocates nothing on the host
@@ -462,6 +464,7 @@ int32_t skv_create(const skv_config* cfg, skv_pool** out) {
     p->page_owner.assign(cfg->num_pages, -1);
     p->seen_stamp.assign(cfg->max_seqs, 0);
     p->copy_busy.assign(cfg->max_seqs, 0);
+    p->n_parked.assign(cfg->max_seqs, 0);
     p->step_len.assign((size_t)cfg->num_layers * cfg->max_seqs, -1);
     for (int32_t i = cfg->num_pages - 1; i >= 0; --i) p->free_pages.push_back(i);
     for (int32_t i = cfg->max_seqs - 1; i >= 0; --i) p->free_seqs.push_back(i);
@@ -565,6 +568,7 @@ int32_t skv_free_sequence(skv_pool* p, int32_t seq, void* stream_) {
         ups.push_back({seq, slot, SKV_PAGE_UNASSIGNED});
     }
     p->n_seq_pages[seq] = 0;
+    p->n_parked[seq] = 0;
     for (int32_t l = 0; l < p->cfg.num_layers; ++l) {
         p->len(l, seq) = 0;
         p->step_len[(size_t)l * p->cfg.max_seqs + seq] = -1;
@@ -766,7 +770,7 @@ int32_t skv_append(skv_pool* p, const skv_append_args* a, void* stream_) {
     // target pages must be resident
     for (int32_t i = 0; i < a->n_seqs; ++i) {
         int32_t first = meta[i].start / p->cfg.page_size;
-        for (int32_t slot = first; slot < p->n_seq_pages[meta[i].seq]; ++slot)
+        for (int32_t slot = first; p->n_parked[meta[i].seq] > 0 && slot < p->n_seq_pages[meta[i].seq]; ++slot)
             if (p->pt(meta[i].seq, slot) < 0)
                 return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", meta[i].seq, slot);
     }
@@ -847,7 +851,7 @@ static int32_t check_readable(skv_pool* p, int32_t layer, const int32_t* seq_ids
         int32_t T = p->len(layer, s);
         if (upto) T = std::min(T, upto[i]);
         int32_t pages = (T + p->cfg.page_size - 1) / p->cfg.page_size;
-        for (int32_t slot = 0; slot < pages; ++slot)
+        for (int32_t slot = 0; p->n_parked[s] > 0 && slot < pages; ++slot)
             if (p->pt(s, slot) < 0) return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", s, slot);
     }
     return SKV_OK;
@@ -909,7 +913,7 @@ int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32
         *total_tokens += T;
         if (q_pos) T = std::min(T, std::max(0, q_pos[i] + 1));
         const int32_t pages = (T + p->cfg.page_size - 1) / p->cfg.page_size;
-        for (int32_t slot = 0; slot < pages; ++slot)
+        for (int32_t slot = 0; p->n_parked[s] > 0 && slot < pages; ++slot)
             if (p->pt(s, slot) < 0) return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", s, slot);
     }
     if (p->host_only) return SKV_OK;
@@ -1190,7 +1194,7 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
         if (need > p->cfg.max_pages_per_seq)
             return p->fail(SKV_ERR_OUT_OF_PAGES, "sequence %d needs %d pages, row holds %d", s, need, p->cfg.max_pages_per_seq);
         need_total += std::max(0, need - p->n_seq_pages[s]);
-        for (int32_t slot = 0; slot < std::min(need, p->n_seq_pages[s]); ++slot)
+        for (int32_t slot = 0; p->n_parked[s] > 0 && slot < std::min(need, p->n_seq_pages[s]); ++slot)
             if (p->pt(s, slot) < 0) return p->fail(SKV_ERR_NOT_RESIDENT, "sequence %d slot %d is not resident", s, slot);
         total += cur + stores;
         longest = std::max(longest, cur + stores);
@@ -1478,6 +1482,7 @@ int32_t skv_evict(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slots,
         int32_t h = p->free_host.back();
         p->free_host.pop_back();
         p->pt(seq, s) = -2 - h;
+        p->n_parked[seq] += 1;
         p->page_owner[e] = -1;
         items.push_back({e, h});
         ups.push_back({seq, s, -2 - h});
@@ -1531,6 +1536,7 @@ int32_t skv_prefetch(skv_pool* p, int32_t seq, int32_t first_slot, int32_t n_slo
         int32_t page = p->free_pages.back();
         p->free_pages.pop_back();
         p->pt(seq, s) = page;
+        p->n_parked[seq] -= 1;
         p->page_owner[page] = seq;
         items.push_back({page, h});
         p->deferred_updates.push_back({seq, s, page});

@@ -410,12 +410,12 @@ class PagedPool:
                     raise_for_status(st, h)
                 return out
         else:
-            begin = exchange.begin
+            advance = exchange.advance
+            a.xchg = C.pointer(exchange._desc)          # the one argument block of the exchange, updated in place per call
 
             def call(layer: int, stream: int):
                 a.layer = layer
-                desc, view = begin()
-                a.xchg = C.pointer(desc)
+                view = advance()
                 st = fn(h, ref, stream)
                 if st:
                     raise_for_status(st, h)

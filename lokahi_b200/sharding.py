@@ -138,6 +138,14 @@ class PeerExchange:
         d.out = self._out_ptrs[parity]
         return d, self._outs[parity]
 
+    def advance(self):
+        """``begin`` for a caller that already holds a pointer to the argument block: returns the result view only."""
+        self.epoch = e = self.epoch + 1
+        d = self._desc
+        d.epoch = e
+        d.out = self._out_ptrs[e & 1]
+        return self._outs[e & 1]
+
     def close(self):
         """Collective: all ranks stop using the buffers before any rank lets go of its own."""
         if self.world > 1 and self.recv is not None:
