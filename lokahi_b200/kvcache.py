@@ -30,6 +30,10 @@ def _positions_to_list(cache_position) -> List[int]:
     return [int(x) for x in np.asarray(cache_position).reshape(-1).tolist()]
 
 
+def _env_flag(name: str) -> bool:
+    return os.environ.get(name, "0") not in ("", "0")
+
+
 def _rows_packed(t: torch.Tensor) -> bool:
     """``[B, H, 1, D]`` whose heads lie back to back inside each batch row (contiguous, or a slice of a wider row)."""
     return t.dim() == 4 and t.shape[2] == 1 and t.stride(3) == 1 and t.stride(1) == t.shape[3]
@@ -54,6 +58,9 @@ class PagedKVCache:
         self._layer_lengths: Dict[int, int] = {}
         self._managed_disk_files: set = set()
         self._seen_tokens = 0
+        # layer files: float32 `key` / `value` / `seen_tokens`, readable by the reference's loader; SKV_COMPACT_KV_FILES=1
+        # (or this attribute) stores bfloat16 layers as raw 16-bit patterns instead, which only this loader reads
+        self.compact_bf16_files = _env_flag("SKV_COMPACT_KV_FILES")
         if cache_dir is not None:
             os.makedirs(cache_dir, exist_ok=True)
 
@@ -246,12 +253,15 @@ class PagedKVCache:
         t0 = time.perf_counter()
         k, v = self.materialize(layer_idx)
         extra = {}
-        if k.dtype == torch.bfloat16:   # NumPy has no bfloat16: store the raw 16-bit patterns
+        if k.dtype == torch.bfloat16 and self.compact_bf16_files:
+            # NumPy has no bfloat16: the raw 16-bit patterns plus a tag.  Half the bytes, but only this loader reads it
+            # (the reference's loader, mlx_kvcache.py:232-247, would take the patterns for integers).
             k_np = k.view(torch.int16).cpu().numpy().view(np.uint16)
             v_np = v.view(torch.int16).cpu().numpy().view(np.uint16)
             extra["stored_dtype"] = "bfloat16"
         else:
-            k_np, v_np = k.cpu().numpy(), v.cpu().numpy()
+            # float32 holds every bfloat16 value exactly: a file either side can read, like the reference's own
+            k_np, v_np = k.float().cpu().numpy(), v.float().cpu().numpy()
         np.savez_compressed(dest, key=k_np, value=v_np, seen_tokens=self._seen_tokens, **extra)
         if self.stats:
             self.stats.set("kv_save_to_disk", t0)

@@ -514,3 +514,35 @@ def test_one_call_step_with_a_sequence_list_matches_the_two_calls(monkeypatch):
     with pytest.raises(ValueError, match="listed twice"):
         pool_b.decode_step(0, qb[:2].contiguous(), k[:2].contiguous(), v[:2].contiguous(), seq_ids=[1, 1])
     assert pool_b.check_device_status() == 0
+
+
+def test_paged_tensor_core_prefill_at_2048_tokens_matches_the_oracle_on_sampled_blocks():
+    """The prefill shape of the DeepSeek-1.3B-shaped decoder (16 MHA heads of 128, 2048-token prompt, bf16, 16-token
+    pages dealt out in a random order): the paged tcgen05 kernel against the oracle on 128-row blocks sampled over
+    sequences, heads and positions (the first block, one across the middle, the last), after a RoPE-on-write append."""
+    rng = np.random.default_rng(2048)
+    n, H, S, D, P = 2, 16, 2048, 128, 16
+    pps = S // P
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=H, head_dim=D, num_pages=n * pps + 5, max_seqs=n,
+                                       max_pages_per_seq=pps, page_size=P, dtype=torch.bfloat16, rope_theta=100000.0,
+                                       rope_scaling_factor=4.0))
+    perm = rng.permutation(n * pps + 5)
+    for s in range(n):
+        assert pool.alloc_sequence() == s
+        pool.set_page_table(s, perm[s * pps:(s + 1) * pps].tolist(), 0)
+    g = torch.Generator(device=DEV).manual_seed(7)
+    q = torch.randn((n, H, S, D), generator=g, device=DEV).to(torch.bfloat16)
+    k = torch.randn((n, H, S, D), generator=g, device=DEV).to(torch.bfloat16)
+    v = torch.randn((n, H, S, D), generator=g, device=DEV).to(torch.bfloat16)
+    k0, q0 = to_np(k), to_np(q)
+    pool.append(0, k, v, start_pos=[0, 0], rope_k=True, q=q)              # rotates q in place, K on the way into the pages
+    out = pool.prefill_attention(0, q)
+    assert pool.check_device_status() == 0
+    kd, vd = pool.gather(0, n_seqs=n)
+    pos = np.arange(S)
+    for s, h, r0 in [(0, 0, 0), (1, 7, 960), (0, 15, S - 128), (1, 3, 1500)]:
+        k_rot = bf16_round(opaged.rope_rows(k0[s].transpose(1, 0, 2), pos, 100000.0, 4.0)).transpose(1, 0, 2)
+        assert np.all(np.abs(to_np(kd[s, h]) - k_rot[h]) <= np.abs(k_rot[h]) * 2.0 ** -7 + 1e-30), "stored K against the oracle's RoPE"
+        ref = oattn.chunked_grouped_attention(to_np(q[s:s + 1, h:h + 1, r0:r0 + 128]), to_np(kd[s:s + 1, h:h + 1]), to_np(vd[s:s + 1, h:h + 1]),
+                                              query_positions=pos[r0:r0 + 128].astype(np.int32), q_block_size=512, k_block_size=512)
+        assert_parity(out[s:s + 1, h:h + 1, r0:r0 + 128], ref, TOL_BF16, f"paged prefill S=2048, sequence {s} head {h} rows {r0}")

@@ -260,3 +260,38 @@ def test_graphed_decode_steps_equal_the_eager_ones():
     for a, b in zip(runs[False], runs[True]):
         assert torch.equal(a, b)
     del rng
+
+
+def test_deepseek_shaped_bf16_decoder_four_layers_2048_token_prompt():
+    """The same geometry at the prompt length of the configuration: 4 of the 24 layers, one sequence, a 2048-token
+    prompt (the paged tensor-core prefill inside the decoder at full length) and 4 cached decode steps, against the
+    NumPy decoder oracle.  The oracle at this size is tens of seconds of CPU, which is what bounds the sample."""
+    cfg = od.make_config(vocab_size=32256, hidden_size=2048, intermediate_size=5504, num_hidden_layers=4,
+                         num_attention_heads=16, num_key_value_heads=None, max_position_embeddings=4096,
+                         rope_theta=100000.0, rope_scaling_factor=4.0)
+    w = od.random_weights(cfg, seed=13)
+    import ml_dtypes
+    w16 = {k: v.astype(ml_dtypes.bfloat16).astype(np.float32) for k, v in w.items()}
+    oracle = od.DecoderOracle(cfg, w16, round_dtype=ml_dtypes.bfloat16, round_glue=True)
+    model = L.PagedDecoder(cfg, _to_torch(w16, torch.bfloat16))
+    rng = np.random.default_rng(14)
+    prompt = rng.integers(0, 32256, size=(1, 2048))
+    cache = L.PagedKVCache(cfg, cache_dir=None)
+    ocache = ConcatKVCache(cfg, cache_dir=None)
+    logits = model(torch.from_numpy(prompt), past_key_values=cache, use_cache=True)
+    ologits = oracle(prompt, past_key_values=ocache, use_cache=True)
+    # Every GEMM output is rounded to bf16 on both sides, after sums taken in a different order, so now and then a
+    # hidden element lands one bf16 step apart (2^-8 relative).  A logit sums 2048 of them: about 0.2 % of the
+    # logits' rms per rounding point, and four layers have some twenty-four such points, i.e. a spread near 1 % of
+    # the rms -- the element-wise criterion (2 % of the rms) is then a two-sigma event.  The normalised maximum
+    # error keeps the 2e-2 bound; the share of elements outside the element-wise criterion may reach 10 %.
+    for r0 in (0, 1000, 2047):                                  # rows sampled over the prompt, the last one included
+        assert_parity_logits(logits[:, r0:r0 + 1], ologits[:, r0:r0 + 1], TOL_BF16, f"prefill logits, row {r0}",
+                             max_outlier_fraction=0.10)
+    nxt = np.argmax(ologits[:, -1, :], axis=-1)[:, None]
+    for step in range(4):
+        logits = model(torch.from_numpy(nxt), past_key_values=cache, use_cache=True)
+        ologits = oracle(nxt, past_key_values=ocache, use_cache=True)
+        assert_parity_logits(logits, ologits, TOL_BF16, f"decode step {step} after a 2048-token prompt", max_outlier_fraction=0.10)
+        nxt = np.argmax(ologits[:, -1, :], axis=-1)[:, None]
+    assert cache.get_seq_length() == 2052 and cache.pool.check_device_status() == 0

@@ -530,3 +530,30 @@ def test_layer_file_in_the_reference_layout_and_float32_loads_into_a_bfloat16_ca
     got = cache[0]
     assert np.array_equal(to_np(got["key"]), bf16_round(k32)) and np.array_equal(to_np(got["value"]), bf16_round(v32))
     assert cache.get_seq_length(0) == 5 and 0 not in cache._disk_offloaded
+
+
+@pytest.mark.gpu
+def test_saved_bfloat16_layer_is_readable_with_the_reference_loader_logic(tmp_path):
+    """What the reference's loader does with a layer file (np.load, ``data["key"]`` / ``data["value"]`` taken as they
+    are, ``seen_tokens`` if present; mlx_kvcache.py:232-247): a bfloat16 layer saved here must give it the stored values
+    (float32 holds them exactly), and the compact 16-bit form stays available behind its switch and round-trips."""
+    cfg = SimpleNamespace(num_hidden_layers=1, max_position_embeddings=64)
+    rng = np.random.default_rng(8)
+    k_np = bf16_round(rng.standard_normal((2, 2, 7, 128), dtype=np.float32))
+    v_np = bf16_round(rng.standard_normal((2, 2, 7, 128), dtype=np.float32))
+    for compact in (False, True):
+        cache = L.PagedKVCache(cfg, cache_dir=str(tmp_path / ("c" if compact else "f")))
+        cache.compact_bf16_files = compact
+        cache.update(_t(k_np, torch.bfloat16), _t(v_np, torch.bfloat16), 0, {"cache_position": list(range(7))})
+        cache.save_to_disk(0)
+        with np.load(cache._disk_offloaded[0]) as data:           # the reference's reading of the file
+            key, value, seen = np.asarray(data["key"]), np.asarray(data["value"]), int(data["seen_tokens"])
+            tagged = "stored_dtype" in data
+        assert seen == 7 and tagged == compact
+        if not compact:
+            assert key.dtype == np.float32 and np.array_equal(key, k_np) and np.array_equal(value, v_np)
+        else:
+            assert key.dtype == np.uint16
+        got = cache[0]                                           # and this loader reads both forms back bit for bit
+        assert np.array_equal(to_np(got["key"]), k_np) and np.array_equal(to_np(got["value"]), v_np)
+        cache.clear()
