@@ -582,7 +582,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid
         const int page = __shfl_sync(0xffffffffu, my_page, k);
         const int stage = k % NS;
         // every lane runs its own bounded wait; the verdict is made warp-uniform before anything branches on it
-        if (!__all_sync(0xffffffffu, mbar_wait(&wbar[stage], (k / NS) & 1))) {
+        if (!mbar_wait_warp(&wbar[stage], (k / NS) & 1)) {
             dead = true;
             break;
         }

@@ -386,8 +386,8 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
             }
             // S of tiles 2m and 2m+1 in one go: eight N = 128 MMAs into columns [0, 128)
             auto issue_qk_pair = [&](int m) {
-                ok = ok && mbar_wait(&bar_k[0], (uint32_t)(m & 1));
-                ok = ok && mbar_wait(&bar_k[1], (uint32_t)(m & 1));
+                ok = ok && mbar_wait_warp(&bar_k[0], (uint32_t)(m & 1));
+                ok = ok && mbar_wait_warp(&bar_k[1], (uint32_t)(m & 1));
                 if (!ok) return;
                 tc_fence_after();
 #pragma unroll
@@ -399,7 +399,7 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 if (lead) umma_commit(bar_s);
                 __syncwarp();
             };
-            ok = mbar_wait(bar_q, 0);
+            ok = mbar_wait_warp(bar_q, 0);
             if (ok) issue_qk_pair(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int m = j >> 1;
@@ -407,7 +407,7 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 if constexpr (!PAGED) {
                     // both K stages are free once the pair's first MMA has completed: refill them for the next pair
                     if ((j & 1) == 0 && next_pair) {
-                        ok = ok && mbar_wait(bar_s, (uint32_t)(m & 1));
+                        ok = ok && mbar_wait_warp(bar_s, (uint32_t)(m & 1));
                         if (!ok) break;
                         if (lead) {
                             load_k(2 * m + 2, nullptr);
@@ -418,21 +418,21 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 }
                 if ((j & 1) == 1 && next_pair) {
                     // the softmax threads hold S of the pair's second tile in registers: S may be overwritten
-                    ok = ok && mbar_wait(bar_r, (uint32_t)(m & 1));
+                    ok = ok && mbar_wait_warp(bar_r, (uint32_t)(m & 1));
                     if (!ok) break;
                     tc_fence_after();
                     issue_qk_pair(m + 1);
                     if (!ok) break;
                 }
                 // softmax of tile j done: P_j is in shared memory, PV_{j-1} has completed
-                ok = ok && mbar_wait(bar_p, (uint32_t)(j & 1));
+                ok = ok && mbar_wait_warp(bar_p, (uint32_t)(j & 1));
                 if (!ok) break;
                 tc_fence_after();
                 if constexpr (!PAGED) {
                     if (lead && j >= 1 && j + 1 < n_tiles) load_v(j + 1, nullptr);     // V stage (j+1)&1 was consumed by PV_{j-1}
                     __syncwarp();
                 }
-                ok = mbar_wait(&bar_v[j & 1], (uint32_t)((j >> 1) & 1));
+                ok = mbar_wait_warp(&bar_v[j & 1], (uint32_t)((j >> 1) & 1));
                 if (!ok) break;
                 const uint32_t vs = v_addr + (uint32_t)(j & 1) * kVStage;
 #pragma unroll
@@ -447,7 +447,7 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     } else {
         // =============================== softmax warps: one query row per thread ===============================
         for (int j = 0; j < n_tiles; ++j) {
-            ok = mbar_wait(bar_s, (uint32_t)((j >> 1) & 1));    // one completion per pair of tiles
+            ok = mbar_wait_warp(bar_s, (uint32_t)((j >> 1) & 1));    // one completion per pair of tiles
             if (!ok) break;
             tc_fence_after();
             const uint32_t s_col = kColS + (uint32_t)(j & 1) * kBN;
@@ -492,7 +492,7 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
             m_run = m_new;
             // P's buffer and the O accumulator are still in use by the previous tile's second MMA
             if (j > 0) {
-                ok = mbar_wait(&bar_o[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1));
+                ok = mbar_wait_warp(&bar_o[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1));
                 if (!ok) break;
                 tc_fence_after();
             }
@@ -523,7 +523,7 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         }
         // wait for the last accumulation
         if (n_tiles > 0 && ok) {
-            ok = mbar_wait(&bar_o[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1));
+            ok = mbar_wait_warp(&bar_o[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1));
             tc_fence_after();
         }
         if (!ok) *sh_abort = 1;

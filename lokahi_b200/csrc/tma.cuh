@@ -79,6 +79,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long l
     }
 }
 
+// The same wait for a whole warp with a warp-uniform verdict: every lane runs its own bounded loop, so at the
+// timeout boundary single lanes could disagree; code that goes on to warp-collective instructions (shuffles,
+// tcgen05.ld / st, __syncwarp) must branch on a verdict all lanes share.  Call it from converged code only.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+}
+
 // One 2-D box from global memory into this CTA's shared memory; completion is signalled on `bar`.
 // x (innermost coordinate, in elements) times the element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {
