@@ -1,0 +1,133 @@
+"""Decode steps fed from pinned host memory: upload, step and read-back as a three-stream pipeline.
+
+A caller whose per-step inputs live in host memory (the q, k, v rows of a step arrive from another process, a
+network card, a CPU stage) pays one host-to-device copy and one device-to-host copy per step.  Issued one after
+the other on one stream they add to the step; here the upload of step s + 1 runs on a copy stream while step s
+computes, the result of step s is read back on a third stream while step s + 1 computes, and the host waits for
+result s - 1 before it enqueues step s + 1 (and for the last result before ``run`` returns).  Two device staging
+buffers and two result buffers alternate.  The per-step choreography (copies, event records and waits) goes
+straight to the CUDA runtime through ctypes, and the step itself is a bound library call
+(``PagedPool.decode_step_binder``), so a step costs the host a few microseconds beside the two launches.
+
+The reference has no counterpart (its arrays live in unified memory); this is the host side of the decode step
+for a discrete GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+
+_H2D, _D2H = 1, 2
+
+
+def _cudart():
+    """The CUDA runtime torch itself uses (already loaded in the process)."""
+    for name in ("libcudart.so.12", "libcudart.so"):
+        try:
+            lib = C.CDLL(name)
+            lib.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+            lib.cudaEventRecord.argtypes = [C.c_void_p, C.c_void_p]
+            lib.cudaStreamWaitEvent.argtypes = [C.c_void_p, C.c_void_p, C.c_uint]
+            lib.cudaEventSynchronize.argtypes = [C.c_void_p]
+            return lib
+        except OSError:
+            continue
+    raise RuntimeError("the CUDA runtime library is not loadable; HostStepPipeline needs it")
+
+
+class HostStepPipeline:
+    """Runs ``decode_step`` for a fixed batch shape with inputs from, and results to, pinned host tensors.
+
+    ``exchange`` (a ``sharding.PeerGather`` / ``PeerSeqMerge``) makes the step the sharded one; ``step_args`` is called
+    with the step index and returns the per-step keyword arguments of ``decode_step_binder`` that vary (``positions`` /
+    ``store`` under sequence sharding), or is None."""
+
+    def __init__(self, pool, layer: int, n_seqs: int, n_q_heads: int, *, exchange=None, step_args=None, n_steps: Optional[int] = None):
+        c = pool.cfg
+        self.pool, self.layer = pool, layer
+        dev = pool.torch_device
+        D, hkv = c.head_dim, c.num_kv_heads
+        self.nq, self.nk = n_seqs * n_q_heads * D, n_seqs * hkv * D
+        self.in_elems = self.nq + 2 * self.nk
+        self.stage = [torch.empty((self.in_elems,), device=dev, dtype=c.dtype) for _ in range(2)]
+        self.views = [(b[:self.nq].view(n_seqs, n_q_heads, D), b[self.nq:self.nq + self.nk].view(n_seqs, hkv, D),
+                       b[self.nq + self.nk:].view(n_seqs, hkv, D)) for b in self.stage]
+        self.exchange = exchange
+        self.results = None if exchange is not None else [torch.empty((n_seqs, n_q_heads, D), device=dev, dtype=c.dtype) for _ in range(2)]
+        self.result_shape = tuple(exchange.out_shape) if exchange is not None else (n_seqs, n_q_heads, D)
+        self.esize = self.stage[0].element_size()
+        self.rt = _cudart()
+        self.up, self.down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self.main = torch.cuda.current_stream(dev)
+        mk = lambda: [torch.cuda.Event() for _ in range(2)]
+        self.ev_up, self.ev_step, self.ev_done = mk(), mk(), mk()
+        for group, stream in ((self.ev_up, self.up), (self.ev_step, self.main), (self.ev_done, self.down)):
+            for e in group:
+                e.record(stream)                       # creates the CUDA event behind the torch object
+        torch.cuda.synchronize(dev)
+        # the step calls on the two staging buffers, bound once; with per-step arguments one call per step
+        self._calls: List = []
+        if step_args is None:
+            for b in range(2):
+                self._calls.append(self._bind(b, {}))
+        else:
+            if n_steps is None:
+                raise ValueError("n_steps is needed with step_args")
+            for i in range(n_steps):
+                self._calls.append(self._bind(i & 1, step_args(i)))
+        self._per_step = step_args is not None
+
+    def _bind(self, b: int, kw: dict):
+        q, k, v = self.views[b]
+        if self.exchange is not None:
+            return self.pool.decode_step_binder(q, k, v, exchange=self.exchange, **kw)
+        return self.pool.decode_step_binder(q, k, v, self.results[b], **kw)
+
+    def run(self, inputs: torch.Tensor, outputs: torch.Tensor) -> None:
+        """``inputs`` pinned ``[n_steps, in_elems]`` (row = q | k | v of a step, flattened), ``outputs`` pinned
+        ``[rows, *result_shape]`` with ``rows >= 2``: the result of step i lands in row ``i % rows`` (a ring when there
+        are fewer rows than steps: row r is rewritten two steps after the host was handed its previous content).
+        Runs the steps in order and returns when the last result is in ``outputs``."""
+        if not (inputs.is_pinned() and outputs.is_pinned()):
+            raise ValueError("inputs and outputs must be pinned host tensors")
+        n = inputs.shape[0]
+        rows_out = outputs.shape[0]
+        if inputs.shape[1] != self.in_elems or tuple(outputs.shape[1:]) != self.result_shape or rows_out < min(n, 2):
+            raise ValueError("inputs / outputs do not match the pipeline's shapes")
+        if self._per_step and n > len(self._calls):
+            raise ValueError("more steps than were bound")
+        rt, esize = self.rt, self.esize
+        up, down, main = self.up.cuda_stream, self.down.cuda_stream, self.main.cuda_stream
+        e_up = [e.cuda_event for e in self.ev_up]
+        e_step = [e.cuda_event for e in self.ev_step]
+        e_done = [e.cuda_event for e in self.ev_done]
+        stage = [t.data_ptr() for t in self.stage]
+        in_ptr, in_row = inputs.data_ptr(), inputs.stride(0) * esize
+        out_ptr, out_row = outputs.data_ptr(), outputs.stride(0) * outputs.element_size()
+        in_bytes, out_bytes = self.in_elems * esize, outputs[0].numel() * outputs.element_size()
+        layer, calls, per_step = self.layer, self._calls, self._per_step
+        memcpy, record, wait, sync = rt.cudaMemcpyAsync, rt.cudaEventRecord, rt.cudaStreamWaitEvent, rt.cudaEventSynchronize
+        wait(up, e_step[0], 0)                                     # whatever ran before has finished with the staging buffers
+        wait(up, e_step[1], 0)
+        memcpy(stage[0], in_ptr, in_bytes, _H2D, up)
+        record(e_up[0], up)
+        for i in range(n):
+            b = i & 1
+            if i + 1 < n:                                          # next step's inputs, while this step computes
+                if i >= 1:
+                    wait(up, e_step[1 - b], 0)                     # step i - 1 has finished reading that staging buffer
+                memcpy(stage[1 - b], in_ptr + (i + 1) * in_row, in_bytes, _H2D, up)
+                record(e_up[1 - b], up)
+            wait(main, e_up[b], 0)
+            if i >= 2:
+                wait(main, e_done[b], 0)                           # the result buffer of this parity has been read back
+            view = calls[i if per_step else b](layer, main)
+            record(e_step[b], main)
+            wait(down, e_step[b], 0)
+            memcpy(out_ptr + (i % rows_out) * out_row, view.data_ptr(), out_bytes, _D2H, down)
+            record(e_done[b], down)
+            if i >= 1:
+                sync(e_done[1 - b])                                # the host consumes result i - 1 here
+        sync(e_done[(n - 1) & 1])

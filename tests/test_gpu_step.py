@@ -391,3 +391,32 @@ def test_consecutive_steps_across_layers_and_after_a_truncation():
         kb, vb = pool_b.gather(layer, n_seqs=n)
         assert torch.equal(ka, kb) and torch.equal(va, vb)
     assert pool_a.check_device_status() == 0 and pool_b.check_device_status() == 0
+
+
+@pytest.mark.parametrize("with_exchange", [False, True])
+def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
+    """`HostStepPipeline`: every step's q | k | v row comes from pinned host memory and every result goes back to it,
+    uploads and read-backs overlapping the steps.  Results (through a two-row ring and through a full-length
+    output) equal the same steps made directly with device tensors; lengths and pages too."""
+    lens = [5, 16, 300, 1023, 2047]
+    n, steps = len(lens), 9
+    pool_a, *_ = _pool(61, lens, 2 * steps)
+    pool_b, *_ = _pool(61, lens, 2 * steps)
+    q_all, k_all, v_all = _inputs(14, steps, n)
+    ref = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(steps)])
+    rows = torch.cat([q_all.reshape(steps, -1), k_all.reshape(steps, -1), v_all.reshape(steps, -1)], dim=1).cpu().pin_memory()
+    ex = L.PeerGather(L.HeadShard(0, 1, HQ, HKV), n, D, torch.bfloat16, torch.device(DEV)) if with_exchange else None
+    pipe = L.HostStepPipeline(pool_b, 0, n, HQ, exchange=ex)
+    shape = (1, n, HQ, D) if with_exchange else (n, HQ, D)
+    full = torch.empty((steps,) + shape, dtype=torch.bfloat16).pin_memory()
+    pipe.run(rows, full)
+    assert torch.equal(full.reshape(steps, n, HQ, D), ref.cpu())
+    ring = torch.empty((2,) + shape, dtype=torch.bfloat16).pin_memory()
+    ref2 = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(steps)])
+    pipe.run(rows, ring)                                   # a second run on the same pipeline, results through a ring
+    assert torch.equal(ring[(steps - 1) % 2].reshape(n, HQ, D), ref2[-1].cpu())
+    assert torch.equal(ring[(steps - 2) % 2].reshape(n, HQ, D), ref2[-2].cpu())
+    assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
+    _same_pages(pool_a, pool_b, n, [t + 2 * steps for t in lens])
+    with pytest.raises(ValueError, match="pinned"):
+        pipe.run(rows.clone(), ring)
