@@ -557,3 +557,31 @@ def test_saved_bfloat16_layer_is_readable_with_the_reference_loader_logic(tmp_pa
         got = cache[0]                                           # and this loader reads both forms back bit for bit
         assert np.array_equal(to_np(got["key"]), k_np) and np.array_equal(to_np(got["value"]), v_np)
         cache.clear()
+
+
+@pytest.mark.gpu
+def test_attention_over_other_sequences_runs_beside_page_copies():
+    """While the pages of one sequence travel to host memory and back, calls that touch only other sequences are not
+    ordered behind the copies (they would find their pages resident anyway); a call on the travelling sequence, or
+    one that takes fresh pages, is.  Results are the ones from before the copies either way."""
+    rng = np.random.default_rng(21)
+    Hq, Hkv, D, P = 8, 2, 128, 16
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=40, max_seqs=3, max_pages_per_seq=12,
+                                       page_size=P, dtype=torch.bfloat16, host_pages=16, rope_theta=10000.0))
+    lens = [150, 100, 40]
+    for s, t in enumerate(lens):
+        assert pool.alloc_sequence() == s
+        kv = _t(bf16_round(rng.standard_normal((1, Hkv, t, D), dtype=np.float32)), torch.bfloat16)
+        pool.append(0, kv, kv, seq_ids=[s], start_pos=[0])
+    q = _t(bf16_round(rng.standard_normal((3, Hq, D), dtype=np.float32)), torch.bfloat16)
+    before = pool.decode_attention(0, q).clone()
+    pool.evict(0, 0, 8)
+    pool.prefetch(0, 0, 8)                                     # sequence 0 is on its way out and back
+    other = pool.decode_attention(0, q[1:].contiguous(), seq_ids=[1, 2])
+    assert torch.equal(other, before[1:])
+    k1 = _t(bf16_round(rng.standard_normal((1, Hkv, D), dtype=np.float32)), torch.bfloat16)
+    step_out = pool.decode_step(0, q[2:3].clone(), k1, k1, seq_ids=[2])   # stays inside its last page: no fresh page
+    assert pool.length(0, 2) == 41 and bool(torch.isfinite(step_out.float()).all())
+    again = pool.decode_attention(0, q[:1].contiguous(), seq_ids=[0])     # the travelling sequence: ordered behind the copies
+    assert torch.equal(again, before[:1])
+    assert pool.check_device_status() == 0 and pool.counters()["pages_prefetched"] == 8

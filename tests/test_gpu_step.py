@@ -420,3 +420,42 @@ def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
     _same_pages(pool_a, pool_b, n, [t + 2 * steps for t in lens])
     with pytest.raises(ValueError, match="pinned"):
         pipe.run(rows.clone(), ring)
+
+
+@pytest.mark.parametrize("mode", ["head_gather", "seq_merge"])
+def test_exchange_on_a_float32_pool_through_the_cuda_core_kernels(mode):
+    """float32 storage, head_dim 64, 4 query heads per KV head... none of it fits the one-kernel step, so the step is
+    the append + attention pair and the exchange runs behind the CUDA-core split-K kernel: same rows as without it."""
+    n, hq, hkv, d = 4, 8, 2, 64
+    lens = [0, 9, 130, 700]
+
+    def make():
+        rng = np.random.default_rng(33)
+        pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=hkv, head_dim=d, num_pages=4 * 50, max_seqs=n,
+                                           max_pages_per_seq=50, page_size=P, dtype=torch.float32, rope_theta=10000.0))
+        for s in range(n):
+            assert pool.alloc_sequence() == s
+            if lens[s]:
+                kv = _t(rng.standard_normal((1, hkv, lens[s], d), dtype=np.float32), torch.float32)
+                pool.append(0, kv, kv * 0.5, seq_ids=[s], start_pos=[0])
+        return pool
+
+    pool_a, pool_b = make(), make()
+    dev = torch.device(DEV)
+    ex = (L.PeerGather(L.HeadShard(0, 1, hq, hkv), n, d, torch.float32, dev) if mode == "head_gather"
+          else L.PeerSeqMerge(0, 1, n, hq, d, torch.float32, dev))
+    g = torch.Generator(device=DEV).manual_seed(4)
+    for step in range(3):
+        q = torch.randn((n, hq, d), generator=g, device=DEV)
+        k = torch.randn((n, hkv, d), generator=g, device=DEV)
+        v = torch.randn((n, hkv, d), generator=g, device=DEV)
+        qa, qb = q.clone(), q.clone()
+        out_a = pool_a.decode_step(0, qa, k, v)
+        view = pool_b.decode_step(0, qb, k, v, exchange=ex)
+        got = view[0] if mode == "head_gather" else view
+        assert torch.equal(qa, qb) and torch.equal(got, out_a), f"step {step}"
+    q = torch.randn((n, hq, d), generator=g, device=DEV)
+    view = pool_b.decode_attention_xchg(0, q, ex, q_pos=[-1, 3, 100, 702])
+    ref = pool_a.decode_attention(0, q, q_pos=[-1, 3, 100, 702])
+    assert torch.equal(view[0] if mode == "head_gather" else view, ref) and not bool(ref[0].any())
+    assert pool_b.check_device_status() == 0
