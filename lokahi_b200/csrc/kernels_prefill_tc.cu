@@ -176,8 +176,6 @@ struct TcParams {
     PoolView pool;
     int32_t layer;
     const int32_t* seq_ids;     // device [B] or nullptr (identity)
-    int32_t stagger_ns;
-    int32_t* stagger_cnt;
 };
 
 template <bool PAGED>
@@ -203,16 +201,6 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // provably warp-uniform for the compiler
-    if (p.stagger_ns > 0) {   // experiment: de-phase the two CTAs of an SM
-        __shared__ int s_odd;
-        if (tid == 0) {
-            uint32_t smid;
-            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            s_odd = atomicAdd(p.stagger_cnt + smid, 1) & 1;
-        }
-        __syncthreads();
-        if (s_odd) __nanosleep(p.stagger_ns);
-    }
     // heavy (late) query tiles first so that the causal triangle balances across SMs
     // (blocks are dispatched x-fastest: all heads' heaviest tiles start first)
     const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;
@@ -629,13 +617,6 @@ cudaError_t launch_attn_tc(const DenseAttnLaunch& a, cudaStream_t stream) {
     p.pool = a.pool;
     p.layer = a.layer;
     p.seq_ids = a.seq_ids;
-    {
-        static int32_t* cnt = nullptr;
-        const char* e = getenv("SKV_PREFILL_STAGGER");
-        p.stagger_ns = e ? atoi(e) : 0;
-        if (p.stagger_ns > 0 && !cnt) { cudaMalloc(&cnt, 1024 * 4); cudaMemset(cnt, 0, 1024 * 4); }
-        p.stagger_cnt = cnt;
-    }
     dim3 grid((unsigned)a.Hq, (unsigned)((a.Lq + kBM - 1) / kBM), (unsigned)a.B);
     if (paged)
         prefill_tc_kernel<true><<<grid, kThreadsPaged, kSmemBytes, stream>>>(p, qmap, kmap, vmap);
