@@ -57,8 +57,11 @@ constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 64;           // keys per tile
 constexpr int kD = 128;           // head_dim
 constexpr int kSoftmaxWarps = 4;   // one query row per thread
-constexpr int kThreadsDense = (kSoftmaxWarps + 1) * 32;   // plus one warp that issues the TMA copies and the MMAs
-constexpr int kThreadsPaged = (kSoftmaxWarps + 2) * 32;   // paged K/V: the copies (four times as many) get a warp of their own
+// Helper warps behind the softmax warps.  Dense K/V: one that issues the MMAs of S = Q . K^T and one that issues the
+// MMAs of O += P . V and, in the gaps, the four TMA copies of a tile (six warps: 168 registers per thread at two CTAs
+// per SM).  Paged K/V: sixteen copies per tile, which get a warp of their own in front of the two issuers.
+constexpr int kThreadsDense = (kSoftmaxWarps + 2) * 32;
+constexpr int kThreadsPaged = (kSoftmaxWarps + 3) * 32;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0;     // S of a pair of tiles: 64 fp32 columns each, [0,64) and [64,128), written by one N = 128 MMA set
 constexpr uint32_t kColO = 128;   // O accumulator: 128 fp32 columns
@@ -86,6 +89,11 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -199,6 +207,9 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         return;
     }
 
+    constexpr int kWarpCopy = PAGED ? kSoftmaxWarps : -1;
+    constexpr int kWarpQK = kSoftmaxWarps + (PAGED ? 1 : 0);
+    constexpr int kWarpPV = kWarpQK + 1;
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // provably warp-uniform for the compiler
     // heavy (late) query tiles first so that the causal triangle balances across SMs
@@ -243,10 +254,10 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
         mbar_init(&bar_v[0], 1);
         mbar_init(&bar_v[1], 1);
         mbar_init(bar_s, 1);
-        mbar_init(bar_r, kSoftmaxWarps * 32);
+        mbar_init(bar_r, kSoftmaxWarps);          // one arrival per softmax warp
         mbar_init(&bar_o[0], 1);
         mbar_init(&bar_o[1], 1);
-        mbar_init(bar_p, kSoftmaxWarps * 32);
+        mbar_init(bar_p, kSoftmaxWarps);
         fence_mbar_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, kTmemCols);
@@ -318,31 +329,34 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     constexpr uint32_t kIdescO = instr_desc(kD, 1);
     bool ok = true;
 
-    if (PAGED && warp == kSoftmaxWarps + 1) {
-        // =============================== producer warp (paged K/V only): TMA copies ===============================
-        // A 64-key tile of 16-token pages is eight copies for K and eight for V, about 80 clocks of issue each:
-        // too much to sit on the MMA warp.  The K stages are refilled
-        // for the next pair as soon as the pair's first MMA has completed, a V stage as soon as the second MMA
-        // that read it has.
+    if (PAGED && warp == kWarpCopy) {
+        // =============================== producer warp (paged K/V): TMA copies ===============================
+        // A tile of 16-token pages is eight copies for K and eight for V, and a copy costs its issuing thread 80
+        // to 150 clocks.  The K stages are refilled for the next pair as soon as the pair's first MMA has
+        // completed, a V stage as soon as the second MMA that read it has.
         if (lane == 0 && n_tiles > 0) {
             mbar_expect_tx(bar_q, 2 * kBM * 128);
             tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, zq, bar_q);
             tma_load_3d(smem + kOffQ + kBM * 128, &qmap, 64, q_tile * kBM, zq, bar_q);
-            // page rows of the current pair of tiles and of the next one: K is fetched a pair ahead, V a tile
-            // ahead, so every page-table entry is read once and serves both
+            // paged: page rows of the current pair of tiles and of the next one; K is fetched a pair ahead, V a
+            // tile ahead, so every page-table entry is read once and serves both
             int y_cur[2][4], y_next[2][4];
-            tile_rows(0, y_cur[0]);
-            tile_rows(1, y_cur[1]);
+            if constexpr (PAGED) {
+                tile_rows(0, y_cur[0]);
+                tile_rows(1, y_cur[1]);
+            }
             load_k(0, y_cur[0]);
-            load_k(1, y_cur[1]);      // always a whole pair: slots the sequence does not have read page 0 and are masked
+            load_k(1, y_cur[1]);      // always a whole pair: rows the sequence does not have are zero-filled (dense) or read from page 0, and masked
             load_v(0, y_cur[0]);
             if (n_tiles > 1) load_v(1, y_cur[1]);
             for (int m = 0; 2 * m < n_tiles && ok; ++m) {
                 const int j0 = 2 * m, j1 = 2 * m + 1;
                 const bool next_pair = 2 * (m + 1) < n_tiles;
                 if (next_pair) {
-                    tile_rows(j0 + 2, y_next[0]);
-                    tile_rows(j0 + 3, y_next[1]);
+                    if constexpr (PAGED) {
+                        tile_rows(j0 + 2, y_next[0]);
+                        tile_rows(j0 + 3, y_next[1]);
+                    }
                     ok = mbar_wait(bar_s, (uint32_t)(m & 1));      // the pair's first MMA is done: both K stages are free
                     if (!ok) break;
                     load_k(j0 + 2, y_next[0]);
@@ -358,21 +372,48 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                     if (!ok) break;
                     load_v(j1 + 1, y_next[0]);
                 }
+                if constexpr (PAGED) {
 #pragma unroll
-                for (int sub = 0; sub < 4; ++sub) {
-                    y_cur[0][sub] = y_next[0][sub];
-                    y_cur[1][sub] = y_next[1][sub];
+                    for (int sub = 0; sub < 4; ++sub) {
+                        y_cur[0][sub] = y_next[0][sub];
+                        y_cur[1][sub] = y_next[1][sub];
+                    }
                 }
             }
             if (!ok) *sh_abort = 1;
         }
-    } else if (warp == kSoftmaxWarps) {
-        // =============================== issuer warp: MMA ===============================
+    } else if (warp == kWarpQK) {
+        // =============================== first issuer warp: S = Q . K^T ===============================
         // The whole warp runs the loop (uniform control flow keeps the MMA descriptors in uniform registers);
-        // lane 0 alone issues the MMAs and the commits.
+        // lane 0 alone issues the MMAs and the commits.  S of tiles 2m and 2m+1 in one go: eight N = 128 MMAs
+        // into columns [0, 128), as soon as the softmax threads hold the previous pair's second tile in registers.
         if (n_tiles > 0) {
             const uint32_t lead = lane == 0 ? 1u : 0u;
-            if constexpr (!PAGED) {   // dense K/V: four copies per tile, issued from this warp
+            ok = mbar_wait_warp(bar_q, 0);
+            for (int m = 0; 2 * m < n_tiles && ok; ++m) {
+                ok = ok && mbar_wait_warp(&bar_k[0], (uint32_t)(m & 1));
+                ok = ok && mbar_wait_warp(&bar_k[1], (uint32_t)(m & 1));
+                if (m > 0) ok = ok && mbar_wait_warp(bar_r, (uint32_t)((m - 1) & 1));
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint32_t blk = (uint32_t)(ks >> 2), in = (uint32_t)(ks & 3) * 32;
+                    umma_ss(tmem_base + kColS, smem_desc(q_addr + blk * (kBM * 128) + in, 16, 1024),
+                            smem_desc(k_addr + blk * (2 * kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u, lead);
+                }
+                if (lead) umma_commit(bar_s);
+                __syncwarp();
+            }
+            if (!ok) *sh_abort = 1;
+        }
+    } else if (warp == kWarpPV) {
+        // =============================== second issuer warp: O += P . V ===============================
+        // One issuing thread gets an MMA out every 90 to 104 clocks, so with a single issuer the pair's eight
+        // S instructions sat between a tile's P and its four O instructions; the two chains now issue side by side.
+        if (n_tiles > 0) {
+            const uint32_t lead = lane == 0 ? 1u : 0u;
+            if constexpr (!PAGED) {
                 if (lead) {
                     mbar_expect_tx(bar_q, 2 * kBM * 128);
                     tma_load_3d(smem + kOffQ, &qmap, 0, q_tile * kBM, zq, bar_q);
@@ -384,56 +425,12 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 }
                 __syncwarp();
             }
-            // S of tiles 2m and 2m+1 in one go: eight N = 128 MMAs into columns [0, 128)
-            auto issue_qk_pair = [&](int m) {
-                ok = ok && mbar_wait_warp(&bar_k[0], (uint32_t)(m & 1));
-                ok = ok && mbar_wait_warp(&bar_k[1], (uint32_t)(m & 1));
-                if (!ok) return;
-                tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint32_t blk = (uint32_t)(ks >> 2), in = (uint32_t)(ks & 3) * 32;
-                    umma_ss(tmem_base + kColS, smem_desc(q_addr + blk * (kBM * 128) + in, 16, 1024),
-                            smem_desc(k_addr + blk * (2 * kBN * 128) + in, 16, 1024), kIdescS, ks > 0 ? 1u : 0u, lead);
-                }
-                if (lead) umma_commit(bar_s);
-                __syncwarp();
-            };
-            ok = mbar_wait_warp(bar_q, 0);
-            if (ok) issue_qk_pair(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int m = j >> 1;
-                const bool next_pair = 2 * (m + 1) < n_tiles;
-                if constexpr (!PAGED) {
-                    // both K stages are free once the pair's first MMA has completed: refill them for the next pair
-                    if ((j & 1) == 0 && next_pair) {
-                        ok = ok && mbar_wait_warp(bar_s, (uint32_t)(m & 1));
-                        if (!ok) break;
-                        if (lead) {
-                            load_k(2 * m + 2, nullptr);
-                            load_k(2 * m + 3, nullptr);
-                        }
-                        __syncwarp();
-                    }
-                }
-                if ((j & 1) == 1 && next_pair) {
-                    // the softmax threads hold S of the pair's second tile in registers: S may be overwritten
-                    ok = ok && mbar_wait_warp(bar_r, (uint32_t)(m & 1));
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_qk_pair(m + 1);
-                    if (!ok) break;
-                }
-                // softmax of tile j done: P_j is in shared memory, PV_{j-1} has completed
+                // softmax of tile j done: P_j is in shared memory, O has been rescaled where needed
                 ok = ok && mbar_wait_warp(bar_p, (uint32_t)(j & 1));
+                ok = ok && mbar_wait_warp(&bar_v[j & 1], (uint32_t)((j >> 1) & 1));
                 if (!ok) break;
                 tc_fence_after();
-                if constexpr (!PAGED) {
-                    if (lead && j >= 1 && j + 1 < n_tiles) load_v(j + 1, nullptr);     // V stage (j+1)&1 was consumed by PV_{j-1}
-                    __syncwarp();
-                }
-                ok = mbar_wait_warp(&bar_v[j & 1], (uint32_t)((j >> 1) & 1));
-                if (!ok) break;
                 const uint32_t vs = v_addr + (uint32_t)(j & 1) * kVStage;
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ++ks)
@@ -441,10 +438,27 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                             smem_desc(vs + (uint32_t)ks * 2048, kBN * 128, 1024), kIdescO, (j > 0 || ks > 0) ? 1u : 0u, lead);
                 if (lead) umma_commit(&bar_o[j & 1]);
                 __syncwarp();
+                if constexpr (!PAGED) {
+                    // Dense K/V: this warp also issues the copies, after the MMAs and without further waiting.  The
+                    // softmax threads waited for the second MMA of tile j-1 before they wrote P_j, so V stage
+                    // (j+1)&1 is free.  K for pair m+1 goes out after tile 2m-1 (pair 1: after tile 0), once the
+                    // first MMA of pair m has completed, which frees both K stages: a tile's time before its use.
+                    if (lead && j >= 1 && j + 1 < n_tiles) load_v(j + 1, nullptr);
+                    const int m_next = j == 0 ? 1 : ((j & 1) ? (j + 3) / 2 : -1);
+                    if (m_next > 0 && 2 * m_next < n_tiles) {
+                        ok = mbar_wait_warp(bar_s, (uint32_t)((m_next - 1) & 1));
+                        if (!ok) break;
+                        if (lead) {
+                            load_k(2 * m_next, nullptr);
+                            load_k(2 * m_next + 1, nullptr);
+                        }
+                    }
+                    __syncwarp();
+                }
             }
             if (!ok) *sh_abort = 1;
         }
-    } else {
+    } else if (warp < kSoftmaxWarps) {
         // =============================== softmax warps: one query row per thread ===============================
         for (int j = 0; j < n_tiles; ++j) {
             ok = mbar_wait_warp(bar_s, (uint32_t)((j >> 1) & 1));    // one completion per pair of tiles
@@ -457,7 +471,8 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
             tc_wait_ld();
             if (j & 1) {   // the pair's scores have left tensor memory: the next pair's first MMA may overwrite them
                 tc_fence_before();
-                mbar_arrive(bar_r);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_r);
             }
             const int t0 = j * kBN;
             if (t0 + kBN > limit) {   // only tiles that cross the row's limit pay for the mask
@@ -465,15 +480,14 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                 for (int t = 0; t < kBN; ++t)
                     if (t0 + t >= limit) s[t] = -INFINITY;
             }
-            float mx4[4] = {s[0], s[1], s[2], s[3]};   // four independent chains instead of one 64-long one
+            float mx8[8];                              // eight independent chains of three-input maxima
 #pragma unroll
-            for (int t = 4; t < kBN; t += 4) {
-                mx4[0] = fmaxf(mx4[0], s[t]);
-                mx4[1] = fmaxf(mx4[1], s[t + 1]);
-                mx4[2] = fmaxf(mx4[2], s[t + 2]);
-                mx4[3] = fmaxf(mx4[3], s[t + 3]);
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;   // sc > 0: the scaled maximum
+            for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(s[i], s[i + 8]);
+#pragma unroll
+            for (int t = 16; t < kBN; t += 16)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx8[i] = max3(mx8[i], s[t + i], s[t + i + 8]);
+            const float mx = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) * sc;   // sc > 0: the scaled maximum
             const bool raise = mx > m_run + 8.0f;               // also true for the first allowed key (m_run = -inf)
             const float m_new = raise ? mx : m_run;
             const float alpha = raise ? ex2(m_run - m_new) : 1.0f;   // ex2(-inf) = 0 when nothing was accumulated yet
@@ -517,9 +531,10 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
                              "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3])
                              : "memory");
             }
-            fence_proxy_async();
+            fence_proxy_async();          // every lane publishes its own stores to the async proxy,
             tc_fence_before();
-            mbar_arrive(bar_p);
+            __syncwarp();                 // then one arrival stands for the warp
+            if (lane == 0) mbar_arrive(bar_p);
         }
         // wait for the last accumulation
         if (n_tiles > 0 && ok) {
@@ -527,41 +542,41 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
             tc_fence_after();
         }
         if (!ok) *sh_abort = 1;
-    }
-    // ---- epilogue: normalise and store ------------------------------------------------------------------
-    __syncthreads();
-    if (*sh_abort) ok = false;
-    if (!ok && p.status && tid == 0) atomicOr(p.status, FLAG_WAIT_TIMEOUT);
-    if (ok && warp < kSoftmaxWarps) {
-        const float inv = 1.0f / fmaxf(l_run, p.eps);
-        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (((int64_t)b * p.Hq + hq) * p.Lq + row) * kD;
+        // ---- epilogue: normalise and store (a CTA whose rows attend nothing writes zeros) ----
+        if (ok) {
+            const float inv = 1.0f / fmaxf(l_run, p.eps);
+            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (((int64_t)b * p.Hq + hq) * p.Lq + row) * kD;
 #pragma unroll
-        for (int cc = 0; cc < kD / 32; ++cc) {
-            float t32[32];
-            if (n_tiles > 0) {   // uniform over the CTA
-                tmem_ld32(lane_addr + kColO + cc * 32, t32);
-                tc_wait_ld();
-            } else {
+            for (int cc = 0; cc < kD / 32; ++cc) {
+                float t32[32];
+                if (n_tiles > 0) {   // uniform over the CTA
+                    tmem_ld32(lane_addr + kColO + cc * 32, t32);
+                    tc_wait_ld();
+                } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) t32[i] = 0.f;
-            }
-            if (row < p.Lq) {
+                    for (int i = 0; i < 32; ++i) t32[i] = 0.f;
+                }
+                if (row < p.Lq) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    uint32_t w[4];
+                    for (int u = 0; u < 4; ++u) {
+                        uint32_t w[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        // a row with no allowed key has l = 0 and only zero-weight products: force an exact 0
-                        const float a0 = l_run > 0.f ? t32[8 * u + 2 * i] * inv : 0.f;
-                        const float a1 = l_run > 0.f ? t32[8 * u + 2 * i + 1] * inv : 0.f;
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(a0, a1);
-                        w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                        for (int i = 0; i < 4; ++i) {
+                            // a row with no allowed key has l = 0 and only zero-weight products: force an exact 0
+                            const float a0 = l_run > 0.f ? t32[8 * u + 2 * i] * inv : 0.f;
+                            const float a1 = l_run > 0.f ? t32[8 * u + 2 * i + 1] * inv : 0.f;
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(a0, a1);
+                            w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * u) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * u) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
         }
     }
+    // a wait that ran out anywhere in the CTA invalidates the result: tell the caller
+    __syncthreads();
+    if (tid == 0 && *sh_abort && p.status) atomicOr(p.status, FLAG_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
