@@ -461,9 +461,11 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
     } else if (warp < kSoftmaxWarps) {
         // =============================== softmax warps: one query row per thread ===============================
         for (int j = 0; j < n_tiles; ++j) {
-            ok = mbar_wait_warp(bar_s, (uint32_t)((j >> 1) & 1));    // one completion per pair of tiles
-            if (!ok) break;
-            tc_fence_after();
+            if ((j & 1) == 0) {   // one completion per pair of tiles: the second tile's scores are there already
+                ok = mbar_wait_warp(bar_s, (uint32_t)((j >> 1) & 1));
+                if (!ok) break;
+                tc_fence_after();
+            }
             const uint32_t s_col = kColS + (uint32_t)(j & 1) * kBN;
             float s[kBN];
             tmem_ld32(lane_addr + s_col, s);
