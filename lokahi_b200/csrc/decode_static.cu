@@ -80,7 +80,7 @@ extern "C" SKV_API int32_t skv_decode_attn_static(skv_pool* pool, int32_t layer,
         int32_t st = prepare_decode(pool, layer, seq_ids, n_seqs, q_pos, n_q_heads, q, out, eps, stream, &d, &total, &launchable);
         if (st != SKV_OK || !launchable) return st;
         d.total_tokens = total;
-        decode_plan(d.pool.page_size, d.pool.max_pages_per_seq, n_seqs, d.pool.num_kv_heads, total, &d.chunk_tokens, &d.max_splits);
+        decode_plan(d.pool.page_size, d.pool.max_pages_per_seq, n_seqs, d.pool.num_kv_heads, total, d.longest, &d.chunk_tokens, &d.max_splits);
         const size_t rows = (size_t)n_seqs * n_q_heads * d.max_splits;
         const size_t need = rows * ((size_t)d.pool.head_dim + 2) * sizeof(float);
         if (need > kStaticScratchBytes) {

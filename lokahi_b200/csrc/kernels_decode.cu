@@ -1095,7 +1095,7 @@ cudaError_t launch_generic(const DecodeLaunch& d, cudaStream_t stream) {
 }  // namespace
 
 void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, int32_t num_kv_heads,
-                 int64_t total_tokens_hint, int32_t* chunk_tokens, int32_t* max_splits) {
+                 int64_t total_tokens_hint, int32_t longest_hint, int32_t* chunk_tokens, int32_t* max_splits) {
     // `splits` bounds the partials per sequence, and with them the workspace, independently of the lengths: a chunk
     // is never shorter than 256 tokens and a sequence never has more than 128 of them.
     const int64_t max_ctx = (int64_t)max_pages_per_seq * page_size;
@@ -1117,6 +1117,14 @@ void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, i
         const int64_t cap = floor_chunk > 1536 ? floor_chunk : 1536;
         if (chunk > cap) chunk = cap;
         if (chunk < floor_chunk) chunk = floor_chunk;
+        // A batch of about equal lengths (a decoder's: every sequence at the same position): cut the longest
+        // sequence into equal chunks instead of full ones and a remainder.  Eight sequences of 2304 tokens with 16
+        // KV heads: 1536 + 768 tokens per sequence took 41 us per layer step, 2 x 1152 takes 36 us.
+        if (longest_hint > 0 && total_tokens_hint * 10 >= (int64_t)9 * longest_hint * n_seqs) {
+            const int64_t n = (longest_hint + chunk - 1) / chunk;
+            const int64_t even = (((int64_t)longest_hint + n - 1) / n + 63) / 64 * 64;
+            if (even >= floor_chunk && even < chunk) chunk = even;
+        }
         if (sw.chunk > 0 && sw.chunk >= floor_chunk) chunk = ((sw.chunk + 63) / 64) * 64;   // SKV_DECODE_CHUNK
     }
     if (chunk > 2048) chunk = 2048;                       // a warp holds at most 32 tile page ids

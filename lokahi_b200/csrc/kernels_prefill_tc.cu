@@ -6,12 +6,15 @@
 // out = wv / max(s, eps) so that a row with no allowed key is exactly 0 (:118, :146).
 //
 // One CTA = 128 query rows of one query head: four softmax warps (thread r owns query row r, which is TMEM
-// lane r) plus a fifth warp that issues every TMA copy and every MMA, so that instruction issue to the
-// tensor cores never sits on a softmax warp's path.  The fifth warp runs its loop in warp-uniform control
-// flow with only lane 0 enabled on the copy / MMA / commit instructions: the descriptors then live in
-// uniform registers.  Measured on B200 with back-to-back MMAs (M128, K16, operands in shared memory): 116
-// clocks per instruction when issued from inside a one-lane branch, 89 issued this way, the same for N = 64
-// and N = 128 (N = 256 runs at the pipe's full rate of 128).  Since N = 64 costs as much as N = 128, the
+// lane r) plus two warps that issue the MMAs, one for S = Q . K^T and one for O += P . V, so that instruction
+// issue to the tensor cores never sits on a softmax warp's path and the two chains of MMAs issue side by side (one
+// thread gets an MMA out every 90 to 104 clocks; with a single issuer the next pair's eight S instructions sat
+// between a tile's P and its four O instructions).  The O warp also issues the TMA copies of dense K/V in its
+// gaps; paged K/V needs four times as many copies and has a warp for them.  An issuing warp runs its loop in
+// warp-uniform control flow with only lane 0 enabled on the copy / MMA / commit instructions: the descriptors
+// then live in uniform registers.  Measured on B200 with back-to-back MMAs (M128, K16, operands in shared
+// memory): 116 clocks per instruction when issued from inside a one-lane branch, 89 issued this way, the same for
+// N = 64 and N = 128 (N = 256 runs at the pipe's full rate of 128).  Since N = 64 costs as much as N = 128, the
 // scores of TWO 64-key tiles come from one set of N = 128 instructions.
 // Per pair of 64-key tiles:
 //   TMA   the pair's K tiles -> shared memory, laid out [dim box][tile][64 keys x 128 B] so that they form one
@@ -40,9 +43,9 @@
 // 16-token pages.  A 64-key tile is four pages; each page is two boxes [16 tokens][64 dims] of the pool's 2-D
 // tensor map, placed 2 KB apart inside the tile's shared-memory region, which gives exactly the layout a
 // [64][64] box would have (the 128-byte swizzle depends on the address only).  That is sixteen copies per tile
-// instead of four, at about 80 clocks of issue each, so they get a sixth warp of their own; it reads each
+// instead of four, at 80 to 150 clocks of issue each, so they get a warp of their own; it reads each
 // page-table entry once (K is fetched a pair of tiles ahead, V a tile ahead).  Slots past the sequence's pages
-// are read from page 0 and masked.  Measured at 4096 tokens, pages in a random order: 0.161 ms against 0.150 ms
+// are read from page 0 and masked.  Measured at 4096 tokens, pages in a random order: 0.159 ms against 0.147 ms
 // for dense K/V.
 #include <cstdlib>
 

@@ -911,6 +911,7 @@ int32_t prepare_decode(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32
         if (!valid_seq(p, s)) return p->fail(SKV_ERR_BAD_ARG, "sequence %d is not live", s);
         int32_t T = p->len(layer, s);
         *total_tokens += T;
+        d->longest = i == 0 ? T : std::max(d->longest, T);
         if (q_pos) T = std::min(T, std::max(0, q_pos[i] + 1));
         const int32_t pages = (T + p->cfg.page_size - 1) / p->cfg.page_size;
         for (int32_t slot = 0; p->n_parked[s] > 0 && slot < pages; ++slot)
@@ -1003,7 +1004,7 @@ int32_t attn_impl(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_
     if (!p->host_only) {   // argument checks that must not depend on what the front half enqueues
         if (n_q_heads > 0 && n_seqs > 0 && n_seqs <= p->cfg.max_seqs) {
             int32_t chunk = 0, splits = 0;
-            decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, 0, &chunk, &splits);
+            decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, 0, 0, &chunk, &splits);
             const size_t least = (size_t)n_seqs * n_q_heads * 1 * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
             int32_t st0 = check_workspace(p, workspace, workspace_bytes, least);
             if (st0 != SKV_OK) return st0;
@@ -1011,12 +1012,8 @@ int32_t attn_impl(skv_pool* p, int32_t layer, const int32_t* seq_ids, int32_t n_
     }
     int32_t st = prepare_decode(p, layer, seq_ids, n_seqs, q_pos, n_q_heads, q, out_arg, eps, stream, &D, &total, &launchable);
     if (st != SKV_OK || !launchable) return st;
-    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, &D.chunk_tokens, &D.max_splits);
-    {
-        int32_t longest = 0;
-        for (int32_t i = 0; i < n_seqs; ++i) longest = std::max(longest, p->len(layer, seq_ids ? seq_ids[i] : i));
-        D.grid_splits = std::max(1, (longest + D.chunk_tokens - 1) / D.chunk_tokens);
-    }
+    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, total, D.longest, &D.chunk_tokens, &D.max_splits);
+    D.grid_splits = std::max(1, (D.longest + D.chunk_tokens - 1) / D.chunk_tokens);
     const size_t need = (size_t)n_seqs * n_q_heads * D.max_splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
     st = check_workspace(p, workspace, workspace_bytes, need);
     if (st != SKV_OK) return st;
@@ -1043,7 +1040,7 @@ size_t skv_decode_workspace_bytes(const skv_pool* p, int32_t n_seqs, int32_t n_q
     if (!p || n_seqs <= 0 || n_q_heads <= 0) return 0;
     int32_t chunk = 0, splits = 0;
     // the largest split count any plan can produce: the smallest chunk
-    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, 0, &chunk, &splits);
+    decode_plan(p->cfg.page_size, p->cfg.max_pages_per_seq, n_seqs, p->cfg.num_kv_heads, 0, 0, &chunk, &splits);
     return (size_t)n_seqs * n_q_heads * splits * ((size_t)p->cfg.head_dim + 2) * sizeof(float);
 }
 
@@ -1202,7 +1199,8 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
     if (need_total > (int64_t)p->free_pages.size())
         return p->fail(SKV_ERR_OUT_OF_PAGES, "need %lld pages, %zu free", (long long)need_total, p->free_pages.size());
     DecodeLaunch D{};
-    decode_plan(P, p->cfg.max_pages_per_seq, n_seqs, Hkv, total, &D.chunk_tokens, &D.max_splits);
+    D.longest = longest;
+    decode_plan(P, p->cfg.max_pages_per_seq, n_seqs, Hkv, total, longest, &D.chunk_tokens, &D.max_splits);
     if (D.max_splits > 128) return p->fail(SKV_ERR_UNSUPPORTED, "a sequence would need %d split-K chunks, 128 is the limit", D.max_splits);
     D.grid_splits = std::max(1, (longest + D.chunk_tokens - 1) / D.chunk_tokens);
     const size_t need_ws = (size_t)n_seqs * a.n_q_heads * D.max_splits * ((size_t)Dh + 2) * sizeof(float);

@@ -123,6 +123,7 @@ struct DecodeLaunch {
     int32_t* tickets;
     int32_t fuse_merge;          // 0: leave the merge to decode_reduce_kernel
     int64_t total_tokens;        // host's sum of the attended lengths (drives the plan and the merge choice)
+    int32_t longest;             // host's longest attended length of the call (drives the plan)
     ExchangeView xchg;
     float* partial_out;          // when set, the merge kernel writes un-normalised [n_seqs][q_heads][head_dim + 2]
                                  // rows (acc..., m, l) instead of the output: the unit of sequence sharding
@@ -145,9 +146,10 @@ struct DecodeLaunch {
     const StepRows* rows;        // host pointer; copied into the kernel parameters at launch
 };
 cudaError_t launch_decode(const DecodeLaunch& d, cudaStream_t stream);
-// chunk length (tokens handled by one CTA) and the number of splits that follow from it
+// chunk length (tokens handled by one CTA) and the number of splits that follow from it; the hints (0 = unknown)
+// are the call's attended tokens in all and its longest sequence
 void decode_plan(int32_t page_size, int32_t max_pages_per_seq, int32_t n_seqs, int32_t num_kv_heads,
-                 int64_t total_tokens_hint, int32_t* chunk_tokens, int32_t* max_splits);
+                 int64_t total_tokens_hint, int32_t longest_hint, int32_t* chunk_tokens, int32_t* max_splits);
 
 struct DenseAttnLaunch {
     const void *q, *k, *v;
