@@ -42,9 +42,13 @@ class HostStepPipeline:
 
     ``exchange`` (a ``sharding.PeerGather`` / ``PeerSeqMerge``) makes the step the sharded one; ``step_args`` is called
     with the step index and returns the per-step keyword arguments of ``decode_step_binder`` that vary (``positions`` /
-    ``store`` under sequence sharding), or is None."""
+    ``store`` under sequence sharding), or is None.  ``consecutive`` passes the library's back-to-back promise: between two
+    steps the compute stream holds only event records and waits (the wait for a step's upload comes before the step,
+    so its inputs are complete when its kernel starts, however early that is), which lets a step's split-K kernel start
+    beside the previous step's merge kernel."""
 
-    def __init__(self, pool, layer: int, n_seqs: int, n_q_heads: int, *, exchange=None, step_args=None, n_steps: Optional[int] = None):
+    def __init__(self, pool, layer: int, n_seqs: int, n_q_heads: int, *, exchange=None, step_args=None, n_steps: Optional[int] = None,
+                 consecutive: bool = True):
         c = pool.cfg
         self.pool, self.layer = pool, layer
         dev = pool.torch_device
@@ -55,6 +59,7 @@ class HostStepPipeline:
         self.views = [(b[:self.nq].view(n_seqs, n_q_heads, D), b[self.nq:self.nq + self.nk].view(n_seqs, hkv, D),
                        b[self.nq + self.nk:].view(n_seqs, hkv, D)) for b in self.stage]
         self.exchange = exchange
+        self.consecutive = bool(consecutive)
         self.results = None if exchange is not None else [torch.empty((n_seqs, n_q_heads, D), device=dev, dtype=c.dtype) for _ in range(2)]
         self.result_shape = tuple(exchange.out_shape) if exchange is not None else (n_seqs, n_q_heads, D)
         self.esize = self.stage[0].element_size()
@@ -81,6 +86,7 @@ class HostStepPipeline:
 
     def _bind(self, b: int, kw: dict):
         q, k, v = self.views[b]
+        kw = dict(kw, consecutive=self.consecutive)
         if self.exchange is not None:
             return self.pool.decode_step_binder(q, k, v, exchange=self.exchange, **kw)
         return self.pool.decode_step_binder(q, k, v, self.results[b], **kw)
