@@ -27,6 +27,8 @@ import time
 
 import numpy as np
 
+TOL_E2E = 2e-2      # end-to-end result against the device-resident step (bf16; the two are expected to agree to the bit)
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -531,6 +533,19 @@ def run_ours(args):
     ms_e2e = max(e0.elapsed_time(e1), wall_e2e_ms)      # the host has every result when the wall clock stops
     if pool.check_device_status() != 0:
         raise SystemExit("device status flag set during the end-to-end leg")
+    # the last result the host received against the same step made again from device-resident inputs, on its own
+    # (the pages hold the rows of the steps before it either way; q is taken from the host copy because a step
+    # rotates q in place)
+    rewind(W + Ke - 1)
+    last = qkv_h[Ke - 1].to(dev)
+    chk = step(last[:nq].view(N_SEQS, hq, D).clone(), last[nq:nq + nk].view(N_SEQS, hkv, D).clone(),
+               last[nq + nk:].view(N_SEQS, hkv, D).clone(), False, W + Ke - 1)
+    torch.cuda.synchronize()
+    chk = chk.float().cpu()
+    e2e_diff = float((chk - out_h[(Ke - 1) & 1].float()).abs().max() / chk.abs().max().clamp_min(1e-30))
+    if not e2e_diff <= TOL_E2E:
+        print(f"end-to-end result differs from the device-resident step: normalised max error {e2e_diff:.3e}", file=sys.stderr)
+        raise SystemExit(3)
 
     # ---- max over ranks ------------------------------------------------------------------------------------------
     stats = torch.tensor(ms_repeats + [ms_e2e, float(attn_ms.mean()), kernel_only_ms or 0.0, float(np.median(host_us))],
@@ -561,8 +576,10 @@ def run_ours(args):
                       "kernel overlaps the previous step's merge kernel",
             "e2e": {"value": N_SEQS * Ke / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / Ke,
                     "h2d_bytes_per_step": int(nq + 2 * nk) * 2, "d2h_bytes_per_step": int(np.prod(res_shape)) * 2,
-                    "pipeline": "HostStepPipeline: upload of step s+1 and read-back of step s-1 overlap step s (three "
-                                "streams); every result is awaited on the host", "host_wall_ms_per_step": wall_e2e_ms / Ke},
+                    "pipeline": ("HostStepPipeline" if mode != "nccl" else "torch calls") +
+                                ": upload of step s+1 and read-back of step s-1 overlap step s (three "
+                                "streams); every result is awaited on the host", "host_wall_ms_per_step": wall_e2e_ms / Ke,
+                    "last_result_vs_device_resident_step": e2e_diff},
             "gpu_launches": int(launches),
             "host_us_per_call": host_us_per_call,
             "kernel_only_ms": kernel_only_ms if world > 1 else None,
