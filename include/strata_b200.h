@@ -286,7 +286,7 @@ SKV_API int32_t skv_attn_dense(const void* q, const void* k, const void* v, void
 
 /* K4 over pages: queries [n_seqs][Hq][Lq][D] against each sequence's first `lengths` tokens of a layer
  * (the attention call of a chunked prefill over the cache, src/ollm/llama_mlx.py:300-308 with L > 1).
- * bf16 pools with head_dim 128 and 16-token pages, Lq >= 32 and 16-byte aligned q/out run on the tensor cores and
+ * bf16 pools with head_dim 128 and pages of a multiple of 16 tokens, Lq >= 32 and 16-byte aligned q/out run on the tensor cores and
  * read K/V straight from the pages; every other case takes the float32 CUDA-core kernel.  positions NULL means
  * the bottom-right default (length - Lq + i); SKV_PREFILL_GENERIC=1 forces the CUDA-core kernel. */
 SKV_API int32_t skv_prefill_attn_paged(skv_pool* pool, int32_t layer, const int32_t* seq_ids, int32_t n_seqs,

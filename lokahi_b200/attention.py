@@ -139,10 +139,10 @@ def chunked_grouped_attention(
             out = cache.pool.decode_attention(k.layer, q.reshape(B, Hq, D).contiguous(), seq_ids=cache.seq_ids,
                                               q_pos=q_pos, eps=eps)
             return out.reshape(B, Hq, 1, D)
-        if Lq >= 32 and D == 128 and q.dtype == torch.bfloat16 and cache.pool.cfg.page_size != 16:
-            # Long query blocks go to the tensor-core kernel.  With 16-token pages it reads the pages themselves
-            # through the pool's tensor maps (the call below); other page sizes are gathered into dense K/V
-            # first: O(Lk) bytes, small next to the O(Lq * Lk) attention work the tensor cores take over.
+        if Lq >= 32 and D == 128 and q.dtype == torch.bfloat16 and cache.pool.cfg.page_size % 16 != 0:
+            # Long query blocks go to the tensor-core kernel.  With pages of a multiple of 16 tokens it reads the
+            # pages themselves through the pool's tensor maps (the call below); other page sizes are gathered into
+            # dense K/V first: O(Lk) bytes, small next to the O(Lq * Lk) attention work the tensor cores take over.
             k_dense, v_dense = cache.materialize(k.layer)
             return chunked_grouped_attention(q, k_dense, v_dense, query_positions=positions, causal=causal,
                                              q_block_size=q_block_size, k_block_size=k_block_size, eps=eps)

@@ -274,24 +274,26 @@ prefill_tc_kernel(TcParams p, const __grid_constant__ CUtensorMap qmap, const __
 
     // K lives as [dim box][stage][64 keys x 128 B]: the two stages of a box are contiguous, so that the two tiles
     // of a pair form one 128-row K-major operand and their scores come from ONE set of N = 128 MMAs.
-    // Paged K/V: first row, in the pool map's row numbering, of page-table slot `slot` for this KV head.  A slot the
-    // sequence does not have is read from page 0 instead: the bytes are finite (the pool starts zeroed and only
+    // Paged K/V: row, in the pool map's row numbering, of a group of 16 tokens of this KV head (pages hold a multiple
+    // of 16 tokens).  A slot the sequence does not have is read from page 0 instead: the bytes are finite (the pool starts zeroed and only
     // ever holds K/V values) and every key at or past the length is masked, so they never reach the output.
-    auto page_row = [&](int slot) -> int {
+    auto group_row = [&](int t) -> int {   // t: first token of a group of 16 (a group never straddles a page)
         const PoolView& pv = p.pool;
+        const int slot = t / pv.page_size;
         int page = 0;
         if (slot < pv.max_pages_per_seq) {
             const int id = __ldg(pv.page_table + (int64_t)seq * pv.max_pages_per_seq + slot);
             if (id >= 0 && id < pv.num_pages)
                 page = id;
-            else if (slot * pv.page_size < Lk)
+            else if (t < Lk)
                 atomicOr(pv.status, FLAG_BAD_PAGE);   // a page inside the history is missing: flagged, not dereferenced
         }
-        return (int)((int64_t)p.layer * (pv.layer_stride_bytes / (kD * 2))) + (page * pv.num_kv_heads + hkv) * pv.page_size;
+        return (int)((int64_t)p.layer * (pv.layer_stride_bytes / (kD * 2))) + (page * pv.num_kv_heads + hkv) * pv.page_size +
+               (t - slot * pv.page_size);
     };
-    auto tile_rows = [&](int j, int* y) {   // the four pages of tile j: four independent loads in flight
+    auto tile_rows = [&](int j, int* y) {   // the four 16-token groups of tile j: four independent loads in flight
 #pragma unroll
-        for (int sub = 0; sub < 4; ++sub) y[sub] = page_row(4 * j + sub);
+        for (int sub = 0; sub < 4; ++sub) y[sub] = group_row(kBN * j + 16 * sub);
     };
     auto load_k = [&](int j, const int* y) {
         uint8_t* dst = smem + kOffK + (j & 1) * (kBN * 128);
@@ -607,8 +609,8 @@ cudaError_t launch_attn_tc(const DenseAttnLaunch& a, cudaStream_t stream) {
     const bool aligned = paged ? ((((uintptr_t)a.q | (uintptr_t)a.out) & 15) == 0)
                                : ((((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out) & 15) == 0);
     if (a.dtype != SKV_BF16 || a.D != kD || !aligned || a.Lq < 32) return cudaErrorNotSupported;
-    // paged K/V: the pool's own tensor maps with [16 tokens][64 dims] boxes, so pages of 16 tokens only
-    if (paged && (a.pool.page_size != 16 || !a.k_map || !a.v_map || a.pool.head_dim != kD)) return cudaErrorNotSupported;
+    // paged K/V: the pool's own tensor maps with [16 tokens][64 dims] boxes, so pages of a multiple of 16 tokens
+    if (paged && (a.pool.page_size % 16 != 0 || !a.k_map || !a.v_map || a.pool.head_dim != kD)) return cudaErrorNotSupported;
     if (!paged && a.Lk < 1) return cudaErrorNotSupported;
     alignas(64) CUtensorMap qmap, kmap, vmap;
     if (!encode_heads_3d(&qmap, a.q, (uint64_t)a.B * a.Hq, (uint64_t)a.Lq, kBM)) return cudaErrorNotSupported;

@@ -1452,7 +1452,7 @@ int32_t skv_prefill_attn_paged(skv_pool* p, int32_t layer, const int32_t* seq_id
     if (st != SKV_OK) return st;
     A.k_map = p->has_maps ? &p->k_map : nullptr;
     A.v_map = p->has_maps ? &p->v_map : nullptr;
-    // bf16, head_dim 128, 16-token pages and at least 32 query rows: the tensor-core kernel reads the pages
+    // bf16, head_dim 128, pages of a multiple of 16 tokens and at least 32 query rows: the tensor-core kernel reads the pages
     // directly through the pool's tensor maps; everything else takes the float32 CUDA-core kernel
     cudaError_t e = cudaErrorNotSupported;
     if (!switches().prefill_generic) e = launch_attn_tc(A, stream);

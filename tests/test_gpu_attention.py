@@ -283,14 +283,16 @@ def test_tensor_core_prefill_at_full_sequence_4096(skv_switch):
     assert parity_errors(out[:, ::8], to_np(ref_all))[0] <= TOL_BF16, "tcgen05 vs CUDA-core at S=4096"
 
 
-def test_tensor_core_prefill_over_pages_matches_oracle_and_the_dense_kernel(skv_switch):
-    """bf16, head_dim 128, 16-token pages, at least 32 query rows: the tcgen05 kernel reads K/V straight from the
-    scattered pages.  Ragged lengths (one shorter than a key tile, one not a multiple of the page size), default
-    bottom-right positions and explicit ones (with fully masked rows), against the oracle on the logical history
-    and against the float32 CUDA-core kernel."""
+@pytest.mark.parametrize("P", [16, 32, 48, 64])
+def test_tensor_core_prefill_over_pages_matches_oracle_and_the_dense_kernel(skv_switch, P):
+    """bf16, head_dim 128, pages of a multiple of 16 tokens, at least 32 query rows: the tcgen05 kernel reads K/V
+    straight from the scattered pages (in groups of 16 tokens, which never straddle a page).  Ragged lengths (one
+    shorter than a key tile, one not a multiple of the page size), default bottom-right positions and explicit
+    ones (with fully masked rows), against the oracle on the logical history and against the float32 CUDA-core
+    kernel."""
     rng = np.random.default_rng(91)
     lens = [40, 64, 200, 777, 1030]
-    n, Hq, Hkv, D, P, Lq = len(lens), 8, 2, 128, 16, 40
+    n, Hq, Hkv, D, Lq = len(lens), 8, 2, 128, 40
     pool, k_ref, v_ref, table, rnd = _paged_setup(rng, torch.bfloat16, n, Hkv, D, P, lens)
     q = _t(rnd(rng.standard_normal((n, Hq, Lq, D), dtype=np.float32)), torch.bfloat16)
     before = L._lib.lib.skv_launch_count()
