@@ -283,6 +283,55 @@ def test_long_context_decode_with_eviction_every_step():
     assert pool.check_device_status() == 0
 
 
+def test_long_context_at_full_length_96k_tokens_with_a_quarter_parked():
+    """One sequence of the long-context configuration at its full length (98304 tokens, one KV head with its 4
+    query heads, bf16, theta 5e5): three one-call decode steps at positions 98304..98306, with the oldest quarter
+    of the pages parked in host memory and brought back before every step, against the oracle on the logical
+    history (64 split-K chunks, 6144 pages in a random order, RoPE angles near 1e5 radians)."""
+    rng = np.random.default_rng(965)
+    Hq, Hkv, D, P, T0, steps, theta = 4, 1, 128, 16, 98304, 3, 500000.0
+    pages = T0 // P + 2
+    pool = L.PagedPool(L.PagedKVConfig(num_layers=1, num_kv_heads=Hkv, head_dim=D, num_pages=pages + 8, max_seqs=1,
+                                       max_pages_per_seq=pages, page_size=P, dtype=torch.bfloat16,
+                                       host_pages=pages // 4 + 2, rope_theta=theta))
+    assert pool.alloc_sequence() == 0
+    order = rng.permutation(pages + 8)[:pages].tolist()
+    pool.set_page_table(0, order, T0)
+    k_pages = bf16_round(rng.standard_normal((pages + 8, Hkv, P, D), dtype=np.float32))
+    v_pages = bf16_round(rng.standard_normal((pages + 8, Hkv, P, D), dtype=np.float32))
+    kp, vp = pool.layer_views(0)
+    kp.copy_(_t(k_pages, torch.bfloat16)); vp.copy_(_t(v_pages, torch.bfloat16))
+    table = np.array(order, np.int32)
+    hist_k = np.zeros((Hkv, T0 + steps, D), np.float32)
+    hist_v = np.zeros_like(hist_k)
+    hist_k[:, :T0] = opaged.logical_kv(k_pages, table, T0)
+    hist_v[:, :T0] = opaged.logical_kv(v_pages, table, T0)
+    for step in range(steps):
+        T = T0 + step
+        n_old = (T // P) // 4
+        pool.evict(0, 0, n_old)
+        pool.prefetch(0, 0, n_old)
+        q = bf16_round(rng.standard_normal((1, Hq, D), dtype=np.float32))
+        k = bf16_round(rng.standard_normal((1, Hkv, D), dtype=np.float32))
+        v = bf16_round(rng.standard_normal((1, Hkv, D), dtype=np.float32))
+        qt = _t(q, torch.bfloat16)
+        out = pool.decode_step(0, qt, _t(k, torch.bfloat16), _t(v, torch.bfloat16))
+        qr = bf16_round(opaged.rope_rows(q, np.array([T]), theta))
+        hist_k[:, T] = bf16_round(opaged.rope_rows(k, np.array([T]), theta))[0]
+        hist_v[:, T] = v[0]
+        # rotated q may sit one bf16 step from the NumPy rotation (sincosf against numpy at 1e5 radians)
+        assert np.max(np.abs(to_np(qt) - qr)) <= 2.0 ** -7 * np.max(np.abs(qr)), f"rotated q, step {step}"
+        ref = oattn_decode(to_np(qt)[0], hist_k[:, :T + 1], hist_v[:, :T + 1], T)
+        assert_parity(out[0], ref, TOL_BF16, f"96k-token decode step {step}")
+    kg, vg = pool.gather(0, n_seqs=1)
+    assert np.array_equal(to_np(vg)[0, :, :T0 + steps], hist_v), "stored V after parking and three appended rows"
+    assert np.max(np.abs(to_np(kg)[0, :, T0:T0 + steps] - hist_k[:, T0:])) <= 2.0 ** -7 * np.max(np.abs(hist_k[:, T0:]))
+    assert np.array_equal(to_np(kg)[0, :, :T0], hist_k[:, :T0])
+    c = pool.counters()
+    assert c["pages_evicted"] == c["pages_prefetched"] == steps * ((T0 // P) // 4)
+    assert pool.check_device_status() == 0
+
+
 def oattn_decode(q, k_hist, v_hist, pos):
     from oracle import attention as oattn
     return oattn.chunked_grouped_attention(q[None, :, None, :], k_hist[None], v_hist[None],
