@@ -992,6 +992,48 @@ def run_longctx(args):
     tokens_now = pool.length(0, 0)
     attn_bytes = float(layers * n_seq * (tokens_now - K // 2) * hkv * D * 2 * 2)
     peak, kind = measured_peak_gbs()
+    # ---- parity, after the timed regions: one more step of the last layer (all pages have travelled to the host and
+    # back several times by now) against the NumPy oracle on one sequence's logical history, on every rank for its own
+    # head; under sharding every slot of the gathered view against what its rank computed (NCCL all-gather) ----------
+    parity = None
+    if not args.no_parity:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        from parity import TOL_BF16, parity_errors, to_np
+        from oracle import attention as oattn
+        from oracle import paged as opaged
+        pool.sync_transfers()
+        lc, sc = layers - 1, n_seq - 1
+        T = pool.length(lc, sc)
+        qc = torch.randn((n_seq, hq, D), generator=gen, device=dev).to(torch.bfloat16)
+        q_in = to_np(qc[sc:sc + 1])
+        if world > 1:
+            view = pool.decode_step(lc, qc, kn, vn, exchange=peers[n_seq])
+            local = view[rank]
+        else:
+            view = local = pool.decode_step(lc, qc, kn, vn, out=outs[n_seq])
+        torch.cuda.synchronize()
+        kd, vd = pool.gather(lc, seq_ids=[sc])
+        ref = oattn.chunked_grouped_attention(to_np(qc[sc])[None, :, None, :], to_np(kd[:, :, :T + 1]), to_np(vd[:, :, :T + 1]),
+                                              query_positions=np.array([T], dtype=np.int32))
+        err = float(parity_errors(local[sc], ref[0, :, 0, :])[0])
+        q_ref = opaged.rope_rows(q_in, np.array([T]), THETA)
+        q_err = float(np.max(np.abs(to_np(qc[sc:sc + 1]) - q_ref)) / np.max(np.abs(q_ref)))
+        exchange_equal = True
+        if world > 1:
+            every = [torch.empty_like(local) for _ in range(world)]
+            dist.all_gather(every, local.contiguous())
+            exchange_equal = all(bool(torch.equal(view[r_], every[r_])) for r_ in range(world))
+        verdict = torch.tensor([err, q_err, 0.0 if exchange_equal else 1.0], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(verdict, op=dist.ReduceOp.MAX)
+        err, q_err, bad = (float(x) for x in verdict.tolist())
+        parity = {"checked": True, "tolerance": TOL_BF16, "layer": lc, "sequence": sc, "tokens": int(T + 1),
+                  "vs_oracle_max_norm_err_max_over_ranks": err, "rotated_q_max_norm_err": q_err,
+                  "gathered_slots_equal_their_ranks_rows": bad == 0.0}
+        if not (err <= TOL_BF16 and q_err <= 2.0 ** -7 and bad == 0.0):
+            if rank == 0:
+                print(json.dumps({"parity": parity, "error": "parity check failed"}), flush=True)
+            raise SystemExit(3)
     for pe in peers.values():
         pe.close()
     if world > 1:
@@ -1017,6 +1059,7 @@ def run_longctx(args):
                       "gbs_each_way_all_gpus": world * (d2h + h2d) / 2 / (copy_ms * 1e-3 / 2) / 1e9,
                       "note": "evict then fetch of the same pages on one copy stream; the two directions do not overlap through mapped host memory"},
         "gpu_launches": int(launches),
+        "parity": parity,
     }
 
 
