@@ -472,7 +472,7 @@ def run_ours(args):
     # ---- end-to-end leg: every step's inputs come from pinned host memory, every step's result goes back ------------
     # `HostStepPipeline` (the package's host side of the decode step): two device staging buffers, the upload of step
     # s + 1 on a copy stream while step s computes, the result of step s read back on a third stream while step s + 1
-    # computes; the host waits for result s - 1 before it enqueues step s + 1, and for the last result before the
+    # computes; the host waits for result s - 2 before it enqueues step s + 1, and for the last results before the
     # clock stops.  With the NCCL gather (the baseline) the same choreography runs from torch calls.
     Ke = K
     rewind(W)

@@ -4,8 +4,10 @@ A caller whose per-step inputs live in host memory (the q, k, v rows of a step a
 network card, a CPU stage) pays one host-to-device copy and one device-to-host copy per step.  Issued one after
 the other on one stream they add to the step; here the upload of step s + 1 runs on a copy stream while step s
 computes, the result of step s is read back on a third stream while step s + 1 computes, and the host waits for
-result s - 1 before it enqueues step s + 1 (and for the last result before ``run`` returns).  Two device staging
-buffers and two result buffers alternate.  The per-step choreography (copies, event records and waits) goes
+result s - ``lookahead`` before it enqueues step s + 1 (and for the last result before ``run`` returns).  Two device
+staging buffers and two result buffers alternate.  With ``lookahead`` 1 the chain "step done, read-back, host wakes,
+next enqueue" has to fit into one step, which it does not when a step is short (30 us on eight GPUs against a
+25 us read-back of the gathered rows); the default 2 gives it two.  The per-step choreography (copies, event records and waits) goes
 straight to the CUDA runtime through ctypes, and the step itself is a bound library call
 (``PagedPool.decode_step_binder``), so a step costs the host a few microseconds beside the two launches.
 
@@ -48,7 +50,7 @@ class HostStepPipeline:
     beside the previous step's merge kernel."""
 
     def __init__(self, pool, layer: int, n_seqs: int, n_q_heads: int, *, exchange=None, step_args=None, n_steps: Optional[int] = None,
-                 consecutive: bool = True):
+                 consecutive: bool = True, lookahead: int = 2):
         c = pool.cfg
         self.pool, self.layer = pool, layer
         dev = pool.torch_device
@@ -60,6 +62,9 @@ class HostStepPipeline:
                        b[self.nq + self.nk:].view(n_seqs, hkv, D)) for b in self.stage]
         self.exchange = exchange
         self.consecutive = bool(consecutive)
+        if lookahead not in (1, 2):
+            raise ValueError("lookahead is 1 or 2 (two result buffers)")
+        self.lookahead = lookahead
         self.results = None if exchange is not None else [torch.empty((n_seqs, n_q_heads, D), device=dev, dtype=c.dtype) for _ in range(2)]
         self.result_shape = tuple(exchange.out_shape) if exchange is not None else (n_seqs, n_q_heads, D)
         self.esize = self.stage[0].element_size()
@@ -94,7 +99,7 @@ class HostStepPipeline:
     def run(self, inputs: torch.Tensor, outputs: torch.Tensor) -> None:
         """``inputs`` pinned ``[n_steps, in_elems]`` (row = q | k | v of a step, flattened), ``outputs`` pinned
         ``[rows, *result_shape]`` with ``rows >= 2``: the result of step i lands in row ``i % rows`` (a ring when there
-        are fewer rows than steps: row r is rewritten two steps after the host was handed its previous content).
+        are fewer rows than steps; a consumer that needs time with a row gives more rows than ``lookahead``).
         Runs the steps in order and returns when the last result is in ``outputs``."""
         if not (inputs.is_pinned() and outputs.is_pinned()):
             raise ValueError("inputs and outputs must be pinned host tensors")
@@ -113,7 +118,7 @@ class HostStepPipeline:
         in_ptr, in_row = inputs.data_ptr(), inputs.stride(0) * esize
         out_ptr, out_row = outputs.data_ptr(), outputs.stride(0) * outputs.element_size()
         in_bytes, out_bytes = self.in_elems * esize, outputs[0].numel() * outputs.element_size()
-        layer, calls, per_step = self.layer, self._calls, self._per_step
+        layer, calls, per_step, look = self.layer, self._calls, self._per_step, self.lookahead
         memcpy, record, wait, sync = rt.cudaMemcpyAsync, rt.cudaEventRecord, rt.cudaStreamWaitEvent, rt.cudaEventSynchronize
         wait(up, e_step[0], 0)                                     # whatever ran before has finished with the staging buffers
         wait(up, e_step[1], 0)
@@ -121,6 +126,8 @@ class HostStepPipeline:
         record(e_up[0], up)
         for i in range(n):
             b = i & 1
+            if look == 2 and i >= 2:
+                sync(e_done[b])                                    # the host consumes result i - 2 here
             if i + 1 < n:                                          # next step's inputs, while this step computes
                 if i >= 1:
                     wait(up, e_step[1 - b], 0)                     # step i - 1 has finished reading that staging buffer
@@ -134,6 +141,8 @@ class HostStepPipeline:
             wait(down, e_step[b], 0)
             memcpy(out_ptr + (i % rows_out) * out_row, view.data_ptr(), out_bytes, _D2H, down)
             record(e_done[b], down)
-            if i >= 1:
+            if look == 1 and i >= 1:
                 sync(e_done[1 - b])                                # the host consumes result i - 1 here
+        if n >= 2:
+            sync(e_done[n & 1])                                    # result n - 2
         sync(e_done[(n - 1) & 1])

@@ -400,8 +400,8 @@ def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
     output) equal the same steps made directly with device tensors; lengths and pages too."""
     lens = [5, 16, 300, 1023, 2047]
     n, steps = len(lens), 9
-    pool_a, *_ = _pool(61, lens, 2 * steps)
-    pool_b, *_ = _pool(61, lens, 2 * steps)
+    pool_a, *_ = _pool(61, lens, 3 * steps)
+    pool_b, *_ = _pool(61, lens, 3 * steps)
     q_all, k_all, v_all = _inputs(14, steps, n)
     ref = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(steps)])
     rows = torch.cat([q_all.reshape(steps, -1), k_all.reshape(steps, -1), v_all.reshape(steps, -1)], dim=1).cpu().pin_memory()
@@ -418,6 +418,13 @@ def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
     assert torch.equal(ring[(steps - 2) % 2].reshape(n, HQ, D), ref2[-2].cpu())
     assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
     _same_pages(pool_a, pool_b, n, [t + 2 * steps for t in lens])
+    # the host one step behind instead of two, and steps that never start beside their predecessors: same results
+    short = 5
+    ref3 = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(short)])
+    pipe1 = L.HostStepPipeline(pool_b, 0, n, HQ, exchange=ex, lookahead=1, consecutive=False)
+    part = torch.empty((short,) + shape, dtype=torch.bfloat16).pin_memory()
+    pipe1.run(rows[:short], part)
+    assert torch.equal(part.reshape(short, n, HQ, D), ref3.cpu())
     with pytest.raises(ValueError, match="pinned"):
         pipe.run(rows.clone(), ring)
 
