@@ -479,9 +479,17 @@ def run_ours(args):
     nq, nk = N_SEQS * hq * D, N_SEQS * hkv * D
     qkv_h = torch.cat([q_all[W:W + Ke].reshape(Ke, nq), k_all[W:W + Ke].reshape(Ke, nk), v_all[W:W + Ke].reshape(Ke, nk)], dim=1).cpu().pin_memory()
     res_shape = tuple(state["view"].shape) if mode != "nccl" else tuple(gathered.shape)
+    # Under sharding every rank holds the whole result after a step.  Rank 0 reads all of it back (one host process has
+    # the step's complete result, as with one GPU); the other ranks read back their own share of it (head sharding: the
+    # rows of their heads; sequence sharding: a 1/N block of the rows), so the result does not cross the host link N times.
+    readback = None
+    if world > 1 and rank > 0 and mode != "nccl":
+        share = int(np.prod(res_shape)) // world
+        readback = (rank * share, share)
+        res_shape = (share,)
     out_h = torch.empty((2,) + res_shape, dtype=torch.bfloat16).pin_memory()
     if mode != "nccl":
-        pipe = L.HostStepPipeline(pool, 0, N_SEQS, hq, exchange=peer,
+        pipe = L.HostStepPipeline(pool, 0, N_SEQS, hq, exchange=peer, readback=readback,
                                   step_args=(lambda i: dict(zip(("positions", "store"), positions_for(W + i)))) if mode == "seq" else None,
                                   n_steps=Ke if mode == "seq" else None)
 
@@ -542,18 +550,20 @@ def run_ours(args):
                last[nq + nk:].view(N_SEQS, hkv, D).clone(), False, W + Ke - 1)
     torch.cuda.synchronize()
     chk = chk.float().cpu()
+    if readback is not None:
+        chk = chk.reshape(-1)[readback[0]:readback[0] + readback[1]]
     e2e_diff = float((chk - out_h[(Ke - 1) & 1].float()).abs().max() / chk.abs().max().clamp_min(1e-30))
     if not e2e_diff <= TOL_E2E:
         print(f"end-to-end result differs from the device-resident step: normalised max error {e2e_diff:.3e}", file=sys.stderr)
         raise SystemExit(3)
 
     # ---- max over ranks ------------------------------------------------------------------------------------------
-    stats = torch.tensor(ms_repeats + [ms_e2e, float(attn_ms.mean()), kernel_only_ms or 0.0, float(np.median(host_us))],
+    stats = torch.tensor(ms_repeats + [ms_e2e, float(attn_ms.mean()), kernel_only_ms or 0.0, float(np.median(host_us)), e2e_diff],
                          device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     stats = [float(x) for x in stats.tolist()]
-    ms_repeats, (ms_e2e, attn_mean_ms, kernel_only_ms, host_us_per_call) = stats[:R], stats[R:]
+    ms_repeats, (ms_e2e, attn_mean_ms, kernel_only_ms, host_us_per_call, e2e_diff) = stats[:R], stats[R:]
     ms_total = float(np.median(ms_repeats))
 
     result = None
@@ -576,6 +586,9 @@ def run_ours(args):
                       "kernel overlaps the previous step's merge kernel",
             "e2e": {"value": N_SEQS * Ke / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / Ke,
                     "h2d_bytes_per_step": int(nq + 2 * nk) * 2, "d2h_bytes_per_step": int(np.prod(res_shape)) * 2,
+                    "bytes_are": "per rank; d2h is rank 0's, which reads back the whole result" +
+                                 (f", the other ranks read back their 1/{world} share of it ({int(np.prod(res_shape)) * 2 // world} bytes)"
+                                  if world > 1 and mode != "nccl" else ""),
                     "pipeline": ("HostStepPipeline" if mode != "nccl" else "torch calls") +
                                 ": upload of step s+1 and read-back of step s-1 overlap step s (three "
                                 "streams); every result is awaited on the host", "host_wall_ms_per_step": wall_e2e_ms / Ke,

@@ -17,7 +17,7 @@ for a discrete GPU.
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Optional
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -47,10 +47,12 @@ class HostStepPipeline:
     ``store`` under sequence sharding), or is None.  ``consecutive`` passes the library's back-to-back promise: between two
     steps the compute stream holds only event records and waits (the wait for a step's upload comes before the step,
     so its inputs are complete when its kernel starts, however early that is), which lets a step's split-K kernel start
-    beside the previous step's merge kernel."""
+    beside the previous step's merge kernel.  ``readback`` = (first element, element count) reads back only that
+    contiguous part of a step's flattened result (under sharding every rank holds the whole gathered result; a rank
+    that only needs its own rows on the host does not pay for N copies of it); ``outputs`` is then ``[rows, count]``."""
 
     def __init__(self, pool, layer: int, n_seqs: int, n_q_heads: int, *, exchange=None, step_args=None, n_steps: Optional[int] = None,
-                 consecutive: bool = True, lookahead: int = 2):
+                 consecutive: bool = True, lookahead: int = 2, readback: Optional[Tuple[int, int]] = None):
         c = pool.cfg
         self.pool, self.layer = pool, layer
         dev = pool.torch_device
@@ -67,6 +69,16 @@ class HostStepPipeline:
         self.lookahead = lookahead
         self.results = None if exchange is not None else [torch.empty((n_seqs, n_q_heads, D), device=dev, dtype=c.dtype) for _ in range(2)]
         self.result_shape = tuple(exchange.out_shape) if exchange is not None else (n_seqs, n_q_heads, D)
+        self.readback = None
+        if readback is not None:
+            first, count = int(readback[0]), int(readback[1])
+            total = 1
+            for d_ in self.result_shape:
+                total *= d_
+            if first < 0 or count <= 0 or first + count > total:
+                raise ValueError("readback lies outside the result")
+            self.readback = (first, count)
+            self.result_shape = (count,)
         self.esize = self.stage[0].element_size()
         self.rt = _cudart()
         self.up, self.down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
@@ -118,6 +130,7 @@ class HostStepPipeline:
         in_ptr, in_row = inputs.data_ptr(), inputs.stride(0) * esize
         out_ptr, out_row = outputs.data_ptr(), outputs.stride(0) * outputs.element_size()
         in_bytes, out_bytes = self.in_elems * esize, outputs[0].numel() * outputs.element_size()
+        src_off = self.readback[0] * outputs.element_size() if self.readback is not None else 0
         layer, calls, per_step, look = self.layer, self._calls, self._per_step, self.lookahead
         memcpy, record, wait, sync = rt.cudaMemcpyAsync, rt.cudaEventRecord, rt.cudaStreamWaitEvent, rt.cudaEventSynchronize
         wait(up, e_step[0], 0)                                     # whatever ran before has finished with the staging buffers
@@ -139,7 +152,7 @@ class HostStepPipeline:
             view = calls[i if per_step else b](layer, main)
             record(e_step[b], main)
             wait(down, e_step[b], 0)
-            memcpy(out_ptr + (i % rows_out) * out_row, view.data_ptr(), out_bytes, _D2H, down)
+            memcpy(out_ptr + (i % rows_out) * out_row, view.data_ptr() + src_off, out_bytes, _D2H, down)
             record(e_done[b], down)
             if look == 1 and i >= 1:
                 sync(e_done[1 - b])                                # the host consumes result i - 1 here
