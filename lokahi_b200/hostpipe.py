@@ -141,19 +141,19 @@ class HostStepPipeline:
             b = i & 1
             if look == 2 and i >= 2:
                 sync(e_done[b])                                    # the host consumes result i - 2 here
+            wait(main, e_up[b], 0)
+            if look == 1 and i >= 2:
+                wait(main, e_done[b], 0)                           # the result buffer of this parity has been read back
+            view = calls[i if per_step else b](layer, main)        # first thing after the host's wait: the step itself
+            record(e_step[b], main)
+            wait(down, e_step[b], 0)
+            memcpy(out_ptr + (i % rows_out) * out_row, view.data_ptr() + src_off, out_bytes, _D2H, down)
+            record(e_done[b], down)
             if i + 1 < n:                                          # next step's inputs, while this step computes
                 if i >= 1:
                     wait(up, e_step[1 - b], 0)                     # step i - 1 has finished reading that staging buffer
                 memcpy(stage[1 - b], in_ptr + (i + 1) * in_row, in_bytes, _H2D, up)
                 record(e_up[1 - b], up)
-            wait(main, e_up[b], 0)
-            if i >= 2:
-                wait(main, e_done[b], 0)                           # the result buffer of this parity has been read back
-            view = calls[i if per_step else b](layer, main)
-            record(e_step[b], main)
-            wait(down, e_step[b], 0)
-            memcpy(out_ptr + (i % rows_out) * out_row, view.data_ptr() + src_off, out_bytes, _D2H, down)
-            record(e_done[b], down)
             if look == 1 and i >= 1:
                 sync(e_done[1 - b])                                # the host consumes result i - 1 here
         if n >= 2:
