@@ -27,6 +27,7 @@ import time
 
 import numpy as np
 
+E2E_LOOKAHEAD = 3   # end-to-end leg: the host runs this many steps ahead of the last result it holds
 TOL_E2E = 2e-2      # end-to-end result against the device-resident step (bf16; the two are expected to agree to the bit)
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -313,8 +314,8 @@ def run_ours(args):
         # peer-mapped buffers need torch symmetric memory on every rank; without it KV-head sharding falls back to
         # the NCCL all-gather on all ranks together (sequence sharding has no such fallback here)
         try:
-            peer = (L.PeerGather(shard, N_SEQS, D, torch.bfloat16, dev) if mode == "fused"
-                    else L.PeerSeqMerge(rank, world, N_SEQS, HQ, D, torch.bfloat16, dev))
+            peer = (L.PeerGather(shard, N_SEQS, D, torch.bfloat16, dev, n_results=E2E_LOOKAHEAD) if mode == "fused"
+                    else L.PeerSeqMerge(rank, world, N_SEQS, HQ, D, torch.bfloat16, dev, n_results=E2E_LOOKAHEAD))
             ok_local = 1
         except Exception as exc:   # noqa: BLE001 - any failure means "no peer mapping here"
             sys.stderr.write(f"[bench] rank {rank}: peer exchange unavailable ({exc})\n")
@@ -472,8 +473,8 @@ def run_ours(args):
     # ---- end-to-end leg: every step's inputs come from pinned host memory, every step's result goes back ------------
     # `HostStepPipeline` (the package's host side of the decode step): two device staging buffers, the upload of step
     # s + 1 on a copy stream while step s computes, the result of step s read back on a third stream while step s + 1
-    # computes; the host waits for result s - 2 before it enqueues step s + 1, and for the last results before the
-    # clock stops.  With the NCCL gather (the baseline) the same choreography runs from torch calls.
+    # computes; the host waits for result s - E2E_LOOKAHEAD before it enqueues step s + 1, and for the last results
+    # before the clock stops.  With the NCCL gather (the baseline) the same choreography runs from torch calls.
     Ke = K
     rewind(W)
     nq, nk = N_SEQS * hq * D, N_SEQS * hkv * D
@@ -487,9 +488,10 @@ def run_ours(args):
         share = int(np.prod(res_shape)) // world
         readback = (rank * share, share)
         res_shape = (share,)
-    out_h = torch.empty((2,) + res_shape, dtype=torch.bfloat16).pin_memory()
+    out_rows = E2E_LOOKAHEAD if mode != "nccl" else 2
+    out_h = torch.empty((out_rows,) + res_shape, dtype=torch.bfloat16).pin_memory()
     if mode != "nccl":
-        pipe = L.HostStepPipeline(pool, 0, N_SEQS, hq, exchange=peer, readback=readback,
+        pipe = L.HostStepPipeline(pool, 0, N_SEQS, hq, exchange=peer, readback=readback, lookahead=E2E_LOOKAHEAD,
                                   step_args=(lambda i: dict(zip(("positions", "store"), positions_for(W + i)))) if mode == "seq" else None,
                                   n_steps=Ke if mode == "seq" else None)
 
@@ -552,7 +554,7 @@ def run_ours(args):
     chk = chk.float().cpu()
     if readback is not None:
         chk = chk.reshape(-1)[readback[0]:readback[0] + readback[1]]
-    e2e_diff = float((chk - out_h[(Ke - 1) & 1].float()).abs().max() / chk.abs().max().clamp_min(1e-30))
+    e2e_diff = float((chk - out_h[(Ke - 1) % out_rows].float()).abs().max() / chk.abs().max().clamp_min(1e-30))
     if not e2e_diff <= TOL_E2E:
         print(f"end-to-end result differs from the device-resident step: normalised max error {e2e_diff:.3e}", file=sys.stderr)
         raise SystemExit(3)
@@ -591,7 +593,9 @@ def run_ours(args):
                                   if world > 1 and mode != "nccl" else ""),
                     "pipeline": ("HostStepPipeline" if mode != "nccl" else "torch calls") +
                                 ": upload of step s+1 and read-back of step s-1 overlap step s (three "
-                                "streams); every result is awaited on the host", "host_wall_ms_per_step": wall_e2e_ms / Ke,
+                                "streams); every result is awaited on the host, which runs "
+                                f"{E2E_LOOKAHEAD if mode != 'nccl' else 1} steps ahead of the last result it holds",
+                    "host_wall_ms_per_step": wall_e2e_ms / Ke,
                     "last_result_vs_device_resident_step": e2e_diff},
             "gpu_launches": int(launches),
             "host_us_per_call": host_us_per_call,

@@ -4,10 +4,10 @@ A caller whose per-step inputs live in host memory (the q, k, v rows of a step a
 network card, a CPU stage) pays one host-to-device copy and one device-to-host copy per step.  Issued one after
 the other on one stream they add to the step; here the upload of step s + 1 runs on a copy stream while step s
 computes, the result of step s is read back on a third stream while step s + 1 computes, and the host waits for
-result s - ``lookahead`` before it enqueues step s + 1 (and for the last result before ``run`` returns).  Two device
-staging buffers and two result buffers alternate.  With ``lookahead`` 1 the chain "step done, read-back, host wakes,
-next enqueue" has to fit into one step, which it does not when a step is short (30 us on eight GPUs against a
-25 us read-back of the gathered rows); the default 2 gives it two.  The per-step choreography (copies, event records and waits) goes
+result s - ``lookahead`` before it enqueues step s + 1 (and for the last results before ``run`` returns).  Two device
+staging buffers alternate and ``max(2, lookahead)`` result buffers rotate.  With ``lookahead`` 1 the chain "step done,
+read-back, host wakes, next enqueue" has to fit into one step, which it does not when a step is short (30 us on eight
+GPUs against a 25 us read-back of the gathered rows); ``lookahead`` steps share it.  The per-step choreography (copies, event records and waits) goes
 straight to the CUDA runtime through ctypes, and the step itself is a bound library call
 (``PagedPool.decode_step_binder``), so a step costs the host a few microseconds beside the two launches.
 
@@ -64,10 +64,13 @@ class HostStepPipeline:
                        b[self.nq + self.nk:].view(n_seqs, hkv, D)) for b in self.stage]
         self.exchange = exchange
         self.consecutive = bool(consecutive)
-        if lookahead not in (1, 2):
-            raise ValueError("lookahead is 1 or 2 (two result buffers)")
+        if not 1 <= lookahead <= 8:
+            raise ValueError("lookahead is 1 to 8")
         self.lookahead = lookahead
-        self.results = None if exchange is not None else [torch.empty((n_seqs, n_q_heads, D), device=dev, dtype=c.dtype) for _ in range(2)]
+        self.n_results = nb = max(2, lookahead)
+        if exchange is not None and exchange.n_results != nb:
+            raise ValueError(f"the exchange rotates {exchange.n_results} result buffers, lookahead {lookahead} needs {nb}")
+        self.results = None if exchange is not None else [torch.empty((n_seqs, n_q_heads, D), device=dev, dtype=c.dtype) for _ in range(nb)]
         self.result_shape = tuple(exchange.out_shape) if exchange is not None else (n_seqs, n_q_heads, D)
         self.readback = None
         if readback is not None:
@@ -83,41 +86,45 @@ class HostStepPipeline:
         self.rt = _cudart()
         self.up, self.down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self.main = torch.cuda.current_stream(dev)
-        mk = lambda: [torch.cuda.Event() for _ in range(2)]
-        self.ev_up, self.ev_step, self.ev_done = mk(), mk(), mk()
+        mk = lambda count: [torch.cuda.Event() for _ in range(count)]
+        self.ev_up, self.ev_step, self.ev_done = mk(2), mk(2), mk(nb)
         for group, stream in ((self.ev_up, self.up), (self.ev_step, self.main), (self.ev_done, self.down)):
             for e in group:
                 e.record(stream)                       # creates the CUDA event behind the torch object
         torch.cuda.synchronize(dev)
         # the step calls on the two staging buffers, bound once; with per-step arguments one call per step
+        # (with an exchange the result buffer is the exchange's business; without one a call is bound to a staging
+        # buffer and a result buffer, which repeat with period 2 * nb)
         self._calls: List = []
         if step_args is None:
-            for b in range(2):
-                self._calls.append(self._bind(b, {}))
+            self._period = 2 if exchange is not None else 2 * nb
+            for i in range(self._period):
+                self._calls.append(self._bind(i & 1, i % nb, {}))
         else:
             if n_steps is None:
                 raise ValueError("n_steps is needed with step_args")
+            self._period = 0
             for i in range(n_steps):
-                self._calls.append(self._bind(i & 1, step_args(i)))
+                self._calls.append(self._bind(i & 1, i % nb, step_args(i)))
         self._per_step = step_args is not None
 
-    def _bind(self, b: int, kw: dict):
+    def _bind(self, b: int, r: int, kw: dict):
         q, k, v = self.views[b]
         kw = dict(kw, consecutive=self.consecutive)
         if self.exchange is not None:
             return self.pool.decode_step_binder(q, k, v, exchange=self.exchange, **kw)
-        return self.pool.decode_step_binder(q, k, v, self.results[b], **kw)
+        return self.pool.decode_step_binder(q, k, v, self.results[r], **kw)
 
     def run(self, inputs: torch.Tensor, outputs: torch.Tensor) -> None:
         """``inputs`` pinned ``[n_steps, in_elems]`` (row = q | k | v of a step, flattened), ``outputs`` pinned
-        ``[rows, *result_shape]`` with ``rows >= 2``: the result of step i lands in row ``i % rows`` (a ring when there
-        are fewer rows than steps; a consumer that needs time with a row gives more rows than ``lookahead``).
+        ``[rows, *result_shape]`` with ``rows >= max(2, lookahead)``: the result of step i lands in row ``i % rows`` (a
+        ring when there are fewer rows than steps; a consumer that needs time with a row gives more rows).
         Runs the steps in order and returns when the last result is in ``outputs``."""
         if not (inputs.is_pinned() and outputs.is_pinned()):
             raise ValueError("inputs and outputs must be pinned host tensors")
         n = inputs.shape[0]
         rows_out = outputs.shape[0]
-        if inputs.shape[1] != self.in_elems or tuple(outputs.shape[1:]) != self.result_shape or rows_out < min(n, 2):
+        if inputs.shape[1] != self.in_elems or tuple(outputs.shape[1:]) != self.result_shape or rows_out < min(n, self.n_results):
             raise ValueError("inputs / outputs do not match the pipeline's shapes")
         if self._per_step and n > len(self._calls):
             raise ValueError("more steps than were bound")
@@ -131,31 +138,30 @@ class HostStepPipeline:
         out_ptr, out_row = outputs.data_ptr(), outputs.stride(0) * outputs.element_size()
         in_bytes, out_bytes = self.in_elems * esize, outputs[0].numel() * outputs.element_size()
         src_off = self.readback[0] * outputs.element_size() if self.readback is not None else 0
-        layer, calls, per_step, look = self.layer, self._calls, self._per_step, self.lookahead
+        layer, calls, per_step, look, nb, period = self.layer, self._calls, self._per_step, self.lookahead, self.n_results, self._period
         memcpy, record, wait, sync = rt.cudaMemcpyAsync, rt.cudaEventRecord, rt.cudaStreamWaitEvent, rt.cudaEventSynchronize
         wait(up, e_step[0], 0)                                     # whatever ran before has finished with the staging buffers
         wait(up, e_step[1], 0)
         memcpy(stage[0], in_ptr, in_bytes, _H2D, up)
         record(e_up[0], up)
         for i in range(n):
-            b = i & 1
-            if look == 2 and i >= 2:
-                sync(e_done[b])                                    # the host consumes result i - 2 here
+            b, r = i & 1, i % nb
+            if look >= 2 and i >= nb:
+                sync(e_done[r])                                    # the host consumes result i - lookahead here
             wait(main, e_up[b], 0)
             if look == 1 and i >= 2:
-                wait(main, e_done[b], 0)                           # the result buffer of this parity has been read back
-            view = calls[i if per_step else b](layer, main)        # first thing after the host's wait: the step itself
+                wait(main, e_done[r], 0)                           # the result buffer of this parity has been read back
+            view = calls[i if per_step else i % period](layer, main)   # first thing after the host's wait: the step itself
             record(e_step[b], main)
             wait(down, e_step[b], 0)
             memcpy(out_ptr + (i % rows_out) * out_row, view.data_ptr() + src_off, out_bytes, _D2H, down)
-            record(e_done[b], down)
+            record(e_done[r], down)
             if i + 1 < n:                                          # next step's inputs, while this step computes
                 if i >= 1:
                     wait(up, e_step[1 - b], 0)                     # step i - 1 has finished reading that staging buffer
                 memcpy(stage[1 - b], in_ptr + (i + 1) * in_row, in_bytes, _H2D, up)
                 record(e_up[1 - b], up)
             if look == 1 and i >= 1:
-                sync(e_done[1 - b])                                # the host consumes result i - 1 here
-        if n >= 2:
-            sync(e_done[n & 1])                                    # result n - 2
-        sync(e_done[(n - 1) & 1])
+                sync(e_done[1 - r])                                # the host consumes result i - 1 here
+        for j in range(max(0, n - nb), n):                         # the results the host has not been handed yet
+            sync(e_done[j % nb])

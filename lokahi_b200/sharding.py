@@ -83,15 +83,19 @@ class PeerExchange:
     into: torch symmetric memory over NVLink, peer-mapped at construction (a collective: every rank of ``group``
     must build the same object at the same point).  Rows cross as 16-byte stores whose 8-byte halves carry the
     call's epoch, so the receiving kernel validates each word by itself.  The result lands in a plain local tensor
-    (two of them, alternating, so that one can still be read while the next step fills the other).  With
+    (``n_results`` of them in rotation, two by default, so that one can still be read while the next steps fill the
+    others).  With
     ``world == 1`` ordinary device memory is used, which runs the same kernel code on one GPU.  K/V never cross
     GPUs; only output rows (or partial rows) do.
     """
 
     def __init__(self, mode: int, rank: int, world: int, n_seqs: int, n_q_heads: int, head_dim: int, dtype: torch.dtype,
-                 device: torch.device, group: Optional[dist.ProcessGroup] = None):
+                 device: torch.device, group: Optional[dist.ProcessGroup] = None, n_results: int = 2):
         import ctypes as C
         from . import _lib
+        if n_results < 2:
+            raise ValueError("an exchange needs at least two result buffers")
+        self.n_results = n_results
         self.mode, self.rank, self.world = mode, rank, world
         self.n_seqs, self.n_q_heads, self.head_dim = n_seqs, n_q_heads, head_dim
         self.epoch = 0
@@ -101,7 +105,7 @@ class PeerExchange:
             raise ValueError("exchange: unsupported mode, world size (1..8) or shape")
         self.out_shape = ((world, n_seqs, n_q_heads, head_dim) if mode == _lib.XCHG_HEAD_GATHER
                           else (n_seqs, n_q_heads, head_dim))
-        self._outs = [torch.zeros(self.out_shape, dtype=dtype, device=device) for _ in range(2)]
+        self._outs = [torch.zeros(self.out_shape, dtype=dtype, device=device) for _ in range(n_results)]
         if world == 1:
             self.recv = torch.zeros(nbytes, dtype=torch.uint8, device=device)
             self.recv_ptrs = [self.recv.data_ptr()]
@@ -132,19 +136,20 @@ class PeerExchange:
     def begin(self):
         """Advance to the next epoch; returns (argument block for the library call, local result view)."""
         self.epoch += 1
-        parity = self.epoch & 1
+        which = self.epoch % self.n_results          # the receive halves alternate by epoch parity inside the kernel
         d = self._desc
         d.epoch = self.epoch
-        d.out = self._out_ptrs[parity]
-        return d, self._outs[parity]
+        d.out = self._out_ptrs[which]
+        return d, self._outs[which]
 
     def advance(self):
         """``begin`` for a caller that already holds a pointer to the argument block: returns the result view only."""
         self.epoch = e = self.epoch + 1
+        which = e % self.n_results
         d = self._desc
         d.epoch = e
-        d.out = self._out_ptrs[e & 1]
-        return self._outs[e & 1]
+        d.out = self._out_ptrs[which]
+        return self._outs[which]
 
     def close(self):
         """Collective: all ranks stop using the buffers before any rank lets go of its own."""
@@ -161,9 +166,10 @@ class PeerGather(PeerExchange):
     reference's head order, src/ollm/backends/mlx_ops.py:152)."""
 
     def __init__(self, shard: HeadShard, n_seqs: int, head_dim: int, dtype: torch.dtype, device: torch.device,
-                 group: Optional[dist.ProcessGroup] = None):
+                 group: Optional[dist.ProcessGroup] = None, n_results: int = 2):
         from . import _lib
-        super().__init__(_lib.XCHG_HEAD_GATHER, shard.rank, shard.world, n_seqs, shard.local_q_heads, head_dim, dtype, device, group)
+        super().__init__(_lib.XCHG_HEAD_GATHER, shard.rank, shard.world, n_seqs, shard.local_q_heads, head_dim, dtype, device, group,
+                         n_results)
         self.shard = shard
         self.shape = self.out_shape
 
@@ -174,9 +180,9 @@ class PeerSeqMerge(PeerExchange):
     finished row to everyone; result ``[n_seqs, q_heads, head_dim]``, identical on all ranks."""
 
     def __init__(self, rank: int, world: int, n_seqs: int, n_q_heads: int, head_dim: int, dtype: torch.dtype,
-                 device: torch.device, group: Optional[dist.ProcessGroup] = None):
+                 device: torch.device, group: Optional[dist.ProcessGroup] = None, n_results: int = 2):
         from . import _lib
-        super().__init__(_lib.XCHG_SEQ_MERGE, rank, world, n_seqs, n_q_heads, head_dim, dtype, device, group)
+        super().__init__(_lib.XCHG_SEQ_MERGE, rank, world, n_seqs, n_q_heads, head_dim, dtype, device, group, n_results)
 
 
 @dataclass(frozen=True)

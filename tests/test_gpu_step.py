@@ -400,8 +400,8 @@ def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
     output) equal the same steps made directly with device tensors; lengths and pages too."""
     lens = [5, 16, 300, 1023, 2047]
     n, steps = len(lens), 9
-    pool_a, *_ = _pool(61, lens, 3 * steps)
-    pool_b, *_ = _pool(61, lens, 3 * steps)
+    pool_a, *_ = _pool(61, lens, 4 * steps)
+    pool_b, *_ = _pool(61, lens, 4 * steps)
     q_all, k_all, v_all = _inputs(14, steps, n)
     ref = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(steps)])
     rows = torch.cat([q_all.reshape(steps, -1), k_all.reshape(steps, -1), v_all.reshape(steps, -1)], dim=1).cpu().pin_memory()
@@ -425,6 +425,18 @@ def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
     part = torch.empty((short,) + shape, dtype=torch.bfloat16).pin_memory()
     pipe1.run(rows[:short], part)
     assert torch.equal(part.reshape(short, n, HQ, D), ref3.cpu())
+    # the host three steps behind: three result buffers in rotation, results through a three-row ring
+    more = 7
+    ref4 = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(more)])
+    ex3 = L.PeerGather(L.HeadShard(0, 1, HQ, HKV), n, D, torch.bfloat16, torch.device(DEV), n_results=3) if with_exchange else None
+    pipe3 = L.HostStepPipeline(pool_b, 0, n, HQ, exchange=ex3, lookahead=3)
+    ring3 = torch.empty((3,) + shape, dtype=torch.bfloat16).pin_memory()
+    pipe3.run(rows[:more], ring3)
+    for s_ in (more - 1, more - 2, more - 3):
+        assert torch.equal(ring3[s_ % 3].reshape(n, HQ, D), ref4[s_].cpu()), f"lookahead 3, step {s_}"
+    with pytest.raises(ValueError, match="match"):
+        pipe3.run(rows[:more], ring)                       # a two-row ring is too short for three steps of look-ahead
+    assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
     with pytest.raises(ValueError, match="pinned"):
         pipe.run(rows.clone(), ring)
 
