@@ -27,7 +27,7 @@ import time
 
 import numpy as np
 
-E2E_LOOKAHEAD = 3   # end-to-end leg: the host runs this many steps ahead of the last result it holds
+E2E_LOOKAHEAD = 2   # end-to-end leg: the host runs this many steps ahead of the last result it holds
 TOL_E2E = 2e-2      # end-to-end result against the device-resident step (bf16; the two are expected to agree to the bit)
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
