@@ -4,10 +4,15 @@ A caller whose per-step inputs live in host memory (the q, k, v rows of a step a
 network card, a CPU stage) pays one host-to-device copy and one device-to-host copy per step.  Issued one after
 the other on one stream they add to the step; here the upload of step s + 1 runs on a copy stream while step s
 computes, the result of step s is read back on a third stream while step s + 1 computes, and the host waits for
-result s - ``lookahead`` before it enqueues step s + 1 (and for the last results before ``run`` returns).  Two device
-staging buffers alternate and ``max(2, lookahead)`` result buffers rotate.  With ``lookahead`` 1 the chain "step done,
-read-back, host wakes, next enqueue" has to fit into one step, which it does not when a step is short (30 us on eight
-GPUs against a 25 us read-back of the gathered rows); ``lookahead`` steps share it.  The per-step choreography (copies, event records and waits) goes
+result s - ``lookahead`` before it enqueues step s + 1 (and for the last results before ``run`` returns).  With
+``lookahead`` 1 the chain "step done, read-back, host wakes, next enqueue" has to fit into one step, which it does not
+when a step is short; the default 2 gives it two.
+Steps can also travel in blocks of ``block``: the block's uploads, its steps and its read-backs are each enqueued
+together, with one event wait before the block's first step and one event record after its last.  Every step still
+gets its own upload and its own read-back; what changes is how often an event sits between two steps on the compute
+stream.  An event record or wait between two steps keeps the second from starting beside the first (the library's
+back-to-back mode), and on eight GPUs a step that starts on its own takes 54 us against 29 us beside its predecessor.
+``2 * block`` device staging buffers and as many result buffers rotate.  The per-step choreography (copies, event records and waits) goes
 straight to the CUDA runtime through ctypes, and the step itself is a bound library call
 (``PagedPool.decode_step_binder``), so a step costs the host a few microseconds beside the two launches.
 
@@ -42,35 +47,37 @@ def _cudart():
 class HostStepPipeline:
     """Runs ``decode_step`` for a fixed batch shape with inputs from, and results to, pinned host tensors.
 
-    ``exchange`` (a ``sharding.PeerGather`` / ``PeerSeqMerge``) makes the step the sharded one; ``step_args`` is called
-    with the step index and returns the per-step keyword arguments of ``decode_step_binder`` that vary (``positions`` /
-    ``store`` under sequence sharding), or is None.  ``consecutive`` passes the library's back-to-back promise: between two
-    steps the compute stream holds only event records and waits (the wait for a step's upload comes before the step,
-    so its inputs are complete when its kernel starts, however early that is), which lets a step's split-K kernel start
-    beside the previous step's merge kernel.  ``readback`` = (first element, element count) reads back only that
-    contiguous part of a step's flattened result (under sharding every rank holds the whole gathered result; a rank
-    that only needs its own rows on the host does not pay for N copies of it); ``outputs`` is then ``[rows, count]``."""
+    ``exchange`` (a ``sharding.PeerGather`` / ``PeerSeqMerge`` built with ``n_results = 2 * block``) makes the step the
+    sharded one; ``step_args`` is called with the step index and returns the per-step keyword arguments of
+    ``decode_step_binder`` that vary (``positions`` / ``store`` under sequence sharding), or is None.  ``consecutive``
+    passes the library's back-to-back promise: between two steps the compute stream holds at most event records and
+    waits (the wait for a block's uploads comes before its first step, so the inputs are complete when a kernel
+    starts, however early that is).  ``readback`` = (first element, element count) reads back only that contiguous part
+    of a step's flattened result (under sharding every rank holds the whole gathered result; a rank that only needs
+    its own rows on the host does not pay for N copies of it); ``outputs`` is then ``[rows, count]``."""
 
     def __init__(self, pool, layer: int, n_seqs: int, n_q_heads: int, *, exchange=None, step_args=None, n_steps: Optional[int] = None,
-                 consecutive: bool = True, lookahead: int = 2, readback: Optional[Tuple[int, int]] = None):
+                 consecutive: bool = True, lookahead: int = 2, block: int = 1, readback: Optional[Tuple[int, int]] = None):
         c = pool.cfg
         self.pool, self.layer = pool, layer
         dev = pool.torch_device
         D, hkv = c.head_dim, c.num_kv_heads
+        if lookahead not in (1, 2):
+            raise ValueError("lookahead is 1 or 2 (blocks)")
+        if not 1 <= block <= 16:
+            raise ValueError("block is 1 to 16 steps")
+        self.lookahead, self.block = lookahead, block
+        self.n_slots = slots = 2 * block
+        if exchange is not None and exchange.n_results != slots:
+            raise ValueError(f"the exchange rotates {exchange.n_results} result buffers, blocks of {block} need {slots}")
         self.nq, self.nk = n_seqs * n_q_heads * D, n_seqs * hkv * D
         self.in_elems = self.nq + 2 * self.nk
-        self.stage = [torch.empty((self.in_elems,), device=dev, dtype=c.dtype) for _ in range(2)]
+        self.stage = [torch.empty((self.in_elems,), device=dev, dtype=c.dtype) for _ in range(slots)]
         self.views = [(b[:self.nq].view(n_seqs, n_q_heads, D), b[self.nq:self.nq + self.nk].view(n_seqs, hkv, D),
                        b[self.nq + self.nk:].view(n_seqs, hkv, D)) for b in self.stage]
         self.exchange = exchange
         self.consecutive = bool(consecutive)
-        if not 1 <= lookahead <= 8:
-            raise ValueError("lookahead is 1 to 8")
-        self.lookahead = lookahead
-        self.n_results = nb = max(2, lookahead)
-        if exchange is not None and exchange.n_results != nb:
-            raise ValueError(f"the exchange rotates {exchange.n_results} result buffers, lookahead {lookahead} needs {nb}")
-        self.results = None if exchange is not None else [torch.empty((n_seqs, n_q_heads, D), device=dev, dtype=c.dtype) for _ in range(nb)]
+        self.results = None if exchange is not None else [torch.empty((n_seqs, n_q_heads, D), device=dev, dtype=c.dtype) for _ in range(slots)]
         self.result_shape = tuple(exchange.out_shape) if exchange is not None else (n_seqs, n_q_heads, D)
         self.readback = None
         if readback is not None:
@@ -86,45 +93,46 @@ class HostStepPipeline:
         self.rt = _cudart()
         self.up, self.down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self.main = torch.cuda.current_stream(dev)
-        mk = lambda count: [torch.cuda.Event() for _ in range(count)]
-        self.ev_up, self.ev_step, self.ev_done = mk(2), mk(2), mk(nb)
+        mk = lambda: [torch.cuda.Event() for _ in range(2)]      # by block parity
+        self.ev_up, self.ev_step, self.ev_done = mk(), mk(), mk()
         for group, stream in ((self.ev_up, self.up), (self.ev_step, self.main), (self.ev_done, self.down)):
             for e in group:
                 e.record(stream)                       # creates the CUDA event behind the torch object
         torch.cuda.synchronize(dev)
-        # the step calls on the two staging buffers, bound once; with per-step arguments one call per step
-        # (with an exchange the result buffer is the exchange's business; without one a call is bound to a staging
-        # buffer and a result buffer, which repeat with period 2 * nb)
+        # the step calls, bound once: one per slot (staging buffer s and result buffer s; with an exchange the result
+        # buffer is the exchange's own rotation of as many buffers), or one per step when arguments vary by step
         self._calls: List = []
         if step_args is None:
-            self._period = 2 if exchange is not None else 2 * nb
-            for i in range(self._period):
-                self._calls.append(self._bind(i & 1, i % nb, {}))
+            for slot in range(slots):
+                self._calls.append(self._bind(slot, {}))
         else:
             if n_steps is None:
                 raise ValueError("n_steps is needed with step_args")
-            self._period = 0
             for i in range(n_steps):
-                self._calls.append(self._bind(i & 1, i % nb, step_args(i)))
+                self._calls.append(self._bind(self._slot(i), step_args(i)))
         self._per_step = step_args is not None
 
-    def _bind(self, b: int, r: int, kw: dict):
-        q, k, v = self.views[b]
+    def _slot(self, i: int) -> int:
+        """Staging / result slot of step i: block parity times the block length, plus the step's place in its block."""
+        return ((i // self.block) & 1) * self.block + i % self.block
+
+    def _bind(self, slot: int, kw: dict):
+        q, k, v = self.views[slot]
         kw = dict(kw, consecutive=self.consecutive)
         if self.exchange is not None:
             return self.pool.decode_step_binder(q, k, v, exchange=self.exchange, **kw)
-        return self.pool.decode_step_binder(q, k, v, self.results[r], **kw)
+        return self.pool.decode_step_binder(q, k, v, self.results[slot], **kw)
 
     def run(self, inputs: torch.Tensor, outputs: torch.Tensor) -> None:
         """``inputs`` pinned ``[n_steps, in_elems]`` (row = q | k | v of a step, flattened), ``outputs`` pinned
-        ``[rows, *result_shape]`` with ``rows >= max(2, lookahead)``: the result of step i lands in row ``i % rows`` (a
-        ring when there are fewer rows than steps; a consumer that needs time with a row gives more rows).
+        ``[rows, *result_shape]`` with ``rows >= 2 * block``: the result of step i lands in row ``i % rows`` (a ring when
+        there are fewer rows than steps; a consumer that needs time with a row gives more rows).
         Runs the steps in order and returns when the last result is in ``outputs``."""
         if not (inputs.is_pinned() and outputs.is_pinned()):
             raise ValueError("inputs and outputs must be pinned host tensors")
         n = inputs.shape[0]
         rows_out = outputs.shape[0]
-        if inputs.shape[1] != self.in_elems or tuple(outputs.shape[1:]) != self.result_shape or rows_out < min(n, self.n_results):
+        if inputs.shape[1] != self.in_elems or tuple(outputs.shape[1:]) != self.result_shape or rows_out < min(n, self.n_slots):
             raise ValueError("inputs / outputs do not match the pipeline's shapes")
         if self._per_step and n > len(self._calls):
             raise ValueError("more steps than were bound")
@@ -138,30 +146,35 @@ class HostStepPipeline:
         out_ptr, out_row = outputs.data_ptr(), outputs.stride(0) * outputs.element_size()
         in_bytes, out_bytes = self.in_elems * esize, outputs[0].numel() * outputs.element_size()
         src_off = self.readback[0] * outputs.element_size() if self.readback is not None else 0
-        layer, calls, per_step, look, nb, period = self.layer, self._calls, self._per_step, self.lookahead, self.n_results, self._period
+        layer, calls, per_step, look, B = self.layer, self._calls, self._per_step, self.lookahead, self.block
         memcpy, record, wait, sync = rt.cudaMemcpyAsync, rt.cudaEventRecord, rt.cudaStreamWaitEvent, rt.cudaEventSynchronize
         wait(up, e_step[0], 0)                                     # whatever ran before has finished with the staging buffers
         wait(up, e_step[1], 0)
-        memcpy(stage[0], in_ptr, in_bytes, _H2D, up)
+        for t in range(min(B, n)):
+            memcpy(stage[t], in_ptr + t * in_row, in_bytes, _H2D, up)
         record(e_up[0], up)
-        for i in range(n):
-            b, r = i & 1, i % nb
-            if look >= 2 and i >= nb:
-                sync(e_done[r])                                    # the host consumes result i - lookahead here
+        for j in range((n + B - 1) // B):                          # block j: steps first .. first + count - 1
+            b, first = j & 1, j * B
+            count = min(B, n - first)
+            if look == 2 and j >= 2:
+                sync(e_done[b])                                    # the host consumes the results of block j - 2 here
             wait(main, e_up[b], 0)
-            if look == 1 and i >= 2:
-                wait(main, e_done[r], 0)                           # the result buffer of this parity has been read back
-            view = calls[i if per_step else i % period](layer, main)   # first thing after the host's wait: the step itself
+            if look == 1 and j >= 2:
+                wait(main, e_done[b], 0)                           # the result buffers of this parity have been read back
+            views = [calls[first + t if per_step else b * B + t](layer, main) for t in range(count)]   # the steps, back to back
             record(e_step[b], main)
             wait(down, e_step[b], 0)
-            memcpy(out_ptr + (i % rows_out) * out_row, view.data_ptr() + src_off, out_bytes, _D2H, down)
-            record(e_done[r], down)
-            if i + 1 < n:                                          # next step's inputs, while this step computes
-                if i >= 1:
-                    wait(up, e_step[1 - b], 0)                     # step i - 1 has finished reading that staging buffer
-                memcpy(stage[1 - b], in_ptr + (i + 1) * in_row, in_bytes, _H2D, up)
+            for t in range(count):
+                memcpy(out_ptr + ((first + t) % rows_out) * out_row, views[t].data_ptr() + src_off, out_bytes, _D2H, down)
+            record(e_done[b], down)
+            nxt = first + count
+            if nxt < n:                                            # the next block's inputs, while this block computes
+                if j >= 1:
+                    wait(up, e_step[1 - b], 0)                     # block j - 1 has finished reading those staging buffers
+                for t in range(min(B, n - nxt)):
+                    memcpy(stage[(1 - b) * B + t], in_ptr + (nxt + t) * in_row, in_bytes, _H2D, up)
                 record(e_up[1 - b], up)
-            if look == 1 and i >= 1:
-                sync(e_done[1 - r])                                # the host consumes result i - 1 here
-        for j in range(max(0, n - nb), n):                         # the results the host has not been handed yet
-            sync(e_done[j % nb])
+            if look == 1 and j >= 1:
+                sync(e_done[1 - b])                                # the host consumes the results of block j - 1 here
+        sync(e_done[0])
+        sync(e_done[1])

@@ -425,17 +425,18 @@ def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
     part = torch.empty((short,) + shape, dtype=torch.bfloat16).pin_memory()
     pipe1.run(rows[:short], part)
     assert torch.equal(part.reshape(short, n, HQ, D), ref3.cpu())
-    # the host three steps behind: three result buffers in rotation, results through a three-row ring
-    more = 7
+    # steps in blocks of three (one event wait before a block, one record after it; 3 + 3 + 2 steps), six buffers in
+    # rotation, results through a six-row ring
+    more = 8
     ref4 = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(more)])
-    ex3 = L.PeerGather(L.HeadShard(0, 1, HQ, HKV), n, D, torch.bfloat16, torch.device(DEV), n_results=3) if with_exchange else None
-    pipe3 = L.HostStepPipeline(pool_b, 0, n, HQ, exchange=ex3, lookahead=3)
-    ring3 = torch.empty((3,) + shape, dtype=torch.bfloat16).pin_memory()
-    pipe3.run(rows[:more], ring3)
-    for s_ in (more - 1, more - 2, more - 3):
-        assert torch.equal(ring3[s_ % 3].reshape(n, HQ, D), ref4[s_].cpu()), f"lookahead 3, step {s_}"
+    ex3 = L.PeerGather(L.HeadShard(0, 1, HQ, HKV), n, D, torch.bfloat16, torch.device(DEV), n_results=6) if with_exchange else None
+    pipe3 = L.HostStepPipeline(pool_b, 0, n, HQ, exchange=ex3, block=3)
+    ring6 = torch.empty((6,) + shape, dtype=torch.bfloat16).pin_memory()
+    pipe3.run(rows[:more], ring6)
+    for s_ in range(more - 6, more):
+        assert torch.equal(ring6[s_ % 6].reshape(n, HQ, D), ref4[s_].cpu()), f"blocks of 3, step {s_}"
     with pytest.raises(ValueError, match="match"):
-        pipe3.run(rows[:more], ring)                       # a two-row ring is too short for three steps of look-ahead
+        pipe3.run(rows[:more], ring)                       # a two-row ring is too short for blocks of three
     assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
     with pytest.raises(ValueError, match="pinned"):
         pipe.run(rows.clone(), ring)
