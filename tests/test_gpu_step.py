@@ -400,8 +400,8 @@ def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
     output) equal the same steps made directly with device tensors; lengths and pages too."""
     lens = [5, 16, 300, 1023, 2047]
     n, steps = len(lens), 9
-    pool_a, *_ = _pool(61, lens, 4 * steps)
-    pool_b, *_ = _pool(61, lens, 4 * steps)
+    pool_a, *_ = _pool(61, lens, 5 * steps)
+    pool_b, *_ = _pool(61, lens, 5 * steps)
     q_all, k_all, v_all = _inputs(14, steps, n)
     ref = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(steps)])
     rows = torch.cat([q_all.reshape(steps, -1), k_all.reshape(steps, -1), v_all.reshape(steps, -1)], dim=1).cpu().pin_memory()
@@ -438,6 +438,19 @@ def test_host_fed_pipeline_gives_the_direct_steps_results(with_exchange):
     with pytest.raises(ValueError, match="match"):
         pipe3.run(rows[:more], ring)                       # a two-row ring is too short for blocks of three
     assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
+    if with_exchange:
+        # arguments that vary by step (the positions and store flags of sequence sharding, here with one rank that
+        # stores everything), calls bound per step, blocks of two
+        base = [int(t) for t in pool_b.lengths(0)]
+        extra = 5
+        ref5 = torch.stack([pool_a.decode_step(0, q_all[s].clone(), k_all[s], v_all[s]) for s in range(extra)])
+        merge = L.PeerSeqMerge(0, 1, n, HQ, D, torch.bfloat16, torch.device(DEV), n_results=4)
+        pipe5 = L.HostStepPipeline(pool_b, 0, n, HQ, exchange=merge, block=2, n_steps=extra,
+                                   step_args=lambda i: {"positions": [t + i for t in base], "store": [True] * n})
+        got5 = torch.empty((extra, n, HQ, D), dtype=torch.bfloat16).pin_memory()
+        pipe5.run(rows[:extra], got5)
+        assert parity_errors(got5, to_np(ref5))[0] <= TOL_BF16, "per-step arguments, blocks of two"
+        assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0)) and pool_b.check_device_status() == 0
     with pytest.raises(ValueError, match="pinned"):
         pipe.run(rows.clone(), ring)
 
