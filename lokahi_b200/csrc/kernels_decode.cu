@@ -361,7 +361,8 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_tma_kernel(const __grid
                                                                     const __grid_constant__ StepRows rows) {
     extern __shared__ uint8_t smem_raw[];
     const PoolView& pv = d.pool;
-    const int split = blockIdx.x, h = blockIdx.y, i = blockIdx.z;
+    const int split = blockIdx.x, h = blockIdx.y;
+    const int i = (FA && rows.ordered) ? (int)rows.order[blockIdx.z] : (int)blockIdx.z;   // a step may hand its longest rows out first
     const bool late_wait = FA && d.early_start;
     if (threadIdx.x == 0) {
         prefetch_tensormap(&kmap);

@@ -98,7 +98,10 @@ struct StepRows {
     int32_t seq[kInlineRows];     // sequence id of row i
     int32_t len[kInlineRows];     // tokens of row i held by this pool before the step
     uint32_t pos[kInlineRows];    // absolute position of the step's token (RoPE angle) | kRowNoStore
+    uint8_t order[kInlineRows];   // when `ordered`: the split-K kernel's grid index z works on row order[z] (longest rows
+    int32_t ordered;              // first, so that a grid of more CTAs than the GPU holds ends on short ones)
 };
+static_assert(kInlineRows <= 256, "row indices are stored in one byte");
 
 struct DecodeLaunch {
     PoolView pool;
@@ -206,6 +209,7 @@ struct Switches {
     int append_scalar;     // SKV_APPEND_SCALAR == "1"
     int pdl;               // SKV_PDL != "0"
     int step_early;        // SKV_STEP_EARLY != "0"
+    int order;             // SKV_DECODE_ORDER: -1 unset (longest rows first when the grid exceeds the GPU), 0 never, 1 always
 };
 const Switches& switches();
 void reload_switches();

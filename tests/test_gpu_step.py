@@ -279,6 +279,32 @@ def test_sequence_sharded_step_on_three_pools_merges_to_the_unsharded_step(split
         assert_parity(merged[i], o[0, :, 0, :], TOL_BF16, f"merged step vs oracle, sequence {i}")
 
 
+def test_longest_rows_first_changes_nothing_but_the_order_of_the_work(skv_switch):
+    """SKV_DECODE_ORDER=1: the split-K grid works on the rows from the longest to the shortest (what a step does by
+    itself when its grid holds more CTAs than the GPU does at once).  Outputs, rotated q, lengths and pages equal the
+    unordered step's bit for bit, with a sequence list, over steps that start early."""
+    lens = [700, 3, 1024, 0, 88, 2047, 512, 16, 300, 1500]
+    n, steps = len(lens), 6
+    pool_a, *_ = _pool(77, lens, steps)
+    pool_b, *_ = _pool(77, lens, steps)
+    q_all, k_all, v_all = _inputs(19, steps, n)
+    ids = list(range(n))
+    outs = {}
+    for name, pool, flag in (("plain", pool_a, "0"), ("ordered", pool_b, "1")):
+        skv_switch("SKV_DECODE_ORDER", flag)
+        qs = q_all.clone()
+        res = torch.empty_like(q_all)
+        torch.cuda.synchronize()
+        for s in range(steps):
+            pool.decode_step(0, qs[s], k_all[s], v_all[s], out=res[s], seq_ids=ids if s % 2 else None, consecutive=s > 0)
+        torch.cuda.synchronize()
+        outs[name] = (res, qs)
+    assert torch.equal(outs["plain"][0], outs["ordered"][0]) and torch.equal(outs["plain"][1], outs["ordered"][1])
+    assert np.array_equal(pool_a.lengths(0), pool_b.lengths(0))
+    _same_pages(pool_a, pool_b, n, [t + steps for t in lens])
+    assert pool_a.check_device_status() == 0 and pool_b.check_device_status() == 0
+
+
 def test_step_with_more_rows_than_the_kernel_parameters_hold():
     """300 sequences: the per-row metadata no longer fits the kernel parameters and is uploaded instead; same
     results as the append + attention pair."""
