@@ -1304,7 +1304,8 @@ int32_t step_impl(skv_pool* p, const skv_step_args& a, cudaStream_t stream) {
         live *= Hkv;
         if (switches().order == 1 || (D.grid_splits <= 2 && live > 3 * (int64_t)p->sm_count)) {
             for (int32_t i = 0; i < n_seqs; ++i) R.order[i] = (uint8_t)i;
-            std::stable_sort(R.order, R.order + n_seqs, [&](uint8_t x, uint8_t y) { return R.len[x] > R.len[y]; });
+            std::sort(R.order, R.order + n_seqs,
+                      [&](uint8_t x, uint8_t y) { return R.len[x] != R.len[y] ? R.len[x] > R.len[y] : x < y; });   // in place, no allocation
             R.ordered = 1;
         }
     }
