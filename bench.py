@@ -1047,10 +1047,10 @@ def run_longctx(args):
             every = [torch.empty_like(local) for _ in range(world)]
             dist.all_gather(every, local.contiguous())
             exchange_equal = all(bool(torch.equal(view[r_], every[r_])) for r_ in range(world))
-        verdict = torch.tensor([err, q_err, 0.0 if exchange_equal else 1.0], device=dev, dtype=torch.float64)
+        worst = torch.tensor([err, q_err, 0.0 if exchange_equal else 1.0], device=dev, dtype=torch.float64)
         if world > 1:
-            dist.all_reduce(verdict, op=dist.ReduceOp.MAX)
-        err, q_err, bad = (float(x) for x in verdict.tolist())
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        err, q_err, bad = (float(x) for x in worst.tolist())
         parity = {"checked": True, "tolerance": TOL_BF16, "layer": lc, "sequence": sc, "tokens": int(T + 1),
                   "vs_oracle_max_norm_err_max_over_ranks": err, "rotated_q_max_norm_err": q_err,
                   "gathered_slots_equal_their_ranks_rows": bad == 0.0}
